@@ -1,0 +1,75 @@
+"""ctypes binding of libcactus_b200.so (include/cactus_b200.h).  No fallback: a missing library is an error."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "lib", "libcactus_b200.so")
+
+_i64, _i32, _f32, _vp, _sz = C.c_int64, C.c_int, C.c_float, C.c_void_p, C.c_size_t
+
+# name -> (restype, argtypes); the same list the header declares, checked by tests/test_abi.py
+SIGNATURES = {
+    "b200_abi_version": (_i32, []),
+    "b200_last_error": (C.c_char_p, []),
+    "b200_device_count": (_i32, []),
+    "b200_device_info": (_i32, [_i32, C.c_char_p, _sz, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_i32)]),
+    "b200_launch_count": (C.c_uint64, []),
+    "b200_weight_bytes": (_sz, [_i32, _i64, _i64]),
+    "b200_weight_upload": (_i32, [_i32, _i64, _i64, _vp, _vp, _i64, _i64, _vp]),
+    "b200_weight_download": (_i32, [_i32, _i64, _i64, _vp, _vp, _i64, _i64, _vp]),
+    "b200_quantize_q8_0": (_i32, [_vp, _i64, _i64, _i64, _vp, _i32, _vp]),
+    "b200_act_bytes": (_sz, [_i64, _i64]),
+    "b200_mul_mat_workspace_bytes": (_sz, [_i32, _i64, _i64, _i64]),
+    "b200_mul_mat_scratch_bytes": (_sz, [_i32, _i64, _i64, _i64]),
+    "b200_mul_mat_q": (_i32, [_i32, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _sz, _i32, _vp]),
+    "b200_quantize_activations": (_i32, [_vp, _i64, _i64, _i64, _vp, _sz, _i32, _vp]),
+    "b200_mul_mat_q_prequant": (_i32, [_i32, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _sz, _vp]),
+    "b200_block_dots": (_i32, [_i32, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _vp, _sz, _i32, _vp]),
+    "b200_flash_attn_scratch_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64]),
+    "b200_flash_attn_ext": (_i32, [_i64, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64,
+                                   _f32, _f32, _f32, _vp, _vp, _sz, _vp]),
+    "b200_mask_index_bytes": (_sz, [_i64, _i64]),
+    "b200_mask_index_build": (_i32, [_vp, _i64, _i64, _i64, _vp, _sz, _vp]),
+    "b200_flash_attn_ext_indexed": (_i32, [_i64, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp,
+                                           _i64, _vp, _f32, _f32, _f32, _vp, _vp, _sz, _vp]),
+    "b200_rms_norm": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _f32, _vp]),
+    "b200_add": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b200_mul": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b200_silu": (_i32, [_vp, _vp, _vp, _i64, _vp]),
+    "b200_rope_norm": (_i32, [_vp, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _f32, _f32, _f32, _vp]),
+    "b200_cpy_f32_f16": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
+    "b200_cpy_f32_f32": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
+    "b200_get_rows_f32": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b200_get_rows_q": (_i32, [_i32, _vp, _i64, _i64, _vp, _vp, _i64, _i64, _vp]),
+}
+
+_lib = None
+
+
+class B200Error(RuntimeError):
+    pass
+
+
+def lib() -> C.CDLL:
+    """Loads the kernel library.  Raises if it has not been built: there is no other compute path."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise B200Error(f"{LIB_PATH} is missing: build it with `python -m cactus_b200.build` (needs nvcc); "
+                            "cactus_b200 has no CPU or framework fallback")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        if L.b200_abi_version() != 1:
+            raise B200Error("libcactus_b200.so has an unexpected ABI version")
+        _lib = L
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise B200Error(f"cactus_b200 error {rc}: {lib().b200_last_error().decode()}")

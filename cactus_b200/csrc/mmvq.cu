@@ -1,0 +1,138 @@
+// MUL_MAT for few activation columns (N <= 8): the HBM-bound decode kernel.
+//
+// Replaces lm_ggml_vec_dot_q4_0_q8_0 / lm_ggml_vec_dot_q8_0_q8_0 under mul_mat
+// (cactus/ggml-cpu/ggml-cpu-quants.c:1906, :3591; cactus/ggml-cpu/ggml-cpu.c:1167-1255).
+//
+// One CTA per 16-row tile of the weight matrix, 8 warps splitting the K dimension by block group.
+// A warp streams 1 KB (Q4_0) / 2 KB (Q8_0) tiles with two/four 128-bit loads per lane, lane (g, t)
+// holding word t of every block of rows g and g+8, multiplies them against the Q8_0 activation words
+// with dp4a and applies the two fp16 block scales per (row, column, block).  Partial sums are folded
+// over the four t lanes with shuffles and over the warps through shared memory in a fixed order, so
+// the result does not depend on scheduling.
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int MMVQ_WARPS = 8;
+
+template <int WTYPE, int NC>
+__global__ void __launch_bounds__(MMVQ_WARPS * 32) mmvq_kernel(TiledDims dims, const uint8_t *__restrict__ w, ActDims act,
+                                                              const uint8_t *__restrict__ aq, float *__restrict__ dst,
+                                                              int64_t dst_nb_row) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t rt = blockIdx.x;
+    float y[2][NC];
+#pragma unroll
+    for (int n = 0; n < NC; ++n) y[0][n] = y[1][n] = 0.0f;
+
+    const uint8_t *wq = w + rt * dims.n_bg * dims.tile_bytes;
+    const uint2 *wd = reinterpret_cast<const uint2 *>(w + dims.qs_bytes + rt * dims.n_bg * 128);
+    const uint2 *ad = reinterpret_cast<const uint2 *>(aq + act.d_offset);
+    constexpr float WS = (WTYPE == B200_TYPE_Q4_0) ? 0.0625f : 1.0f;  // Q4_0 nibbles sit in the high half of each byte: x16
+
+    for (int64_t bg = warp; bg < dims.n_bg; bg += MMVQ_WARPS) {
+        // weights of this tile
+        uint32_t wa[8], wb[8];  // row g / row g+8: Q4_0 uses [0..3] (blocks), Q8_0 [2*j], [2*j+1] (word t, word 4+t)
+        if (WTYPE == B200_TYPE_Q4_0) {
+            const uint4 *p = reinterpret_cast<const uint4 *>(wq + bg * 1024) + lane * 2;
+            const uint4 u0 = __ldg(p), u1 = __ldg(p + 1);
+            wa[0] = u0.x; wa[1] = u0.y; wa[2] = u0.z; wa[3] = u0.w;
+            wb[0] = u1.x; wb[1] = u1.y; wb[2] = u1.z; wb[3] = u1.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint4 u = __ldg(reinterpret_cast<const uint4 *>(wq + bg * 2048 + j * 512) + lane);
+                wa[2 * j] = u.x; wb[2 * j] = u.y; wa[2 * j + 1] = u.z; wb[2 * j + 1] = u.w;
+            }
+        }
+        const uint2 sa = __ldg(wd + bg * 16 + g), sb = __ldg(wd + bg * 16 + g + 8);
+        float dwa[4], dwb[4];
+        {
+            const __half2 a01 = *reinterpret_cast<const __half2 *>(&sa.x), a23 = *reinterpret_cast<const __half2 *>(&sa.y);
+            const __half2 b01 = *reinterpret_cast<const __half2 *>(&sb.x), b23 = *reinterpret_cast<const __half2 *>(&sb.y);
+            dwa[0] = __low2float(a01) * WS; dwa[1] = __high2float(a01) * WS; dwa[2] = __low2float(a23) * WS; dwa[3] = __high2float(a23) * WS;
+            dwb[0] = __low2float(b01) * WS; dwb[1] = __high2float(b01) * WS; dwb[2] = __low2float(b23) * WS; dwb[3] = __high2float(b23) * WS;
+        }
+#pragma unroll
+        for (int n = 0; n < NC; ++n) {
+            const uint2 sd = __ldg(ad + bg * 8 + n);
+            const __half2 d01 = *reinterpret_cast<const __half2 *>(&sd.x), d23 = *reinterpret_cast<const __half2 *>(&sd.y);
+            const float da[4] = {__low2float(d01), __high2float(d01), __low2float(d23), __high2float(d23)};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint2 a = __ldg(reinterpret_cast<const uint2 *>(aq + (bg * 4 + j) * 256) + n * 4 + t);
+                int s0, s1;
+                if (WTYPE == B200_TYPE_Q4_0) {
+                    s0 = __dp4a((int) ((wa[j] << 4) & 0xF0F0F0F0u), (int) a.x, 0);
+                    s0 = __dp4a((int) (wa[j] & 0xF0F0F0F0u), (int) a.y, s0);
+                    s1 = __dp4a((int) ((wb[j] << 4) & 0xF0F0F0F0u), (int) a.x, 0);
+                    s1 = __dp4a((int) (wb[j] & 0xF0F0F0F0u), (int) a.y, s1);
+                } else {
+                    s0 = __dp4a((int) wa[2 * j], (int) a.x, 0);
+                    s0 = __dp4a((int) wa[2 * j + 1], (int) a.y, s0);
+                    s1 = __dp4a((int) wb[2 * j], (int) a.x, 0);
+                    s1 = __dp4a((int) wb[2 * j + 1], (int) a.y, s1);
+                }
+                y[0][n] = fmaf(dwa[j] * da[j], (float) s0, y[0][n]);
+                y[1][n] = fmaf(dwb[j] * da[j], (float) s1, y[1][n]);
+            }
+        }
+    }
+
+    // fold the four t lanes
+#pragma unroll
+    for (int n = 0; n < NC; ++n) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            y[h][n] += __shfl_xor_sync(0xffffffffu, y[h][n], 1);
+            y[h][n] += __shfl_xor_sync(0xffffffffu, y[h][n], 2);
+        }
+    }
+    __shared__ float red[MMVQ_WARPS][16][NC];
+    if (t == 0) {
+#pragma unroll
+        for (int n = 0; n < NC; ++n) {
+            red[warp][g][n] = y[0][n];
+            red[warp][g + 8][n] = y[1][n];
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 16 * NC; i += MMVQ_WARPS * 32) {
+        const int n = i >> 4, r = i & 15;
+        const int64_t row = rt * 16 + r;
+        if (row < dims.M) {
+            float s = 0.0f;
+#pragma unroll
+            for (int wv = 0; wv < MMVQ_WARPS; ++wv) s += red[wv][r][n];
+            *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + n * dst_nb_row + row * 4) = s;
+        }
+    }
+}
+
+template <int WTYPE>
+static int launch_mmvq_t(const TiledDims &d, const uint8_t *w, const ActDims &a, const uint8_t *aq, float *dst,
+                         int64_t dst_nb_row, cudaStream_t st) {
+    const unsigned grid = (unsigned) d.n_rt;
+    const unsigned block = MMVQ_WARPS * 32;
+    switch (a.N) {
+        case 1: mmvq_kernel<WTYPE, 1><<<grid, block, 0, st>>>(d, w, a, aq, dst, dst_nb_row); break;
+        case 2: mmvq_kernel<WTYPE, 2><<<grid, block, 0, st>>>(d, w, a, aq, dst, dst_nb_row); break;
+        case 3: mmvq_kernel<WTYPE, 3><<<grid, block, 0, st>>>(d, w, a, aq, dst, dst_nb_row); break;
+        case 4: mmvq_kernel<WTYPE, 4><<<grid, block, 0, st>>>(d, w, a, aq, dst, dst_nb_row); break;
+        case 5: mmvq_kernel<WTYPE, 5><<<grid, block, 0, st>>>(d, w, a, aq, dst, dst_nb_row); break;
+        case 6: mmvq_kernel<WTYPE, 6><<<grid, block, 0, st>>>(d, w, a, aq, dst, dst_nb_row); break;
+        case 7: mmvq_kernel<WTYPE, 7><<<grid, block, 0, st>>>(d, w, a, aq, dst, dst_nb_row); break;
+        case 8: mmvq_kernel<WTYPE, 8><<<grid, block, 0, st>>>(d, w, a, aq, dst, dst_nb_row); break;
+        default: return set_error(B200_E_INVALID, "mmvq handles 1..8 columns, got %lld", (long long) a.N);
+    }
+    return check_launch("mmvq");
+}
+
+int launch_mmvq(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
+                cudaStream_t st) {
+    if (wtype == B200_TYPE_Q4_0) return launch_mmvq_t<B200_TYPE_Q4_0>(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, st);
+    return launch_mmvq_t<B200_TYPE_Q8_0>(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, st);
+}
+
+}  // namespace b200

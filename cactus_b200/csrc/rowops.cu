@@ -1,0 +1,169 @@
+// The small row ops that keep a llama layer on the device: RMS_NORM(+MUL), ADD, MUL, SILU(+MUL), ROPE,
+// CPY and GET_ROWS on f32 tables (cactus/ggml-cpu/ops.cpp, cactus/ggml-cpu/binary-ops.cpp).
+#include "common.cuh"
+
+namespace b200 {
+
+// RMS_NORM: ops.cpp:3268-3316.  The reference sums squares in double and scales by 1/sqrtf(mean + eps);
+// a following MUL by the weight row (binary-ops.cpp:152-154) is fused when w != NULL.
+__global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__ x, int64_t x_nb_row, const float *__restrict__ w,
+                                                      float *__restrict__ dst, int64_t dst_nb_row, int64_t d, float eps) {
+    const int64_t r = blockIdx.x;
+    const float *xr = reinterpret_cast<const float *>(reinterpret_cast<const char *>(x) + r * x_nb_row);
+    float *o = reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + r * dst_nb_row);
+    double sum = 0.0;
+    for (int64_t i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = xr[i];
+        sum += (double) (v * v);
+    }
+    __shared__ double red[8];
+    for (int o2 = 16; o2 > 0; o2 >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o2);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    double tot = 0.0;
+    for (int i = 0; i < (int) (blockDim.x >> 5); ++i) tot += red[i];
+    const float mean = (float) (tot / (double) d);
+    const float sc = 1.0f / sqrtf(mean + eps);
+    for (int64_t i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = xr[i] * sc;
+        o[i] = w ? v * w[i] : v;
+    }
+}
+
+template <int OP>  // 0 add, 1 mul
+__global__ void __launch_bounds__(256) binary_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ dst,
+                                                    int64_t d, int64_t total, int64_t b_rows) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const float bv = b_rows == 1 ? b[i % d] : b[i];
+    dst[i] = OP == 0 ? a[i] + bv : a[i] * bv;
+}
+
+// SILU: ops.cpp:2902-2981 (x / (1 + exp(-x))), optionally times b
+__global__ void __launch_bounds__(256) silu_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ dst, int64_t n) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float x = a[i];
+    const float s = x / (1.0f + expf(-x));
+    dst[i] = b ? s * b[i] : s;
+}
+
+// ROPE mode 0: ops.cpp:5080-5118, 5178-5362.  theta_i = pos * theta_scale^i, built by repeated
+// multiplication in the reference; one thread per (token, head) walks the pairs in the same order so
+// the angles are bit-identical.
+__global__ void __launch_bounds__(128) rope_norm_kernel(const float *__restrict__ x, int64_t x_nb_head, int64_t x_nb_tok,
+                                                       float *__restrict__ dst, int64_t dst_nb_head, int64_t dst_nb_tok, int64_t D,
+                                                       int64_t H, int64_t T, int n_dims, const int32_t *__restrict__ pos,
+                                                       const float *__restrict__ ff, float theta_scale, float freq_scale,
+                                                       float attn_factor) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= H * T) return;
+    const int64_t t = i / H, h = i - t * H;
+    const float *s = reinterpret_cast<const float *>(reinterpret_cast<const char *>(x) + t * x_nb_tok + h * x_nb_head);
+    float *o = reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + t * dst_nb_tok + h * dst_nb_head);
+    float theta = (float) pos[t];
+    for (int k = 0; k < n_dims; k += 2) {
+        const float f = ff ? ff[k / 2] : 1.0f;
+        const float th = freq_scale * (theta / f);
+        const float c = cosf(th) * attn_factor, sn = sinf(th) * attn_factor;
+        const float x0 = s[k], x1 = s[k + 1];
+        o[k] = x0 * c - x1 * sn;
+        o[k + 1] = x0 * sn + x1 * c;
+        theta *= theta_scale;
+    }
+    for (int64_t k = n_dims; k < D; ++k) o[k] = s[k];
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256) cpy_kernel(const float *__restrict__ x, int64_t x_nb_row, TO *__restrict__ dst, int64_t dst_nb_row,
+                                                 int64_t d, int64_t rows) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= d * rows) return;
+    const int64_t r = i / d, c = i - r * d;
+    const float v = reinterpret_cast<const float *>(reinterpret_cast<const char *>(x) + r * x_nb_row)[c];
+    TO *o = reinterpret_cast<TO *>(reinterpret_cast<char *>(dst) + r * dst_nb_row);
+    if constexpr (sizeof(TO) == 2) o[c] = __float2half_rn(v);
+    else o[c] = v;
+}
+
+__global__ void __launch_bounds__(256) get_rows_f32_kernel(const float *__restrict__ table, int64_t table_nb_row,
+                                                          const int32_t *__restrict__ ids, float *__restrict__ dst, int64_t dst_nb_row,
+                                                          int64_t d, int64_t n_ids) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= d * n_ids) return;
+    const int64_t r = i / d, c = i - r * d;
+    const float *src = reinterpret_cast<const float *>(reinterpret_cast<const char *>(table) + (int64_t) ids[r] * table_nb_row);
+    reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + r * dst_nb_row)[c] = src[c];
+}
+
+static inline unsigned blocks_for(int64_t n, int per = 256) { return (unsigned) ((n + per - 1) / per); }
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_rms_norm(const float *x, int64_t x_nb_row, const float *w, float *dst, int64_t dst_nb_row, int64_t d, int64_t rows,
+                  float eps, b200_stream_t stream) {
+    B200_REQUIRE(x && dst && d > 0 && rows >= 0 && x_nb_row % 4 == 0 && dst_nb_row % 4 == 0, "bad rms_norm arguments");
+    if (rows == 0) return B200_OK;
+    rms_norm_kernel<<<(unsigned) rows, 256, 0, (cudaStream_t) stream>>>(x, x_nb_row, w, dst, dst_nb_row, d, eps);
+    return check_launch("rms_norm");
+}
+
+int b200_add(const float *a, const float *b, float *dst, int64_t d, int64_t rows, int64_t b_rows, b200_stream_t stream) {
+    B200_REQUIRE(a && b && dst && d > 0 && rows >= 0 && (b_rows == 1 || b_rows == rows), "bad add arguments");
+    if (rows == 0) return B200_OK;
+    binary_kernel<0><<<blocks_for(d * rows), 256, 0, (cudaStream_t) stream>>>(a, b, dst, d, d * rows, b_rows);
+    return check_launch("add");
+}
+
+int b200_mul(const float *a, const float *b, float *dst, int64_t d, int64_t rows, int64_t b_rows, b200_stream_t stream) {
+    B200_REQUIRE(a && b && dst && d > 0 && rows >= 0 && (b_rows == 1 || b_rows == rows), "bad mul arguments");
+    if (rows == 0) return B200_OK;
+    binary_kernel<1><<<blocks_for(d * rows), 256, 0, (cudaStream_t) stream>>>(a, b, dst, d, d * rows, b_rows);
+    return check_launch("mul");
+}
+
+int b200_silu(const float *a, const float *b, float *dst, int64_t n, b200_stream_t stream) {
+    B200_REQUIRE(a && dst && n >= 0, "bad silu arguments");
+    if (n == 0) return B200_OK;
+    silu_kernel<<<blocks_for(n), 256, 0, (cudaStream_t) stream>>>(a, b, dst, n);
+    return check_launch("silu");
+}
+
+int b200_rope_norm(const float *x, int64_t x_nb_head, int64_t x_nb_tok, float *dst, int64_t dst_nb_head, int64_t dst_nb_tok,
+                   int64_t D, int64_t H, int64_t T, int n_dims, const int32_t *pos, const float *freq_factors, float freq_base,
+                   float freq_scale, float attn_factor, b200_stream_t stream) {
+    B200_REQUIRE(x && dst && pos && D > 0 && H > 0 && T >= 0 && n_dims > 0 && n_dims <= D && n_dims % 2 == 0, "bad rope arguments");
+    if (T == 0) return B200_OK;
+    const float theta_scale = powf(freq_base, -2.0f / (float) n_dims);
+    rope_norm_kernel<<<blocks_for(H * T, 128), 128, 0, (cudaStream_t) stream>>>(x, x_nb_head, x_nb_tok, dst, dst_nb_head, dst_nb_tok, D, H, T,
+                                                                              n_dims, pos, freq_factors, theta_scale, freq_scale, attn_factor);
+    return check_launch("rope_norm");
+}
+
+int b200_cpy_f32_f16(const float *x, int64_t x_nb_row, void *dst, int64_t dst_nb_row, int64_t d, int64_t rows, b200_stream_t stream) {
+    B200_REQUIRE(x && dst && d > 0 && rows >= 0 && x_nb_row % 4 == 0 && dst_nb_row % 2 == 0, "bad cpy arguments");
+    if (rows == 0) return B200_OK;
+    cpy_kernel<__half><<<blocks_for(d * rows), 256, 0, (cudaStream_t) stream>>>(x, x_nb_row, (__half *) dst, dst_nb_row, d, rows);
+    return check_launch("cpy_f32_f16");
+}
+
+int b200_cpy_f32_f32(const float *x, int64_t x_nb_row, float *dst, int64_t dst_nb_row, int64_t d, int64_t rows, b200_stream_t stream) {
+    B200_REQUIRE(x && dst && d > 0 && rows >= 0 && x_nb_row % 4 == 0 && dst_nb_row % 4 == 0, "bad cpy arguments");
+    if (rows == 0) return B200_OK;
+    cpy_kernel<float><<<blocks_for(d * rows), 256, 0, (cudaStream_t) stream>>>(x, x_nb_row, dst, dst_nb_row, d, rows);
+    return check_launch("cpy_f32_f32");
+}
+
+int b200_get_rows_f32(const float *table, int64_t table_nb_row, const int32_t *ids, float *dst, int64_t dst_nb_row, int64_t d,
+                      int64_t n_ids, b200_stream_t stream) {
+    B200_REQUIRE(table && ids && dst && d > 0 && n_ids >= 0, "bad get_rows arguments");
+    if (n_ids == 0) return B200_OK;
+    get_rows_f32_kernel<<<blocks_for(d * n_ids), 256, 0, (cudaStream_t) stream>>>(table, table_nb_row, ids, dst, dst_nb_row, d, n_ids);
+    return check_launch("get_rows_f32");
+}
+
+}  // extern "C"

@@ -1,0 +1,186 @@
+/*
+ * cactus_b200 -- C ABI of the B200 (sm_100a) kernels behind the ggml backend plug-in.
+ *
+ * This is the boundary between host code (the ggml-backend plug-in in C++, or any FFI binding) and the
+ * hand-written CUDA kernels.  Plain pointers, sizes and byte strides only; no C++ or framework types.
+ * Unless said otherwise every pointer is a DEVICE pointer, every call is asynchronous on `stream`
+ * (a cudaStream_t passed as void*, NULL = the legacy default stream) and returns 0 on success or a
+ * negative B200_E_* code; b200_last_error() gives the message for the calling thread.
+ *
+ * Each entry point names the routine of the reference (cactus's vendored ggml, paths relative to the
+ * reference project root) whose work it takes over when the plug-in's graph_compute
+ * (cactus/ggml-backend-impl.h:110) dispatches a node.
+ *
+ * Tensor conventions are ggml's: ne[0] is the contiguous dimension.  A mul_mat computes
+ * dst[n][m] = sum_k W[m][k] * x[n][k]   with W = src0 [K, M], x = src1 [K, N], dst [M, N].
+ */
+#ifndef CACTUS_B200_H
+#define CACTUS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define B200_API __declspec(dllexport)
+#else
+#define B200_API __attribute__((visibility("default")))
+#endif
+
+#define B200_ABI_VERSION 1
+
+/* error codes */
+#define B200_OK 0
+#define B200_E_INVALID (-1)   /* bad argument (shape, alignment, type) */
+#define B200_E_CUDA (-2)      /* a CUDA runtime call or launch failed */
+#define B200_E_SCRATCH (-3)   /* scratch buffer too small */
+#define B200_E_NODEVICE (-4)  /* no sm_100 device */
+
+/* weight types: the ids of the reference's enum lm_ggml_type (cactus/ggml.h:351-360) */
+#define B200_TYPE_F32 0
+#define B200_TYPE_F16 1
+#define B200_TYPE_Q4_0 2
+#define B200_TYPE_Q8_0 8
+
+/* Q8_0 activation quantiser arithmetic (cactus/ggml-cpu/ggml-cpu-quants.c:732-1045) */
+#define B200_Q8_AVX2 0   /* id = 127/max, round to nearest even: the x86 AVX/AVX2 branch (:802-885) */
+#define B200_Q8_SCALAR 1 /* id = 1/d, roundf: quantize_row_q8_0_ref (cactus/ggml-quants.c:188-211) */
+
+typedef void *b200_stream_t;
+
+B200_API int b200_abi_version(void);
+B200_API const char *b200_last_error(void);
+/* number of sm_100 devices visible; fills name/total memory of `device` when the pointers are non-NULL */
+B200_API int b200_device_count(void);
+B200_API int b200_device_info(int device, char *name, size_t name_len, size_t *free_bytes, size_t *total_bytes, int *sm_count);
+/* kernels launched by this library in the calling process since load (for launch accounting) */
+B200_API uint64_t b200_launch_count(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Weight storage.
+ *
+ * Quantised weights live on the device in a tiled layout ("T16": 16-row x 4-block tiles in the
+ * register order of the int8 tensor-core fragments, nibbles stored as two's-complement, scales in a
+ * separate plane).  b200_weight_bytes gives the device size for a [K, M] tensor; b200_weight_upload
+ * converts from the reference's row-major block_q4_0 / block_q8_0 stream (cactus/ggml-common.h:167-172,
+ * :209-214), as a backend buffer's set_tensor (cactus/ggml-backend-impl.h:51) does at model load;
+ * b200_weight_download is the exact inverse (get_tensor, :52).  `src`/`dst` of upload/download are
+ * DEVICE pointers to the row-major stream (the plug-in stages host data through a device bounce
+ * buffer); `rows_begin/rows_count` select a range of rows (multiple of 16 unless it ends at M) so that
+ * a loader may upload in pieces.
+ * ---------------------------------------------------------------------------------------------- */
+B200_API size_t b200_weight_bytes(int wtype, int64_t K, int64_t M);
+B200_API int b200_weight_upload(int wtype, int64_t K, int64_t M, const void *src_rowmajor, void *dst_tiled,
+                                int64_t rows_begin, int64_t rows_count, b200_stream_t stream);
+B200_API int b200_weight_download(int wtype, int64_t K, int64_t M, const void *src_tiled, void *dst_rowmajor,
+                                  int64_t rows_begin, int64_t rows_count, b200_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * quantize_row_q8_0 (cactus/ggml-cpu/ggml-cpu-quants.c:732) over N rows of K floats.
+ * Output in the reference's block_q8_0 layout (34-byte blocks, row after row): bit-exact with the
+ * selected variant.  Used for parity checks; mul_mat quantises internally with the same device code.
+ * ---------------------------------------------------------------------------------------------- */
+B200_API int b200_quantize_q8_0(const float *x, int64_t x_row_stride_bytes, int64_t K, int64_t N, void *dst_blocks,
+                                int variant, b200_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * MUL_MAT with quantised weights: lm_ggml_compute_forward_mul_mat (cactus/ggml-cpu/ggml-cpu.c:1257-1449)
+ * = quantize_row_q8_0 on every src1 row, then lm_ggml_vec_dot_q4_0_q8_0 / _q8_0_q8_0
+ * (ggml-cpu-quants.c:1906 / :3591) for every (row, column).
+ *   w        tiled weights from b200_weight_upload, [K, M]
+ *   x        f32 activations, N rows of K, row stride in bytes
+ *   dst      f32, N rows of M, row stride in bytes
+ *   scratch  b200_mul_mat_scratch_bytes(wtype, K, M, N) bytes of device memory, 256-byte aligned,
+ *            private to the call until it completes: the quantised activations (b200_act_bytes) followed
+ *            by the split-K workspace (b200_mul_mat_workspace_bytes)
+ * N <= 8 uses the HBM-bound dp4a kernel, larger N the int8 tensor-core kernel.
+ * ---------------------------------------------------------------------------------------------- */
+B200_API size_t b200_act_bytes(int64_t K, int64_t N);
+B200_API size_t b200_mul_mat_workspace_bytes(int wtype, int64_t K, int64_t M, int64_t N);
+B200_API size_t b200_mul_mat_scratch_bytes(int wtype, int64_t K, int64_t M, int64_t N);
+B200_API int b200_mul_mat_q(int wtype, const void *w, int64_t K, int64_t M, const float *x, int64_t x_row_stride_bytes,
+                            int64_t N, float *dst, int64_t dst_row_stride_bytes, void *scratch, size_t scratch_bytes,
+                            int variant, b200_stream_t stream);
+/* The two halves of b200_mul_mat_q, so one quantised activation tensor can feed several weights
+ * (wq/wk/wv, gate/up): quantise once into `act` (b200_act_bytes), then multiply; `workspace`
+ * (b200_mul_mat_workspace_bytes, may be 0 -> NULL) is private to each multiply. */
+B200_API int b200_quantize_activations(const float *x, int64_t x_row_stride_bytes, int64_t K, int64_t N, void *act,
+                                       size_t act_bytes, int variant, b200_stream_t stream);
+B200_API int b200_mul_mat_q_prequant(int wtype, const void *w, int64_t K, int64_t M, const void *act, int64_t N,
+                                     float *dst, int64_t dst_row_stride_bytes, void *workspace, size_t workspace_bytes,
+                                     b200_stream_t stream);
+/* Exact per-block integer dots of the same kernel inputs (debug/parity): out int32 [N][M][K/32]. */
+B200_API int b200_block_dots(int wtype, const void *w, int64_t K, int64_t M, const float *x, int64_t x_row_stride_bytes,
+                             int64_t N, int32_t *out, void *act, size_t act_bytes, int variant, b200_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * FLASH_ATTN_EXT: lm_ggml_compute_forward_flash_attn_ext_f16 (cactus/ggml-cpu/ops.cpp:6948-7165) for
+ * f32 Q, f16 K/V (the unified KV cache, cactus/llama-kv-cache.cpp:583-656) and an f16 mask.
+ *   q     f32, element (d, token t, head h) at byte offset t*q_nb_tok + h*q_nb_head + 4*d
+ *   k, v  f16, element (d, cell c, kv-head g) at byte offset c*k_nb_cell + g*k_nb_head + 2*d
+ *   mask  f16 [n_kv] per token row, row stride mask_nb_row bytes; a cell is skipped iff its mask is -inf
+ *         (:7078-7081); may be NULL (no masking)
+ *   dst   f32 [D, H, Nq] contiguous: row (t*H + h)
+ *   scale, max_bias, logit_softcap: op_params of the node (cactus/ggml.c:4405-4444)
+ *   scratch b200_flash_attn_scratch_bytes(...) bytes, 256-byte aligned
+ * D in {64, 128}; H a multiple of Hkv (grouped-query attention).
+ * ---------------------------------------------------------------------------------------------- */
+B200_API size_t b200_flash_attn_scratch_bytes(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, int64_t n_kv);
+B200_API int b200_flash_attn_ext(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, int64_t n_kv,
+                                 const float *q, int64_t q_nb_tok, int64_t q_nb_head,
+                                 const void *k, int64_t k_nb_cell, int64_t k_nb_head,
+                                 const void *v, int64_t v_nb_cell, int64_t v_nb_head,
+                                 const void *mask, int64_t mask_nb_row,
+                                 float scale, float max_bias, float logit_softcap,
+                                 float *dst, void *scratch, size_t scratch_bytes, b200_stream_t stream);
+/* The mask scan alone: per token row, the list of cells whose mask is not -inf.  A plug-in runs it
+ * once per graph and shares the result between all layers (the mask tensor is the same node).
+ * b200_flash_attn_ext_indexed then skips its own scan. */
+B200_API size_t b200_mask_index_bytes(int64_t Nq, int64_t n_kv);
+B200_API int b200_mask_index_build(const void *mask, int64_t mask_nb_row, int64_t Nq, int64_t n_kv, void *index,
+                                   size_t index_bytes, b200_stream_t stream);
+B200_API int b200_flash_attn_ext_indexed(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, int64_t n_kv,
+                                         const float *q, int64_t q_nb_tok, int64_t q_nb_head,
+                                         const void *k, int64_t k_nb_cell, int64_t k_nb_head,
+                                         const void *v, int64_t v_nb_cell, int64_t v_nb_head,
+                                         const void *mask, int64_t mask_nb_row, const void *index,
+                                         float scale, float max_bias, float logit_softcap,
+                                         float *dst, void *scratch, size_t scratch_bytes, b200_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * The small ops that keep a llama layer on the device (cactus/ggml-cpu/ops.cpp, binary-ops.cpp).
+ * All rows are f32 with the given byte strides unless noted.
+ * ---------------------------------------------------------------------------------------------- */
+/* RMS_NORM (ops.cpp:3268-3316); w may be NULL; with w it also applies the following MUL by a weight row
+ * (binary-ops.cpp:152-154), which is how llama builds every norm (cactus/llama-graph.cpp:527-560) */
+B200_API int b200_rms_norm(const float *x, int64_t x_nb_row, const float *w, float *dst, int64_t dst_nb_row, int64_t d,
+                           int64_t rows, float eps, b200_stream_t stream);
+/* ADD / MUL of same-shape contiguous tensors, or with b broadcast along rows when b_rows == 1 */
+B200_API int b200_add(const float *a, const float *b, float *dst, int64_t d, int64_t rows, int64_t b_rows, b200_stream_t stream);
+B200_API int b200_mul(const float *a, const float *b, float *dst, int64_t d, int64_t rows, int64_t b_rows, b200_stream_t stream);
+/* UNARY SILU (ops.cpp:2902-2981); with b != NULL also the following MUL (llama-graph.cpp:619-664) */
+B200_API int b200_silu(const float *a, const float *b, float *dst, int64_t n, b200_stream_t stream);
+/* ROPE, mode 0 ("norm", adjacent pairs), no YaRN extrapolation (ops.cpp:5080-5118, 5178-5362):
+ * x [D, H, T] with byte strides, int32 pos[T]; freq_factors may be NULL; n_dims <= D */
+B200_API int b200_rope_norm(const float *x, int64_t x_nb_head, int64_t x_nb_tok, float *dst, int64_t dst_nb_head,
+                            int64_t dst_nb_tok, int64_t D, int64_t H, int64_t T, int n_dims, const int32_t *pos,
+                            const float *freq_factors, float freq_base, float freq_scale, float attn_factor,
+                            b200_stream_t stream);
+/* CPY f32 -> f16 / f32 -> f32 (ops.cpp:657, :4180): rows of d elements with byte strides on both sides */
+B200_API int b200_cpy_f32_f16(const float *x, int64_t x_nb_row, void *dst, int64_t dst_nb_row, int64_t d, int64_t rows,
+                              b200_stream_t stream);
+B200_API int b200_cpy_f32_f32(const float *x, int64_t x_nb_row, float *dst, int64_t dst_nb_row, int64_t d, int64_t rows,
+                              b200_stream_t stream);
+/* GET_ROWS (ops.cpp:4236-4403): table f32 (row stride bytes) or tiled quantised weights [d, n_table_rows] */
+B200_API int b200_get_rows_f32(const float *table, int64_t table_nb_row, const int32_t *ids, float *dst, int64_t dst_nb_row,
+                               int64_t d, int64_t n_ids, b200_stream_t stream);
+B200_API int b200_get_rows_q(int wtype, const void *table_tiled, int64_t d, int64_t n_table_rows, const int32_t *ids,
+                             float *dst, int64_t dst_nb_row, int64_t n_ids, b200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,58 @@
+"""The C-ABI library loads and exports exactly the symbols include/cactus_b200.h declares (no GPU needed)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    hdr = open(os.path.join(ROOT, "include", "cactus_b200.h")).read()
+    return sorted(set(re.findall(r"B200_API[^;]*?\b(b200_\w+)\s*\(", hdr)))
+
+
+def test_library_exports_every_declared_symbol():
+    from cactus_b200 import LIB_PATH
+    from cactus_b200.build import build
+    build()
+    assert os.path.exists(LIB_PATH)
+    L = ctypes.CDLL(LIB_PATH)
+    names = declared_symbols()
+    assert len(names) >= 30
+    for n in names:
+        assert hasattr(L, n), f"{n} declared in the header but not exported"
+
+
+def test_python_binding_covers_the_header():
+    from cactus_b200._lib import SIGNATURES
+    assert sorted(SIGNATURES) == declared_symbols()
+
+
+def test_size_queries_and_argument_checks_without_a_gpu():
+    from cactus_b200._lib import lib
+    L = lib()
+    assert L.b200_abi_version() == 1
+    # T16 layout: rows padded to 16, blocks to 4; 18 bytes per Q4_0 block, 34 per Q8_0 block
+    assert L.b200_weight_bytes(2, 4096, 4096) == 4096 * 128 * 18
+    assert L.b200_weight_bytes(8, 2048, 128256) == 128256 * 64 * 34
+    assert L.b200_weight_bytes(2, 64, 33) == 48 * 4 * 18
+    assert L.b200_weight_bytes(2, 100, 16) == 0      # K not a multiple of 32
+    assert L.b200_weight_bytes(3, 128, 16) == 0      # unsupported type
+    assert L.b200_act_bytes(4096, 1) == 128 * 256 + 32 * 64
+    assert L.b200_mul_mat_scratch_bytes(2, 4096, 4096, 8) == L.b200_act_bytes(4096, 8)
+    assert L.b200_mask_index_bytes(64, 65536) == 64 * 1024 * 8
+    # invalid arguments are rejected before any CUDA call
+    rc = L.b200_mul_mat_q(5, None, 64, 16, None, 256, 1, None, 64, None, 0, 0, None)
+    assert rc == -1 and b"bad mul_mat" in L.b200_last_error()
+    rc = L.b200_flash_attn_ext(96, 8, 8, 1, 256, None, 0, 0, None, 0, 0, None, 0, 0, None, 0, 1.0, 0.0, 0.0, None, None, 0, None)
+    assert rc == -1 and b"head size" in L.b200_last_error()
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    import cactus_b200._lib as m
+    monkeypatch.setattr(m, "_lib", None)
+    monkeypatch.setattr(m, "LIB_PATH", "/nonexistent/libcactus_b200.so")
+    with pytest.raises(m.B200Error, match="no CPU or framework fallback"):
+        m.lib()

@@ -1,0 +1,117 @@
+"""K5 on the GPU: FLASH_ATTN_EXT for ragged multi-sequence batches over the f16 cache.
+
+Tolerance: max|gpu - ref| / max|ref| <= 2e-3 against the reference (whose output accumulator is fp16);
+the distance to a double-accumulating restatement is checked too, since the kernel accumulates in fp32.
+"""
+import numpy as np
+import pytest
+import torch
+
+import inputs
+from gpu_util import dev, f16, host, rel_max_err
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+def run_case(c, **kw):
+    from cactus_b200 import ops
+    out = ops.flash_attn_ext(dev(c["q"]), f16(c["kc"]), f16(c["vc"]), f16(c["mask"]), c["scale"], n_kv=c["n_kv"],
+                             max_bias=c.get("max_bias", 0.0), logit_softcap=c.get("softcap", 0.0), **kw)
+    return host(out)
+
+
+def test_cases_vs_golden(golden):
+    for name, c in inputs.fattn_cases().items():
+        got = run_case(c)
+        assert rel_max_err(got[c["valid_rows"]], golden["fa_" + name]) < TOL, name
+
+
+@pytest.mark.parametrize("spec", [
+    (128, 32, 8, 2048, [(700, 1), (64, 1), (1, 1), (333, 1), (900, 1)]),      # ragged decode batch, GQA 4
+    (64, 32, 8, 1024, [(512, 1), (100, 1)]),                                  # head size 64 (1B architecture)
+    (128, 64, 8, 1024, [(300, 2), (77, 1)]),                                  # GQA 8 (70B architecture)
+    (128, 4, 4, 512, [(100, 3)]),                                             # no GQA
+    (128, 6, 2, 512, [(40, 2), (200, 2)]),                                    # GQA 3: one head per CTA
+    (128, 8, 2, 8192, [(5000, 1)]),                                           # one sequence, long: KV splits
+    (128, 8, 2, 4096, [(1500, 40), (900, 24)]),                               # prefill chunks of two sequences
+])
+def test_ragged_batches_vs_oracle(oracle, spec):
+    D, H, Hkv, cells, seqs = spec
+    c = inputs.ragged_case(hash(spec[:4]) % 1000, D, H, Hkv, cells, seqs)
+    ref = oracle.flash_attn_ext(c["q"], c["kc"], c["vc"], c["mask"], c["scale"], n_kv=c["n_kv"])
+    truth = oracle.flash_attn_ext(c["q"], c["kc"], c["vc"], c["mask"], c["scale"], n_kv=c["n_kv"], acc_mode=1)
+    got = run_case(c)
+    v = c["valid_rows"]
+    assert np.isfinite(got[v]).all()
+    assert rel_max_err(got[v], ref[v]) < TOL
+    # fp32 accumulation sits closer to the double-accumulated result than the fp16-accumulating reference does
+    assert rel_max_err(got[v], truth[v]) <= rel_max_err(ref[v], truth[v]) + 1e-5
+
+
+def test_no_mask(oracle):
+    from cactus_b200 import ops
+    c = inputs.ragged_case(5, 128, 8, 2, 256, [(256, 2)], pad=256)
+    ref = oracle.flash_attn_ext(c["q"], c["kc"], c["vc"], np.zeros_like(c["mask"]), c["scale"], n_kv=256)
+    out = host(ops.flash_attn_ext(dev(c["q"]), f16(c["kc"]), f16(c["vc"]), None, c["scale"], n_kv=256))
+    assert rel_max_err(out, ref) < TOL
+
+
+def test_padding_rows_do_not_poison_real_rows(oracle):
+    """Mask rows beyond the real tokens are all -inf (cactus/llama-kv-cache.cpp:752-759); only Nq rows are
+    computed, and a cache full of NaN bit patterns in unattended cells must not leak."""
+    c = inputs.ragged_case(6, 128, 8, 2, 512, [(100, 3), (50, 1)])
+    kc, vc = c["kc"].copy(), c["vc"].copy()
+    unused = c["cell_seq"] < 0
+    kc[unused] = 0x7E00   # NaN
+    vc[unused] = 0x7E00
+    c2 = dict(c, kc=kc, vc=vc)
+    ref = oracle.flash_attn_ext(c["q"], c["kc"], c["vc"], c["mask"], c["scale"], n_kv=c["n_kv"])
+    got = run_case(c2)
+    assert np.isfinite(got).all() and rel_max_err(got, ref) < TOL
+
+
+def test_config2_shape_sampled(oracle):
+    """Config 2: 32 query heads, 8 KV heads, head 128, 8192 slots, 16 sequences with ragged contexts and
+    1-256 query tokens each.  Context lengths drawn from U[64, 4096] are rescaled to fit the 8192 slots
+    and the query tokens clipped to a 512-token ubatch; the oracle checks a sample of the tokens."""
+    rng = np.random.default_rng(0)
+    ctx = rng.integers(64, 4097, 16)
+    nq = rng.integers(1, 257, 16)
+    ctx = np.maximum(64, (ctx * min(1.0, 8192 / ctx.sum() * 0.999)).astype(int))
+    while ctx.sum() > 8192:
+        ctx[np.argmax(ctx)] -= ctx.sum() - 8192
+    nq = np.minimum(nq, ctx)
+    nq = np.maximum(1, (nq * min(1.0, 512 / nq.sum())).astype(int))
+    c = inputs.ragged_case(0, 128, 32, 8, 8192, list(zip(ctx.tolist(), nq.tolist())))
+    got = run_case(c)
+    pick = np.sort(rng.choice(len(c["tok_pos"]), 24, replace=False))
+    maskp = np.full((64, c["n_kv"]), 0xFC00, np.uint16)
+    maskp[:24] = c["mask"][pick]
+    ref = oracle.flash_attn_ext(c["q"][pick], c["kc"], c["vc"], maskp, c["scale"], n_kv=c["n_kv"])
+    assert np.isfinite(got).all()
+    assert rel_max_err(got[pick], ref) < TOL
+
+
+def test_permutation_property_full_size():
+    """Size-independent property at 65536 cells x 64 sequences: attention does not depend on where a
+    sequence's cells sit in the cache, so permuting the cells (and the mask columns) leaves the output
+    unchanged up to float reordering."""
+    from cactus_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(1)
+    n_kv, Nq, H, Hkv, D = 65536, 64, 32, 8, 128
+    k = torch.randn((n_kv, Hkv, D), device="cuda", generator=g).half()
+    v = torch.randn((n_kv, Hkv, D), device="cuda", generator=g).half()
+    q = torch.randn((Nq, H, D), device="cuda", generator=g)
+    seq = torch.randint(0, 64, (n_kv,), device="cuda", generator=g)
+    mask = torch.full((64, n_kv), float("-inf"), device="cuda", dtype=torch.float16)
+    mask[seq[None, :] == torch.arange(64, device="cuda")[:, None]] = 0
+    a = ops.flash_attn_ext(q, k, v, mask, D ** -0.5)
+    perm = torch.randperm(n_kv, device="cuda", generator=g)
+    b = ops.flash_attn_ext(q, k[perm].contiguous(), v[perm].contiguous(), mask[:, perm].contiguous(), D ** -0.5)
+    assert torch.isfinite(a).all()
+    assert rel_max_err(host(a), host(b)) < 1e-4
+    # and the softmax weights sum to one: with V = 1 everywhere the output is exactly 1
+    ones = torch.ones_like(v)
+    o = ops.flash_attn_ext(q, k, ones, mask, D ** -0.5)
+    assert float((o - 1).abs().max()) < 1e-5
