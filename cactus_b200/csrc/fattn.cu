@@ -58,6 +58,7 @@ __global__ void __launch_bounds__(FA_THREADS) fattn_vec_kernel(FattnParams p) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int e = lane & 7;          // lane inside the sub-warp
     const int sg = warp * 4 + (lane >> 3);  // sub-warp 0..15
+    const unsigned sub_mask = 0xFFu << (lane & 24);  // the 8 lanes of this sub-warp
     const int64_t j = blockIdx.x;    // token
     const int hk = blockIdx.y / p.hgroups, hg = blockIdx.y % p.hgroups;
     const int split = blockIdx.z;
@@ -124,6 +125,8 @@ __global__ void __launch_bounds__(FA_THREADS) fattn_vec_kernel(FattnParams p) {
         }
         __syncthreads();
         const int count = list_count;
+        // sub-warps run the same number of rounds; the shuffles below name only the 8 lanes of a sub-warp,
+        // and a sub-warp without a cell in the last round skips it as a whole
         for (int idx = sg; idx < count; idx += 16) {
             const int64_t cell = cell_list[idx];
             const char *kp = p.k + cell * p.k_nb_cell + (int64_t) hk * p.k_nb_head + e * E * 2;
@@ -152,9 +155,9 @@ __global__ void __launch_bounds__(FA_THREADS) fattn_vec_kernel(FattnParams p) {
                 float a = 0.0f;
 #pragma unroll
                 for (int i = 0; i < E; ++i) a = fmaf(qf[h][i], kf[i], a);
-                a += __shfl_xor_sync(0xffffffffu, a, 1);
-                a += __shfl_xor_sync(0xffffffffu, a, 2);
-                a += __shfl_xor_sync(0xffffffffu, a, 4);
+                a += __shfl_xor_sync(sub_mask, a, 1);
+                a += __shfl_xor_sync(sub_mask, a, 2);
+                a += __shfl_xor_sync(sub_mask, a, 4);
                 a *= p.scale;
                 if (p.softcap != 0.0f) a = p.softcap * tanhf(a);
                 s[h] = a + slope[h] * mval;

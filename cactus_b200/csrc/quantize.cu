@@ -33,9 +33,10 @@ __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float *__restr
         }
     }
     float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+    const unsigned grp = 0xFFu << (threadIdx.x & 24);  // the 8 lanes that share this block
+    amax = fmaxf(amax, __shfl_xor_sync(grp, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(grp, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(grp, amax, 4));
     __half d;
     float id;
     q8_scales(amax, variant, &d, &id);
@@ -190,7 +191,9 @@ __global__ void __launch_bounds__(256) get_rows_q_kernel(TiledDims dims, const u
     o[k] = (float) tiled_quant<WTYPE>(dims, w, row, b, (int) (k & 31)) * tiled_scale<WTYPE>(dims, w, row, b);
 }
 
-// exact integer dot of weight block (m, b) with activation block (n, b): out[(n*M + m)*nb + b]
+// exact integer dot of weight block (m, b) with activation block (n, b): out[(n*M + m)*nb + b].
+// Uses the same word-level dp4a arithmetic as the mul_mat kernels (Q4_0 nibbles in the high half of each
+// byte, i.e. 16x the value, undone by an exact shift).
 template <int WTYPE>
 __global__ void __launch_bounds__(256) block_dots_kernel(TiledDims dims, ActDims act, const uint8_t *__restrict__ w,
                                                         const uint8_t *__restrict__ aq, int32_t *__restrict__ out) {
@@ -200,15 +203,26 @@ __global__ void __launch_bounds__(256) block_dots_kernel(TiledDims dims, ActDims
     const int64_t b = gid % dims.nb;
     const int64_t m = (gid / dims.nb) % dims.M;
     const int64_t n = gid / (dims.nb * dims.M);
-    const uint8_t *tile = aq + ((n >> 3) * act.nbp + b) * 256;
-    const int g = (int) (n & 7);
+    const uint2 *atile = reinterpret_cast<const uint2 *>(aq + ((n >> 3) * act.nbp + b) * 256) + (n & 7) * 4;
+    const int64_t rt = m >> 4;
+    const int r = (int) (m & 15), g = r & 7, hi_row = r >> 3;
+    const int jb = (int) (b & 3);
+    const uint8_t *tile = w + (rt * dims.n_bg + (b >> 2)) * dims.tile_bytes;
     int sum = 0;
-    for (int e = 0; e < 32; ++e) {
-        const int wi = (e & 15) >> 2;
-        const int8_t a = (int8_t) tile[(g * 4 + wi) * 8 + (e >= 16 ? 4 : 0) + (e & 3)];
-        sum += tiled_quant<WTYPE>(dims, w, m, b, e) * (int) a;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        const uint2 a = atile[t];
+        if (WTYPE == B200_TYPE_Q4_0) {
+            const uint32_t word = reinterpret_cast<const uint32_t *>(tile + (g * 4 + t) * 32)[hi_row * 4 + jb];
+            sum = __dp4a((int) ((word << 4) & 0xF0F0F0F0u), (int) a.x, sum);
+            sum = __dp4a((int) (word & 0xF0F0F0F0u), (int) a.y, sum);
+        } else {
+            const uint32_t *lane = reinterpret_cast<const uint32_t *>(tile + jb * 512 + (g * 4 + t) * 16);
+            sum = __dp4a((int) lane[hi_row], (int) a.x, sum);
+            sum = __dp4a((int) lane[2 + hi_row], (int) a.y, sum);
+        }
     }
-    out[gid] = sum;
+    out[gid] = (WTYPE == B200_TYPE_Q4_0) ? (sum >> 4) : sum;
 }
 
 static int check_wtype(int wtype) {

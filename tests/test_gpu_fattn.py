@@ -1,7 +1,12 @@
 """K5 on the GPU: FLASH_ATTN_EXT for ragged multi-sequence batches over the f16 cache.
 
-Tolerance: max|gpu - ref| / max|ref| <= 2e-3 against the reference (whose output accumulator is fp16);
-the distance to a double-accumulating restatement is checked too, since the kernel accumulates in fp32.
+Tolerance, in the normalised metric max|a - b| / max|b|:
+  * against the same computation with a double accumulator (the oracle's acc_mode 1, same fp16-rounded Q
+    and f16 K/V): <= 2e-3 -- in practice ~3e-7, because the kernel accumulates in fp32;
+  * against the reference itself: <= 2e-3 plus the reference's own distance from that double-accumulated
+    result.  The reference keeps its output accumulator in fp16 (cactus/ggml-cpu/ops.cpp:7103-7117) and is
+    by itself up to ~3e-3 away from the exact result on these cases, so a kernel that is more accurate
+    than the reference cannot be closer to it than that.
 """
 import numpy as np
 import pytest
@@ -21,10 +26,15 @@ def run_case(c, **kw):
     return host(out)
 
 
-def test_cases_vs_golden(golden):
+def test_cases_vs_golden(oracle, golden):
     for name, c in inputs.fattn_cases().items():
         got = run_case(c)
-        assert rel_max_err(got[c["valid_rows"]], golden["fa_" + name]) < TOL, name
+        v = c["valid_rows"]
+        truth = oracle.flash_attn_ext(c["q"], c["kc"], c["vc"], c["mask"], c["scale"], n_kv=c["n_kv"],
+                                      max_bias=c.get("max_bias", 0.0), softcap=c.get("softcap", 0.0), acc_mode=1)[v]
+        ref = golden["fa_" + name]
+        assert rel_max_err(got[v], truth) < 1e-5, name
+        assert rel_max_err(got[v], ref) < TOL + rel_max_err(ref, truth), name
 
 
 @pytest.mark.parametrize("spec", [
@@ -44,17 +54,16 @@ def test_ragged_batches_vs_oracle(oracle, spec):
     got = run_case(c)
     v = c["valid_rows"]
     assert np.isfinite(got[v]).all()
-    assert rel_max_err(got[v], ref[v]) < TOL
-    # fp32 accumulation sits closer to the double-accumulated result than the fp16-accumulating reference does
-    assert rel_max_err(got[v], truth[v]) <= rel_max_err(ref[v], truth[v]) + 1e-5
+    assert rel_max_err(got[v], truth[v]) < 1e-5
+    assert rel_max_err(got[v], ref[v]) < TOL + rel_max_err(ref[v], truth[v])
 
 
 def test_no_mask(oracle):
     from cactus_b200 import ops
     c = inputs.ragged_case(5, 128, 8, 2, 256, [(256, 2)], pad=256)
-    ref = oracle.flash_attn_ext(c["q"], c["kc"], c["vc"], np.zeros_like(c["mask"]), c["scale"], n_kv=256)
+    truth = oracle.flash_attn_ext(c["q"], c["kc"], c["vc"], np.zeros_like(c["mask"]), c["scale"], n_kv=256, acc_mode=1)
     out = host(ops.flash_attn_ext(dev(c["q"]), f16(c["kc"]), f16(c["vc"]), None, c["scale"], n_kv=256))
-    assert rel_max_err(out, ref) < TOL
+    assert rel_max_err(out, truth) < 1e-5
 
 
 def test_padding_rows_do_not_poison_real_rows(oracle):
@@ -66,9 +75,9 @@ def test_padding_rows_do_not_poison_real_rows(oracle):
     kc[unused] = 0x7E00   # NaN
     vc[unused] = 0x7E00
     c2 = dict(c, kc=kc, vc=vc)
-    ref = oracle.flash_attn_ext(c["q"], c["kc"], c["vc"], c["mask"], c["scale"], n_kv=c["n_kv"])
+    truth = oracle.flash_attn_ext(c["q"], c["kc"], c["vc"], c["mask"], c["scale"], n_kv=c["n_kv"], acc_mode=1)
     got = run_case(c2)
-    assert np.isfinite(got).all() and rel_max_err(got, ref) < TOL
+    assert np.isfinite(got).all() and rel_max_err(got, truth) < 1e-5
 
 
 def test_config2_shape_sampled(oracle):
@@ -88,9 +97,11 @@ def test_config2_shape_sampled(oracle):
     pick = np.sort(rng.choice(len(c["tok_pos"]), 24, replace=False))
     maskp = np.full((64, c["n_kv"]), 0xFC00, np.uint16)
     maskp[:24] = c["mask"][pick]
-    ref = oracle.flash_attn_ext(c["q"][pick], c["kc"], c["vc"], maskp, c["scale"], n_kv=c["n_kv"])
+    ref = oracle.flash_attn_ext(c["q"][pick], c["kc"], c["vc"], maskp, c["scale"], n_kv=c["n_kv"])[:24]
+    truth = oracle.flash_attn_ext(c["q"][pick], c["kc"], c["vc"], maskp, c["scale"], n_kv=c["n_kv"], acc_mode=1)[:24]
     assert np.isfinite(got).all()
-    assert rel_max_err(got[pick], ref) < TOL
+    assert rel_max_err(got[pick], truth) < 1e-5
+    assert rel_max_err(got[pick], ref) < TOL + rel_max_err(ref, truth)
 
 
 def test_permutation_property_full_size():

@@ -90,6 +90,6 @@ def test_get_rows_on_tiled_table(oracle):
     for wtype in (Q4_0, Q8_0):
         w = (rng.standard_normal((70, 128)) * 0.02).astype(np.float32)
         wq = oracle.quantize_weights(wtype, w)
-        ids = np.array([0, 69, 3, 3, 17], np.int32)
+        ids = np.array([0, 69, 3, 3, 17, 9, 15, 30, 60, 8], np.int32)   # rows in both halves of a 16-row tile
         got = host(ops.get_rows(ops.QWeight.from_blocks(wtype, 128, 70, wq), dev(ids)))
         assert np.array_equal(got.view(np.uint32), oracle.get_rows(wtype, wq, ids, 128).view(np.uint32))
