@@ -1,0 +1,328 @@
+"""Benchmark: Q4_0 decode tok/s, Llama-3-8B architecture, 64 ragged sequences in a unified f16 KV cache of
+65536 cells (BASELINE.json configs[3]); mul_mat HBM GB/s against the measured peak.
+
+    python bench.py --gpus 1 --steps K --warmup W            # this repository's CUDA path
+    python bench.py --impl reference --steps K --warmup W    # the reference's ggml-cpu on the host cores
+
+One "step" is one decode ubatch: every one of the 64 sequences advances by one token (32 layers of
+quantised mul_mat + ragged flash attention + the small row ops, then the output head), i.e. 64 tokens.
+With N > 1 (torchrun) every rank runs its own replica with its own 64 sequences (the 8B model fits one
+GPU; there is no data-path collective), so the job is weak-scaled and `value` sums the ranks.
+
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from cactus_b200.workloads import N_CELLS, N_DECODE, N_SEQ, decode_attention_case, decode_step_inputs, prefilled_cells, prompt_lengths  # noqa: E402
+
+METRIC = "Q4_0 decode tok/s (8B arch, 64 seqs)"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a timed region runs."""
+
+    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+                for n, v in zip(names, r[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except (ValueError, IndexError):
+                pass
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# -------------------------------------------------------------------------------------------------
+# CPU arm: the reference's own ggml-cpu (oracle/_ref) or, where that is absent, the plain-C port.
+# -------------------------------------------------------------------------------------------------
+def cpu_layer_sample(reps: int, warmup: int):
+    """Times, on the host cores, the hot path of ONE layer of the 8B decode step at 64 columns (7 mul_mats
+    + flash attention over the ragged cache) plus a 1/8 slice of the output head, and scales to the 32-layer step."""
+    from cactus_b200.engine import LLAMA_3_8B as cfg
+    from oracle.binding import Oracle, Q4_0, Reference
+    ref = Reference.load(build=False)
+    orc = Oracle()
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    rng = np.random.default_rng(0)
+    lens, _ = prompt_lengths()
+    t_layer = 0.0
+    if ref is not None:
+        kind, threads = "reference", cores
+        for _, K, M in cfg.mul_mat_shapes():
+            wq = rng.integers(0, 256, (M, K // 32 * 18), dtype=np.uint8)
+            wq.reshape(M, K // 32, 18)[:, :, 1] = 0x1C   # fp16 scales ~ 2^-8
+            x = rng.standard_normal((N_SEQ, K)).astype(np.float32)
+            _, t = ref.mul_mat(Q4_0, wq, x, n_threads=threads, warmup=warmup, reps=reps)
+            t_layer += t
+        # attention: 64 decode tokens over a cache holding the 64 prompts
+        c = decode_attention_case(lens, cfg)
+        _, t = ref.flash_attn_ext(c["q"], c["kc"], c["vc"], c["mask"], c["scale"], n_kv=c["n_kv"], n_threads=threads, warmup=warmup, reps=reps)
+        t_layer += t
+        Mh = cfg.vocab // 8
+        wq = rng.integers(0, 256, (Mh, cfg.d_model // 32 * 18), dtype=np.uint8)
+        wq.reshape(Mh, cfg.d_model // 32, 18)[:, :, 1] = 0x1C
+        _, t_head = ref.mul_mat(Q4_0, wq, rng.standard_normal((N_SEQ, cfg.d_model)).astype(np.float32), n_threads=threads, warmup=warmup, reps=reps)
+        t_head *= 8
+        sample = "1 of 32 layers (7 mul_mat at 64 columns + flash_attn over the 64-sequence cache) + 1/8 of the output head, scaled to the full step"
+    else:
+        kind, threads = "port", 1
+        K, M = 4096, 4096
+        wq = rng.integers(0, 256, (M // 8, K // 32 * 18), dtype=np.uint8)
+        wq.reshape(M // 8, K // 32, 18)[:, :, 1] = 0x1C
+        x = rng.standard_normal((N_SEQ, K)).astype(np.float32)
+        t0 = time.perf_counter()
+        orc.mul_mat(Q4_0, wq, x)
+        t = (time.perf_counter() - t0) * 8
+        macs_layer = sum(K * M for _, K, M in cfg.mul_mat_shapes())
+        t_layer = t * macs_layer / (4096 * 4096)
+        t_head = t * cfg.vocab * cfg.d_model / (4096 * 4096)
+        sample = "1/8 of one 4096x4096 Q4_0 mul_mat at 64 columns with the scalar C port, scaled by MACs to the full step (attention not included)"
+    step = cfg.n_layer * t_layer + t_head
+    return {"value": N_SEQ / step, "unit": "tok/s", "cores": threads, "kind": kind, "sample": sample, "step_seconds": step}
+
+
+# -------------------------------------------------------------------------------------------------
+# GPU arm
+# -------------------------------------------------------------------------------------------------
+def mul_mat_roofline(eng, cfg, reps: int = 3):
+    """Times the dominant kernel -- the Q4_0 mul_mat at 64 columns -- over all of the step's weights, launch
+    by launch on the launching stream with CUDA events (weights of 32 distinct layers, 4.2 GB, so nothing is
+    L2-resident), and relates the algorithmic bytes to the duration."""
+    import torch
+    from cactus_b200._lib import check, lib
+    L = lib()
+    st = torch.cuda.current_stream().cuda_stream
+    names = {"wq": "attn_q", "wk": "attn_k", "wv": "attn_v", "wo": "attn_output", "gate": "ffn_gate", "up": "ffn_up", "down": "ffn_down"}
+    T = N_SEQ
+    per_shape, total_bytes, total_ms, launches = {}, 0.0, 0.0, 0
+    shapes = [(s, K, M, [f"blk.{il}.{names[s]}.weight" for il in range(cfg.n_layer)], cfg.layer_type) for s, K, M in cfg.mul_mat_shapes()]
+    shapes.append(("output", cfg.d_model, cfg.vocab, ["output.weight"], cfg.head_type))
+    for short, K, M, tensors, wtype in shapes:
+        act = eng.act_ff if K == cfg.d_ff else eng.act_d
+        out = {cfg.d_model: eng.tmp, cfg.d_ff: eng.gate, cfg.vocab: eng.logits}.get(M, eng.k)
+        bb = 18 if wtype == 2 else 34
+        alg = M * (K // 32) * bb + T * K * 4 + T * M * 4      # weights + f32 activations in + f32 out
+        best = None
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for name in tensors:
+                w = eng.w.tensors[name]
+                check(L.b200_mul_mat_q_prequant(w.wtype, w.data.data_ptr(), w.K, w.M, act.data_ptr(), T, out.data_ptr(), out.stride(0) * 4,
+                                                eng.ws.data_ptr(), eng.ws.numel(), st))
+            e1.record()
+            e1.synchronize()
+            ms = e0.elapsed_time(e1) / len(tensors)
+            best = ms if best is None else min(best, ms)
+        per_shape[short] = {"K": K, "M": M, "ms": round(best, 5), "GBps": round(alg / best / 1e6, 1)}
+        total_bytes += alg * len(tensors)
+        total_ms += best * len(tensors)
+        launches += len(tensors)
+    peak, which = peaks()
+    achieved = total_bytes / total_ms / 1e6
+    return {"bound": "hbm", "kernel": "mmq_kernel<Q4_0,64> (all mul_mat launches of one decode step)", "achieved": round(achieved, 1),
+            "peak": peak, "peak_source": which, "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": None,
+            "algorithmic_bytes_per_step": int(total_bytes), "ms_per_step_in_mul_mat": round(total_ms, 4), "per_shape": per_shape}
+
+
+def gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    from cactus_b200 import lib
+    from cactus_b200.engine import LLAMA_3_8B, LlamaConfig, LlamaEngine, LlamaWeights
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    L = lib()
+
+    cfg = LLAMA_3_8B if not args.small else LlamaConfig(4, 1024, 8, 2, 4096, 32000)
+    lens, scale = prompt_lengths()
+    cell_pos, cell_seq, head = prefilled_cells(lens)
+    weights = LlamaWeights.random(cfg, seed=rank)
+    eng = LlamaEngine(weights, N_CELLS, max_tokens=N_SEQ)
+    gen = torch.Generator(device="cuda").manual_seed(100 + rank)
+    for il in range(cfg.n_layer):      # the prefilled prompts: synthetic K/V ~ N(0, 1) in the cells the prompts own
+        eng.k_cache[il][:head].copy_(torch.randn((head, eng.k_cache[il].shape[1]), device="cuda", generator=gen).half())
+        eng.v_cache[il][:head].copy_(torch.randn((head, eng.v_cache[il].shape[1]), device="cuda", generator=gen).half())
+    cp0, cs0 = torch.from_numpy(cell_pos).cuda(), torch.from_numpy(cell_seq).cuda()
+
+    def reset_state():
+        eng.cell_pos.copy_(cp0)
+        eng.cell_seq.copy_(cs0)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    K, W = args.steps, max(args.warmup, 3)
+    assert K >= 1
+    total = W + K
+    steps_dev = torch.from_numpy(np.stack([np.stack(decode_step_inputs(lens, head, s % N_DECODE)) for s in range(total)])).cuda()  # [total,4,64]
+
+    # ---- value: inputs resident in HBM, device-timed ---------------------------------------------
+    reset_state()
+    for s in range(W):
+        eng.inp.copy_(steps_dev[s])
+        eng.run_device(N_SEQ)
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = eng.launches_per_step[N_SEQ]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for s in range(W, total):
+        if s % N_DECODE == 0:
+            reset_state()
+        eng.inp.copy_(steps_dev[s])
+        eng.run_device(N_SEQ)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    t = torch.tensor([ms], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    value = world * N_SEQ * K / (ms_max / 1e3)
+
+    # ---- e2e: the public call with host buffers, H2D of the inputs and D2H of the logits inside ---
+    reset_state()
+    tok = None
+    e2e_steps = min(K, N_DECODE - W)
+    for s in range(W):
+        _, tok = eng.decode(*decode_step_inputs(lens, head, s, tokens=tok))
+    barrier()
+    t0 = time.perf_counter()
+    for s in range(W, W + e2e_steps):
+        logits, tok = eng.decode(*decode_step_inputs(lens, head, s, tokens=tok))
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    t = torch.tensor([dt], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e = world * N_SEQ * e2e_steps / float(t.item())
+    h2d = 4 * N_SEQ * 4
+    d2h = N_SEQ * cfg.vocab * 4 + N_SEQ * 4
+
+    roof = mul_mat_roofline(eng, cfg) if rank == 0 else None
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_layer_sample(reps=2, warmup=1)
+
+    if rank == 0:
+        kv_bytes = int(lens.sum() + N_SEQ * (W + K / 2)) * cfg.n_layer * 2 * cfg.n_kv_head * cfg.head_dim * 2
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": round(ms_max / K, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 x int4/int8 block dots, f32 accumulate; f16 KV", "data": "synthetic",
+            "config": {"workload": "BASELINE configs[3]: Llama-3-8B architecture, random N(0,0.02) weights in Q4_0, 64 sequences, "
+                                   "unified f16 KV cache of 65536 cells, one decode ubatch of 64 tokens per step",
+                       "prompt_lengths": f"U[16,2048] seed 0 scaled by {scale:.3f} to leave 128 decode cells per sequence; "
+                                         f"{int(lens.sum())} prompt cells hold synthetic N(0,1) K/V",
+                       "parallelism": "one replica per GPU, no collective" if world > 1 else "single GPU",
+                       "l2": "inputs larger than L2: 4.2 GB of weights and ~7 GB of KV are streamed every step"},
+            "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            "gpu_launches": int(launches0 * K), "launches_per_step": int(launches0),
+            "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
+            "step_bytes": {"weights": cfg.weight_bytes_per_step(), "kv_read_about": kv_bytes},
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    K, W = args.steps, args.warmup
+    reps = max(1, min(K, 5))
+    t0 = time.perf_counter()
+    r = cpu_layer_sample(reps=reps, warmup=min(W, 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(r["value"], 3), "unit": "tok/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")),
+        "steps": K, "warmup": W, "ms_per_step": round(r["step_seconds"] * 1e3, 2), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 x int4 block dots (AVX2), f32 accumulate", "data": "synthetic",
+        "config": {"workload": "BASELINE configs[3] decode ubatch of 64 tokens, reference ggml-cpu on the host cores, timed on a bounded sample",
+                   "sample": r["sample"], "timed_reps_per_op": reps, "wall_seconds": None},
+        "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": round(r["value"], 3), "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    line["config"]["wall_seconds"] = round(time.perf_counter() - t0, 1)
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--small", action="store_true", help="a small model for debugging the harness (not a bench number)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

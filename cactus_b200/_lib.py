@@ -43,6 +43,10 @@ SIGNATURES = {
     "b200_cpy_f32_f32": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "b200_get_rows_f32": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_get_rows_q": (_i32, [_i32, _vp, _i64, _i64, _vp, _vp, _i64, _i64, _vp]),
+    "b200_kq_mask_build": (_i32, [_vp, _vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp]),
+    "b200_scatter_i32": (_i32, [_vp, _vp, _vp, _i64, _vp]),
+    "b200_set_rows_f16": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "b200_argmax_rows": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp]),
 }
 
 _lib = None

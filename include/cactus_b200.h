@@ -180,6 +180,23 @@ B200_API int b200_get_rows_f32(const float *table, int64_t table_nb_row, const i
 B200_API int b200_get_rows_q(int wtype, const void *table_tiled, int64_t d, int64_t n_table_rows, const int32_t *ids,
                              float *dst, int64_t dst_nb_row, int64_t n_ids, b200_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * KV-cache bookkeeping on the device (what the reference does on the host around the graph).
+ * ---------------------------------------------------------------------------------------------- */
+/* llama_kv_cache_unified::set_input_kq_mask (cactus/llama-kv-cache.cpp:696-761), one sequence id per cell,
+ * no sliding window: mask f16 [pad64(n_tokens)][n_kv], 0 where cell_seq == tok_seq and cell_pos <= tok_pos,
+ * -inf elsewhere and in the padding rows. */
+B200_API int b200_kq_mask_build(const int32_t *cell_pos, const int32_t *cell_seq, int64_t n_kv, const int32_t *tok_pos,
+                                const int32_t *tok_seq, int64_t n_tokens, void *mask, int64_t mask_nb_row, b200_stream_t stream);
+/* dst[idx[i]] = src[i]: records the (pos, seq) of the cells find_slot (llama-kv-cache.cpp:476-569) hands to a ubatch */
+B200_API int b200_scatter_i32(int32_t *dst, const int32_t *idx, const int32_t *src, int64_t n, b200_stream_t stream);
+/* cpy_k / cpy_v (llama-kv-cache.cpp:617-656): f32 rows -> f16 cache rows slots[r] */
+B200_API int b200_set_rows_f16(const float *x, int64_t x_nb_row, const int32_t *slots, void *dst, int64_t dst_nb_row,
+                               int64_t d, int64_t rows, b200_stream_t stream);
+/* greedy sampling of each logits row (the argmax a caller runs after llama_get_logits,
+ * cactus/cactus_completion.cpp:210); ties go to the lowest index */
+B200_API int b200_argmax_rows(const float *x, int64_t x_nb_row, int64_t d, int64_t rows, int32_t *out, b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
