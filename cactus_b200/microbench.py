@@ -1,0 +1,139 @@
+"""Small single-kernel workloads for timing and profiling (run under ncu on a GPU box):
+
+    python -m cactus_b200.microbench mul_mat --K 4096 --M 14336 --N 64 --copies 8 --reps 3
+    python -m cactus_b200.microbench fattn --seqs 64 --ctx 900 --reps 3
+    python -m cactus_b200.microbench quantize --K 4096 --N 64
+
+`--copies` distinct weight tensors are cycled so the weights streamed per pass exceed the 126 MB L2.
+Prints one JSON line with the CUDA-event time per launch and the algorithmic GB/s.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import numpy as np
+import torch
+
+from . import ops
+from ._lib import check, lib
+from .engine import random_blocks
+
+
+def time_launches(fn, reps):
+    best = None
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        n = fn()
+        e1.record()
+        e1.synchronize()
+        ms = e0.elapsed_time(e1) / n
+        best = ms if best is None else min(best, ms)
+    return best
+
+
+def bench_mul_mat(a):
+    L = lib()
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    ws = [ops.QWeight.from_blocks(a.wtype, a.K, a.M, random_blocks(a.wtype, a.M, a.K, gen)) for _ in range(a.copies)]
+    x = torch.randn((a.N, a.K), device="cuda", generator=gen)
+    out = torch.empty((a.N, a.M), device="cuda")
+    act = torch.empty(L.b200_act_bytes(a.K, a.N), dtype=torch.uint8, device="cuda")
+    wsp = torch.empty(max(256, L.b200_mul_mat_workspace_bytes(a.wtype, a.K, a.M, a.N)), dtype=torch.uint8, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    check(L.b200_quantize_activations(x.data_ptr(), a.K * 4, a.K, a.N, act.data_ptr(), act.numel(), 0, st))
+
+    def run():
+        for w in ws:
+            check(L.b200_mul_mat_q_prequant(w.wtype, w.data.data_ptr(), w.K, w.M, act.data_ptr(), a.N, out.data_ptr(), a.M * 4,
+                                            wsp.data_ptr(), wsp.numel(), st))
+        return len(ws)
+
+    run()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        run()
+    ms = time_launches(lambda: (g.replay(), len(ws))[1], a.reps)
+    bb = 18 if a.wtype == 2 else 34
+    alg = a.M * (a.K // 32) * bb + a.N * a.K * 4 + a.N * a.M * 4
+    return {"kernel": "mul_mat", "K": a.K, "M": a.M, "N": a.N, "wtype": a.wtype, "ms_per_launch": ms, "GBps": alg / ms / 1e6,
+            "TOPS": 2 * a.M * a.N * a.K / ms / 1e9}
+
+
+def bench_fattn(a):
+    L = lib()
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    D, H, Hkv = a.D, a.H, a.Hkv
+    n_cells = (a.seqs * a.ctx + 255) // 256 * 256
+    layers = a.copies
+    ks = [torch.randn((n_cells, Hkv * D), device="cuda", generator=gen).half() for _ in range(layers)]
+    vs = [torch.randn((n_cells, Hkv * D), device="cuda", generator=gen).half() for _ in range(layers)]
+    q = torch.randn((a.seqs, H * D), device="cuda", generator=gen)
+    cell_seq = (torch.arange(n_cells, device="cuda") // a.ctx).to(torch.int32)
+    cell_seq[cell_seq >= a.seqs] = -1
+    cell_pos = (torch.arange(n_cells, device="cuda") % a.ctx).to(torch.int32)
+    tok_pos = torch.full((a.seqs,), a.ctx - 1, dtype=torch.int32, device="cuda")
+    tok_seq = torch.arange(a.seqs, dtype=torch.int32, device="cuda")
+    mask = torch.empty(((a.seqs + 63) // 64 * 64, n_cells), dtype=torch.float16, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    check(L.b200_kq_mask_build(cell_pos.data_ptr(), cell_seq.data_ptr(), n_cells, tok_pos.data_ptr(), tok_seq.data_ptr(), a.seqs,
+                               mask.data_ptr(), n_cells * 2, st))
+    index = torch.empty(L.b200_mask_index_bytes(a.seqs, n_cells), dtype=torch.uint8, device="cuda")
+    check(L.b200_mask_index_build(mask.data_ptr(), n_cells * 2, a.seqs, n_cells, index.data_ptr(), index.numel(), st))
+    scratch = torch.empty(max(256, L.b200_flash_attn_scratch_bytes(D, H, Hkv, a.seqs, n_cells)), dtype=torch.uint8, device="cuda")
+    out = torch.empty((a.seqs, H * D), device="cuda")
+
+    def run():
+        for k, v in zip(ks, vs):
+            check(L.b200_flash_attn_ext_indexed(D, H, Hkv, a.seqs, n_cells, q.data_ptr(), H * D * 4, D * 4, k.data_ptr(), Hkv * D * 2, D * 2,
+                                                v.data_ptr(), Hkv * D * 2, D * 2, mask.data_ptr(), n_cells * 2, index.data_ptr(),
+                                                D ** -0.5, 0.0, 0.0, out.data_ptr(), scratch.data_ptr(), scratch.numel(), st))
+        return layers
+
+    run()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        run()
+    ms = time_launches(lambda: (g.replay(), layers)[1], a.reps)
+    alg = a.seqs * a.ctx * Hkv * D * 2 * 2 + 2 * a.seqs * H * D * 4
+    return {"kernel": "flash_attn_ext", "seqs": a.seqs, "ctx": a.ctx, "D": D, "H": H, "Hkv": Hkv, "ms_per_launch": ms, "GBps": alg / ms / 1e6}
+
+
+def bench_quantize(a):
+    L = lib()
+    x = torch.randn((a.N, a.K), device="cuda")
+    act = torch.empty(L.b200_act_bytes(a.K, a.N), dtype=torch.uint8, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+
+    def run():
+        for _ in range(20):
+            check(L.b200_quantize_activations(x.data_ptr(), a.K * 4, a.K, a.N, act.data_ptr(), act.numel(), 0, st))
+        return 20
+
+    run()
+    ms = time_launches(run, a.reps)
+    return {"kernel": "quantize_q8_0", "K": a.K, "N": a.N, "ms_per_launch": ms, "GBps": (a.N * a.K * 4 + a.N * a.K * 34 / 32) / ms / 1e6}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["mul_mat", "fattn", "quantize"])
+    ap.add_argument("--K", type=int, default=4096)
+    ap.add_argument("--M", type=int, default=14336)
+    ap.add_argument("--N", type=int, default=64)
+    ap.add_argument("--wtype", type=int, default=2)
+    ap.add_argument("--copies", type=int, default=8)
+    ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--seqs", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=900)
+    ap.add_argument("--D", type=int, default=128)
+    ap.add_argument("--H", type=int, default=32)
+    ap.add_argument("--Hkv", type=int, default=8)
+    a = ap.parse_args()
+    r = {"mul_mat": bench_mul_mat, "fattn": bench_fattn, "quantize": bench_quantize}[a.kernel](a)
+    print(json.dumps(r))
+
+
+if __name__ == "__main__":
+    main()

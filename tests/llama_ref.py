@@ -6,8 +6,8 @@ from oracle.binding import Q4_0, Q8_0  # noqa: F401
 
 
 class OracleLlama:
-    def __init__(self, oracle, cfg, arrays, n_cells):
-        self.o, self.cfg, self.a, self.n_cells = oracle, cfg, arrays, n_cells
+    def __init__(self, oracle, cfg, arrays, n_cells, acc_mode=0):
+        self.o, self.cfg, self.a, self.n_cells, self.acc_mode = oracle, cfg, arrays, n_cells, acc_mode
         kvd = cfg.n_kv_head * cfg.head_dim
         self.kc = [np.zeros((n_cells, cfg.n_kv_head, cfg.head_dim), np.uint16) for _ in range(cfg.n_layer)]
         self.vc = [np.zeros((n_cells, cfg.n_kv_head, cfg.head_dim), np.uint16) for _ in range(cfg.n_layer)]
@@ -33,7 +33,7 @@ class OracleLlama:
             k = o.rope_norm(k.reshape(T, Hkv, D), pos, cfg.rope_theta)
             self.kc[il][slots] = o.cpy_f32_f16(k)
             self.vc[il][slots] = o.cpy_f32_f16(v.reshape(T, Hkv, D))
-            att = o.flash_attn_ext(q, self.kc[il], self.vc[il], mask, float(D) ** -0.5, n_kv=self.n_cells)
+            att = o.flash_attn_ext(q, self.kc[il], self.vc[il], mask, float(D) ** -0.5, n_kv=self.n_cells, acc_mode=self.acc_mode)
             ao, _ = o.mul_mat(cfg.layer_type, a[p + "attn_output.weight"], att.reshape(T, H * D))
             x = o.add(x, ao)
             h = o.rms_norm_mul(x, a[p + "ffn_norm.weight"], cfg.eps)
