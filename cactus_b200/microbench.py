@@ -45,6 +45,7 @@ def bench_mul_mat(a):
     check(L.b200_quantize_activations(x.data_ptr(), a.K * 4, a.K, a.N, act.data_ptr(), act.numel(), 0, st))
 
     def run():
+        st = torch.cuda.current_stream().cuda_stream   # the capture stream while a graph is being recorded
         for w in ws:
             check(L.b200_mul_mat_q_prequant(w.wtype, w.data.data_ptr(), w.K, w.M, act.data_ptr(), a.N, out.data_ptr(), a.M * 4,
                                             wsp.data_ptr(), wsp.numel(), st))
@@ -85,6 +86,7 @@ def bench_fattn(a):
     out = torch.empty((a.seqs, H * D), device="cuda")
 
     def run():
+        st = torch.cuda.current_stream().cuda_stream
         for k, v in zip(ks, vs):
             check(L.b200_flash_attn_ext_indexed(D, H, Hkv, a.seqs, n_cells, q.data_ptr(), H * D * 4, D * 4, k.data_ptr(), Hkv * D * 2, D * 2,
                                                 v.data_ptr(), Hkv * D * 2, D * 2, mask.data_ptr(), n_cells * 2, index.data_ptr(),
