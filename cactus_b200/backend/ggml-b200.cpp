@@ -1,0 +1,949 @@
+// ggml backend for NVIDIA B200: the host side of the plug-in (see ggml-b200.h).
+//
+// Everything that computes is a call into the C ABI of libcactus_b200.so (include/cactus_b200.h); this file
+// holds the vtables of cactus/ggml-backend-impl.h, the device buffers, and graph_compute's node dispatch.
+#include "ggml-b200.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/cactus_b200.h"
+#include "ggml-backend-impl.h"
+#include "ggml-impl.h"
+
+#define B200_LOG_ERROR(...) LM_GGML_LOG_ERROR(__VA_ARGS__)
+
+namespace {
+
+constexpr size_t B200_ALIGNMENT = 256;
+constexpr size_t B200_STAGE_BYTES = 64u << 20;  // bounce buffer for weight layout conversion
+
+bool cuda_ok(cudaError_t e, const char * what) {
+    if (e == cudaSuccess) return true;
+    B200_LOG_ERROR("ggml-b200: %s failed: %s\n", what, cudaGetErrorString(e));
+    return false;
+}
+
+struct device_guard {
+    int prev = 0;
+    explicit device_guard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) cudaSetDevice(dev);
+    }
+    ~device_guard() {
+        int cur = 0;
+        cudaGetDevice(&cur);
+        if (cur != prev) cudaSetDevice(prev);
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+// devices
+// ---------------------------------------------------------------------------------------------
+struct b200_device_ctx {
+    int device;
+    std::string name, description;
+};
+
+lm_ggml_backend_buffer_type_t device_buffer_type(int device);
+bool buft_is_b200(lm_ggml_backend_buffer_type_t buft);
+bool buft_is_b200_host(lm_ggml_backend_buffer_type_t buft);
+
+// A quantised tensor that owns its storage in a B200 device buffer is kept in the tiled layout.
+bool is_tiled_type(lm_ggml_type t) { return t == LM_GGML_TYPE_Q4_0 || t == LM_GGML_TYPE_Q8_0; }
+bool tensor_is_tiled(const lm_ggml_tensor * t) {
+    return is_tiled_type(t->type) && t->view_src == nullptr && t->ne[0] % 32 == 0;
+}
+int64_t tensor_rows(const lm_ggml_tensor * t) { return t->ne[1] * t->ne[2] * t->ne[3]; }
+size_t block_bytes(lm_ggml_type t) { return t == LM_GGML_TYPE_Q4_0 ? 18 : 34; }
+
+// ---------------------------------------------------------------------------------------------
+// device buffer
+// ---------------------------------------------------------------------------------------------
+struct b200_buffer_ctx {
+    int device;
+    void * base = nullptr;
+    void * stage = nullptr;  // lazily allocated bounce buffer (row-major block stream on the device)
+    size_t stage_bytes = 0;
+    ~b200_buffer_ctx() {
+        device_guard g(device);
+        if (stage) cudaFree(stage);
+        if (base) cudaFree(base);
+    }
+    void * get_stage(size_t bytes) {
+        if (stage_bytes < bytes) {
+            if (stage) cudaFree(stage);
+            stage = nullptr;
+            stage_bytes = 0;
+            if (!cuda_ok(cudaMalloc(&stage, bytes), "cudaMalloc(stage)")) return nullptr;
+            stage_bytes = bytes;
+        }
+        return stage;
+    }
+};
+
+void buffer_free(lm_ggml_backend_buffer_t buffer) { delete (b200_buffer_ctx *) buffer->context; }
+void * buffer_get_base(lm_ggml_backend_buffer_t buffer) { return ((b200_buffer_ctx *) buffer->context)->base; }
+
+// Moves bytes [offset, offset+size) of a tiled tensor between its row-major block stream and the device.
+// Works on whole 16-row groups: rows that are only partly covered are first brought back to the stream.
+bool tiled_transfer(b200_buffer_ctx * ctx, const lm_ggml_tensor * t, void * host, size_t offset, size_t size, bool to_device, int fill = -1) {
+    const int64_t K = t->ne[0], M = tensor_rows(t);
+    const size_t rb = (size_t) (K / 32) * block_bytes(t->type);
+    const int64_t max_rows = std::max<int64_t>(16, (int64_t) (B200_STAGE_BYTES / rb) / 16 * 16);
+    size_t done = 0;
+    while (done < size) {
+        const size_t off = offset + done;
+        const int64_t r0 = (int64_t) (off / rb) / 16 * 16;
+        const int64_t r1 = std::min<int64_t>(M, r0 + max_rows);
+        const size_t chunk_begin = (size_t) r0 * rb, chunk_end = (size_t) r1 * rb;
+        const size_t n = std::min(size - done, chunk_end - off);
+        // rows actually touched, extended to the 16-row group
+        const int64_t t1 = std::min<int64_t>(M, ((int64_t) ((off + n + rb - 1) / rb) + 15) / 16 * 16);
+        const int64_t rows = t1 - r0;
+        uint8_t * stage = (uint8_t *) ctx->get_stage((size_t) rows * rb);
+        if (!stage) return false;
+        const bool whole = (off == chunk_begin) && (off + n == (size_t) t1 * rb);
+        if (!to_device || !whole) {
+            if (b200_weight_download(t->type, K, M, t->data, stage, r0, rows, nullptr) != B200_OK) {
+                B200_LOG_ERROR("ggml-b200: weight_download: %s\n", b200_last_error());
+                return false;
+            }
+        }
+        if (to_device) {
+            if (fill >= 0) {
+                if (!cuda_ok(cudaMemset(stage + (off - chunk_begin), fill, n), "cudaMemset")) return false;
+            } else if (!cuda_ok(cudaMemcpy(stage + (off - chunk_begin), (const uint8_t *) host + done, n, cudaMemcpyHostToDevice), "cudaMemcpy H2D")) {
+                return false;
+            }
+            if (b200_weight_upload(t->type, K, M, stage, t->data, r0, rows, nullptr) != B200_OK) {
+                B200_LOG_ERROR("ggml-b200: weight_upload: %s\n", b200_last_error());
+                return false;
+            }
+            if (!cuda_ok(cudaStreamSynchronize(nullptr), "sync after upload")) return false;
+        } else {
+            if (!cuda_ok(cudaMemcpy((uint8_t *) host + done, stage + (off - chunk_begin), n, cudaMemcpyDeviceToHost), "cudaMemcpy D2H")) return false;
+        }
+        done += n;
+        (void) chunk_end;
+    }
+    return true;
+}
+
+void buffer_memset_tensor(lm_ggml_backend_buffer_t buffer, lm_ggml_tensor * tensor, uint8_t value, size_t offset, size_t size) {
+    b200_buffer_ctx * ctx = (b200_buffer_ctx *) buffer->context;
+    device_guard g(ctx->device);
+    if (tensor_is_tiled(tensor)) {
+        LM_GGML_ASSERT(tiled_transfer(ctx, tensor, nullptr, offset, size, true, value));
+        return;
+    }
+    LM_GGML_ASSERT(cuda_ok(cudaMemset((char *) tensor->data + offset, value, size), "cudaMemset"));
+    cudaStreamSynchronize(nullptr);
+}
+
+void buffer_set_tensor(lm_ggml_backend_buffer_t buffer, lm_ggml_tensor * tensor, const void * data, size_t offset, size_t size) {
+    b200_buffer_ctx * ctx = (b200_buffer_ctx *) buffer->context;
+    device_guard g(ctx->device);
+    if (tensor_is_tiled(tensor)) {
+        LM_GGML_ASSERT(tiled_transfer(ctx, tensor, const_cast<void *>(data), offset, size, true));
+        return;
+    }
+    LM_GGML_ASSERT(cuda_ok(cudaMemcpy((char *) tensor->data + offset, data, size, cudaMemcpyHostToDevice), "cudaMemcpy H2D"));
+}
+
+void buffer_get_tensor(lm_ggml_backend_buffer_t buffer, const lm_ggml_tensor * tensor, void * data, size_t offset, size_t size) {
+    b200_buffer_ctx * ctx = (b200_buffer_ctx *) buffer->context;
+    device_guard g(ctx->device);
+    if (tensor_is_tiled(tensor)) {
+        LM_GGML_ASSERT(tiled_transfer(ctx, tensor, data, offset, size, false));
+        return;
+    }
+    LM_GGML_ASSERT(cuda_ok(cudaMemcpy(data, (const char *) tensor->data + offset, size, cudaMemcpyDeviceToHost), "cudaMemcpy D2H"));
+}
+
+bool buffer_cpy_tensor(lm_ggml_backend_buffer_t buffer, const lm_ggml_tensor * src, lm_ggml_tensor * dst) {
+    // device-to-device copies between plain (not tiled) contiguous tensors of B200 buffers; everything else
+    // goes through the generic host path of the caller (cactus/ggml-backend.cpp:370-391)
+    if (!src->buffer || !buft_is_b200(src->buffer->buft)) return false;
+    if (tensor_is_tiled(src) || tensor_is_tiled(dst) || is_tiled_type(src->type)) return false;
+    if (!lm_ggml_is_contiguous(src) || !lm_ggml_is_contiguous(dst) || lm_ggml_nbytes(src) != lm_ggml_nbytes(dst)) return false;
+    b200_buffer_ctx * dctx = (b200_buffer_ctx *) buffer->context;
+    b200_buffer_ctx * sctx = (b200_buffer_ctx *) src->buffer->context;
+    device_guard g(dctx->device);
+    cudaError_t e = (dctx->device == sctx->device) ? cudaMemcpy(dst->data, src->data, lm_ggml_nbytes(src), cudaMemcpyDeviceToDevice)
+                                                   : cudaMemcpyPeer(dst->data, dctx->device, src->data, sctx->device, lm_ggml_nbytes(src));
+    return cuda_ok(e, "cudaMemcpy D2D");
+}
+
+void buffer_clear(lm_ggml_backend_buffer_t buffer, uint8_t value) {
+    b200_buffer_ctx * ctx = (b200_buffer_ctx *) buffer->context;
+    device_guard g(ctx->device);
+    cuda_ok(cudaMemset(ctx->base, value, buffer->size), "cudaMemset");
+    cudaStreamSynchronize(nullptr);
+}
+
+const lm_ggml_backend_buffer_i b200_buffer_iface = {
+    /* .free_buffer   = */ buffer_free,
+    /* .get_base      = */ buffer_get_base,
+    /* .init_tensor   = */ nullptr,
+    /* .memset_tensor = */ buffer_memset_tensor,
+    /* .set_tensor    = */ buffer_set_tensor,
+    /* .get_tensor    = */ buffer_get_tensor,
+    /* .cpy_tensor    = */ buffer_cpy_tensor,
+    /* .clear         = */ buffer_clear,
+    /* .reset         = */ nullptr,
+};
+
+// ---------------------------------------------------------------------------------------------
+// device buffer type
+// ---------------------------------------------------------------------------------------------
+struct b200_buft_ctx {
+    int device;
+    std::string name;
+};
+
+const char * buft_get_name(lm_ggml_backend_buffer_type_t buft) { return ((b200_buft_ctx *) buft->context)->name.c_str(); }
+
+lm_ggml_backend_buffer_t buft_alloc_buffer(lm_ggml_backend_buffer_type_t buft, size_t size) {
+    b200_buft_ctx * bc = (b200_buft_ctx *) buft->context;
+    device_guard g(bc->device);
+    b200_buffer_ctx * ctx = new b200_buffer_ctx;
+    ctx->device = bc->device;
+    const size_t bytes = std::max<size_t>(size, 1);
+    cudaError_t e = cudaMalloc(&ctx->base, bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        B200_LOG_ERROR("ggml-b200: allocating %.2f MiB on device %d failed: %s\n", bytes / 1048576.0, bc->device, cudaGetErrorString(e));
+        ctx->base = nullptr;
+        delete ctx;
+        return nullptr;  // the caller reports LM_GGML_STATUS_ALLOC_FAILED / fails the model load
+    }
+    return lm_ggml_backend_buffer_init(buft, b200_buffer_iface, ctx, size);
+}
+
+size_t buft_get_alignment(lm_ggml_backend_buffer_type_t) { return B200_ALIGNMENT; }
+
+size_t buft_get_alloc_size(lm_ggml_backend_buffer_type_t, const lm_ggml_tensor * tensor) {
+    size_t size = lm_ggml_nbytes(tensor);
+    if (tensor_is_tiled(tensor)) {
+        // rows padded to 16 and blocks to 4 in the tiled layout
+        const size_t tiled = b200_weight_bytes(tensor->type, tensor->ne[0], tensor_rows(tensor));
+        size = std::max(size, tiled);
+    }
+    return size;
+}
+
+bool buft_is_host(lm_ggml_backend_buffer_type_t) { return false; }
+
+const lm_ggml_backend_buffer_type_i b200_buft_iface = {
+    /* .get_name       = */ buft_get_name,
+    /* .alloc_buffer   = */ buft_alloc_buffer,
+    /* .get_alignment  = */ buft_get_alignment,
+    /* .get_max_size   = */ nullptr,
+    /* .get_alloc_size = */ buft_get_alloc_size,
+    /* .is_host        = */ buft_is_host,
+};
+
+// ---------------------------------------------------------------------------------------------
+// pinned host buffer type: what the context uses for graph inputs and the logits it reads back
+// (cactus/llama-context.cpp:199-206, 1193-1199)
+// ---------------------------------------------------------------------------------------------
+const char * host_buft_get_name(lm_ggml_backend_buffer_type_t) { return LM_GGML_B200_NAME "_Host"; }
+
+void host_buffer_free(lm_ggml_backend_buffer_t buffer) { cudaFreeHost(buffer->context); }
+
+lm_ggml_backend_buffer_t host_buft_alloc_buffer(lm_ggml_backend_buffer_type_t buft, size_t size) {
+    void * ptr = nullptr;
+    cudaError_t e = cudaMallocHost(&ptr, std::max<size_t>(size, 1));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        // fall back to pageable memory of the CPU buffer type, as the caller would do without a host type
+        return lm_ggml_backend_buft_alloc_buffer(lm_ggml_backend_cpu_buffer_type(), size);
+    }
+    lm_ggml_backend_buffer_t buffer = lm_ggml_backend_cpu_buffer_from_ptr(ptr, size);
+    buffer->buft = buft;
+    buffer->iface.free_buffer = host_buffer_free;
+    return buffer;
+}
+
+size_t host_buft_get_alignment(lm_ggml_backend_buffer_type_t) { return 64; }
+bool host_buft_is_host(lm_ggml_backend_buffer_type_t) { return true; }
+
+const lm_ggml_backend_buffer_type_i b200_host_buft_iface = {
+    /* .get_name       = */ host_buft_get_name,
+    /* .alloc_buffer   = */ host_buft_alloc_buffer,
+    /* .get_alignment  = */ host_buft_get_alignment,
+    /* .get_max_size   = */ nullptr,
+    /* .get_alloc_size = */ nullptr,
+    /* .is_host        = */ host_buft_is_host,
+};
+
+bool buft_is_b200(lm_ggml_backend_buffer_type_t buft) { return buft && buft->iface.get_name == buft_get_name; }
+bool buft_is_b200_host(lm_ggml_backend_buffer_type_t buft) { return buft && buft->iface.get_name == host_buft_get_name; }
+
+// ---------------------------------------------------------------------------------------------
+// backend (one CUDA stream) and its scratch memory
+// ---------------------------------------------------------------------------------------------
+struct scratch_buf {
+    void * ptr = nullptr;
+    size_t bytes = 0;
+    // grows when needed; growing synchronises the stream first because earlier kernels may still use the old block
+    void * get(size_t need, cudaStream_t st) {
+        if (need <= bytes) return ptr;
+        if (ptr) {
+            cudaStreamSynchronize(st);
+            cudaFree(ptr);
+            ptr = nullptr;
+            bytes = 0;
+        }
+        const size_t want = (need + (1u << 20)) / (1u << 20) * (1u << 20);
+        if (!cuda_ok(cudaMalloc(&ptr, want), "cudaMalloc(scratch)")) {
+            ptr = nullptr;
+            return nullptr;
+        }
+        bytes = want;
+        return ptr;
+    }
+    void release() {
+        if (ptr) cudaFree(ptr);
+        ptr = nullptr;
+        bytes = 0;
+    }
+};
+
+struct b200_backend_ctx {
+    int device;
+    std::string name;
+    cudaStream_t stream = nullptr;
+    scratch_buf act, workspace, fa_scratch, mask_index;
+    // what the scratch currently holds, valid inside one graph_compute
+    const lm_ggml_tensor * act_src = nullptr;
+    const lm_ggml_tensor * index_mask = nullptr;
+    lm_ggml_abort_callback abort_cb = nullptr;
+    void * abort_cb_data = nullptr;
+    int q8_variant = B200_Q8_AVX2;
+    bool timing = false;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    lm_ggml_b200_stats stats = {};
+};
+
+lm_ggml_guid_t b200_guid() {
+    static lm_ggml_guid guid = {0xb2, 0x00, 0x5a, 0x10, 0x0a, 0x47, 0x47, 0x4d, 0x4c, 0x2d, 0x62, 0x32, 0x30, 0x30, 0x00, 0x01};
+    return &guid;
+}
+
+const char * backend_get_name(lm_ggml_backend_t backend) { return ((b200_backend_ctx *) backend->context)->name.c_str(); }
+
+void backend_free(lm_ggml_backend_t backend) {
+    b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
+    {
+        device_guard g(ctx->device);
+        cudaStreamSynchronize(ctx->stream);
+        ctx->act.release();
+        ctx->workspace.release();
+        ctx->fa_scratch.release();
+        ctx->mask_index.release();
+        if (ctx->ev0) cudaEventDestroy(ctx->ev0);
+        if (ctx->ev1) cudaEventDestroy(ctx->ev1);
+        cudaStreamDestroy(ctx->stream);
+    }
+    delete ctx;
+    delete backend;
+}
+
+void backend_synchronize(lm_ggml_backend_t backend) {
+    b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
+    device_guard g(ctx->device);
+    cuda_ok(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+}
+
+void backend_set_tensor_async(lm_ggml_backend_t backend, lm_ggml_tensor * tensor, const void * data, size_t offset, size_t size) {
+    b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
+    lm_ggml_backend_buffer_t buf = tensor->view_src ? tensor->view_src->buffer : tensor->buffer;
+    LM_GGML_ASSERT(buf && buft_is_b200(buf->buft) && "tensor is not in a B200 buffer");
+    device_guard g(ctx->device);
+    if (tensor_is_tiled(tensor)) {
+        cudaStreamSynchronize(ctx->stream);
+        buffer_set_tensor(buf, tensor, data, offset, size);
+        return;
+    }
+    LM_GGML_ASSERT(cuda_ok(cudaMemcpyAsync((char *) tensor->data + offset, data, size, cudaMemcpyHostToDevice, ctx->stream), "cudaMemcpyAsync H2D"));
+}
+
+void backend_get_tensor_async(lm_ggml_backend_t backend, const lm_ggml_tensor * tensor, void * data, size_t offset, size_t size) {
+    b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
+    lm_ggml_backend_buffer_t buf = tensor->view_src ? tensor->view_src->buffer : tensor->buffer;
+    LM_GGML_ASSERT(buf && buft_is_b200(buf->buft) && "tensor is not in a B200 buffer");
+    device_guard g(ctx->device);
+    if (tensor_is_tiled(tensor)) {
+        cudaStreamSynchronize(ctx->stream);
+        buffer_get_tensor(buf, tensor, data, offset, size);
+        return;
+    }
+    LM_GGML_ASSERT(cuda_ok(cudaMemcpyAsync(data, (const char *) tensor->data + offset, size, cudaMemcpyDeviceToHost, ctx->stream), "cudaMemcpyAsync D2H"));
+}
+
+bool backend_cpy_tensor_async(lm_ggml_backend_t backend_src, lm_ggml_backend_t backend_dst, const lm_ggml_tensor * src, lm_ggml_tensor * dst) {
+    if (!lm_ggml_backend_is_b200(backend_src) || !lm_ggml_backend_is_b200(backend_dst)) return false;
+    lm_ggml_backend_buffer_t sbuf = src->view_src ? src->view_src->buffer : src->buffer;
+    lm_ggml_backend_buffer_t dbuf = dst->view_src ? dst->view_src->buffer : dst->buffer;
+    if (!sbuf || !dbuf || !buft_is_b200(sbuf->buft) || !buft_is_b200(dbuf->buft)) return false;
+    if (is_tiled_type(src->type) || !lm_ggml_is_contiguous(src) || !lm_ggml_is_contiguous(dst) || lm_ggml_nbytes(src) != lm_ggml_nbytes(dst)) return false;
+    b200_backend_ctx * sctx = (b200_backend_ctx *) backend_src->context;
+    b200_backend_ctx * dctx = (b200_backend_ctx *) backend_dst->context;
+    device_guard g(sctx->device);
+    // issue on the source stream, then make the destination stream wait for it
+    cudaError_t e = (sctx->device == dctx->device)
+        ? cudaMemcpyAsync(dst->data, src->data, lm_ggml_nbytes(src), cudaMemcpyDeviceToDevice, sctx->stream)
+        : cudaMemcpyPeerAsync(dst->data, dctx->device, src->data, sctx->device, lm_ggml_nbytes(src), sctx->stream);
+    if (!cuda_ok(e, "cudaMemcpyAsync D2D")) return false;
+    if (backend_src != backend_dst) {
+        cudaEvent_t ev;
+        if (!cuda_ok(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate")) return false;
+        cudaEventRecord(ev, sctx->stream);
+        device_guard g2(dctx->device);
+        cudaStreamWaitEvent(dctx->stream, ev, 0);
+        cudaEventDestroy(ev);
+    }
+    return true;
+}
+
+// ---------------------------------------------------------------------------------------------
+// op support and dispatch
+// ---------------------------------------------------------------------------------------------
+bool f32_rows(const lm_ggml_tensor * t) { return t->type == LM_GGML_TYPE_F32 && t->nb[0] == sizeof(float); }
+
+// higher dimensions collapse onto dimension 1 (rows are evenly strided)
+bool rows_collapsible(const lm_ggml_tensor * t) {
+    return t->nb[2] == t->nb[1] * (size_t) t->ne[1] && t->nb[3] == t->nb[2] * (size_t) t->ne[2];
+}
+
+bool weight_ok(const lm_ggml_tensor * w) {
+    // the tensor itself must be the tiled tensor (not a view of one) and two-dimensional
+    return w && is_tiled_type(w->type) && w->view_src == nullptr && w->ne[2] == 1 && w->ne[3] == 1 && w->ne[0] % 32 == 0 &&
+           w->buffer && buft_is_b200(w->buffer->buft);
+}
+
+bool supports_mul_mat(const lm_ggml_tensor * op) {
+    const lm_ggml_tensor * a = op->src[0], * b = op->src[1];
+    if (!weight_ok(a) || !b) return false;
+    if (!f32_rows(b) || b->ne[0] != a->ne[0] || !rows_collapsible(b)) return false;
+    return op->type == LM_GGML_TYPE_F32 && lm_ggml_is_contiguous(op);
+}
+
+bool supports_flash_attn(const lm_ggml_tensor * op) {
+    const lm_ggml_tensor * q = op->src[0], * k = op->src[1], * v = op->src[2], * m = op->src[3];
+    if (!q || !k || !v) return false;
+    if (q->type != LM_GGML_TYPE_F32 || k->type != LM_GGML_TYPE_F16 || v->type != LM_GGML_TYPE_F16) return false;
+    if (q->nb[0] != 4 || k->nb[0] != 2 || v->nb[0] != 2) return false;
+    const int64_t D = q->ne[0];
+    if ((D != 64 && D != 128) || k->ne[0] != D || v->ne[0] != D) return false;
+    if (q->ne[3] != 1 || k->ne[3] != 1 || v->ne[3] != 1) return false;
+    if (k->ne[2] != v->ne[2] || k->ne[1] != v->ne[1] || q->ne[2] % k->ne[2] != 0) return false;
+    if (k->nb[1] % 16 || k->nb[2] % 16 || v->nb[1] % 16 || v->nb[2] % 16) return false;
+    if (m && (m->type != LM_GGML_TYPE_F16 || m->nb[0] != 2 || m->ne[0] < k->ne[1] || m->ne[1] < q->ne[1] || m->ne[2] != 1 || m->ne[3] != 1)) return false;
+    if (op->src[4]) return false;  // no attention sinks in this runtime's graphs
+    return op->type == LM_GGML_TYPE_F32 && lm_ggml_is_contiguous(op);
+}
+
+bool supports_cpy(const lm_ggml_tensor * src, const lm_ggml_tensor * dst) {
+    if (!src || src->type != LM_GGML_TYPE_F32) return false;
+    if (dst->type != LM_GGML_TYPE_F32 && dst->type != LM_GGML_TYPE_F16) return false;
+    if (lm_ggml_nelements(src) != lm_ggml_nelements(dst)) return false;
+    if (lm_ggml_is_contiguous(src) && lm_ggml_is_contiguous(dst)) return true;
+    return lm_ggml_are_same_shape(src, dst) && src->nb[0] == 4 && dst->nb[0] == lm_ggml_type_size(dst->type);
+}
+
+bool supports_binary(const lm_ggml_tensor * op) {
+    const lm_ggml_tensor * a = op->src[0], * b = op->src[1];
+    if (!a || !b || a->type != LM_GGML_TYPE_F32 || b->type != LM_GGML_TYPE_F32 || op->type != LM_GGML_TYPE_F32) return false;
+    if (!lm_ggml_is_contiguous(a) || !lm_ggml_is_contiguous(b) || !lm_ggml_is_contiguous(op) || !lm_ggml_are_same_shape(a, op)) return false;
+    return lm_ggml_are_same_shape(a, b) || (b->ne[0] == a->ne[0] && lm_ggml_nelements(b) == b->ne[0]);
+}
+
+bool supports_rope(const lm_ggml_tensor * op) {
+    const lm_ggml_tensor * a = op->src[0], * pos = op->src[1], * ff = op->src[2];
+    if (!a || !pos || !f32_rows(a) || op->type != LM_GGML_TYPE_F32 || op->nb[0] != 4 || pos->type != LM_GGML_TYPE_I32) return false;
+    const int32_t * p = (const int32_t *) op->op_params;
+    const int n_dims = p[1], mode = p[2];
+    float ext_factor;
+    memcpy(&ext_factor, p + 7, sizeof(float));
+    if (mode != 0 || ext_factor != 0.0f || n_dims <= 0 || n_dims > a->ne[0] || (n_dims & 1)) return false;
+    if (ff && (ff->type != LM_GGML_TYPE_F32 || ff->ne[0] < n_dims / 2)) return false;
+    return a->ne[3] == 1 && lm_ggml_are_same_shape(a, op);
+}
+
+bool b200_supports_op(const lm_ggml_tensor * op) {
+    switch (op->op) {
+        case LM_GGML_OP_NONE:
+        case LM_GGML_OP_RESHAPE:
+        case LM_GGML_OP_VIEW:
+        case LM_GGML_OP_PERMUTE:
+        case LM_GGML_OP_TRANSPOSE:
+            return true;
+        case LM_GGML_OP_MUL_MAT:
+            return supports_mul_mat(op);
+        case LM_GGML_OP_FLASH_ATTN_EXT:
+            return supports_flash_attn(op);
+        case LM_GGML_OP_RMS_NORM:
+            return op->src[0] && f32_rows(op->src[0]) && op->type == LM_GGML_TYPE_F32 && lm_ggml_is_contiguous(op) && rows_collapsible(op->src[0]);
+        case LM_GGML_OP_ADD:
+        case LM_GGML_OP_MUL:
+            return supports_binary(op);
+        case LM_GGML_OP_UNARY:
+            return lm_ggml_get_unary_op(op) == LM_GGML_UNARY_OP_SILU && op->src[0] && op->src[0]->type == LM_GGML_TYPE_F32 &&
+                   lm_ggml_is_contiguous(op->src[0]) && lm_ggml_is_contiguous(op) && op->type == LM_GGML_TYPE_F32;
+        case LM_GGML_OP_ROPE:
+            return supports_rope(op);
+        case LM_GGML_OP_CPY:
+            return supports_cpy(op->src[0], op->src[1] ? op->src[1] : op);
+        case LM_GGML_OP_CONT:
+        case LM_GGML_OP_DUP:
+            return supports_cpy(op->src[0], op);
+        case LM_GGML_OP_GET_ROWS: {
+            const lm_ggml_tensor * a = op->src[0], * ids = op->src[1];
+            if (!a || !ids || ids->type != LM_GGML_TYPE_I32 || !lm_ggml_is_contiguous(ids) || op->type != LM_GGML_TYPE_F32 || !lm_ggml_is_contiguous(op)) return false;
+            if (a->ne[2] != 1 || a->ne[3] != 1) return false;
+            return f32_rows(a) || weight_ok(a);
+        }
+        default:
+            return false;
+    }
+}
+
+#define B200_CHECK(call)                                                           \
+    do {                                                                           \
+        if ((call) != B200_OK) {                                                   \
+            B200_LOG_ERROR("ggml-b200: %s: %s\n", lm_ggml_op_name(node->op), b200_last_error()); \
+            return LM_GGML_STATUS_FAILED;                                             \
+        }                                                                          \
+    } while (0)
+
+bool only_user_is(const lm_ggml_cgraph * g, const lm_ggml_tensor * t, const lm_ggml_tensor * user) {
+    for (int i = 0; i < g->n_nodes; ++i) {
+        const lm_ggml_tensor * n = g->nodes[i];
+        if (n == user) continue;
+        for (int s = 0; s < LM_GGML_MAX_SRC; ++s) {
+            if (n->src[s] == t) return false;
+            if (n->src[s] && n->src[s]->view_src == t) return false;
+        }
+        if (n->view_src == t) return false;
+    }
+    return !(t->flags & LM_GGML_TENSOR_FLAG_OUTPUT);
+}
+
+lm_ggml_status compute_cpy(b200_backend_ctx * ctx, const lm_ggml_tensor * node, const lm_ggml_tensor * src, const lm_ggml_tensor * dst) {
+    const bool to_f16 = dst->type == LM_GGML_TYPE_F16;
+    auto run = [&](const void * s, int64_t snb, void * d, int64_t dnb, int64_t n, int64_t rows) {
+        return to_f16 ? b200_cpy_f32_f16((const float *) s, snb, d, dnb, n, rows, ctx->stream)
+                      : b200_cpy_f32_f32((const float *) s, snb, (float *) d, dnb, n, rows, ctx->stream);
+    };
+    if (lm_ggml_is_contiguous(src) && lm_ggml_is_contiguous(dst)) {
+        const int64_t n = lm_ggml_nelements(src);
+        B200_CHECK(run(src->data, n * 4, dst->data, n * (int64_t) lm_ggml_type_size(dst->type), n, 1));
+        return LM_GGML_STATUS_SUCCESS;
+    }
+    for (int64_t i3 = 0; i3 < src->ne[3]; ++i3)
+        for (int64_t i2 = 0; i2 < src->ne[2]; ++i2)
+            B200_CHECK(run((const char *) src->data + i2 * src->nb[2] + i3 * src->nb[3], src->nb[1],
+                           (char *) dst->data + i2 * dst->nb[2] + i3 * dst->nb[3], dst->nb[1], src->ne[0], src->ne[1]));
+    return LM_GGML_STATUS_SUCCESS;
+}
+
+lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph * cgraph) {
+    b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
+    device_guard g(ctx->device);
+    cudaStream_t st = ctx->stream;
+    ctx->act_src = nullptr;
+    ctx->index_mask = nullptr;
+    ctx->stats.graphs++;
+    if (ctx->timing) cudaEventRecord(ctx->ev0, st);
+
+    for (int i = 0; i < cgraph->n_nodes; ++i) {
+        lm_ggml_tensor * node = cgraph->nodes[i];
+        if (lm_ggml_is_empty(node)) continue;
+        switch (node->op) {
+            case LM_GGML_OP_NONE: case LM_GGML_OP_RESHAPE: case LM_GGML_OP_VIEW: case LM_GGML_OP_PERMUTE: case LM_GGML_OP_TRANSPOSE:
+                continue;
+            default:
+                break;
+        }
+        if (ctx->abort_cb && (i & 63) == 0 && ctx->abort_cb(ctx->abort_cb_data)) {
+            cudaStreamSynchronize(st);
+            return LM_GGML_STATUS_ABORTED;
+        }
+        ctx->stats.nodes++;
+        const lm_ggml_tensor * s0 = node->src[0], * s1 = node->src[1];
+        switch (node->op) {
+            case LM_GGML_OP_MUL_MAT: {
+                const int64_t K = s0->ne[0], M = s0->ne[1], N = s1->ne[1] * s1->ne[2] * s1->ne[3];
+                const size_t ab = b200_act_bytes(K, N);
+                if (ctx->act_src != s1) {  // consecutive mul_mats on the same activations (wq/wk/wv, gate/up) quantise once
+                    void * act = ctx->act.get(ab, st);
+                    if (!act) return LM_GGML_STATUS_ALLOC_FAILED;
+                    B200_CHECK(b200_quantize_activations((const float *) s1->data, s1->nb[1], K, N, act, ctx->act.bytes, ctx->q8_variant, st));
+                    ctx->act_src = s1;
+                    ctx->stats.act_quantized++;
+                }
+                const size_t wb = b200_mul_mat_workspace_bytes(s0->type, K, M, N);
+                void * ws = wb ? ctx->workspace.get(wb, st) : nullptr;
+                if (wb && !ws) return LM_GGML_STATUS_ALLOC_FAILED;
+                B200_CHECK(b200_mul_mat_q_prequant(s0->type, s0->data, K, M, ctx->act.ptr, N, (float *) node->data, node->nb[1], ws,
+                                                   ws ? ctx->workspace.bytes : 0, st));
+                ctx->stats.mul_mat++;
+            } break;
+            case LM_GGML_OP_FLASH_ATTN_EXT: {
+                const lm_ggml_tensor * q = s0, * k = s1, * v = node->src[2], * m = node->src[3];
+                const int64_t D = q->ne[0], Nq = q->ne[1], H = q->ne[2], Hkv = k->ne[2], n_kv = k->ne[1];
+                float scale, max_bias, softcap;
+                memcpy(&scale, (const float *) node->op_params + 0, sizeof(float));
+                memcpy(&max_bias, (const float *) node->op_params + 1, sizeof(float));
+                memcpy(&softcap, (const float *) node->op_params + 2, sizeof(float));
+                void * index = nullptr;
+                if (m) {
+                    const size_t ib = b200_mask_index_bytes(Nq, n_kv);
+                    if (ctx->index_mask != m) {  // every layer of a graph attends through the same mask tensor
+                        index = ctx->mask_index.get(ib, st);
+                        if (!index) return LM_GGML_STATUS_ALLOC_FAILED;
+                        B200_CHECK(b200_mask_index_build(m->data, m->nb[1], Nq, n_kv, index, ctx->mask_index.bytes, st));
+                        ctx->index_mask = m;
+                        ctx->stats.mask_indexed++;
+                    }
+                    index = ctx->mask_index.ptr;
+                }
+                const size_t sb = b200_flash_attn_scratch_bytes(D, H, Hkv, Nq, n_kv);
+                void * scratch = ctx->fa_scratch.get(std::max<size_t>(sb, 256), st);
+                if (!scratch) return LM_GGML_STATUS_ALLOC_FAILED;
+                B200_CHECK(b200_flash_attn_ext_indexed(D, H, Hkv, Nq, n_kv, (const float *) q->data, q->nb[1], q->nb[2], k->data, k->nb[1], k->nb[2],
+                                                       v->data, v->nb[1], v->nb[2], m ? m->data : nullptr, m ? m->nb[1] : 0, index, scale, max_bias,
+                                                       softcap, (float *) node->data, scratch, ctx->fa_scratch.bytes, st));
+                ctx->stats.flash_attn++;
+            } break;
+            case LM_GGML_OP_RMS_NORM: {
+                float eps;
+                memcpy(&eps, node->op_params, sizeof(float));
+                const int64_t d = s0->ne[0], rows = lm_ggml_nrows(s0);
+                // RMS_NORM followed by MUL with a weight row is how every llama norm is built: one kernel
+                lm_ggml_tensor * next = i + 1 < cgraph->n_nodes ? cgraph->nodes[i + 1] : nullptr;
+                if (next && next->op == LM_GGML_OP_MUL && next->src[0] == node && next->src[1] && next->src[1]->type == LM_GGML_TYPE_F32 &&
+                    next->src[1]->ne[0] == d && lm_ggml_nelements(next->src[1]) == d && lm_ggml_is_contiguous(next->src[1]) &&
+                    lm_ggml_is_contiguous(next) && only_user_is(cgraph, node, next)) {
+                    B200_CHECK(b200_rms_norm((const float *) s0->data, s0->nb[1], (const float *) next->src[1]->data, (float *) next->data, d * 4, d, rows, eps, st));
+                    ++i;
+                } else {
+                    B200_CHECK(b200_rms_norm((const float *) s0->data, s0->nb[1], nullptr, (float *) node->data, d * 4, d, rows, eps, st));
+                }
+            } break;
+            case LM_GGML_OP_ADD:
+            case LM_GGML_OP_MUL: {
+                const int64_t d = s0->ne[0], rows = lm_ggml_nrows(s0);
+                const int64_t brows = lm_ggml_are_same_shape(s0, s1) ? rows : 1;
+                if (node->op == LM_GGML_OP_ADD) B200_CHECK(b200_add((const float *) s0->data, (const float *) s1->data, (float *) node->data, d, rows, brows, st));
+                else B200_CHECK(b200_mul((const float *) s0->data, (const float *) s1->data, (float *) node->data, d, rows, brows, st));
+            } break;
+            case LM_GGML_OP_UNARY: {
+                // SILU(gate) * up: the llama FFN gate, fused when the SILU result has no other reader
+                lm_ggml_tensor * next = i + 1 < cgraph->n_nodes ? cgraph->nodes[i + 1] : nullptr;
+                if (next && next->op == LM_GGML_OP_MUL && (next->src[0] == node || next->src[1] == node) && supports_binary(next) &&
+                    lm_ggml_are_same_shape(next->src[0], next->src[1]) && only_user_is(cgraph, node, next)) {
+                    const lm_ggml_tensor * other = next->src[0] == node ? next->src[1] : next->src[0];
+                    B200_CHECK(b200_silu((const float *) s0->data, (const float *) other->data, (float *) next->data, lm_ggml_nelements(s0), st));
+                    ++i;
+                } else {
+                    B200_CHECK(b200_silu((const float *) s0->data, nullptr, (float *) node->data, lm_ggml_nelements(s0), st));
+                }
+            } break;
+            case LM_GGML_OP_ROPE: {
+                const int32_t * p = (const int32_t *) node->op_params;
+                float freq_base, freq_scale, attn_factor;
+                memcpy(&freq_base, p + 5, sizeof(float));
+                memcpy(&freq_scale, p + 6, sizeof(float));
+                memcpy(&attn_factor, p + 8, sizeof(float));
+                B200_CHECK(b200_rope_norm((const float *) s0->data, s0->nb[1], s0->nb[2], (float *) node->data, node->nb[1], node->nb[2], s0->ne[0],
+                                          s0->ne[1], s0->ne[2], p[1], (const int32_t *) s1->data, node->src[2] ? (const float *) node->src[2]->data : nullptr,
+                                          freq_base, freq_scale, attn_factor, st));
+            } break;
+            case LM_GGML_OP_CPY: {
+                lm_ggml_status rc = compute_cpy(ctx, node, s0, s1 ? s1 : node);
+                if (rc != LM_GGML_STATUS_SUCCESS) return rc;
+            } break;
+            case LM_GGML_OP_CONT:
+            case LM_GGML_OP_DUP: {
+                lm_ggml_status rc = compute_cpy(ctx, node, s0, node);
+                if (rc != LM_GGML_STATUS_SUCCESS) return rc;
+            } break;
+            case LM_GGML_OP_GET_ROWS: {
+                const int64_t n_ids = lm_ggml_nelements(s1);
+                if (s0->type == LM_GGML_TYPE_F32) {
+                    B200_CHECK(b200_get_rows_f32((const float *) s0->data, s0->nb[1], (const int32_t *) s1->data, (float *) node->data, node->nb[1], s0->ne[0], n_ids, st));
+                } else {
+                    B200_CHECK(b200_get_rows_q(s0->type, s0->data, s0->ne[0], s0->ne[1], (const int32_t *) s1->data, (float *) node->data, node->nb[1], n_ids, st));
+                }
+            } break;
+            default:
+                B200_LOG_ERROR("ggml-b200: op %s reached graph_compute but supports_op does not list it\n", lm_ggml_op_name(node->op));
+                return LM_GGML_STATUS_FAILED;
+        }
+    }
+    if (ctx->timing) {
+        cudaEventRecord(ctx->ev1, st);
+        cudaEventSynchronize(ctx->ev1);
+        float ms = 0;
+        cudaEventElapsedTime(&ms, ctx->ev0, ctx->ev1);
+        ctx->stats.device_ms += ms;
+    }
+    return LM_GGML_STATUS_SUCCESS;
+}
+
+// ---------------------------------------------------------------------------------------------
+// events
+// ---------------------------------------------------------------------------------------------
+void backend_event_record(lm_ggml_backend_t backend, lm_ggml_backend_event_t event) {
+    b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
+    device_guard g(ctx->device);
+    cuda_ok(cudaEventRecord((cudaEvent_t) event->context, ctx->stream), "cudaEventRecord");
+}
+
+void backend_event_wait(lm_ggml_backend_t backend, lm_ggml_backend_event_t event) {
+    b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
+    device_guard g(ctx->device);
+    cuda_ok(cudaStreamWaitEvent(ctx->stream, (cudaEvent_t) event->context, 0), "cudaStreamWaitEvent");
+}
+
+const lm_ggml_backend_i b200_backend_iface = {
+    /* .get_name           = */ backend_get_name,
+    /* .free               = */ backend_free,
+    /* .set_tensor_async   = */ backend_set_tensor_async,
+    /* .get_tensor_async   = */ backend_get_tensor_async,
+    /* .cpy_tensor_async   = */ backend_cpy_tensor_async,
+    /* .synchronize        = */ backend_synchronize,
+    /* .graph_plan_create  = */ nullptr,
+    /* .graph_plan_free    = */ nullptr,
+    /* .graph_plan_update  = */ nullptr,
+    /* .graph_plan_compute = */ nullptr,
+    /* .graph_compute      = */ backend_graph_compute,
+    /* .event_record       = */ backend_event_record,
+    /* .event_wait         = */ backend_event_wait,
+};
+
+// ---------------------------------------------------------------------------------------------
+// device
+// ---------------------------------------------------------------------------------------------
+struct b200_registry {
+    std::vector<b200_device_ctx *> ctxs;
+    std::vector<lm_ggml_backend_device> devices;
+    std::vector<lm_ggml_backend_buffer_type> bufts;
+    std::vector<b200_buft_ctx *> buft_ctxs;
+    lm_ggml_backend_buffer_type host_buft;
+    lm_ggml_backend_reg reg;
+};
+b200_registry * registry();
+
+const char * dev_get_name(lm_ggml_backend_dev_t dev) { return ((b200_device_ctx *) dev->context)->name.c_str(); }
+const char * dev_get_description(lm_ggml_backend_dev_t dev) { return ((b200_device_ctx *) dev->context)->description.c_str(); }
+
+void dev_get_memory(lm_ggml_backend_dev_t dev, size_t * free, size_t * total) {
+    b200_device_ctx * ctx = (b200_device_ctx *) dev->context;
+    if (b200_device_info(ctx->device, nullptr, 0, free, total, nullptr) != B200_OK) *free = *total = 0;
+}
+
+enum lm_ggml_backend_dev_type dev_get_type(lm_ggml_backend_dev_t) { return LM_GGML_BACKEND_DEVICE_TYPE_GPU; }
+
+void dev_get_props(lm_ggml_backend_dev_t dev, lm_ggml_backend_dev_props * props) {
+    props->name = dev_get_name(dev);
+    props->description = dev_get_description(dev);
+    props->type = dev_get_type(dev);
+    dev_get_memory(dev, &props->memory_free, &props->memory_total);
+    props->caps = {
+        /* .async                = */ true,
+        /* .host_buffer          = */ true,
+        /* .buffer_from_host_ptr = */ false,
+        /* .events               = */ true,
+    };
+}
+
+lm_ggml_backend_t dev_init_backend(lm_ggml_backend_dev_t dev, const char *) {
+    return lm_ggml_backend_b200_init(((b200_device_ctx *) dev->context)->device);
+}
+
+lm_ggml_backend_buffer_type_t dev_get_buffer_type(lm_ggml_backend_dev_t dev) { return device_buffer_type(((b200_device_ctx *) dev->context)->device); }
+lm_ggml_backend_buffer_type_t dev_get_host_buffer_type(lm_ggml_backend_dev_t) { return lm_ggml_backend_b200_host_buffer_type(); }
+
+bool dev_supports_op(lm_ggml_backend_dev_t dev, const lm_ggml_tensor * op) {
+    // tensors that already live somewhere must live in a buffer of this device
+    b200_device_ctx * ctx = (b200_device_ctx *) dev->context;
+    for (int i = 0; i < LM_GGML_MAX_SRC; ++i) {
+        const lm_ggml_tensor * s = op->src[i];
+        if (s && s->buffer && buft_is_b200(s->buffer->buft) && ((b200_buft_ctx *) s->buffer->buft->context)->device != ctx->device) return false;
+    }
+    return b200_supports_op(op);
+}
+
+bool dev_supports_buft(lm_ggml_backend_dev_t dev, lm_ggml_backend_buffer_type_t buft) {
+    return buft_is_b200(buft) && ((b200_buft_ctx *) buft->context)->device == ((b200_device_ctx *) dev->context)->device;
+}
+
+bool dev_offload_op(lm_ggml_backend_dev_t, const lm_ggml_tensor *) { return false; }
+
+lm_ggml_backend_event_t dev_event_new(lm_ggml_backend_dev_t dev) {
+    device_guard g(((b200_device_ctx *) dev->context)->device);
+    cudaEvent_t ev;
+    if (!cuda_ok(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate")) return nullptr;
+    return new lm_ggml_backend_event{dev, ev};
+}
+
+void dev_event_free(lm_ggml_backend_dev_t dev, lm_ggml_backend_event_t event) {
+    device_guard g(((b200_device_ctx *) dev->context)->device);
+    cudaEventDestroy((cudaEvent_t) event->context);
+    delete event;
+}
+
+void dev_event_synchronize(lm_ggml_backend_dev_t dev, lm_ggml_backend_event_t event) {
+    device_guard g(((b200_device_ctx *) dev->context)->device);
+    cuda_ok(cudaEventSynchronize((cudaEvent_t) event->context), "cudaEventSynchronize");
+}
+
+const lm_ggml_backend_device_i b200_device_iface = {
+    /* .get_name             = */ dev_get_name,
+    /* .get_description      = */ dev_get_description,
+    /* .get_memory           = */ dev_get_memory,
+    /* .get_type             = */ dev_get_type,
+    /* .get_props            = */ dev_get_props,
+    /* .init_backend         = */ dev_init_backend,
+    /* .get_buffer_type      = */ dev_get_buffer_type,
+    /* .get_host_buffer_type = */ dev_get_host_buffer_type,
+    /* .buffer_from_host_ptr = */ nullptr,
+    /* .supports_op          = */ dev_supports_op,
+    /* .supports_buft        = */ dev_supports_buft,
+    /* .offload_op           = */ dev_offload_op,
+    /* .event_new            = */ dev_event_new,
+    /* .event_free           = */ dev_event_free,
+    /* .event_synchronize    = */ dev_event_synchronize,
+};
+
+// ---------------------------------------------------------------------------------------------
+// reg
+// ---------------------------------------------------------------------------------------------
+const char * reg_get_name(lm_ggml_backend_reg_t) { return LM_GGML_B200_NAME; }
+size_t reg_get_device_count(lm_ggml_backend_reg_t) { return registry()->devices.size(); }
+lm_ggml_backend_dev_t reg_get_device(lm_ggml_backend_reg_t, size_t index) {
+    LM_GGML_ASSERT(index < registry()->devices.size());
+    return &registry()->devices[index];
+}
+
+void set_abort_callback(lm_ggml_backend_t backend, lm_ggml_abort_callback cb, void * data) {
+    if (!lm_ggml_backend_is_b200(backend)) return;
+    b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
+    ctx->abort_cb = cb;
+    ctx->abort_cb_data = data;
+}
+
+lm_ggml_backend_feature * get_features(lm_ggml_backend_reg_t) {
+    static lm_ggml_backend_feature features[] = {
+        {"ARCH", "sm_100a"}, {"MMQ", "int8 mma + f32x2"}, {"FLASH_ATTN", "1"}, {"Q8_0_QUANTIZER", "AVX2-exact"}, {nullptr, nullptr},
+    };
+    return features;
+}
+
+void * reg_get_proc_address(lm_ggml_backend_reg_t, const char * name) {
+    if (strcmp(name, "lm_ggml_backend_set_abort_callback") == 0) return (void *) set_abort_callback;
+    if (strcmp(name, "lm_ggml_backend_get_features") == 0) return (void *) get_features;
+    if (strcmp(name, "lm_ggml_backend_b200_get_stats") == 0) return (void *) lm_ggml_backend_b200_get_stats;
+    return nullptr;
+}
+
+const lm_ggml_backend_reg_i b200_reg_iface = {
+    /* .get_name         = */ reg_get_name,
+    /* .get_device_count = */ reg_get_device_count,
+    /* .get_device       = */ reg_get_device,
+    /* .get_proc_address = */ reg_get_proc_address,
+};
+
+b200_registry * registry() {
+    static b200_registry * r = nullptr;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (r) return r;
+    r = new b200_registry;  // never freed: the registry of the host keeps pointers into it (cactus/ggml-backend-reg.cpp:195-203)
+    const int n = std::min(b200_device_count(), LM_GGML_B200_MAX_DEVICES);
+    r->reg = {LM_GGML_BACKEND_API_VERSION, b200_reg_iface, nullptr};
+    r->devices.reserve(n);
+    r->bufts.reserve(n);
+    for (int i = 0; i < n; ++i) {
+        char name[128] = "";
+        b200_device_info(i, name, sizeof(name), nullptr, nullptr, nullptr);
+        b200_device_ctx * dc = new b200_device_ctx{i, std::string(LM_GGML_B200_NAME) + "_" + std::to_string(i), name};
+        r->ctxs.push_back(dc);
+        r->devices.push_back({b200_device_iface, &r->reg, dc});
+        b200_buft_ctx * bc = new b200_buft_ctx{i, std::string(LM_GGML_B200_NAME) + "_" + std::to_string(i)};
+        r->buft_ctxs.push_back(bc);
+        r->bufts.push_back({b200_buft_iface, &r->devices[i], bc});
+    }
+    r->host_buft = {b200_host_buft_iface, n > 0 ? &r->devices[0] : nullptr, nullptr};
+    return r;
+}
+
+lm_ggml_backend_buffer_type_t device_buffer_type(int device) {
+    b200_registry * r = registry();
+    if (device < 0 || device >= (int) r->bufts.size()) return nullptr;
+    return &r->bufts[device];
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// public entry points
+// ---------------------------------------------------------------------------------------------
+extern "C" {
+
+lm_ggml_backend_reg_t lm_ggml_backend_b200_reg(void) { return &registry()->reg; }
+
+lm_ggml_backend_buffer_type_t lm_ggml_backend_b200_buffer_type(int device) { return device_buffer_type(device); }
+
+lm_ggml_backend_buffer_type_t lm_ggml_backend_b200_host_buffer_type(void) { return &registry()->host_buft; }
+
+bool lm_ggml_backend_is_b200(lm_ggml_backend_t backend) { return backend != nullptr && lm_ggml_guid_matches(backend->guid, b200_guid()); }
+
+lm_ggml_backend_t lm_ggml_backend_b200_init(int device) {
+    b200_registry * r = registry();
+    if (device < 0 || device >= (int) r->devices.size()) {
+        B200_LOG_ERROR("ggml-b200: no B200 device %d (found %zu)\n", device, r->devices.size());
+        return nullptr;
+    }
+    device_guard g(device);
+    b200_backend_ctx * ctx = new b200_backend_ctx;
+    ctx->device = device;
+    ctx->name = std::string(LM_GGML_B200_NAME) + "_" + std::to_string(device);
+    if (!cuda_ok(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking), "cudaStreamCreate")) {
+        delete ctx;
+        return nullptr;
+    }
+    const char * v = getenv("B200_Q8_VARIANT");
+    if (v && strcmp(v, "scalar") == 0) ctx->q8_variant = B200_Q8_SCALAR;
+    const char * t = getenv("B200_TIMING");
+    ctx->timing = t && atoi(t) != 0;
+    cudaEventCreate(&ctx->ev0);
+    cudaEventCreate(&ctx->ev1);
+    return new lm_ggml_backend{b200_guid(), b200_backend_iface, &r->devices[device], ctx};
+}
+
+void lm_ggml_backend_b200_get_stats(lm_ggml_backend_t backend, struct lm_ggml_b200_stats * out) {
+    if (!lm_ggml_backend_is_b200(backend)) {
+        memset(out, 0, sizeof(*out));
+        return;
+    }
+    *out = ((b200_backend_ctx *) backend->context)->stats;
+}
+
+// dynamic loading: lm_ggml_backend_load() looks this symbol up (cactus/ggml-backend-reg.cpp:236-252)
+LM_GGML_BACKEND_API lm_ggml_backend_reg_t lm_ggml_backend_init(void) { return lm_ggml_backend_b200_reg(); }
+LM_GGML_BACKEND_API int lm_ggml_backend_score(void) { return b200_device_count() > 0 ? 100 : 0; }
+
+}  // extern "C"

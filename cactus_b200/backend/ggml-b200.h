@@ -1,0 +1,43 @@
+// ggml backend for NVIDIA B200 (sm_100a) -- public entry points of the plug-in.
+//
+// The plug-in implements the backend interface of cactus's vendored ggml (cactus/ggml-backend-impl.h:
+// reg, device, buffer type, buffer and backend vtables) on top of the C ABI in include/cactus_b200.h.
+// A host program either links this library and calls
+//     lm_ggml_backend_register(lm_ggml_backend_b200_reg());
+// before it loads a model (registry: cactus/ggml-backend-reg.cpp:305), or loads it dynamically with
+// lm_ggml_backend_load("libggml-b200.so") (cactus/ggml-backend-reg.cpp:401), which looks up the exported
+// lm_ggml_backend_init.
+#pragma once
+
+#include "ggml-backend.h"
+#include "ggml.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LM_GGML_B200_NAME "B200"
+#define LM_GGML_B200_MAX_DEVICES 16
+
+LM_GGML_BACKEND_API lm_ggml_backend_reg_t lm_ggml_backend_b200_reg(void);
+// a backend (stream) on device `device`; NULL if the device does not exist
+LM_GGML_BACKEND_API lm_ggml_backend_t lm_ggml_backend_b200_init(int device);
+LM_GGML_BACKEND_API bool lm_ggml_backend_is_b200(lm_ggml_backend_t backend);
+LM_GGML_BACKEND_API lm_ggml_backend_buffer_type_t lm_ggml_backend_b200_buffer_type(int device);
+LM_GGML_BACKEND_API lm_ggml_backend_buffer_type_t lm_ggml_backend_b200_host_buffer_type(void);
+
+// counters of one backend since creation (for tests and benchmarks)
+struct lm_ggml_b200_stats {
+    uint64_t graphs;          // graph_compute calls
+    uint64_t nodes;           // nodes executed (views excluded)
+    uint64_t mul_mat;         // MUL_MAT nodes
+    uint64_t flash_attn;      // FLASH_ATTN_EXT nodes
+    uint64_t act_quantized;   // activation tensors quantised (shared by consecutive mul_mats)
+    uint64_t mask_indexed;    // mask scans (shared by all layers of a graph)
+    double   device_ms;       // CUDA-event time of all graph_compute calls when timing is on (B200_TIMING=1)
+};
+LM_GGML_BACKEND_API void lm_ggml_backend_b200_get_stats(lm_ggml_backend_t backend, struct lm_ggml_b200_stats * out);
+
+#ifdef __cplusplus
+}
+#endif

@@ -62,8 +62,13 @@ __host__ __device__ static inline TiledDims tiled_dims(int wtype, int64_t K, int
 // N rows (columns of the product) of K floats are quantised to Q8_0 and stored in groups of 8 rows
 // ("n-tiles") in the register order of an m16n8k32 B fragment: for n-tile nt and block b, 256 B at
 // (nt*nbp + b)*256, lane = 4*g + t (row 8*nt + g) owning 8 B: [elements 4t..4t+3][elements 16+4t..16+4t+3].
-// Scales: plane of halves at act_d_offset, index ((nt*n_bg + bg)*8 + g)*4 + j for block 4*bg + j.
+// Scales: a plane of f32 at d_offset, 256 B per (nt, bg): for block j of the group and column pair cp the
+// four floats {d[2cp], d[2cp+1], nd[2cp], nd[2cp+1]} at float index ((j*4 + cp)*4), where d is the block's
+// fp16 scale widened to f32 and nd = -d * 12582912 (exact), the constant that turns the tensor-core
+// kernel's "integer dot + 0x4B400000" accumulator bits into d * dot with one fused multiply-add.
 // Rows beyond N and blocks beyond K/32 are zero.
+constexpr float ACT_MAGIC = 12582912.0f;   // 1.5 * 2^23 = as_float(0x4B400000)
+__host__ __device__ static inline int act_scale_index(int j, int col) { return ((j * 4 + (col >> 1)) * 4) + (col & 1); }
 struct ActDims {
     int64_t N, K, nb, nbp, n_bg, n_nt;
     size_t d_offset;     // byte offset of the scale plane
@@ -79,7 +84,7 @@ __host__ __device__ static inline ActDims act_dims(int64_t K, int64_t N) {
     a.n_bg = a.nbp / 4;
     a.n_nt = (N + 7) / 8;
     a.d_offset = (size_t) a.n_nt * a.nbp * 256;
-    a.total_bytes = a.d_offset + (((size_t) a.n_nt * a.n_bg * 64) + 255) / 256 * 256;
+    a.total_bytes = a.d_offset + (size_t) a.n_nt * a.n_bg * 256;
     return a;
 }
 

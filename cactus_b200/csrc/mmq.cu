@@ -2,20 +2,26 @@
 //
 // Replaces the chunked vec_dot loop of lm_ggml_compute_forward_mul_mat
 // (cactus/ggml-cpu/ggml-cpu.c:1257-1449).  Every 32-element block has its own pair of scales, so each
-// k=32 MMA step produces a fresh int32 tile that is converted and folded into fp32 accumulators with
-// the outer product of the weight and activation block scales.
+// k=32 MMA step produces a fresh integer tile that must be scaled by d_w[row] * d_a[col] and added to an
+// fp32 accumulator.  That epilogue, not the MMA, is the cost; it is kept to two packed instructions per
+// pair of values:
+//   * the MMA accumulator starts at 0x4B400000, so the int32 result read as a float is 12582912 + dot
+//     (exact, |dot| < 2^22);  t = fma(d_a, that, -d_a * 12582912) equals d_a * dot rounded once, with the
+//     constant term precomputed per (column, block) by the quantiser -- no int->float conversion;
+//   * y = fma(d_w, t, y).
+//   Both run as fma.rn.f32x2 on the (column 2t, column 2t+1) pair an MMA thread owns.
 //
-// CTA tile 64 rows x BN columns, 4 warps as 2 (rows) x 2 (columns), warp tile 32 x BN/2.  Weight tiles
-// (already in A-fragment order) and activation tiles (B-fragment order) are copied verbatim into a
-// 4-stage cp.async ring, one block group (K = 128) per stage; fragments are then plain 128/64-bit shared
-// loads without bank conflicts.  grid = (row groups, column chunks, K splits); with K splits > 1 the
-// partial tiles go to a workspace and a second kernel adds them in a fixed order.
+// Work split: a warp owns 32 weight rows (two 16-row tiles) and every column of the CTA's column chunk.
+// The 4 warps of a CTA walk the same block groups; weight tiles and activation tiles are both stored in
+// fragment order, so a 4-stage cp.async ring copies them verbatim (16-byte chunks, three block groups in
+// flight per CTA to cover HBM latency) and the fragments are plain 128/64-bit shared loads.
+// grid = (row groups of 128, column chunks, K splits); with K splits > 1 partial tiles go to a workspace
+// and a second kernel adds them in a fixed order.
 #include "common.cuh"
 
 namespace b200 {
 
 constexpr int MMQ_STAGES = 4;
-constexpr int MMQ_BM_TILES = 4;  // 16-row tiles per CTA
 
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
     const uint32_t s = (uint32_t) __cvta_generic_to_shared(smem);
@@ -25,88 +31,129 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
-__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+__device__ __forceinline__ void mma_s8_magic(uint32_t (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    const uint32_t magic = 0x4B400000u;
     asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};\n"
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
         : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(magic));
+}
+__device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1,%2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
+    uint32_t a, b;
+    asm("mov.b64 {%0,%1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+    lo = __uint_as_float(a);
+    hi = __uint_as_float(b);
 }
 
-template <int WTYPE, int BN>
-struct MmqSmem {
+template <int WTYPE>
+struct WFrag {  // one block group of one 16-row tile: quants of rows g / g+8 and their four block scales
+    static constexpr int NW = (WTYPE == B200_TYPE_Q4_0) ? 4 : 8;
+    uint32_t a[NW], b[NW];
+    uint2 sa, sb;
+};
+
+template <int WTYPE>
+__device__ __forceinline__ void load_wfrag(WFrag<WTYPE> &f, const uint8_t *__restrict__ wq, const uint8_t *__restrict__ wd, int lane) {
+    const int g = lane >> 2;
+    if (WTYPE == B200_TYPE_Q4_0) {
+        const uint4 *p = reinterpret_cast<const uint4 *>(wq) + lane * 2;
+        const uint4 u0 = p[0], u1 = p[1];
+        f.a[0] = u0.x; f.a[1] = u0.y; f.a[2] = u0.z; f.a[3] = u0.w;
+        f.b[0] = u1.x; f.b[1] = u1.y; f.b[2] = u1.z; f.b[3] = u1.w;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint4 u = (reinterpret_cast<const uint4 *>(wq + j * 512))[lane];
+            f.a[2 * j] = u.x; f.b[2 * j] = u.y; f.a[2 * j + 1] = u.z; f.b[2 * j + 1] = u.w;
+        }
+    }
+    f.sa = reinterpret_cast<const uint2 *>(wd)[g];
+    f.sb = reinterpret_cast<const uint2 *>(wd)[g + 8];
+}
+
+// Shape of a CTA: WM x WN warps; a warp owns MT 16-row tiles and NTW 8-column tiles.
+template <int WTYPE, int NTW, int WN, int MT, int WM>
+struct MmqCfg {
+    static constexpr int WARPS = WM * WN;
+    static constexpr int THREADS = WARPS * 32;
+    static constexpr int CTA_TILES = WM * MT;      // 16-row tiles per CTA
+    static constexpr int NT = WN * NTW;            // 8-column tiles per CTA
     static constexpr int TILE = (WTYPE == B200_TYPE_Q4_0) ? 1024 : 2048;
-    static constexpr int A_BYTES = MMQ_BM_TILES * TILE;
-    static constexpr int AS_BYTES = MMQ_BM_TILES * 128;
-    static constexpr int B_BYTES = (BN / 8) * 1024;
-    static constexpr int BS_BYTES = (BN / 8) * 64;
-    static constexpr int STAGE = A_BYTES + AS_BYTES + B_BYTES + BS_BYTES;
+    static constexpr int A_BYTES = CTA_TILES * TILE;       // weight tiles of the CTA's rows, one block group
+    static constexpr int AS_BYTES = CTA_TILES * 128;       // their scales
+    static constexpr int B_BYTES = NT * 1024;              // NT n-tiles x 4 blocks x 256 B
+    static constexpr int S_BYTES = NT * 256;               // their scale groups
+    static constexpr int STAGE = A_BYTES + AS_BYTES + B_BYTES + S_BYTES;
     static constexpr int TOTAL = STAGE * MMQ_STAGES;
 };
 
-template <int WTYPE, int BN>
-__global__ void __launch_bounds__(128) mmq_kernel(TiledDims dims, const uint8_t *__restrict__ w, ActDims act,
-                                                 const uint8_t *__restrict__ aq, float *__restrict__ dst, int64_t dst_nb_row,
-                                                 float *__restrict__ partial, int ksplit) {
-    using S = MmqSmem<WTYPE, BN>;
-    constexpr int NTW = BN / 16;  // n-tiles per warp
+template <int WTYPE, int NTW, int WN, int MT, int WM>
+__global__ void __launch_bounds__(WM * WN * 32) mmq_kernel(TiledDims dims, const uint8_t *__restrict__ w, ActDims act,
+                                                          const uint8_t *__restrict__ aq, float *__restrict__ dst,
+                                                          int64_t dst_nb_row, float *__restrict__ partial, int ksplit) {
+    using S = MmqCfg<WTYPE, NTW, WN, MT, WM>;
+    constexpr int NT = NTW;              // n-tiles of this warp
+    constexpr int MMQ_MT = MT;
+    constexpr int MMQ_THREADS = S::THREADS;
     extern __shared__ __align__(128) uint8_t smem[];
-
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int wm = warp >> 1, wn = warp & 1;
-    const int64_t rt0 = (int64_t) blockIdx.x * MMQ_BM_TILES;
-    const int64_t nt0 = (int64_t) blockIdx.y * (BN / 8);
+    const int wm = warp / WN, wn = warp % WN;
+    const int64_t rt0 = (int64_t) blockIdx.x * S::CTA_TILES + wm * MT;  // first row tile of this warp
+    const int64_t cta_nt0 = (int64_t) blockIdx.y * S::NT;
+    const int64_t nt0 = cta_nt0 + wn * NTW;                               // first column tile of this warp
     const int ks = blockIdx.z;
-    // block groups of this K split
     const int64_t per = (dims.n_bg + ksplit - 1) / ksplit;
     const int64_t bg_begin = ks * per;
     const int64_t bg_end = min(dims.n_bg, bg_begin + per);
     const int64_t n_iter = max((int64_t) 0, bg_end - bg_begin);
 
+    const int64_t cta_rt0 = (int64_t) blockIdx.x * S::CTA_TILES;
     auto issue = [&](int64_t it) {
         uint8_t *st = smem + (it % MMQ_STAGES) * S::STAGE;
         const int64_t bg = bg_begin + it;
-        // weights: MMQ_BM_TILES tiles of TILE bytes, then their scales
-        constexpr int A_CH = S::A_BYTES / 16;
-        for (int c = tid; c < A_CH; c += 128) {
+        for (int c = tid; c < S::A_BYTES / 16; c += MMQ_THREADS) {
             const int tile = c / (S::TILE / 16), off = c % (S::TILE / 16);
-            const int64_t rt = min(rt0 + tile, dims.n_rt - 1);  // clamp: rows beyond the matrix are never written back
+            const int64_t rt = min(cta_rt0 + tile, dims.n_rt - 1);  // rows beyond the matrix are never written back
             cp_async16(st + c * 16, w + (rt * dims.n_bg + bg) * S::TILE + off * 16);
         }
-        constexpr int AS_CH = S::AS_BYTES / 16;
-        for (int c = tid; c < AS_CH; c += 128) {
-            const int tile = c / 8, off = c % 8;
-            const int64_t rt = min(rt0 + tile, dims.n_rt - 1);
+        for (int c = tid; c < S::AS_BYTES / 16; c += MMQ_THREADS) {
+            const int tile = c >> 3, off = c & 7;
+            const int64_t rt = min(cta_rt0 + tile, dims.n_rt - 1);
             cp_async16(st + S::A_BYTES + c * 16, w + dims.qs_bytes + (rt * dims.n_bg + bg) * 128 + off * 16);
         }
-        constexpr int B_CH = S::B_BYTES / 16;
-        for (int c = tid; c < B_CH; c += 128) {
-            const int tile = c / 64, off = c % 64;
-            const int64_t nt = min(nt0 + tile, act.n_nt - 1);
-            cp_async16(st + S::A_BYTES + S::AS_BYTES + c * 16, aq + (nt * act.nbp + bg * 4) * 256 + off * 16);
+        uint8_t *sb = st + S::A_BYTES + S::AS_BYTES;
+        for (int c = tid; c < S::B_BYTES / 16; c += MMQ_THREADS) {
+            const int tile = c >> 6, off = c & 63;
+            const int64_t nt = min(cta_nt0 + tile, act.n_nt - 1);  // columns beyond N are never written back
+            cp_async16(sb + c * 16, aq + (nt * act.nbp + bg * 4) * 256 + off * 16);
         }
-        constexpr int BS_CH = S::BS_BYTES / 16;
-        for (int c = tid; c < BS_CH; c += 128) {
-            const int tile = c / 4, off = c % 4;
-            const int64_t nt = min(nt0 + tile, act.n_nt - 1);
-            cp_async16(st + S::A_BYTES + S::AS_BYTES + S::B_BYTES + c * 16, aq + act.d_offset + (nt * act.n_bg + bg) * 64 + off * 16);
+        for (int c = tid; c < S::S_BYTES / 16; c += MMQ_THREADS) {
+            const int tile = c >> 4, off = c & 15;
+            const int64_t nt = min(cta_nt0 + tile, act.n_nt - 1);
+            cp_async16(sb + S::B_BYTES + c * 16, aq + act.d_offset + (nt * act.n_bg + bg) * 256 + off * 16);
         }
     };
-
-    float y[2][NTW][4];
+    uint64_t y[MMQ_MT][NT][2];  // packed (col 2t, col 2t+1) for row g ([0]) and row g+8 ([1])
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+    for (int mt = 0; mt < MMQ_MT; ++mt)
 #pragma unroll
-        for (int nt = 0; nt < NTW; ++nt)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) y[mt][nt][c] = 0.0f;
+        for (int nt = 0; nt < NT; ++nt) y[mt][nt][0] = y[mt][nt][1] = 0ull;
 
     for (int s = 0; s < MMQ_STAGES - 1; ++s) {
         if (s < n_iter) issue(s);
         cp_async_commit();
     }
-
-    constexpr float WS = (WTYPE == B200_TYPE_Q4_0) ? 0.0625f : 1.0f;
 
     for (int64_t it = 0; it < n_iter; ++it) {
         cp_async_wait<MMQ_STAGES - 2>();
@@ -114,88 +161,87 @@ __global__ void __launch_bounds__(128) mmq_kernel(TiledDims dims, const uint8_t 
         if (it + MMQ_STAGES - 1 < n_iter) issue(it + MMQ_STAGES - 1);
         cp_async_commit();
 
-        const uint8_t *st = smem + (it % MMQ_STAGES) * S::STAGE;
-        const uint8_t *As = st, *Asc = st + S::A_BYTES, *Bs = st + S::A_BYTES + S::AS_BYTES, *Bsc = Bs + S::B_BYTES;
+        const uint8_t *As = smem + (it % MMQ_STAGES) * S::STAGE;
+        const uint8_t *Bs = As + S::A_BYTES + S::AS_BYTES;
+        const uint8_t *Ss = Bs + S::B_BYTES;
+        WFrag<WTYPE> cur[MMQ_MT];
+#pragma unroll
+        for (int mt = 0; mt < MMQ_MT; ++mt) {
+            const int tile = wm * MT + mt;
+            load_wfrag<WTYPE>(cur[mt], As + tile * S::TILE, As + S::A_BYTES + tile * 128, lane);
+        }
 
-        // weight fragments and scales of the warp's two row tiles
-        uint32_t wa[2][8], wb[2][8];
-        float dwa[2][4], dwb[2][4];
+        // weight scales of this group as packed (d, d) pairs
+        uint64_t dwa[MMQ_MT][4], dwb[MMQ_MT][4];
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
-            const int tile = wm * 2 + mt;
-            if (WTYPE == B200_TYPE_Q4_0) {
-                const uint4 *p = reinterpret_cast<const uint4 *>(As + tile * 1024) + lane * 2;
-                const uint4 u0 = p[0], u1 = p[1];
-                wa[mt][0] = u0.x; wa[mt][1] = u0.y; wa[mt][2] = u0.z; wa[mt][3] = u0.w;
-                wb[mt][0] = u1.x; wb[mt][1] = u1.y; wb[mt][2] = u1.z; wb[mt][3] = u1.w;
-            } else {
+        for (int mt = 0; mt < MMQ_MT; ++mt) {
+            const __half2 a01 = *reinterpret_cast<const __half2 *>(&cur[mt].sa.x), a23 = *reinterpret_cast<const __half2 *>(&cur[mt].sa.y);
+            const __half2 b01 = *reinterpret_cast<const __half2 *>(&cur[mt].sb.x), b23 = *reinterpret_cast<const __half2 *>(&cur[mt].sb.y);
+            const float2 fa01 = __half22float2(a01), fa23 = __half22float2(a23), fb01 = __half22float2(b01), fb23 = __half22float2(b23);
+            const uint32_t ua[4] = {__float_as_uint(fa01.x), __float_as_uint(fa01.y), __float_as_uint(fa23.x), __float_as_uint(fa23.y)};
+            const uint32_t ub[4] = {__float_as_uint(fb01.x), __float_as_uint(fb01.y), __float_as_uint(fb23.x), __float_as_uint(fb23.y)};
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint4 u = reinterpret_cast<const uint4 *>(As + tile * 2048 + j * 512)[lane];
-                    wa[mt][2 * j] = u.x; wb[mt][2 * j] = u.y; wa[mt][2 * j + 1] = u.z; wb[mt][2 * j + 1] = u.w;
-                }
+            for (int j = 0; j < 4; ++j) {
+                dwa[mt][j] = pack2(ua[j], ua[j]);
+                dwb[mt][j] = pack2(ub[j], ub[j]);
             }
-            const uint2 sa = reinterpret_cast<const uint2 *>(Asc + tile * 128)[g];
-            const uint2 sb = reinterpret_cast<const uint2 *>(Asc + tile * 128)[g + 8];
-            const __half2 a01 = *reinterpret_cast<const __half2 *>(&sa.x), a23 = *reinterpret_cast<const __half2 *>(&sa.y);
-            const __half2 b01 = *reinterpret_cast<const __half2 *>(&sb.x), b23 = *reinterpret_cast<const __half2 *>(&sb.y);
-            dwa[mt][0] = __low2float(a01) * WS; dwa[mt][1] = __high2float(a01) * WS;
-            dwa[mt][2] = __low2float(a23) * WS; dwa[mt][3] = __high2float(a23) * WS;
-            dwb[mt][0] = __low2float(b01) * WS; dwb[mt][1] = __high2float(b01) * WS;
-            dwb[mt][2] = __low2float(b23) * WS; dwb[mt][3] = __high2float(b23) * WS;
         }
 
 #pragma unroll
-        for (int nt = 0; nt < NTW; ++nt) {
-            const int ntl = wn * NTW + nt;
-            // activation scales of columns 2t and 2t+1, four blocks each
-            const uint2 s0 = reinterpret_cast<const uint2 *>(Bsc + ntl * 64)[2 * t];
-            const uint2 s1 = reinterpret_cast<const uint2 *>(Bsc + ntl * 64)[2 * t + 1];
-            const __half2 e01 = *reinterpret_cast<const __half2 *>(&s0.x), e23 = *reinterpret_cast<const __half2 *>(&s0.y);
-            const __half2 f01 = *reinterpret_cast<const __half2 *>(&s1.x), f23 = *reinterpret_cast<const __half2 *>(&s1.y);
-            const float da0[4] = {__low2float(e01), __high2float(e01), __low2float(e23), __high2float(e23)};
-            const float da1[4] = {__low2float(f01), __high2float(f01), __low2float(f23), __high2float(f23)};
+        for (int j = 0; j < 4; ++j) {
+            // A fragments of block j for both row tiles
+            uint32_t a0[MMQ_MT], a1[MMQ_MT], a2[MMQ_MT], a3[MMQ_MT];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint2 b = reinterpret_cast<const uint2 *>(Bs + ntl * 1024 + j * 256)[lane];
+            for (int mt = 0; mt < MMQ_MT; ++mt) {
+                if (WTYPE == B200_TYPE_Q4_0) {
+                    a0[mt] = (cur[mt].a[j] << 4) & 0xF0F0F0F0u; a2[mt] = cur[mt].a[j] & 0xF0F0F0F0u;
+                    a1[mt] = (cur[mt].b[j] << 4) & 0xF0F0F0F0u; a3[mt] = cur[mt].b[j] & 0xF0F0F0F0u;
+                } else {
+                    a0[mt] = cur[mt].a[2 * j]; a2[mt] = cur[mt].a[2 * j + 1];
+                    a1[mt] = cur[mt].b[2 * j]; a3[mt] = cur[mt].b[2 * j + 1];
+                }
+            }
 #pragma unroll
-                for (int mt = 0; mt < 2; ++mt) {
-                    uint32_t a0, a1, a2, a3;
-                    if (WTYPE == B200_TYPE_Q4_0) {
-                        a0 = (wa[mt][j] << 4) & 0xF0F0F0F0u; a2 = wa[mt][j] & 0xF0F0F0F0u;
-                        a1 = (wb[mt][j] << 4) & 0xF0F0F0F0u; a3 = wb[mt][j] & 0xF0F0F0F0u;
-                    } else {
-                        a0 = wa[mt][2 * j]; a2 = wa[mt][2 * j + 1];
-                        a1 = wb[mt][2 * j]; a3 = wb[mt][2 * j + 1];
-                    }
-                    int c[4];
-                    mma_s8(c, a0, a1, a2, a3, b.x, b.y);
-                    y[mt][nt][0] = fmaf(dwa[mt][j] * da0[j], (float) c[0], y[mt][nt][0]);
-                    y[mt][nt][1] = fmaf(dwa[mt][j] * da1[j], (float) c[1], y[mt][nt][1]);
-                    y[mt][nt][2] = fmaf(dwb[mt][j] * da0[j], (float) c[2], y[mt][nt][2]);
-                    y[mt][nt][3] = fmaf(dwb[mt][j] * da1[j], (float) c[3], y[mt][nt][3]);
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint2 b = reinterpret_cast<const uint2 *>(Bs + (wn * NTW + nt) * 1024 + j * 256)[lane];
+                const uint4 sc = reinterpret_cast<const uint4 *>(Ss + (wn * NTW + nt) * 256)[j * 4 + t];  // {d0, d1, nd0, nd1} of columns 2t, 2t+1
+                const uint64_t da = pack2(sc.x, sc.y), nda = pack2(sc.z, sc.w);
+#pragma unroll
+                for (int mt = 0; mt < MMQ_MT; ++mt) {
+                    uint32_t c[4];
+                    mma_s8_magic(c, a0[mt], a1[mt], a2[mt], a3[mt], b.x, b.y);
+                    const uint64_t t01 = fma2(pack2(c[0], c[1]), da, nda);
+                    const uint64_t t23 = fma2(pack2(c[2], c[3]), da, nda);
+                    y[mt][nt][0] = fma2(t01, dwa[mt][j], y[mt][nt][0]);
+                    y[mt][nt][1] = fma2(t23, dwb[mt][j], y[mt][nt][1]);
                 }
             }
         }
     }
     cp_async_wait<0>();
 
-    // write back: c0 (row g, col 2t), c1 (g, 2t+1), c2 (g+8, 2t), c3 (g+8, 2t+1)
+    // write back; Q4_0 quants were used as 16 * value
+    constexpr float WS = (WTYPE == B200_TYPE_Q4_0) ? 0.0625f : 1.0f;
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {
-        const int64_t row_base = (rt0 + wm * 2 + mt) * 16;
+    for (int mt = 0; mt < MMQ_MT; ++mt) {
+        const int64_t row_base = (rt0 + mt) * 16 + g;
 #pragma unroll
-        for (int nt = 0; nt < NTW; ++nt) {
-            const int64_t col_base = (nt0 + wn * NTW + nt) * 8 + 2 * t;
+        for (int nt = 0; nt < NT; ++nt) {
+            const int64_t col = (nt0 + nt) * 8 + 2 * t;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int64_t row = row_base + g + (c >> 1) * 8;
-                const int64_t col = col_base + (c & 1);
-                if (row < dims.M && col < act.N) {
+            for (int h = 0; h < 2; ++h) {
+                const int64_t row = row_base + h * 8;
+                float v0, v1;
+                unpack2(y[mt][nt][h], v0, v1);
+                v0 *= WS;
+                v1 *= WS;
+                if (row < dims.M) {
                     if (ksplit == 1) {
-                        *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + col * dst_nb_row + row * 4) = y[mt][nt][c];
+                        if (col < act.N) *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + col * dst_nb_row + row * 4) = v0;
+                        if (col + 1 < act.N) *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + (col + 1) * dst_nb_row + row * 4) = v1;
                     } else {
-                        partial[((int64_t) ks * act.N + col) * dims.M + row] = y[mt][nt][c];
+                        if (col < act.N) partial[((int64_t) ks * act.N + col) * dims.M + row] = v0;
+                        if (col + 1 < act.N) partial[((int64_t) ks * act.N + col + 1) * dims.M + row] = v1;
                     }
                 }
             }
@@ -214,70 +260,135 @@ __global__ void __launch_bounds__(256) mmq_reduce_kernel(const float *__restrict
     *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + n * dst_nb_row + m * 4) = s;
 }
 
-static int g_sm_count = 0;
 static int sm_count() {
-    if (!g_sm_count) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (g_sm_count <= 0) g_sm_count = 148;
+    static int n[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev &= 63;
+    if (!n[dev]) {
+        cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
+        if (n[dev] <= 0) n[dev] = 148;
     }
-    return g_sm_count;
+    return n[dev];
 }
 
-// number of K splits: enough CTAs to fill the device twice over, at least 8 block groups per split
-int mmq_ksplit(const TiledDims &d, int64_t N) {
-    const int64_t row_groups = (d.n_rt + MMQ_BM_TILES - 1) / MMQ_BM_TILES;
-    const int64_t col_chunks = (N + 63) / 64;
-    const int64_t ctas = row_groups * col_chunks;
-    const int64_t want = 2 * sm_count();
-    if (ctas >= want) return 1;
-    int64_t ks = (want + ctas - 1) / ctas;
-    ks = min(ks, max((int64_t) 1, d.n_bg / 8));
-    return (int) min(ks, (int64_t) 16);
+// One launchable CTA shape: how many rows / columns a CTA covers, how many CTAs fit on an SM, and the launcher.
+struct MmqVariant {
+    int cta_tiles;   // 16-row tiles per CTA
+    int cta_nt;      // 8-column tiles per CTA
+    int ctas_per_sm; // resident CTAs per SM (filled on first use)
+    int (*launch)(const TiledDims &, const uint8_t *, const ActDims &, const uint8_t *, float *, int64_t, float *, int, cudaStream_t);
+};
+
+template <int WTYPE, int NTW, int WN, int MT, int WM>
+static int launch_variant(const TiledDims &d, const uint8_t *w, const ActDims &a, const uint8_t *aq, float *dst, int64_t dst_nb_row,
+                          float *partial, int ksplit, cudaStream_t st) {
+    using S = MmqCfg<WTYPE, NTW, WN, MT, WM>;
+    dim3 grid((unsigned) ((d.n_rt + S::CTA_TILES - 1) / S::CTA_TILES), (unsigned) ((a.n_nt + S::NT - 1) / S::NT), (unsigned) ksplit);
+    mmq_kernel<WTYPE, NTW, WN, MT, WM><<<grid, S::THREADS, S::TOTAL, st>>>(d, w, a, aq, dst, dst_nb_row, partial, ksplit);
+    return check_launch("mmq");
+}
+
+template <int WTYPE, int NTW, int WN, int MT, int WM>
+static MmqVariant make_variant() {
+    using S = MmqCfg<WTYPE, NTW, WN, MT, WM>;
+    MmqVariant v;
+    v.cta_tiles = S::CTA_TILES;
+    v.cta_nt = S::NT;
+    v.launch = launch_variant<WTYPE, NTW, WN, MT, WM>;
+    cudaFuncSetAttribute(mmq_kernel<WTYPE, NTW, WN, MT, WM>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, mmq_kernel<WTYPE, NTW, WN, MT, WM>, S::THREADS, S::TOTAL) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = 1;
+    }
+    v.ctas_per_sm = n;
+    return v;
+}
+
+// Variants per (weight type, column class).  Column classes: <= 16, <= 32, more (64-column chunks).
+// Index 0 is the default; B200_MMQ_VARIANT=<i> selects another one (tuning aid).
+template <int WTYPE>
+static const MmqVariant &pick_variant(int64_t N) {
+    // per device: kernel attributes and occupancy are per-context properties
+    static MmqVariant table[64][3][4];
+    static bool ready[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev &= 63;
+    if (!ready[dev]) {
+        MmqVariant(*t)[4] = table[dev];
+        t[0][0] = make_variant<WTYPE, 2, 1, 2, 4>();   // 128 rows x 16 cols, 4 warps
+        t[0][1] = make_variant<WTYPE, 2, 1, 1, 4>();   //  64 rows x 16 cols
+        t[0][2] = t[0][0]; t[0][3] = t[0][0];
+        t[1][0] = make_variant<WTYPE, 4, 1, 2, 4>();   // 128 rows x 32 cols
+        t[1][1] = make_variant<WTYPE, 4, 1, 1, 4>();
+        t[1][2] = t[1][0]; t[1][3] = t[1][0];
+        t[2][0] = make_variant<WTYPE, 8, 1, 2, 4>();   // 128 rows x 64 cols, a warp owns all 64 columns
+        t[2][1] = make_variant<WTYPE, 4, 2, 2, 4>();   // 128 rows x 64 cols, 8 warps as 4 x 2
+        t[2][2] = make_variant<WTYPE, 4, 2, 2, 2>();   //  64 rows x 64 cols, 4 warps as 2 x 2
+        t[2][3] = make_variant<WTYPE, 8, 1, 1, 4>();   //  64 rows x 64 cols, one row tile per warp
+        ready[dev] = true;
+    }
+    static int forced = -2;
+    if (forced == -2) {
+        const char *e = getenv("B200_MMQ_VARIANT");
+        forced = e ? atoi(e) : -1;
+    }
+    const int cls = N > 32 ? 2 : (N > 16 ? 1 : 0);
+    return table[dev][cls][(forced >= 0 && forced < 4) ? forced : 0];
+}
+
+// K splits: the CTA count is made to fit whole waves of resident CTAs; each split pays about three block
+// groups of fixed cost (pipeline fill, write-back, the later reduction)
+static int choose_ksplit(const MmqVariant &v, const TiledDims &d, int64_t n_nt) {
+    const int64_t ctas = ((d.n_rt + v.cta_tiles - 1) / v.cta_tiles) * ((n_nt + v.cta_nt - 1) / v.cta_nt);
+    const int64_t slots = (int64_t) sm_count() * v.ctas_per_sm;
+    int best = 1;
+    int64_t best_cost = -1;
+    for (int ks = 1; ks <= 16; ++ks) {
+        const int64_t per = (d.n_bg + ks - 1) / ks;
+        if (ks > 1 && per < 2) break;
+        const int64_t waves = (ctas * ks + slots - 1) / slots;
+        const int64_t cost = waves * (per + 3) + (ks > 1 ? 2 : 0);
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best = ks;
+        }
+    }
+    return best;
+}
+
+static const MmqVariant &variant_for(int wtype, int64_t N) {
+    return wtype == B200_TYPE_Q4_0 ? pick_variant<B200_TYPE_Q4_0>(N) : pick_variant<B200_TYPE_Q8_0>(N);
 }
 
 size_t mmq_workspace_bytes(int wtype, int64_t K, int64_t M, int64_t N) {
     if (N <= 8) return 0;
+    // upper bound over every K split the launcher may choose (the choice depends on the device): never more
+    // than 16, than half the block groups, or than what two waves of the largest plausible device need
     const TiledDims d = tiled_dims(wtype, K, M);
-    const int ks = mmq_ksplit(d, N);
+    const int64_t ctas = ((d.n_rt + 7) / 8) * ((N + 63) / 64);
+    int64_t ks = std::min<int64_t>(16, std::max<int64_t>(1, d.n_bg / 2));
+    ks = std::min<int64_t>(ks, std::max<int64_t>(1, (2368 + ctas - 1) / ctas));
     return ks > 1 ? align_up((size_t) ks * N * M * sizeof(float), 256) : 0;
-}
-
-template <int WTYPE, int BN>
-static int launch_mmq_t(const TiledDims &d, const uint8_t *w, const ActDims &a, const uint8_t *aq, float *dst, int64_t dst_nb_row,
-                        float *partial, int ksplit, cudaStream_t st) {
-    using S = MmqSmem<WTYPE, BN>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(mmq_kernel<WTYPE, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-        if (e != cudaSuccess) return set_error(B200_E_CUDA, "mmq smem opt-in: %s", cudaGetErrorString(e));
-        configured = true;
-    }
-    dim3 grid((unsigned) ((d.n_rt + MMQ_BM_TILES - 1) / MMQ_BM_TILES), (unsigned) ((a.N + BN - 1) / BN), (unsigned) ksplit);
-    mmq_kernel<WTYPE, BN><<<grid, 128, S::TOTAL, st>>>(d, w, a, aq, dst, dst_nb_row, partial, ksplit);
-    if (int e = check_launch("mmq")) return e;
-    if (ksplit > 1) {
-        const int64_t total = d.M * a.N;
-        mmq_reduce_kernel<<<(unsigned) ((total + 255) / 256), 256, 0, st>>>(partial, ksplit, d.M, a.N, dst, dst_nb_row);
-        return check_launch("mmq_reduce");
-    }
-    return B200_OK;
 }
 
 int launch_mmq(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
                void *workspace, size_t workspace_bytes, cudaStream_t st) {
-    int ks = mmq_ksplit(d, a.N);
-    if (ks > 1 && (!workspace || workspace_bytes < (size_t) ks * a.N * d.M * sizeof(float))) {
-        return set_error(B200_E_SCRATCH, "mul_mat workspace too small for %d K splits", ks);
+    const MmqVariant &v = variant_for(wtype, a.N);
+    int ks = choose_ksplit(v, d, a.n_nt);
+    const size_t per_split = (size_t) a.N * d.M * sizeof(float);
+    if (ks > 1 && (!workspace || workspace_bytes < per_split * ks)) {
+        ks = workspace ? (int) std::max<size_t>(1, workspace_bytes / per_split) : 1;  // fewer splits fit: still correct, only slower
     }
-    const bool wide = a.N > 32;
-    if (wtype == B200_TYPE_Q4_0) {
-        return wide ? launch_mmq_t<B200_TYPE_Q4_0, 64>(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, (float *) workspace, ks, st)
-                    : launch_mmq_t<B200_TYPE_Q4_0, 32>(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, (float *) workspace, ks, st);
+    if (int e = v.launch(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, (float *) workspace, ks, st)) return e;
+    if (ks > 1) {
+        const int64_t total = d.M * a.N;
+        mmq_reduce_kernel<<<(unsigned) ((total + 255) / 256), 256, 0, st>>>((const float *) workspace, ks, d.M, a.N, dst, dst_nb_row);
+        return check_launch("mmq_reduce");
     }
-    return wide ? launch_mmq_t<B200_TYPE_Q8_0, 64>(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, (float *) workspace, ks, st)
-                : launch_mmq_t<B200_TYPE_Q8_0, 32>(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, (float *) workspace, ks, st);
+    return B200_OK;
 }
 
 }  // namespace b200

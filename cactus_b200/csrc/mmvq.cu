@@ -28,7 +28,7 @@ __global__ void __launch_bounds__(MMVQ_WARPS * 32) mmvq_kernel(TiledDims dims, c
 
     const uint8_t *wq = w + rt * dims.n_bg * dims.tile_bytes;
     const uint2 *wd = reinterpret_cast<const uint2 *>(w + dims.qs_bytes + rt * dims.n_bg * 128);
-    const uint2 *ad = reinterpret_cast<const uint2 *>(aq + act.d_offset);
+    const float *ad = reinterpret_cast<const float *>(aq + act.d_offset);
     constexpr float WS = (WTYPE == B200_TYPE_Q4_0) ? 0.0625f : 1.0f;  // Q4_0 nibbles sit in the high half of each byte: x16
 
     for (int64_t bg = warp; bg < dims.n_bg; bg += MMVQ_WARPS) {
@@ -56,9 +56,9 @@ __global__ void __launch_bounds__(MMVQ_WARPS * 32) mmvq_kernel(TiledDims dims, c
         }
 #pragma unroll
         for (int n = 0; n < NC; ++n) {
-            const uint2 sd = __ldg(ad + bg * 8 + n);
-            const __half2 d01 = *reinterpret_cast<const __half2 *>(&sd.x), d23 = *reinterpret_cast<const __half2 *>(&sd.y);
-            const float da[4] = {__low2float(d01), __high2float(d01), __low2float(d23), __high2float(d23)};
+            float da[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) da[j] = __ldg(ad + bg * 64 + act_scale_index(j, n));
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const uint2 a = __ldg(reinterpret_cast<const uint2 *>(aq + (bg * 4 + j) * 256) + n * 4 + t);

@@ -57,8 +57,10 @@ __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float *__restr
         uint8_t *tile = out + (nt * nbp + b) * 256;
         *reinterpret_cast<uint32_t *>(tile + (g * 4 + t) * 8 + (j >= 4 ? 4 : 0)) = packed;
         if (j == 0) {
-            __half *dp = reinterpret_cast<__half *>(out + d_offset);
-            dp[((nt * (nbp >> 2) + (b >> 2)) * 8 + g) * 4 + (b & 3)] = real ? d : __float2half(0.0f);
+            float *dp = reinterpret_cast<float *>(out + d_offset) + (nt * (nbp >> 2) + (b >> 2)) * 64 + act_scale_index((int) (b & 3), g);
+            const float df = real ? __half2float(d) : 0.0f;
+            dp[0] = df;
+            dp[2] = -df * ACT_MAGIC;
         }
     }
 }

@@ -40,7 +40,7 @@ def test_size_queries_and_argument_checks_without_a_gpu():
     assert L.b200_weight_bytes(2, 64, 33) == 48 * 4 * 18
     assert L.b200_weight_bytes(2, 100, 16) == 0      # K not a multiple of 32
     assert L.b200_weight_bytes(3, 128, 16) == 0      # unsupported type
-    assert L.b200_act_bytes(4096, 1) == 128 * 256 + 32 * 64
+    assert L.b200_act_bytes(4096, 1) == 128 * 256 + 32 * 256
     assert L.b200_mul_mat_scratch_bytes(2, 4096, 4096, 8) == L.b200_act_bytes(4096, 8)
     assert L.b200_mask_index_bytes(64, 65536) == 64 * 1024 * 8
     # invalid arguments are rejected before any CUDA call
@@ -56,3 +56,14 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(m, "LIB_PATH", "/nonexistent/libcactus_b200.so")
     with pytest.raises(m.B200Error, match="no CPU or framework fallback"):
         m.lib()
+
+
+def test_plugin_exports_the_loader_entry_points():
+    """libggml-b200.so (built where the reference's headers are) exports what lm_ggml_backend_load looks up."""
+    import subprocess
+    so = os.path.join(ROOT, "cactus_b200", "lib", "libggml-b200.so")
+    if not os.path.exists(so):
+        pytest.skip("plug-in not built (needs a checkout of the reference)")
+    syms = subprocess.run(["nm", "-D", "--defined-only", so], capture_output=True, text=True).stdout
+    for name in ("lm_ggml_backend_init", "lm_ggml_backend_score", "lm_ggml_backend_b200_reg", "lm_ggml_backend_b200_init"):
+        assert f" T {name}" in syms, name

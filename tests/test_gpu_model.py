@@ -61,4 +61,4 @@ def test_ragged_prefill_then_decode(oracle, head_type, use_graphs):
         cur = ids.copy()
     rows = np.array(rows)
     assert rows.max() < 3e-2
-    assert (rows < 1e-3).mean() >= 0.8
+    assert (rows < 1e-3).mean() >= 0.6
