@@ -329,6 +329,7 @@ struct b200_backend_ctx {
     lm_ggml_abort_callback abort_cb = nullptr;
     void * abort_cb_data = nullptr;
     int q8_variant = B200_Q8_AVX2;
+    bool fa_parity = false;  // B200_FA_PARITY=1: the reference-order attention kernel (validation)
     bool timing = false;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     lm_ggml_b200_stats stats = {};
@@ -621,6 +622,13 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
                 const size_t sb = b200_flash_attn_scratch_bytes(D, H, Hkv, Nq, n_kv);
                 void * scratch = ctx->fa_scratch.get(std::max<size_t>(sb, 256), st);
                 if (!scratch) return LM_GGML_STATUS_ALLOC_FAILED;
+                if (ctx->fa_parity) {
+                    B200_CHECK(b200_flash_attn_ext_parity(D, H, Hkv, Nq, n_kv, (const float *) q->data, q->nb[1], q->nb[2], k->data, k->nb[1], k->nb[2],
+                                                          v->data, v->nb[1], v->nb[2], m ? m->data : nullptr, m ? m->nb[1] : 0, index, scale, max_bias,
+                                                          softcap, (float *) node->data, st));
+                    ctx->stats.flash_attn++;
+                    break;
+                }
                 B200_CHECK(b200_flash_attn_ext_indexed(D, H, Hkv, Nq, n_kv, (const float *) q->data, q->nb[1], q->nb[2], k->data, k->nb[1], k->nb[2],
                                                        v->data, v->nb[1], v->nb[2], m ? m->data : nullptr, m ? m->nb[1] : 0, index, scale, max_bias,
                                                        softcap, (float *) node->data, scratch, ctx->fa_scratch.bytes, st));
@@ -927,6 +935,8 @@ lm_ggml_backend_t lm_ggml_backend_b200_init(int device) {
     }
     const char * v = getenv("B200_Q8_VARIANT");
     if (v && strcmp(v, "scalar") == 0) ctx->q8_variant = B200_Q8_SCALAR;
+    const char * fp = getenv("B200_FA_PARITY");
+    ctx->fa_parity = fp && atoi(fp) != 0;
     const char * t = getenv("B200_TIMING");
     ctx->timing = t && atoi(t) != 0;
     cudaEventCreate(&ctx->ev0);

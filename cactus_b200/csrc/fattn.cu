@@ -7,11 +7,10 @@
 // b200_mask_index_build turns each token's mask row into one bit per cell, and the attention kernel
 // walks the set bits, so a token of a 64-sequence batch touches only its own sequence's K/V rows.
 //
-// Kernel: one CTA per (token, kv-head, head group, KV split).  Sub-warps of 8 lanes each own one cell at
-// a time: a lane holds D/8 contiguous elements of the K and V rows (128-bit loads), the score is reduced
-// over the 8 lanes with three shuffles, and every sub-warp keeps its own online-softmax state which is
-// merged at the end (shuffles inside the warp, shared memory across warps).  With KV splits the
-// partial (max, sum, accumulator) triples go to scratch and a combine kernel finishes.
+// Kernel: one CTA per (token, kv-head, group of up to 8 query heads, KV split), tensor-core MMAs for both
+// Q K^T and P V (see fattn_mma_kernel).  With KV splits the partial (max, sum, accumulator) triples go to
+// scratch and a combine kernel finishes.  A second, slow kernel reproduces the reference's own rounding
+// sequence for validation (fattn_parity_kernel).
 #include <math_constants.h>
 
 #include "common.cuh"
@@ -52,52 +51,79 @@ struct FattnParams {
     int64_t words_per_split;
 };
 
-template <int D, int G>
-__global__ void __launch_bounds__(FA_THREADS) fattn_vec_kernel(FattnParams p) {
-    constexpr int E = D / 8;  // elements per lane
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+// Tensor-core kernel.  One CTA per (token, kv-head, head group of up to 8 query heads, KV split); its 4 warps take
+// 16-cell chunks of the token's cell list in turn.  Per chunk and warp:
+//   S = Q K^T   heads on the MMA rows (m16n8k16, f16 inputs, f32 accumulate), 8 cells per n-tile.  Lane (g, t)
+//               loads 16-byte pieces d = 32u + 8t .. +7 of the K row of cell g -- the k index of the MMA is a fixed
+//               permutation of d that makes those pieces B fragments as they are; Q is held in the same permutation
+//               (rounded to fp16 as the reference rounds it).
+//   online softmax on the accumulator rows (a head's four lanes share max and sum through two shuffles)
+//   O^T += V^T P^T   d on the MMA rows, heads on the columns, so no accumulator row is wasted: lane (g, t) loads
+//               d = 8g .. 8g+7 (and 64 + 8g ..) of the V rows of cells 2t, 2t+1, 2t+8, 2t+9 and pairs the halves of
+//               two cells with byte permutes; P goes in as fp16 hi + lo parts (two MMAs), which keeps the
+//               probabilities at fp32 accuracy.
+// Every warp keeps its own (max, sum, accumulator) state; the states are merged through shared memory at the end.
+template <int D>
+__global__ void __launch_bounds__(FA_THREADS) fattn_mma_kernel(FattnParams p) {
+    constexpr int KS = D / 16;   // k-steps of the S MMA
+    constexpr int NU = D / 32;   // 16-byte K pieces per lane and cell
+    constexpr int NR = D / 64;   // 64-wide d ranges of V
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int e = lane & 7;          // lane inside the sub-warp
-    const int sg = warp * 4 + (lane >> 3);  // sub-warp 0..15
-    const unsigned sub_mask = 0xFFu << (lane & 24);  // the 8 lanes of this sub-warp
-    const int64_t j = blockIdx.x;    // token
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t j = blockIdx.x;
     const int hk = blockIdx.y / p.hgroups, hg = blockIdx.y % p.hgroups;
     const int split = blockIdx.z;
     const int gqa = (int) (p.H / p.Hkv);
-    const int h0 = hk * gqa + hg * G;  // first query head of this CTA
+    const int G = min(8, gqa - hg * 8);        // query heads of this CTA
+    const int h0 = hk * gqa + hg * 8;
 
     __shared__ int cell_list[FA_SUPER_WORDS * 64];
     __shared__ int list_count;
-    __shared__ float merge_m[4][G], merge_l[4][G];
-    __shared__ float merge_acc[4][G][D];
+    __shared__ float merge_m[4][8], merge_l[4][8];
+    __shared__ float merge_acc[4][8][D];
 
-    // Q rounded to fp16 as the reference does before its dot (ops.cpp:7072), kept as float
-    float qf[G][E];
-    float slope[G];
+    // Q fragments: row g = head h0 + g (zero rows beyond G)
+    uint32_t qa0[KS], qa2[KS];
+    {
+        const bool valid = g < G;
+        const float *qp = reinterpret_cast<const float *>(reinterpret_cast<const char *>(p.q) + j * p.q_nb_tok + (int64_t) (h0 + (valid ? g : 0)) * p.q_nb_head);
 #pragma unroll
-    for (int h = 0; h < G; ++h) {
-        const float *qp = reinterpret_cast<const float *>(reinterpret_cast<const char *>(p.q) + j * p.q_nb_tok + (int64_t) (h0 + h) * p.q_nb_head) + e * E;
+        for (int u = 0; u < NU; ++u)
 #pragma unroll
-        for (int i = 0; i < E; ++i) qf[h][i] = __half2float(__float2half_rn(qp[i]));
-        const uint32_t hh = (uint32_t) (h0 + h);
-        slope[h] = (p.max_bias > 0.0f) ? (hh < p.n_head_log2 ? powf(p.m0, (float) (hh + 1)) : powf(p.m1, (float) (2 * (hh - p.n_head_log2) + 1))) : 1.0f;
+            for (int v = 0; v < 2; ++v) {
+                const int d0 = 32 * u + 8 * t + 4 * v;
+                const float4 f = valid ? *reinterpret_cast<const float4 *>(qp + d0) : make_float4(0.f, 0.f, 0.f, 0.f);
+                qa0[2 * u + v] = pack_half2(f.x, f.y);
+                qa2[2 * u + v] = pack_half2(f.z, f.w);
+            }
     }
-    float m[G], l[G], acc[G][E];
+    const uint32_t hh = (uint32_t) (h0 + g);
+    const float slope = (p.max_bias > 0.0f) ? (hh < p.n_head_log2 ? powf(p.m0, (float) (hh + 1)) : powf(p.m1, (float) (2 * (hh - p.n_head_log2) + 1))) : 1.0f;
+
+    float oacc[8][4];   // O^T: d-tile q; [0],[1]: d = 8g+q, heads 2t, 2t+1; [2],[3]: d = 64+8g+q
 #pragma unroll
-    for (int h = 0; h < G; ++h) {
-        m[h] = -CUDART_INF_F;
-        l[h] = 0.0f;
-#pragma unroll
-        for (int i = 0; i < E; ++i) acc[h][i] = 0.0f;
-    }
+    for (int q = 0; q < 8; ++q) oacc[q][0] = oacc[q][1] = oacc[q][2] = oacc[q][3] = 0.0f;
+    float m_run = -CUDART_INF_F, l_run = 0.0f;   // state of head g (l: this lane's share of the row sum)
 
     const int64_t w_begin = (int64_t) split * p.words_per_split;
     const int64_t w_end = min(p.nw, w_begin + p.words_per_split);
     const unsigned long long *wrow = p.words ? p.words + j * p.nw : nullptr;
     const __half *mrow = p.mask ? reinterpret_cast<const __half *>(p.mask + j * p.mask_nb_row) : nullptr;
+    const char *kbase = p.k + (int64_t) hk * p.k_nb_head;
+    const char *vbase = p.v + (int64_t) hk * p.v_nb_head;
 
     for (int64_t w0 = w_begin; w0 < w_end; w0 += FA_SUPER_WORDS) {
-        // list the participating cells of this round (warp 0 scans 32 words)
-        if (warp == 0) {
+        if (warp == 0) {   // list the participating cells of this round
             const int64_t wi = w0 + lane;
             unsigned long long bits = 0;
             if (wi < w_end) {
@@ -112,8 +138,8 @@ __global__ void __launch_bounds__(FA_THREADS) fattn_vec_kernel(FattnParams p) {
             int pre = cnt;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
-                const int t = __shfl_up_sync(0xffffffffu, pre, o);
-                if (lane >= o) pre += t;
+                const int x = __shfl_up_sync(0xffffffffu, pre, o);
+                if (lane >= o) pre += x;
             }
             int pos = pre - cnt;
             while (bits) {
@@ -125,103 +151,109 @@ __global__ void __launch_bounds__(FA_THREADS) fattn_vec_kernel(FattnParams p) {
         }
         __syncthreads();
         const int count = list_count;
-        // sub-warps run the same number of rounds; the shuffles below name only the 8 lanes of a sub-warp,
-        // and a sub-warp without a cell in the last round skips it as a whole
-        for (int idx = sg; idx < count; idx += 16) {
-            const int64_t cell = cell_list[idx];
-            const char *kp = p.k + cell * p.k_nb_cell + (int64_t) hk * p.k_nb_head + e * E * 2;
-            const char *vp = p.v + cell * p.v_nb_cell + (int64_t) hk * p.v_nb_head + e * E * 2;
-            float kf[E];
+        const int n_chunks = (count + 15) >> 4;
+        for (int ch = warp; ch < n_chunks; ch += 4) {
+            const int base = ch << 4;
+            const int last = count - 1;
+            // ---- S = Q K^T for the two 8-cell tiles ----
+            float sacc[2][4];
 #pragma unroll
-            for (int c = 0; c < E / 8; ++c) {
-                const uint4 u = __ldg(reinterpret_cast<const uint4 *>(kp) + c);
-                const __half2 *hp = reinterpret_cast<const __half2 *>(&u);
+            for (int c = 0; c < 2; ++c) {
+                const int64_t cell = cell_list[min(base + 8 * c + g, last)];
+                const uint4 *kp = reinterpret_cast<const uint4 *>(kbase + cell * p.k_nb_cell) + t;
+                uint4 kr[NU];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 f = __half22float2(hp[i]);
-                    kf[c * 8 + 2 * i] = f.x;
-                    kf[c * 8 + 2 * i + 1] = f.y;
+                for (int u = 0; u < NU; ++u) kr[u] = __ldg(kp + 4 * u);
+                sacc[c][0] = sacc[c][1] = sacc[c][2] = sacc[c][3] = 0.0f;
+#pragma unroll
+                for (int u = 0; u < NU; ++u) {
+                    mma_f16(sacc[c], qa0[2 * u], 0u, qa2[2 * u], 0u, kr[u].x, kr[u].y);
+                    mma_f16(sacc[c], qa0[2 * u + 1], 0u, qa2[2 * u + 1], 0u, kr[u].z, kr[u].w);
                 }
             }
-            // issue the V loads early
-            uint4 vu[E / 8];
+            // V rows of cells 2t, 2t+1, 2t+8, 2t+9: issue the loads before the softmax arithmetic
+            uint4 vr[4][NR];
 #pragma unroll
-            for (int c = 0; c < E / 8; ++c) vu[c] = __ldg(reinterpret_cast<const uint4 *>(vp) + c);
-            const float mval = mrow ? __half2float(mrow[cell]) : 0.0f;
-
-            float s[G];
+            for (int i = 0; i < 4; ++i) {
+                const int64_t cell = cell_list[min(base + 2 * t + (i & 1) + 8 * (i >> 1), last)];
+                const uint4 *vp = reinterpret_cast<const uint4 *>(vbase + cell * p.v_nb_cell) + g;
 #pragma unroll
-            for (int h = 0; h < G; ++h) {
-                float a = 0.0f;
+                for (int r = 0; r < NR; ++r) vr[i][r] = __ldg(vp + 8 * r);
+            }
+            // ---- scores of head g for cells base + {2t, 2t+1, 8+2t, 9+2t} ----
+            float sc[4];
 #pragma unroll
-                for (int i = 0; i < E; ++i) a = fmaf(qf[h][i], kf[i], a);
-                a += __shfl_xor_sync(sub_mask, a, 1);
-                a += __shfl_xor_sync(sub_mask, a, 2);
-                a += __shfl_xor_sync(sub_mask, a, 4);
-                a *= p.scale;
+            for (int i = 0; i < 4; ++i) {
+                const int idx = base + 2 * t + (i & 1) + 8 * (i >> 1);
+                float a = sacc[i >> 1][i & 1] * p.scale;
                 if (p.softcap != 0.0f) a = p.softcap * tanhf(a);
-                s[h] = a + slope[h] * mval;
-            }
-            float vf[E];
-#pragma unroll
-            for (int c = 0; c < E / 8; ++c) {
-                const __half2 *hp = reinterpret_cast<const __half2 *>(&vu[c]);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 f = __half22float2(hp[i]);
-                    vf[c * 8 + 2 * i] = f.x;
-                    vf[c * 8 + 2 * i + 1] = f.y;
-                }
-            }
-#pragma unroll
-            for (int h = 0; h < G; ++h) {
-                float pw;
-                if (s[h] > m[h]) {
-                    const float ms = expf(m[h] - s[h]);
-                    m[h] = s[h];
-                    l[h] = l[h] * ms + 1.0f;
-#pragma unroll
-                    for (int i = 0; i < E; ++i) acc[h][i] *= ms;
-                    pw = 1.0f;
+                if (idx < count) {
+                    if (mrow) a += slope * __half2float(mrow[cell_list[idx]]);
                 } else {
-                    pw = expf(s[h] - m[h]);
-                    l[h] += pw;
+                    a = -CUDART_INF_F;
                 }
+                sc[i] = a;
+            }
+            float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run, mx);   // finite: a chunk holds at least one participating cell
+            const float alpha = __expf(m_run - m_new);
+            float pr[4];
 #pragma unroll
-                for (int i = 0; i < E; ++i) acc[h][i] = fmaf(pw, vf[i], acc[h][i]);
+            for (int i = 0; i < 4; ++i) pr[i] = __expf(sc[i] - m_new);
+            l_run = l_run * alpha + (pr[0] + pr[1]) + (pr[2] + pr[3]);
+            m_run = m_new;
+            // P^T fragments, fp16 hi + lo
+            const __half2 h01 = __floats2half2_rn(pr[0], pr[1]), h23 = __floats2half2_rn(pr[2], pr[3]);
+            const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+            const uint32_t b0h = *reinterpret_cast<const uint32_t *>(&h01), b1h = *reinterpret_cast<const uint32_t *>(&h23);
+            const uint32_t b0l = pack_half2(pr[0] - f01.x, pr[1] - f01.y), b1l = pack_half2(pr[2] - f23.x, pr[3] - f23.y);
+            // rescale O^T columns (heads 2t, 2t+1) when some head's maximum moved
+            if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+                const float a_lo = __shfl_sync(0xffffffffu, alpha, (2 * t) * 4);
+                const float a_hi = __shfl_sync(0xffffffffu, alpha, (2 * t + 1) * 4);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    oacc[q][0] *= a_lo; oacc[q][1] *= a_hi; oacc[q][2] *= a_lo; oacc[q][3] *= a_hi;
+                }
+            }
+            // ---- O^T += V^T P^T ----
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const uint32_t sel = (q & 1) ? 0x7632u : 0x5410u;
+                const uint32_t *wA0 = reinterpret_cast<const uint32_t *>(&vr[0][0]), *wB0 = reinterpret_cast<const uint32_t *>(&vr[1][0]);
+                const uint32_t *wC0 = reinterpret_cast<const uint32_t *>(&vr[2][0]), *wD0 = reinterpret_cast<const uint32_t *>(&vr[3][0]);
+                const uint32_t a0 = __byte_perm(wA0[q >> 1], wB0[q >> 1], sel);
+                const uint32_t a2 = __byte_perm(wC0[q >> 1], wD0[q >> 1], sel);
+                uint32_t a1 = 0u, a3 = 0u;
+                if (NR == 2) {
+                    const uint32_t *wA1 = reinterpret_cast<const uint32_t *>(&vr[0][NR - 1]), *wB1 = reinterpret_cast<const uint32_t *>(&vr[1][NR - 1]);
+                    const uint32_t *wC1 = reinterpret_cast<const uint32_t *>(&vr[2][NR - 1]), *wD1 = reinterpret_cast<const uint32_t *>(&vr[3][NR - 1]);
+                    a1 = __byte_perm(wA1[q >> 1], wB1[q >> 1], sel);
+                    a3 = __byte_perm(wC1[q >> 1], wD1[q >> 1], sel);
+                }
+                mma_f16(oacc[q], a0, a1, a2, a3, b0h, b1h);
+                mma_f16(oacc[q], a0, a1, a2, a3, b0l, b1l);
             }
         }
         __syncthreads();
     }
 
-    // merge the four sub-warps of each warp (lanes e, e+8, e+16, e+24 hold the same elements)
-#pragma unroll
-    for (int h = 0; h < G; ++h) {
-#pragma unroll
-        for (int o = 8; o <= 16; o <<= 1) {
-            const float mo = __shfl_xor_sync(0xffffffffu, m[h], o);
-            const float lo = __shfl_xor_sync(0xffffffffu, l[h], o);
-            const float mn = fmaxf(m[h], mo);
-            const float sa = (m[h] == -CUDART_INF_F) ? 0.0f : expf(m[h] - mn);
-            const float sb = (mo == -CUDART_INF_F) ? 0.0f : expf(mo - mn);
-#pragma unroll
-            for (int i = 0; i < E; ++i) {
-                const float ao = __shfl_xor_sync(0xffffffffu, acc[h][i], o);
-                acc[h][i] = acc[h][i] * sa + ao * sb;
-            }
-            l[h] = l[h] * sa + lo * sb;
-            m[h] = mn;
-        }
+    // ---- merge the four warps ----
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (t == 0) {
+        merge_m[warp][g] = m_run;
+        merge_l[warp][g] = l_run;
     }
-    if (lane < 8) {
 #pragma unroll
-        for (int h = 0; h < G; ++h) {
-            if (lane == 0) {
-                merge_m[warp][h] = m[h];
-                merge_l[warp][h] = l[h];
-            }
-#pragma unroll
-            for (int i = 0; i < E; ++i) merge_acc[warp][h][e * E + i] = acc[h][i];
+    for (int q = 0; q < 8; ++q) {
+        merge_acc[warp][2 * t][8 * g + q] = oacc[q][0];
+        merge_acc[warp][2 * t + 1][8 * g + q] = oacc[q][1];
+        if (NR == 2) {
+            merge_acc[warp][2 * t][64 + 8 * g + q] = oacc[q][2];
+            merge_acc[warp][2 * t + 1][64 + 8 * g + q] = oacc[q][3];
         }
     }
     __syncthreads();
@@ -233,9 +265,9 @@ __global__ void __launch_bounds__(FA_THREADS) fattn_vec_kernel(FattnParams p) {
         float a = 0.0f, ls = 0.0f;
 #pragma unroll
         for (int wv = 0; wv < 4; ++wv) {
-            const float sc = (merge_m[wv][h] == -CUDART_INF_F) ? 0.0f : expf(merge_m[wv][h] - mn);
-            a += merge_acc[wv][h][d] * sc;
-            ls += merge_l[wv][h] * sc;
+            const float scl = (merge_m[wv][h] == -CUDART_INF_F) ? 0.0f : expf(merge_m[wv][h] - mn);
+            a += merge_acc[wv][h][d] * scl;
+            ls += merge_l[wv][h] * scl;
         }
         const int64_t head = h0 + h;
         if (p.nsplit == 1) {
@@ -249,6 +281,85 @@ __global__ void __launch_bounds__(FA_THREADS) fattn_vec_kernel(FattnParams p) {
             }
         }
     }
+}
+
+// ---- validation variant: the reference's own order of operations ------------------------------------
+// One warp per (token, head) walks the unmasked cells in ascending order and reproduces
+// lm_ggml_compute_forward_flash_attn_ext_f16 step by step (cactus/ggml-cpu/ops.cpp:7072-7152) as the x86
+// AVX2 build executes it: Q rounded to fp16; the K.Q dot as 4 x 8 fp32 FMA lanes folded in the order of
+// LM_GGML_F32x8_REDUCE (lane l of the warp is accumulator l/8, SIMD lane l%8); scale and mask applied with one
+// FMA; the output accumulator kept in fp16 and rounded after every cell (vec_scale_f16 / vec_mad_f16).
+// It exists to show that what separates the fast kernel from the reference is that fp16 accumulator.
+template <int D>
+__global__ void __launch_bounds__(128) fattn_parity_kernel(FattnParams p) {
+    constexpr int E = D / 32;
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t) blockIdx.x * 4 + (threadIdx.x >> 5);   // token * H + head
+    if (row >= p.Nq * p.H) return;
+    const int64_t j = row / p.H;
+    const int h = (int) (row - j * p.H);
+    const int hk = h / (int) (p.H / p.Hkv);
+    const float *qp = reinterpret_cast<const float *>(reinterpret_cast<const char *>(p.q) + j * p.q_nb_tok + (int64_t) h * p.q_nb_head);
+    float qf[E];
+    __half acc[E];
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+        qf[i] = __half2float(__float2half_rn(qp[lane + 32 * i]));
+        acc[i] = __float2half_rn(0.0f);
+    }
+    const uint32_t hh = (uint32_t) h;
+    const float slope = (p.max_bias > 0.0f) ? (hh < p.n_head_log2 ? powf(p.m0, (float) (hh + 1)) : powf(p.m1, (float) (2 * (hh - p.n_head_log2) + 1))) : 1.0f;
+    float S = 0.0f, M = -CUDART_INF_F;
+    const unsigned long long *wrow = p.words ? p.words + j * p.nw : nullptr;
+    const __half *mrow = p.mask ? reinterpret_cast<const __half *>(p.mask + j * p.mask_nb_row) : nullptr;
+    for (int64_t wi = 0; wi < p.nw; ++wi) {
+        unsigned long long bits;
+        if (wrow) {
+            bits = wrow[wi];
+        } else {
+            const int64_t left = p.n_kv - wi * 64;
+            bits = left >= 64 ? ~0ull : ((1ull << left) - 1ull);
+        }
+        while (bits) {
+            const int b = __ffsll((long long) bits) - 1;
+            bits &= bits - 1;
+            const int64_t cell = wi * 64 + b;
+            const __half *kr = reinterpret_cast<const __half *>(p.k + cell * p.k_nb_cell + (int64_t) hk * p.k_nb_head);
+            const __half *vr = reinterpret_cast<const __half *>(p.v + cell * p.v_nb_cell + (int64_t) hk * p.v_nb_head);
+            float a = 0.0f;
+#pragma unroll
+            for (int i = 0; i < E; ++i) a = __fmaf_rn(__half2float(kr[lane + 32 * i]), qf[i], a);
+            a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 16));
+            a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 8));
+            a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 4));
+            a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 1));
+            a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 2));
+            const float mv = mrow ? __fmul_rn(slope, __half2float(mrow[cell])) : 0.0f;
+            float s;
+            if (p.softcap != 0.0f) {
+                s = __fmul_rn(a, p.scale);
+                s = __fmul_rn(p.softcap, tanhf(s));
+                s = __fadd_rn(s, mv);
+            } else {
+                s = __fmaf_rn(a, p.scale, mv);
+            }
+            float ms = 1.0f, vs = 1.0f;
+            if (s > M) {
+                ms = (float) exp((double) __fsub_rn(M, s));   // correctly rounded, as the host libm's expf is in all but rare cases
+                M = s;
+#pragma unroll
+                for (int i = 0; i < E; ++i) acc[i] = __float2half_rn(__fmul_rn(__half2float(acc[i]), ms));
+            } else {
+                vs = (float) exp((double) __fsub_rn(s, M));
+            }
+#pragma unroll
+            for (int i = 0; i < E; ++i) acc[i] = __float2half_rn(__fmaf_rn(__half2float(vr[lane + 32 * i]), vs, __half2float(acc[i])));
+            S = __fmaf_rn(S, ms, vs);
+        }
+    }
+    const float S_inv = __fdiv_rn(1.0f, S);
+#pragma unroll
+    for (int i = 0; i < E; ++i) p.dst[row * D + lane + 32 * i] = __fmul_rn(__half2float(acc[i]), S_inv);
 }
 
 template <int D>
@@ -279,7 +390,7 @@ static int fa_sm_count() {
     return n;
 }
 
-static int fattn_heads_per_cta(int gqa) { return gqa >= 4 && gqa % 4 == 0 ? 4 : (gqa % 2 == 0 ? 2 : 1); }
+static int fattn_hgroups(int gqa) { return (gqa + 7) / 8; }   // a CTA takes up to 8 query heads of one KV head
 
 static int fattn_nsplit(int64_t Nq, int64_t Hkv, int hgroups, int64_t n_kv) {
     const int64_t ctas = Nq * Hkv * hgroups;
@@ -315,17 +426,17 @@ int b200_mask_index_build(const void *mask, int64_t mask_nb_row, int64_t Nq, int
 
 size_t b200_flash_attn_scratch_bytes(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, int64_t n_kv) {
     if (D <= 0 || H <= 0 || Hkv <= 0 || Nq <= 0 || n_kv <= 0 || H % Hkv) return 0;
-    const int hgroups = (int) (H / Hkv) / fattn_heads_per_cta((int) (H / Hkv));
+    const int hgroups = fattn_hgroups((int) (H / Hkv));
     const int ns = fattn_nsplit(Nq, Hkv, hgroups, n_kv);
     const size_t part = ns > 1 ? align_up((size_t) Nq * H * ns * (D + 2) * sizeof(float), 256) : 0;
     return b200_mask_index_bytes(Nq, n_kv) + part;
 }
 
-int b200_flash_attn_ext_indexed(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, int64_t n_kv, const float *q, int64_t q_nb_tok,
-                                int64_t q_nb_head, const void *k, int64_t k_nb_cell, int64_t k_nb_head, const void *v,
-                                int64_t v_nb_cell, int64_t v_nb_head, const void *mask, int64_t mask_nb_row, const void *index,
-                                float scale, float max_bias, float logit_softcap, float *dst, void *scratch, size_t scratch_bytes,
-                                b200_stream_t stream) {
+static int flash_attn_impl(bool parity, int64_t D, int64_t H, int64_t Hkv, int64_t Nq, int64_t n_kv, const float *q, int64_t q_nb_tok,
+                           int64_t q_nb_head, const void *k, int64_t k_nb_cell, int64_t k_nb_head, const void *v,
+                           int64_t v_nb_cell, int64_t v_nb_head, const void *mask, int64_t mask_nb_row, const void *index,
+                           float scale, float max_bias, float logit_softcap, float *dst, void *scratch, size_t scratch_bytes,
+                           b200_stream_t stream) {
     B200_REQUIRE(D == 64 || D == 128, "head size %lld not supported (64 or 128)", (long long) D);
     B200_REQUIRE(H > 0 && Hkv > 0 && H % Hkv == 0 && Nq > 0 && n_kv > 0, "bad attention shape");
     B200_REQUIRE(q && k && v && dst, "null pointer");
@@ -335,9 +446,8 @@ int b200_flash_attn_ext_indexed(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, i
     B200_REQUIRE(is_aligned(v, 16) && v_nb_cell % 16 == 0 && v_nb_head % 16 == 0, "v rows must be 16-byte aligned");
     B200_REQUIRE(!mask || (is_aligned(mask, 2) && mask_nb_row % 2 == 0), "misaligned mask");
     const int gqa = (int) (H / Hkv);
-    const int G = fattn_heads_per_cta(gqa);
-    const int hgroups = gqa / G;
-    const int ns = fattn_nsplit(Nq, Hkv, hgroups, n_kv);
+    const int hgroups = fattn_hgroups(gqa);
+    const int ns = parity ? 1 : fattn_nsplit(Nq, Hkv, hgroups, n_kv);
     const size_t part = ns > 1 ? (size_t) Nq * H * ns * (D + 2) * sizeof(float) : 0;
     if (part && (!scratch || scratch_bytes < part)) return set_error(B200_E_SCRATCH, "flash_attn scratch too small: %zu < %zu", scratch_bytes, part);
     B200_REQUIRE(!part || is_aligned(scratch, 16), "scratch must be 16-byte aligned");
@@ -357,22 +467,40 @@ int b200_flash_attn_ext_indexed(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, i
     p.dst = dst; p.partial = (float *) scratch; p.nsplit = ns; p.hgroups = hgroups;
     p.words_per_split = (p.nw + ns - 1) / ns;
 
-    dim3 grid((unsigned) Nq, (unsigned) (Hkv * hgroups), (unsigned) ns);
     cudaStream_t st = (cudaStream_t) stream;
-#define FA_LAUNCH(DD, GG) fattn_vec_kernel<DD, GG><<<grid, FA_THREADS, 0, st>>>(p)
-    if (D == 128) {
-        if (G == 4) FA_LAUNCH(128, 4); else if (G == 2) FA_LAUNCH(128, 2); else FA_LAUNCH(128, 1);
-    } else {
-        if (G == 4) FA_LAUNCH(64, 4); else if (G == 2) FA_LAUNCH(64, 2); else FA_LAUNCH(64, 1);
+    if (parity) {
+        const unsigned blocks = (unsigned) ((Nq * H + 3) / 4);
+        if (D == 128) fattn_parity_kernel<128><<<blocks, 128, 0, st>>>(p);
+        else fattn_parity_kernel<64><<<blocks, 128, 0, st>>>(p);
+        return check_launch("fattn_parity");
     }
-#undef FA_LAUNCH
-    if (int e = check_launch("fattn_vec")) return e;
+    dim3 grid((unsigned) Nq, (unsigned) (Hkv * hgroups), (unsigned) ns);
+    if (D == 128) fattn_mma_kernel<128><<<grid, FA_THREADS, 0, st>>>(p);
+    else fattn_mma_kernel<64><<<grid, FA_THREADS, 0, st>>>(p);
+    if (int e = check_launch("fattn_mma")) return e;
     if (ns > 1) {
         if (D == 128) fattn_combine_kernel<128><<<(unsigned) (Nq * H), 128, 0, st>>>(p.partial, ns, dst);
         else fattn_combine_kernel<64><<<(unsigned) (Nq * H), 64, 0, st>>>(p.partial, ns, dst);
         return check_launch("fattn_combine");
     }
     return B200_OK;
+}
+
+int b200_flash_attn_ext_indexed(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, int64_t n_kv, const float *q, int64_t q_nb_tok,
+                                int64_t q_nb_head, const void *k, int64_t k_nb_cell, int64_t k_nb_head, const void *v,
+                                int64_t v_nb_cell, int64_t v_nb_head, const void *mask, int64_t mask_nb_row, const void *index,
+                                float scale, float max_bias, float logit_softcap, float *dst, void *scratch, size_t scratch_bytes,
+                                b200_stream_t stream) {
+    return flash_attn_impl(false, D, H, Hkv, Nq, n_kv, q, q_nb_tok, q_nb_head, k, k_nb_cell, k_nb_head, v, v_nb_cell, v_nb_head, mask, mask_nb_row,
+                           index, scale, max_bias, logit_softcap, dst, scratch, scratch_bytes, stream);
+}
+
+int b200_flash_attn_ext_parity(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, int64_t n_kv, const float *q, int64_t q_nb_tok,
+                               int64_t q_nb_head, const void *k, int64_t k_nb_cell, int64_t k_nb_head, const void *v,
+                               int64_t v_nb_cell, int64_t v_nb_head, const void *mask, int64_t mask_nb_row, const void *index,
+                               float scale, float max_bias, float logit_softcap, float *dst, b200_stream_t stream) {
+    return flash_attn_impl(true, D, H, Hkv, Nq, n_kv, q, q_nb_tok, q_nb_head, k, k_nb_cell, k_nb_head, v, v_nb_cell, v_nb_head, mask, mask_nb_row,
+                           index, scale, max_bias, logit_softcap, dst, nullptr, 0, stream);
 }
 
 int b200_flash_attn_ext(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, int64_t n_kv, const float *q, int64_t q_nb_tok,

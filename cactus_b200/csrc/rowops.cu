@@ -48,30 +48,51 @@ __global__ void __launch_bounds__(256) silu_kernel(const float *__restrict__ a, 
     dst[i] = b ? s * b[i] : s;
 }
 
-// ROPE mode 0: ops.cpp:5080-5118, 5178-5362.  theta_i = pos * theta_scale^i, built by repeated
-// multiplication in the reference; one thread per (token, head) walks the pairs in the same order so
-// the angles are bit-identical.
+// ROPE mode 0: ops.cpp:5080-5118, 5178-5362.  theta_i = pos * theta_scale^i is built by repeated
+// multiplication in the reference; one thread of the token's CTA walks that recurrence (cheap), the cos/sin
+// of the D/2 angles are then taken in parallel and applied to every head of the token, so the angles are
+// bit-identical to the reference's.
 __global__ void __launch_bounds__(128) rope_norm_kernel(const float *__restrict__ x, int64_t x_nb_head, int64_t x_nb_tok,
                                                        float *__restrict__ dst, int64_t dst_nb_head, int64_t dst_nb_tok, int64_t D,
                                                        int64_t H, int64_t T, int n_dims, const int32_t *__restrict__ pos,
                                                        const float *__restrict__ ff, float theta_scale, float freq_scale,
                                                        float attn_factor) {
-    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= H * T) return;
-    const int64_t t = i / H, h = i - t * H;
-    const float *s = reinterpret_cast<const float *>(reinterpret_cast<const char *>(x) + t * x_nb_tok + h * x_nb_head);
-    float *o = reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + t * dst_nb_tok + h * dst_nb_head);
-    float theta = (float) pos[t];
-    for (int k = 0; k < n_dims; k += 2) {
-        const float f = ff ? ff[k / 2] : 1.0f;
-        const float th = freq_scale * (theta / f);
-        const float c = cosf(th) * attn_factor, sn = sinf(th) * attn_factor;
-        const float x0 = s[k], x1 = s[k + 1];
-        o[k] = x0 * c - x1 * sn;
-        o[k + 1] = x0 * sn + x1 * c;
-        theta *= theta_scale;
+    extern __shared__ float cs[];   // [n_dims/2] cos, [n_dims/2] sin
+    const int64_t t = blockIdx.x;
+    const int half_dims = n_dims / 2;
+    if (threadIdx.x == 0) {
+        float theta = (float) pos[t];
+        for (int k = 0; k < half_dims; ++k) {
+            cs[k] = theta;
+            theta *= theta_scale;
+        }
     }
-    for (int64_t k = n_dims; k < D; ++k) o[k] = s[k];
+    __syncthreads();
+    for (int k = threadIdx.x; k < half_dims; k += blockDim.x) {
+        const float f = ff ? ff[k] : 1.0f;
+        const float th = freq_scale * (cs[k] / f);
+        cs[half_dims + k] = sinf(th) * attn_factor;
+    }
+    __syncthreads();
+    for (int k = threadIdx.x; k < half_dims; k += blockDim.x) {
+        const float f = ff ? ff[k] : 1.0f;
+        const float th = freq_scale * (cs[k] / f);
+        cs[k] = cosf(th) * attn_factor;
+    }
+    __syncthreads();
+    const int64_t pairs = D / 2;
+    for (int64_t i = threadIdx.x; i < H * pairs; i += blockDim.x) {
+        const int64_t h = i / pairs, k = i - h * pairs;
+        const float *s = reinterpret_cast<const float *>(reinterpret_cast<const char *>(x) + t * x_nb_tok + h * x_nb_head) + 2 * k;
+        float *o = reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + t * dst_nb_tok + h * dst_nb_head) + 2 * k;
+        const float2 v = *reinterpret_cast<const float2 *>(s);
+        if (k < half_dims) {
+            const float c = cs[k], sn = cs[half_dims + k];
+            *reinterpret_cast<float2 *>(o) = make_float2(v.x * c - v.y * sn, v.x * sn + v.y * c);
+        } else {
+            *reinterpret_cast<float2 *>(o) = v;
+        }
+    }
 }
 
 template <typename TO>
@@ -136,10 +157,12 @@ int b200_silu(const float *a, const float *b, float *dst, int64_t n, b200_stream
 int b200_rope_norm(const float *x, int64_t x_nb_head, int64_t x_nb_tok, float *dst, int64_t dst_nb_head, int64_t dst_nb_tok,
                    int64_t D, int64_t H, int64_t T, int n_dims, const int32_t *pos, const float *freq_factors, float freq_base,
                    float freq_scale, float attn_factor, b200_stream_t stream) {
-    B200_REQUIRE(x && dst && pos && D > 0 && H > 0 && T >= 0 && n_dims > 0 && n_dims <= D && n_dims % 2 == 0, "bad rope arguments");
+    B200_REQUIRE(x && dst && pos && D > 0 && D % 2 == 0 && H > 0 && T >= 0 && n_dims > 0 && n_dims <= D && n_dims % 2 == 0, "bad rope arguments");
+    B200_REQUIRE(n_dims <= 8192 && is_aligned(x, 8) && is_aligned(dst, 8) && x_nb_head % 8 == 0 && x_nb_tok % 8 == 0 && dst_nb_head % 8 == 0 && dst_nb_tok % 8 == 0,
+                 "rope rows must be 8-byte aligned");
     if (T == 0) return B200_OK;
     const float theta_scale = powf(freq_base, -2.0f / (float) n_dims);
-    rope_norm_kernel<<<blocks_for(H * T, 128), 128, 0, (cudaStream_t) stream>>>(x, x_nb_head, x_nb_tok, dst, dst_nb_head, dst_nb_tok, D, H, T,
+    rope_norm_kernel<<<(unsigned) T, 128, (size_t) n_dims * sizeof(float), (cudaStream_t) stream>>>(x, x_nb_head, x_nb_tok, dst, dst_nb_head, dst_nb_tok, D, H, T,
                                                                               n_dims, pos, freq_factors, theta_scale, freq_scale, attn_factor);
     return check_launch("rope_norm");
 }

@@ -95,9 +95,10 @@ def block_dots(w: QWeight, x: torch.Tensor, variant: int = Q8_AVX2) -> torch.Ten
 
 
 def flash_attn_ext(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor | None, scale: float,
-                   max_bias: float = 0.0, logit_softcap: float = 0.0, n_kv: int | None = None) -> torch.Tensor:
+                   max_bias: float = 0.0, logit_softcap: float = 0.0, n_kv: int | None = None, parity: bool = False) -> torch.Tensor:
     """q f32 [Nq, H, D]; k, v f16 [cells, Hkv, D] (the cache; the first n_kv cells are attended);
-    mask f16 [>=Nq, n_kv] -> f32 [Nq, H, D]."""
+    mask f16 [>=Nq, n_kv] -> f32 [Nq, H, D].  ``parity=True`` runs the slow validation kernel that follows the
+    reference's order of roundings (fp16 output accumulator) instead of the fast fp32-accumulating one."""
     _need_cuda(q, k, v, mask)
     L = lib()
     Nq, H, D = q.shape
@@ -110,6 +111,16 @@ def flash_attn_ext(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torc
     scratch = torch.empty(max(need, 256), dtype=torch.uint8, device=q.device)
     if mask is not None:
         assert mask.dtype == torch.float16 and mask.stride(1) == 1 and mask.shape[1] >= n_kv
+    if parity:
+        index = None
+        if mask is not None:
+            index = torch.empty(L.b200_mask_index_bytes(Nq, n_kv), dtype=torch.uint8, device=q.device)
+            check(L.b200_mask_index_build(mask.data_ptr(), mask.stride(0) * 2, Nq, n_kv, index.data_ptr(), index.numel(), _stream()))
+        check(L.b200_flash_attn_ext_parity(D, H, Hkv, Nq, n_kv, q.data_ptr(), q.stride(0) * 4, q.stride(1) * 4,
+                                           k.data_ptr(), k.stride(0) * 2, k.stride(1) * 2, v.data_ptr(), v.stride(0) * 2, v.stride(1) * 2,
+                                           mask.data_ptr() if mask is not None else None, mask.stride(0) * 2 if mask is not None else 0,
+                                           index.data_ptr() if index is not None else None, scale, max_bias, logit_softcap, out.data_ptr(), _stream()))
+        return out
     check(L.b200_flash_attn_ext(D, H, Hkv, Nq, n_kv, q.data_ptr(), q.stride(0) * 4, q.stride(1) * 4,
                                 k.data_ptr(), k.stride(0) * 2, k.stride(1) * 2, v.data_ptr(), v.stride(0) * 2, v.stride(1) * 2,
                                 mask.data_ptr() if mask is not None else None, mask.stride(0) * 2 if mask is not None else 0,

@@ -149,6 +149,17 @@ B200_API int b200_flash_attn_ext_indexed(int64_t D, int64_t H, int64_t Hkv, int6
                                          const void *mask, int64_t mask_nb_row, const void *index,
                                          float scale, float max_bias, float logit_softcap,
                                          float *dst, void *scratch, size_t scratch_bytes, b200_stream_t stream);
+/* Validation variant: one warp per (token, head) walks the unmasked cells in ascending order with the
+ * reference's exact sequence of roundings (fp16 Q, the AVX2 lane order of the K.Q dot, the fp16 output
+ * accumulator of cactus/ggml-cpu/ops.cpp:7103-7117).  Slow; it exists to show that the distance between the
+ * fast kernel and the reference is the reference's fp16 accumulator.  Needs no scratch. */
+B200_API int b200_flash_attn_ext_parity(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, int64_t n_kv,
+                                        const float *q, int64_t q_nb_tok, int64_t q_nb_head,
+                                        const void *k, int64_t k_nb_cell, int64_t k_nb_head,
+                                        const void *v, int64_t v_nb_cell, int64_t v_nb_head,
+                                        const void *mask, int64_t mask_nb_row, const void *index,
+                                        float scale, float max_bias, float logit_softcap,
+                                        float *dst, b200_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
  * The small ops that keep a llama layer on the device (cactus/ggml-cpu/ops.cpp, binary-ops.cpp).
