@@ -21,7 +21,6 @@
 
 namespace b200 {
 
-constexpr int MMQ_STAGES = 4;
 
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
     const uint32_t s = (uint32_t) __cvta_generic_to_shared(smem);
@@ -37,6 +36,35 @@ __device__ __forceinline__ void mma_s8_magic(uint32_t (&c)[4], uint32_t a0, uint
         "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
         : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(magic));
+}
+// One k=32 step of a 16x8 tile and its epilogue in a single block, so the accumulator pairs stay in aligned
+// register pairs: c = A.B + 0x4B400000 (bits of 12582912 + dot); t = d_a * c - d_a * 12582912; y += d_w * t.
+__device__ __forceinline__ void mma_scale_acc(uint64_t &y01, uint64_t &y23, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                              uint32_t b1, uint64_t da, uint64_t nda, uint64_t dw01, uint64_t dw23) {
+    asm("{\n"
+        ".reg .b32 c0, c1, c2, c3;\n"
+        ".reg .b64 p01, p23;\n"
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {c0,c1,c2,c3}, {%2,%3,%4,%5}, {%6,%7}, {%12,%12,%12,%12};\n"
+        "mov.b64 p01, {c0,c1};\n"
+        "mov.b64 p23, {c2,c3};\n"
+        "fma.rn.f32x2 p01, p01, %8, %9;\n"
+        "fma.rn.f32x2 p23, p23, %8, %9;\n"
+        "fma.rn.f32x2 %0, p01, %10, %0;\n"
+        "fma.rn.f32x2 %1, p23, %11, %1;\n"
+        "}\n"
+        : "+l"(y01), "+l"(y23)
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "l"(da), "l"(nda), "l"(dw01), "l"(dw23), "r"(0x4B400000u));
+}
+// k=32 MMA step alone, accumulator pairs returned packed (aligned register pairs for the f32x2 epilogue)
+__device__ __forceinline__ void mma_s8_magic2(uint64_t &p01, uint64_t &p23, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("{\n"
+        ".reg .b32 c0, c1, c2, c3;\n"
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {c0,c1,c2,c3}, {%2,%3,%4,%5}, {%6,%7}, {%8,%8,%8,%8};\n"
+        "mov.b64 %0, {c0,c1};\n"
+        "mov.b64 %1, {c2,c3};\n"
+        "}\n"
+        : "=l"(p01), "=l"(p23)
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0x4B400000u));
 }
 __device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
     uint64_t r;
@@ -82,7 +110,7 @@ __device__ __forceinline__ void load_wfrag(WFrag<WTYPE> &f, const uint8_t *__res
 }
 
 // Shape of a CTA: WM x WN warps; a warp owns MT 16-row tiles and NTW 8-column tiles.
-template <int WTYPE, int NTW, int WN, int MT, int WM>
+template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES>
 struct MmqCfg {
     static constexpr int WARPS = WM * WN;
     static constexpr int THREADS = WARPS * 32;
@@ -94,14 +122,15 @@ struct MmqCfg {
     static constexpr int B_BYTES = NT * 1024;              // NT n-tiles x 4 blocks x 256 B
     static constexpr int S_BYTES = NT * 256;               // their scale groups
     static constexpr int STAGE = A_BYTES + AS_BYTES + B_BYTES + S_BYTES;
-    static constexpr int TOTAL = STAGE * MMQ_STAGES;
+    static constexpr int TOTAL = STAGE * STAGES;
 };
 
-template <int WTYPE, int NTW, int WN, int MT, int WM>
-__global__ void __launch_bounds__(WM * WN * 32) mmq_kernel(TiledDims dims, const uint8_t *__restrict__ w, ActDims act,
+template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB>
+__global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims, const uint8_t *__restrict__ w, ActDims act,
                                                           const uint8_t *__restrict__ aq, float *__restrict__ dst,
                                                           int64_t dst_nb_row, float *__restrict__ partial, int ksplit) {
-    using S = MmqCfg<WTYPE, NTW, WN, MT, WM>;
+    using S = MmqCfg<WTYPE, NTW, WN, MT, WM, STAGES>;
+    constexpr int MMQ_STAGES = STAGES;
     constexpr int NT = NTW;              // n-tiles of this warp
     constexpr int MMQ_MT = MT;
     constexpr int MMQ_THREADS = S::THREADS;
@@ -118,30 +147,62 @@ __global__ void __launch_bounds__(WM * WN * 32) mmq_kernel(TiledDims dims, const
     const int64_t bg_end = min(dims.n_bg, bg_begin + per);
     const int64_t n_iter = max((int64_t) 0, bg_end - bg_begin);
 
+    // Copy plan of this thread, fixed for the whole K loop: 16-byte chunk c of a stage comes from
+    // base + (src16[k] + bg * step16) * 16.  Offsets are in 16-byte units and fit 32 bits.
     const int64_t cta_rt0 = (int64_t) blockIdx.x * S::CTA_TILES;
+    constexpr int A_CH = S::A_BYTES / 16, AS_CH = S::AS_BYTES / 16, B_CH = S::B_BYTES / 16, S_CH = S::S_BYTES / 16;
+    constexpr int A_N = (A_CH + MMQ_THREADS - 1) / MMQ_THREADS, AS_N = (AS_CH + MMQ_THREADS - 1) / MMQ_THREADS;
+    constexpr int B_N = (B_CH + MMQ_THREADS - 1) / MMQ_THREADS, S_N = (S_CH + MMQ_THREADS - 1) / MMQ_THREADS;
+    uint32_t a_src[A_N], as_src[AS_N], b_src[B_N], s_src[S_N];
+    const uint8_t *w_sc = w + dims.qs_bytes, *a_sc = aq + act.d_offset;
+#pragma unroll
+    for (int k = 0; k < A_N; ++k) {
+        const int c = tid + k * MMQ_THREADS;
+        const int tile = c / (S::TILE / 16), off = c % (S::TILE / 16);
+        const int64_t rt = min(cta_rt0 + tile, dims.n_rt - 1);  // rows beyond the matrix are never written back
+        a_src[k] = (uint32_t) (rt * dims.n_bg * (S::TILE / 16) + off);
+    }
+#pragma unroll
+    for (int k = 0; k < AS_N; ++k) {
+        const int c = tid + k * MMQ_THREADS;
+        const int64_t rt = min(cta_rt0 + (c >> 3), dims.n_rt - 1);
+        as_src[k] = (uint32_t) (rt * dims.n_bg * 8 + (c & 7));
+    }
+#pragma unroll
+    for (int k = 0; k < B_N; ++k) {
+        const int c = tid + k * MMQ_THREADS;
+        const int64_t nt = min(cta_nt0 + (c >> 6), act.n_nt - 1);  // columns beyond N are never written back
+        b_src[k] = (uint32_t) (nt * act.nbp * 16 + (c & 63));
+    }
+#pragma unroll
+    for (int k = 0; k < S_N; ++k) {
+        const int c = tid + k * MMQ_THREADS;
+        const int64_t nt = min(cta_nt0 + (c >> 4), act.n_nt - 1);
+        s_src[k] = (uint32_t) (nt * act.n_bg * 16 + (c & 15));
+    }
     auto issue = [&](int64_t it) {
         uint8_t *st = smem + (it % MMQ_STAGES) * S::STAGE;
-        const int64_t bg = bg_begin + it;
-        for (int c = tid; c < S::A_BYTES / 16; c += MMQ_THREADS) {
-            const int tile = c / (S::TILE / 16), off = c % (S::TILE / 16);
-            const int64_t rt = min(cta_rt0 + tile, dims.n_rt - 1);  // rows beyond the matrix are never written back
-            cp_async16(st + c * 16, w + (rt * dims.n_bg + bg) * S::TILE + off * 16);
+        const uint32_t bg = (uint32_t) (bg_begin + it);
+#pragma unroll
+        for (int k = 0; k < A_N; ++k) {
+            const int c = tid + k * MMQ_THREADS;
+            if (A_CH % MMQ_THREADS == 0 || c < A_CH) cp_async16(st + c * 16, w + (size_t) (a_src[k] + bg * (S::TILE / 16)) * 16);
         }
-        for (int c = tid; c < S::AS_BYTES / 16; c += MMQ_THREADS) {
-            const int tile = c >> 3, off = c & 7;
-            const int64_t rt = min(cta_rt0 + tile, dims.n_rt - 1);
-            cp_async16(st + S::A_BYTES + c * 16, w + dims.qs_bytes + (rt * dims.n_bg + bg) * 128 + off * 16);
+#pragma unroll
+        for (int k = 0; k < AS_N; ++k) {
+            const int c = tid + k * MMQ_THREADS;
+            if (AS_CH % MMQ_THREADS == 0 || c < AS_CH) cp_async16(st + S::A_BYTES + c * 16, w_sc + (size_t) (as_src[k] + bg * 8) * 16);
         }
         uint8_t *sb = st + S::A_BYTES + S::AS_BYTES;
-        for (int c = tid; c < S::B_BYTES / 16; c += MMQ_THREADS) {
-            const int tile = c >> 6, off = c & 63;
-            const int64_t nt = min(cta_nt0 + tile, act.n_nt - 1);  // columns beyond N are never written back
-            cp_async16(sb + c * 16, aq + (nt * act.nbp + bg * 4) * 256 + off * 16);
+#pragma unroll
+        for (int k = 0; k < B_N; ++k) {
+            const int c = tid + k * MMQ_THREADS;
+            if (B_CH % MMQ_THREADS == 0 || c < B_CH) cp_async16(sb + c * 16, aq + (size_t) (b_src[k] + bg * 64) * 16);
         }
-        for (int c = tid; c < S::S_BYTES / 16; c += MMQ_THREADS) {
-            const int tile = c >> 4, off = c & 15;
-            const int64_t nt = min(cta_nt0 + tile, act.n_nt - 1);
-            cp_async16(sb + S::B_BYTES + c * 16, aq + act.d_offset + (nt * act.n_bg + bg) * 256 + off * 16);
+#pragma unroll
+        for (int k = 0; k < S_N; ++k) {
+            const int c = tid + k * MMQ_THREADS;
+            if (S_CH % MMQ_THREADS == 0 || c < S_CH) cp_async16(sb + S::B_BYTES + c * 16, a_sc + (size_t) (s_src[k] + bg * 16) * 16);
         }
     };
     uint64_t y[MMQ_MT][NT][2];  // packed (col 2t, col 2t+1) for row g ([0]) and row g+8 ([1])
@@ -171,51 +232,64 @@ __global__ void __launch_bounds__(WM * WN * 32) mmq_kernel(TiledDims dims, const
             load_wfrag<WTYPE>(cur[mt], As + tile * S::TILE, As + S::A_BYTES + tile * 128, lane);
         }
 
-        // weight scales of this group as packed (d, d) pairs
-        uint64_t dwa[MMQ_MT][4], dwb[MMQ_MT][4];
-#pragma unroll
-        for (int mt = 0; mt < MMQ_MT; ++mt) {
-            const __half2 a01 = *reinterpret_cast<const __half2 *>(&cur[mt].sa.x), a23 = *reinterpret_cast<const __half2 *>(&cur[mt].sa.y);
-            const __half2 b01 = *reinterpret_cast<const __half2 *>(&cur[mt].sb.x), b23 = *reinterpret_cast<const __half2 *>(&cur[mt].sb.y);
-            const float2 fa01 = __half22float2(a01), fa23 = __half22float2(a23), fb01 = __half22float2(b01), fb23 = __half22float2(b23);
-            const uint32_t ua[4] = {__float_as_uint(fa01.x), __float_as_uint(fa01.y), __float_as_uint(fa23.x), __float_as_uint(fa23.y)};
-            const uint32_t ub[4] = {__float_as_uint(fb01.x), __float_as_uint(fb01.y), __float_as_uint(fb23.x), __float_as_uint(fb23.y)};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                dwa[mt][j] = pack2(ua[j], ua[j]);
-                dwb[mt][j] = pack2(ub[j], ub[j]);
-            }
-        }
-
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            // A fragments of block j for both row tiles
-            uint32_t a0[MMQ_MT], a1[MMQ_MT], a2[MMQ_MT], a3[MMQ_MT];
-#pragma unroll
-            for (int mt = 0; mt < MMQ_MT; ++mt) {
-                if (WTYPE == B200_TYPE_Q4_0) {
-                    a0[mt] = (cur[mt].a[j] << 4) & 0xF0F0F0F0u; a2[mt] = cur[mt].a[j] & 0xF0F0F0F0u;
-                    a1[mt] = (cur[mt].b[j] << 4) & 0xF0F0F0F0u; a3[mt] = cur[mt].b[j] & 0xF0F0F0F0u;
-                } else {
-                    a0[mt] = cur[mt].a[2 * j]; a2[mt] = cur[mt].a[2 * j + 1];
-                    a1[mt] = cur[mt].b[2 * j]; a3[mt] = cur[mt].b[2 * j + 1];
-                }
-            }
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const uint2 b = reinterpret_cast<const uint2 *>(Bs + (wn * NTW + nt) * 1024 + j * 256)[lane];
-                const uint4 sc = reinterpret_cast<const uint4 *>(Ss + (wn * NTW + nt) * 256)[j * 4 + t];  // {d0, d1, nd0, nd1} of columns 2t, 2t+1
-                const uint64_t da = pack2(sc.x, sc.y), nda = pack2(sc.z, sc.w);
+        // 4 blocks x NT/2 column-tile pairs = a flat sequence of steps.  The MMAs of step s+1 are issued before the
+        // epilogue FMAs of step s, so the tensor-pipe latency of one step hides behind the FP32 work of the previous one.
+        constexpr int NP = NT / 2;
+        constexpr int NSTEP = 4 * NP;
+        uint32_t a0[MMQ_MT], a1[MMQ_MT], a2[MMQ_MT], a3[MMQ_MT];
+        uint64_t dwa[2][MMQ_MT], dwb[2][MMQ_MT];   // weight scales of the block of the step in flight / the step being finished
+        uint64_t p01[2][2][MMQ_MT], p23[2][2][MMQ_MT];
+        uint4 sc[2][2];                              // {d0, d1, nd0, nd1} of the two column tiles of a step
+        auto start = [&](int step, int buf) {
+            const int j = step / NP, np = step % NP;
+            if (np == 0) {
+                // A fragments of block j for the warp's row tiles, and the block's weight scales as packed (d, d) pairs
 #pragma unroll
                 for (int mt = 0; mt < MMQ_MT; ++mt) {
-                    uint32_t c[4];
-                    mma_s8_magic(c, a0[mt], a1[mt], a2[mt], a3[mt], b.x, b.y);
-                    const uint64_t t01 = fma2(pack2(c[0], c[1]), da, nda);
-                    const uint64_t t23 = fma2(pack2(c[2], c[3]), da, nda);
-                    y[mt][nt][0] = fma2(t01, dwa[mt][j], y[mt][nt][0]);
-                    y[mt][nt][1] = fma2(t23, dwb[mt][j], y[mt][nt][1]);
+                    const uint32_t ha = (j < 2) ? cur[mt].sa.x : cur[mt].sa.y, hb = (j < 2) ? cur[mt].sb.x : cur[mt].sb.y;
+                    const __half2 h2a = *reinterpret_cast<const __half2 *>(&ha), h2b = *reinterpret_cast<const __half2 *>(&hb);
+                    const uint32_t ua = __float_as_uint((j & 1) ? __high2float(h2a) : __low2float(h2a));
+                    const uint32_t ub = __float_as_uint((j & 1) ? __high2float(h2b) : __low2float(h2b));
+                    dwa[j & 1][mt] = pack2(ua, ua);
+                    dwb[j & 1][mt] = pack2(ub, ub);
+                    if (WTYPE == B200_TYPE_Q4_0) {
+                        a0[mt] = (cur[mt].a[j] << 4) & 0xF0F0F0F0u; a2[mt] = cur[mt].a[j] & 0xF0F0F0F0u;
+                        a1[mt] = (cur[mt].b[j] << 4) & 0xF0F0F0F0u; a3[mt] = cur[mt].b[j] & 0xF0F0F0F0u;
+                    } else {
+                        a0[mt] = cur[mt].a[2 * j]; a2[mt] = cur[mt].a[2 * j + 1];
+                        a1[mt] = cur[mt].b[2 * j]; a3[mt] = cur[mt].b[2 * j + 1];
+                    }
                 }
             }
+            const int ntl = wn * NTW + 2 * np;
+            const uint2 b0 = reinterpret_cast<const uint2 *>(Bs + ntl * 1024 + j * 256)[lane];
+            const uint2 b1 = reinterpret_cast<const uint2 *>(Bs + (ntl + 1) * 1024 + j * 256)[lane];
+            sc[buf][0] = reinterpret_cast<const uint4 *>(Ss + ntl * 256)[j * 4 + t];
+            sc[buf][1] = reinterpret_cast<const uint4 *>(Ss + (ntl + 1) * 256)[j * 4 + t];
+#pragma unroll
+            for (int mt = 0; mt < MMQ_MT; ++mt) {
+                mma_s8_magic2(p01[buf][0][mt], p23[buf][0][mt], a0[mt], a1[mt], a2[mt], a3[mt], b0.x, b0.y);
+                mma_s8_magic2(p01[buf][1][mt], p23[buf][1][mt], a0[mt], a1[mt], a2[mt], a3[mt], b1.x, b1.y);
+            }
+        };
+        auto finish = [&](int step, int buf) {
+            const int j = step / NP, np = step % NP;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const uint64_t da = pack2(sc[buf][i].x, sc[buf][i].y), nda = pack2(sc[buf][i].z, sc[buf][i].w);
+#pragma unroll
+                for (int mt = 0; mt < MMQ_MT; ++mt) {
+                    const uint64_t t01 = fma2(p01[buf][i][mt], da, nda), t23 = fma2(p23[buf][i][mt], da, nda);
+                    y[mt][2 * np + i][0] = fma2(t01, dwa[j & 1][mt], y[mt][2 * np + i][0]);
+                    y[mt][2 * np + i][1] = fma2(t23, dwb[j & 1][mt], y[mt][2 * np + i][1]);
+                }
+            }
+        };
+        start(0, 0);
+#pragma unroll
+        for (int step = 0; step < NSTEP; ++step) {
+            if (step + 1 < NSTEP) start(step + 1, (step + 1) & 1);
+            finish(step, step & 1);
         }
     }
     cp_async_wait<0>();
@@ -280,25 +354,25 @@ struct MmqVariant {
     int (*launch)(const TiledDims &, const uint8_t *, const ActDims &, const uint8_t *, float *, int64_t, float *, int, cudaStream_t);
 };
 
-template <int WTYPE, int NTW, int WN, int MT, int WM>
+template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB>
 static int launch_variant(const TiledDims &d, const uint8_t *w, const ActDims &a, const uint8_t *aq, float *dst, int64_t dst_nb_row,
                           float *partial, int ksplit, cudaStream_t st) {
-    using S = MmqCfg<WTYPE, NTW, WN, MT, WM>;
+    using S = MmqCfg<WTYPE, NTW, WN, MT, WM, STAGES>;
     dim3 grid((unsigned) ((d.n_rt + S::CTA_TILES - 1) / S::CTA_TILES), (unsigned) ((a.n_nt + S::NT - 1) / S::NT), (unsigned) ksplit);
-    mmq_kernel<WTYPE, NTW, WN, MT, WM><<<grid, S::THREADS, S::TOTAL, st>>>(d, w, a, aq, dst, dst_nb_row, partial, ksplit);
+    mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB><<<grid, S::THREADS, S::TOTAL, st>>>(d, w, a, aq, dst, dst_nb_row, partial, ksplit);
     return check_launch("mmq");
 }
 
-template <int WTYPE, int NTW, int WN, int MT, int WM>
+template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES = 4, int MINB = 1>
 static MmqVariant make_variant() {
-    using S = MmqCfg<WTYPE, NTW, WN, MT, WM>;
+    using S = MmqCfg<WTYPE, NTW, WN, MT, WM, STAGES>;
     MmqVariant v;
     v.cta_tiles = S::CTA_TILES;
     v.cta_nt = S::NT;
-    v.launch = launch_variant<WTYPE, NTW, WN, MT, WM>;
-    cudaFuncSetAttribute(mmq_kernel<WTYPE, NTW, WN, MT, WM>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    v.launch = launch_variant<WTYPE, NTW, WN, MT, WM, STAGES, MINB>;
+    cudaFuncSetAttribute(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, mmq_kernel<WTYPE, NTW, WN, MT, WM>, S::THREADS, S::TOTAL) != cudaSuccess || n <= 0) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB>, S::THREADS, S::TOTAL) != cudaSuccess || n <= 0) {
         cudaGetLastError();
         n = 1;
     }
@@ -324,10 +398,10 @@ static const MmqVariant &pick_variant(int64_t N) {
         t[1][0] = make_variant<WTYPE, 4, 1, 2, 4>();   // 128 rows x 32 cols
         t[1][1] = make_variant<WTYPE, 4, 1, 1, 4>();
         t[1][2] = t[1][0]; t[1][3] = t[1][0];
-        t[2][0] = make_variant<WTYPE, 8, 1, 2, 4>();   // 128 rows x 64 cols, a warp owns all 64 columns
-        t[2][1] = make_variant<WTYPE, 4, 2, 2, 4>();   // 128 rows x 64 cols, 8 warps as 4 x 2
-        t[2][2] = make_variant<WTYPE, 4, 2, 2, 2>();   //  64 rows x 64 cols, 4 warps as 2 x 2
-        t[2][3] = make_variant<WTYPE, 8, 1, 1, 4>();   //  64 rows x 64 cols, one row tile per warp
+        t[2][0] = make_variant<WTYPE, 8, 1, 2, 4, 4, 2>();   // 128 rows x 64 cols, a warp owns all 64 columns, 2 CTAs/SM
+        t[2][1] = make_variant<WTYPE, 4, 2, 4, 2, 4, 2>();   // 128 rows x 64 cols, 4 warps as 2 x 2, warp tile 64 x 32
+        t[2][2] = make_variant<WTYPE, 4, 2, 4, 1, 4, 3>();   //  64 rows x 64 cols, 2 warps, warp tile 64 x 32
+        t[2][3] = make_variant<WTYPE, 4, 2, 2, 4, 3, 2>();   // 128 rows x 64 cols, 8 warps as 4 x 2, 3 stages
         ready[dev] = true;
     }
     static int forced = -2;

