@@ -1,5 +1,7 @@
 // C ABI of MUL_MAT: argument checks and the choice between the dp4a kernel (N <= 8) and the
 // tensor-core kernel (N > 8).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -11,6 +13,34 @@ size_t mmq_workspace_bytes(int wtype, int64_t K, int64_t M, int64_t N);
 }  // namespace b200
 
 using namespace b200;
+
+// ---------------------------------------------------------------------------------------------
+// Scratch for b200_mul_mat_q_noalloc: room for the quantised activations of up to 8 columns of
+// B200_NOALLOC_MAX_K values (one 8-column tile of 256-byte block groups plus its scale plane).
+// The array lives in every device that loads this library, from load until the process exits.
+// In host code the name below is only a handle for cudaGetSymbolAddress, never a device address.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t NOALLOC_SCRATCH_BYTES = (size_t) B200_NOALLOC_MAX_K / 32 * 256 + (size_t) B200_NOALLOC_MAX_K / 128 * 256;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+// device address of the array on the current device, looked up once per device
+static int noalloc_scratch_ptr(void **out) {
+    static void *ptrs[64] = {nullptr};
+    static std::mutex mu;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return set_error(B200_E_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= 64) return set_error(B200_E_INVALID, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ptrs[dev]) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) return set_error(B200_E_CUDA, "cudaGetSymbolAddress(scratch): %s", cudaGetErrorString(e));
+        ptrs[dev] = p;
+    }
+    *out = ptrs[dev];
+    return B200_OK;
+}
 
 static bool shape_ok(int wtype, int64_t K, int64_t M, int64_t N) {
     return (wtype == B200_TYPE_Q4_0 || wtype == B200_TYPE_Q8_0) && K > 0 && K % 32 == 0 && M > 0 && N > 0;
@@ -49,6 +79,20 @@ int b200_mul_mat_q(int wtype, const void *w, int64_t K, int64_t M, const float *
     if (!scratch || scratch_bytes < ab + wb) return set_error(B200_E_SCRATCH, "scratch too small: %zu < %zu", scratch_bytes, ab + wb);
     if (int e = b200_quantize_activations(x, x_row_stride_bytes, K, N, scratch, ab, variant, stream)) return e;
     return b200_mul_mat_q_prequant(wtype, w, K, M, scratch, N, dst, dst_row_stride_bytes, wb ? (char *) scratch + ab : nullptr, wb, stream);
+}
+
+int b200_mul_mat_q_noalloc(int wtype, const void *w, int64_t K, int64_t M, const float *x, int64_t x_row_stride_bytes, int64_t N,
+                           float *dst, int64_t dst_row_stride_bytes, int variant, b200_stream_t stream) {
+    B200_REQUIRE(shape_ok(wtype, K, M, N), "bad mul_mat shape/type: type %d K %lld M %lld N %lld", wtype, (long long) K, (long long) M, (long long) N);
+    B200_REQUIRE(N <= B200_NOALLOC_MAX_N, "b200_mul_mat_q_noalloc handles at most %d columns, got %lld", B200_NOALLOC_MAX_N, (long long) N);
+    B200_REQUIRE(K <= B200_NOALLOC_MAX_K, "b200_mul_mat_q_noalloc handles rows of at most %d values, got %lld", B200_NOALLOC_MAX_K, (long long) K);
+    const size_t ab = b200_act_bytes(K, N);
+    B200_REQUIRE(ab <= NOALLOC_SCRATCH_BYTES, "built-in scratch too small for K %lld", (long long) K);
+    void *scratch = nullptr;
+    if (int e = noalloc_scratch_ptr(&scratch)) return e;
+    // the quantiser rewrites every byte of the region it uses (padding included), so nothing has to be cleared
+    if (int e = b200_quantize_activations(x, x_row_stride_bytes, K, N, scratch, ab, variant, stream)) return e;
+    return b200_mul_mat_q_prequant(wtype, w, K, M, scratch, N, dst, dst_row_stride_bytes, nullptr, 0, stream);
 }
 
 }  // extern "C"

@@ -112,6 +112,23 @@ B200_API int b200_quantize_activations(const float *x, int64_t x_row_stride_byte
 B200_API int b200_mul_mat_q_prequant(int wtype, const void *w, int64_t K, int64_t M, const void *act, int64_t N,
                                      float *dst, int64_t dst_row_stride_bytes, void *workspace, size_t workspace_bytes,
                                      b200_stream_t stream);
+/* No counterpart in the reference: b200_mul_mat_q for callers that must not allocate device memory.
+ *
+ * Some hosts cannot hand this library a scratch buffer: code running under a memory budget that was fixed at
+ * start-up, a plug-in loaded into a process whose allocator owns all device memory, or a caller inside a region
+ * where cudaMalloc is forbidden.  For them the quantised activations go into an array that is built into the
+ * library image (320 KiB of device memory on every GPU that loads the library, held until the process exits), so
+ * the call takes inputs and outputs only and performs no cudaMalloc / cudaFree of its own.
+ *
+ * Limits: N <= B200_NOALLOC_MAX_N columns (the decode kernel) and K <= B200_NOALLOC_MAX_K; larger sizes are
+ * refused with B200_E_INVALID.  Results are those of b200_mul_mat_q.  The first call on a device looks up the
+ * array's device address (a one-off set-up step): make that first call outside any stream capture.  All calls
+ * share the one array, which keeps whatever the last call left in it: two calls that overlap on the GPU (different
+ * streams, or different threads without ordering between them) race; calls ordered on one stream are fine. */
+#define B200_NOALLOC_MAX_N 8
+#define B200_NOALLOC_MAX_K 32768
+B200_API int b200_mul_mat_q_noalloc(int wtype, const void *w, int64_t K, int64_t M, const float *x, int64_t x_row_stride_bytes,
+                                    int64_t N, float *dst, int64_t dst_row_stride_bytes, int variant, b200_stream_t stream);
 /* Exact per-block integer dots of the same kernel inputs (debug/parity): out int32 [N][M][K/32]. */
 B200_API int b200_block_dots(int wtype, const void *w, int64_t K, int64_t M, const float *x, int64_t x_row_stride_bytes,
                              int64_t N, int32_t *out, void *act, size_t act_bytes, int variant, b200_stream_t stream);
