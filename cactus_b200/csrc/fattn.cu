@@ -36,6 +36,27 @@ __global__ void __launch_bounds__(256) mask_index_kernel(const __half *__restric
     if (lane == 0) words[wid] = (unsigned long long) lo | ((unsigned long long) hi << 32);
 }
 
+// Second pass of the mask scan: per token, the indices of the 64-cell words that have any participating cell,
+// in ascending order, and their count.  A token of a 64-sequence batch owns a few dozen of the 1024 words of a
+// 65536-cell cache, and the attention kernel walks only those.
+__global__ void __launch_bounds__(256) mask_words_compact_kernel(const unsigned long long *__restrict__ words, int64_t Nq, int64_t nw,
+                                                                int32_t *__restrict__ wlist, int32_t *__restrict__ wcount) {
+    const int lane = threadIdx.x & 31;
+    const int64_t j = ((int64_t) blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (j >= Nq) return;
+    const unsigned long long *row = words + j * nw;
+    int32_t *out = wlist + j * nw;
+    int base = 0;
+    for (int64_t w0 = 0; w0 < nw; w0 += 32) {
+        const int64_t wi = w0 + lane;
+        const bool nz = wi < nw && row[wi] != 0ull;
+        const unsigned m = __ballot_sync(0xffffffffu, nz);
+        if (nz) out[base + __popc(m & ((1u << lane) - 1u))] = (int32_t) wi;
+        base += __popc(m);
+    }
+    if (lane == 0) wcount[j] = base;
+}
+
 struct FattnParams {
     int64_t H, Hkv, Nq, n_kv, nw;
     const float *q; int64_t q_nb_tok, q_nb_head;
@@ -43,12 +64,12 @@ struct FattnParams {
     const char *v; int64_t v_nb_cell, v_nb_head;
     const char *mask; int64_t mask_nb_row;
     const unsigned long long *words;  // NULL: every cell takes part
+    const int32_t *wlist, *wcount;    // per token: indices of the non-empty words and their number (with words)
     float scale, max_bias, softcap, m0, m1;
     uint32_t n_head_log2;
     float *dst;
     float *partial;  // [Nq][H][nsplit][D + 2]
     int nsplit, hgroups;
-    int64_t words_per_split;
 };
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -115,21 +136,29 @@ __global__ void __launch_bounds__(FA_THREADS) fattn_mma_kernel(FattnParams p) {
     for (int q = 0; q < 8; ++q) oacc[q][0] = oacc[q][1] = oacc[q][2] = oacc[q][3] = 0.0f;
     float m_run = -CUDART_INF_F, l_run = 0.0f;   // state of head g (l: this lane's share of the row sum)
 
-    const int64_t w_begin = (int64_t) split * p.words_per_split;
-    const int64_t w_end = min(p.nw, w_begin + p.words_per_split);
+    // the words this CTA walks: entries [w_begin, w_end) of the token's list of non-empty words (or of all words
+    // when there is no mask), an equal share per KV split
     const unsigned long long *wrow = p.words ? p.words + j * p.nw : nullptr;
+    const int32_t *wl = p.words ? p.wlist + j * p.nw : nullptr;
+    const int64_t n_words = p.words ? (int64_t) p.wcount[j] : p.nw;
+    const int64_t per_split = (n_words + p.nsplit - 1) / p.nsplit;
+    const int64_t w_begin = (int64_t) split * per_split;
+    const int64_t w_end = min(n_words, w_begin + per_split);
     const __half *mrow = p.mask ? reinterpret_cast<const __half *>(p.mask + j * p.mask_nb_row) : nullptr;
     const char *kbase = p.k + (int64_t) hk * p.k_nb_head;
     const char *vbase = p.v + (int64_t) hk * p.v_nb_head;
 
     for (int64_t w0 = w_begin; w0 < w_end; w0 += FA_SUPER_WORDS) {
         if (warp == 0) {   // list the participating cells of this round
-            const int64_t wi = w0 + lane;
+            const int64_t e = w0 + lane;
             unsigned long long bits = 0;
-            if (wi < w_end) {
+            int64_t wi = 0;
+            if (e < w_end) {
                 if (wrow) {
+                    wi = wl[e];
                     bits = wrow[wi];
                 } else {
+                    wi = e;
                     const int64_t left = p.n_kv - wi * 64;
                     bits = left >= 64 ? ~0ull : ((1ull << left) - 1ull);
                 }
@@ -407,9 +436,14 @@ using namespace b200;
 
 extern "C" {
 
+// index layout: words [Nq][nw] u64 | list of non-empty word indices [Nq][nw] i32 | their counts [Nq] i32
+static size_t index_list_offset(int64_t Nq, int64_t nw) { return align_up((size_t) Nq * nw * 8, 256); }
+static size_t index_count_offset(int64_t Nq, int64_t nw) { return index_list_offset(Nq, nw) + align_up((size_t) Nq * nw * 4, 256); }
+
 size_t b200_mask_index_bytes(int64_t Nq, int64_t n_kv) {
     if (Nq <= 0 || n_kv <= 0) return 0;
-    return align_up((size_t) Nq * ((n_kv + 63) / 64) * 8, 256);
+    const int64_t nw = (n_kv + 63) / 64;
+    return index_count_offset(Nq, nw) + align_up((size_t) Nq * 4, 256);
 }
 
 int b200_mask_index_build(const void *mask, int64_t mask_nb_row, int64_t Nq, int64_t n_kv, void *index, size_t index_bytes,
@@ -421,7 +455,11 @@ int b200_mask_index_build(const void *mask, int64_t mask_nb_row, int64_t Nq, int
     const int64_t threads = Nq * nw * 32;
     mask_index_kernel<<<(unsigned) ((threads + 255) / 256), 256, 0, (cudaStream_t) stream>>>(
         (const __half *) mask, mask_nb_row, Nq, n_kv, nw, (unsigned long long *) index);
-    return check_launch("mask_index");
+    if (int e = check_launch("mask_index")) return e;
+    mask_words_compact_kernel<<<(unsigned) ((Nq * 32 + 255) / 256), 256, 0, (cudaStream_t) stream>>>(
+        (const unsigned long long *) index, Nq, nw, (int32_t *) ((char *) index + index_list_offset(Nq, nw)),
+        (int32_t *) ((char *) index + index_count_offset(Nq, nw)));
+    return check_launch("mask_words_compact");
 }
 
 size_t b200_flash_attn_scratch_bytes(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, int64_t n_kv) {
@@ -459,13 +497,14 @@ static int flash_attn_impl(bool parity, int64_t D, int64_t H, int64_t Hkv, int64
     p.v = (const char *) v; p.v_nb_cell = v_nb_cell; p.v_nb_head = v_nb_head;
     p.mask = (const char *) mask; p.mask_nb_row = mask_nb_row;
     p.words = (const unsigned long long *) index;
+    p.wlist = index ? (const int32_t *) ((const char *) index + index_list_offset(Nq, p.nw)) : nullptr;
+    p.wcount = index ? (const int32_t *) ((const char *) index + index_count_offset(Nq, p.nw)) : nullptr;
     p.scale = logit_softcap != 0.0f ? scale / logit_softcap : scale;
     p.max_bias = max_bias; p.softcap = logit_softcap;
     p.n_head_log2 = 1u << (uint32_t) floor(log2((double) H));
     p.m0 = powf(2.0f, -(max_bias) / p.n_head_log2);
     p.m1 = powf(2.0f, -(max_bias / 2.0f) / p.n_head_log2);
     p.dst = dst; p.partial = (float *) scratch; p.nsplit = ns; p.hgroups = hgroups;
-    p.words_per_split = (p.nw + ns - 1) / ns;
 
     cudaStream_t st = (cudaStream_t) stream;
     if (parity) {
