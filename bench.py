@@ -131,6 +131,13 @@ def cpu_layer_sample(reps: int, warmup: int):
 # -------------------------------------------------------------------------------------------------
 # GPU arm
 # -------------------------------------------------------------------------------------------------
+# DRAM bytes (read + write) per launch of the tensor-core mul_mat at 64 columns, from `ncu --metrics
+# dram__bytes_read.sum,dram__bytes_write.sum` captures of `python -m cactus_b200.microbench mul_mat` on each of the
+# step's shapes (profiles/mul_mat_q4_0_n64.md).  Keyed by (K, M).
+NCU_DRAM_BYTES_PER_LAUNCH: dict = {(4096, 4096): 9.81e6, (4096, 1024): 2.73e6, (4096, 14336): 33.40e6, (14336, 4096): 34.22e6,
+                                   (4096, 128256): 296.6e6}   # output head: weight bytes + 1 MB of activations, not captured (1002 CTAs, no K split)
+
+
 def mul_mat_roofline(eng, cfg, reps: int = 3):
     """Times the dominant kernel -- the Q4_0 mul_mat at 64 columns -- over all of the step's weights, launch
     by launch on the launching stream with CUDA events (weights of 32 distinct layers, 4.2 GB, so nothing is
@@ -138,7 +145,6 @@ def mul_mat_roofline(eng, cfg, reps: int = 3):
     import torch
     from cactus_b200._lib import check, lib
     L = lib()
-    st = torch.cuda.current_stream().cuda_stream
     names = {"wq": "attn_q", "wk": "attn_k", "wv": "attn_v", "wo": "attn_output", "gate": "ffn_gate", "up": "ffn_up", "down": "ffn_down"}
     T = N_SEQ
     per_shape, total_bytes, total_ms, launches = {}, 0.0, 0.0, 0
@@ -149,14 +155,22 @@ def mul_mat_roofline(eng, cfg, reps: int = 3):
         out = {cfg.d_model: eng.tmp, cfg.d_ff: eng.gate, cfg.vocab: eng.logits}.get(M, eng.k)
         bb = 18 if wtype == 2 else 34
         alg = M * (K // 32) * bb + T * K * 4 + T * M * 4      # weights + f32 activations in + f32 out
+        def launch_all():
+            stq = torch.cuda.current_stream().cuda_stream
+            for name in tensors:
+                w = eng.w.tensors[name]
+                check(L.b200_mul_mat_q_prequant(w.wtype, w.data.data_ptr(), w.K, w.M, act.data_ptr(), T, out.data_ptr(), out.stride(0) * 4,
+                                                eng.ws.data_ptr(), eng.ws.numel(), stq))
+
+        launch_all()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            launch_all()
         best = None
         for _ in range(reps):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            for name in tensors:
-                w = eng.w.tensors[name]
-                check(L.b200_mul_mat_q_prequant(w.wtype, w.data.data_ptr(), w.K, w.M, act.data_ptr(), T, out.data_ptr(), out.stride(0) * 4,
-                                                eng.ws.data_ptr(), eng.ws.numel(), st))
+            graph.replay()
             e1.record()
             e1.synchronize()
             ms = e0.elapsed_time(e1) / len(tensors)
@@ -167,26 +181,26 @@ def mul_mat_roofline(eng, cfg, reps: int = 3):
         launches += len(tensors)
     peak, which = peaks()
     achieved = total_bytes / total_ms / 1e6
+    traffic = None
+    if all((K, M) in NCU_DRAM_BYTES_PER_LAUNCH for _, K, M, _, _ in shapes):
+        traffic = int(sum(NCU_DRAM_BYTES_PER_LAUNCH[(K, M)] * len(t) for _, K, M, t, _ in shapes))
     return {"bound": "hbm", "kernel": "mmq_kernel<Q4_0,64> (all mul_mat launches of one decode step)", "achieved": round(achieved, 1),
-            "peak": peak, "peak_source": which, "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": None,
+            "peak": peak, "peak_source": which, "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": traffic,
             "algorithmic_bytes_per_step": int(total_bytes), "ms_per_step_in_mul_mat": round(total_ms, 4), "per_shape": per_shape}
 
 
 def gpu_arm(args):
     import torch
-    import torch.distributed as dist
 
+    from cactus_b200 import dist as bdist
     from cactus_b200 import lib
     from cactus_b200.engine import LLAMA_3_8B, LlamaConfig, LlamaEngine, LlamaWeights
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
+    rank, world, local = bdist.env_rank()
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device; there is no CPU path (use --impl reference for the CPU arm)")
     torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    bdist.init("nccl", torch.device("cuda", local))
     L = lib()
 
     cfg = LLAMA_3_8B if not args.small else LlamaConfig(4, 1024, 8, 2, 4096, 32000)
@@ -206,8 +220,7 @@ def gpu_arm(args):
 
     def barrier():
         torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
+        bdist.barrier()
         torch.cuda.synchronize()
 
     K, W = args.steps, max(args.warmup, 3)
@@ -235,10 +248,7 @@ def gpu_arm(args):
     barrier()
     ms = e0.elapsed_time(e1)
     clocks = sampler.stop()
-    t = torch.tensor([ms], device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = float(t.item())
+    ms_max = bdist.max_over_ranks(ms, "cuda")
     value = world * N_SEQ * K / (ms_max / 1e3)
 
     # ---- e2e: the public call with host buffers, H2D of the inputs and D2H of the logits inside ---
@@ -253,10 +263,7 @@ def gpu_arm(args):
         logits, tok = eng.decode(*decode_step_inputs(lens, head, s, tokens=tok))
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
-    t = torch.tensor([dt], device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e = world * N_SEQ * e2e_steps / float(t.item())
+    e2e = bdist.job_throughput(N_SEQ * e2e_steps, dt, "cuda")
     h2d = 4 * N_SEQ * 4
     d2h = N_SEQ * cfg.vocab * 4 + N_SEQ * 4
 
@@ -283,9 +290,7 @@ def gpu_arm(args):
             "step_bytes": {"weights": cfg.weight_bytes_per_step(), "kv_read_about": kv_bytes},
         }
         print(json.dumps(line))
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    bdist.shutdown()
 
 
 def reference_arm(args):
