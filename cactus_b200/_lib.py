@@ -16,6 +16,7 @@ SIGNATURES = {
     "b200_device_count": (_i32, []),
     "b200_device_info": (_i32, [_i32, C.c_char_p, _sz, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_i32)]),
     "b200_launch_count": (C.c_uint64, []),
+    "b200_kernel_status": (C.c_int, []),
     "b200_weight_bytes": (_sz, [_i32, _i64, _i64]),
     "b200_weight_upload": (_i32, [_i32, _i64, _i64, _vp, _vp, _i64, _i64, _vp]),
     "b200_weight_download": (_i32, [_i32, _i64, _i64, _vp, _vp, _i64, _i64, _vp]),

@@ -128,7 +128,7 @@ struct MmqCfg {
 template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB>
 __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims, const uint8_t *__restrict__ w, ActDims act,
                                                           const uint8_t *__restrict__ aq, float *__restrict__ dst,
-                                                          int64_t dst_nb_row, float *__restrict__ partial, int ksplit) {
+                                                          int64_t dst_nb_row, float *__restrict__ partial, int ksplit, int canon) {
     using S = MmqCfg<WTYPE, NTW, WN, MT, WM, STAGES>;
     constexpr int MMQ_STAGES = STAGES;
     constexpr int NT = NTW;              // n-tiles of this warp
@@ -262,8 +262,15 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
                 }
             }
             const int ntl = wn * NTW + 2 * np;
-            const uint2 b0 = reinterpret_cast<const uint2 *>(Bs + ntl * 1024 + j * 256)[lane];
-            const uint2 b1 = reinterpret_cast<const uint2 *>(Bs + (ntl + 1) * 1024 + j * 256)[lane];
+            uint2 b0, b1;
+            if (canon) {   // activations kept as two 8-column x 16-byte core matrices per block (the tcgen05 kernel's order)
+                const uint8_t *q0 = Bs + ntl * 1024 + j * 256 + g * 16 + t * 4, *q1 = q0 + 1024;
+                b0 = make_uint2(*reinterpret_cast<const uint32_t *>(q0), *reinterpret_cast<const uint32_t *>(q0 + 128));
+                b1 = make_uint2(*reinterpret_cast<const uint32_t *>(q1), *reinterpret_cast<const uint32_t *>(q1 + 128));
+            } else {
+                b0 = reinterpret_cast<const uint2 *>(Bs + ntl * 1024 + j * 256)[lane];
+                b1 = reinterpret_cast<const uint2 *>(Bs + (ntl + 1) * 1024 + j * 256)[lane];
+            }
             sc[buf][0] = reinterpret_cast<const uint4 *>(Ss + ntl * 256)[j * 4 + t];
             sc[buf][1] = reinterpret_cast<const uint4 *>(Ss + (ntl + 1) * 256)[j * 4 + t];
 #pragma unroll
@@ -351,15 +358,15 @@ struct MmqVariant {
     int cta_tiles;   // 16-row tiles per CTA
     int cta_nt;      // 8-column tiles per CTA
     int ctas_per_sm; // resident CTAs per SM (filled on first use)
-    int (*launch)(const TiledDims &, const uint8_t *, const ActDims &, const uint8_t *, float *, int64_t, float *, int, cudaStream_t);
+    int (*launch)(const TiledDims &, const uint8_t *, const ActDims &, const uint8_t *, float *, int64_t, float *, int, int, cudaStream_t);
 };
 
 template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB>
 static int launch_variant(const TiledDims &d, const uint8_t *w, const ActDims &a, const uint8_t *aq, float *dst, int64_t dst_nb_row,
-                          float *partial, int ksplit, cudaStream_t st) {
+                          float *partial, int ksplit, int canon, cudaStream_t st) {
     using S = MmqCfg<WTYPE, NTW, WN, MT, WM, STAGES>;
     dim3 grid((unsigned) ((d.n_rt + S::CTA_TILES - 1) / S::CTA_TILES), (unsigned) ((a.n_nt + S::NT - 1) / S::NT), (unsigned) ksplit);
-    mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB><<<grid, S::THREADS, S::TOTAL, st>>>(d, w, a, aq, dst, dst_nb_row, partial, ksplit);
+    mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB><<<grid, S::THREADS, S::TOTAL, st>>>(d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon);
     return check_launch("mmq");
 }
 
@@ -448,15 +455,20 @@ size_t mmq_workspace_bytes(int wtype, int64_t K, int64_t M, int64_t N) {
     return ks > 1 ? align_up((size_t) ks * N * M * sizeof(float), 256) : 0;
 }
 
+void launch_mmq_reduce(const float *partial, int ks, int64_t M, int64_t N, float *dst, int64_t dst_nb_row, cudaStream_t st) {
+    const int64_t total = M * N;
+    mmq_reduce_kernel<<<(unsigned) ((total + 255) / 256), 256, 0, st>>>(partial, ks, M, N, dst, dst_nb_row);
+}
+
 int launch_mmq(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
-               void *workspace, size_t workspace_bytes, cudaStream_t st) {
+               void *workspace, size_t workspace_bytes, cudaStream_t st, bool canon) {
     const MmqVariant &v = variant_for(wtype, a.N);
     int ks = choose_ksplit(v, d, a.n_nt);
     const size_t per_split = (size_t) a.N * d.M * sizeof(float);
     if (ks > 1 && (!workspace || workspace_bytes < per_split * ks)) {
         ks = workspace ? (int) std::max<size_t>(1, workspace_bytes / per_split) : 1;  // fewer splits fit: still correct, only slower
     }
-    if (int e = v.launch(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, (float *) workspace, ks, st)) return e;
+    if (int e = v.launch(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, (float *) workspace, ks, canon ? 1 : 0, st)) return e;
     if (ks > 1) {
         const int64_t total = d.M * a.N;
         mmq_reduce_kernel<<<(unsigned) ((total + 255) / 256), 256, 0, st>>>((const float *) workspace, ks, d.M, a.N, dst, dst_nb_row);

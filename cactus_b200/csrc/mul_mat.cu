@@ -5,10 +5,13 @@
 #include "common.cuh"
 
 namespace b200 {
-int launch_quantize_b8(const float *x, int64_t x_nb_row, int64_t K, int64_t N, void *scratch, int variant, cudaStream_t st);
+int launch_quantize_b8(const float *x, int64_t x_nb_row, int64_t K, int64_t N, void *scratch, int variant, bool canonical, cudaStream_t st);
+bool act_layout_canonical(int64_t N);
+int launch_mmq_tc(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
+                  void *workspace, size_t workspace_bytes, cudaStream_t st);
 int launch_mmvq(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row, cudaStream_t st);
 int launch_mmq(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
-               void *workspace, size_t workspace_bytes, cudaStream_t st);
+               void *workspace, size_t workspace_bytes, cudaStream_t st, bool canon);
 size_t mmq_workspace_bytes(int wtype, int64_t K, int64_t M, int64_t N);
 }  // namespace b200
 
@@ -68,7 +71,8 @@ int b200_mul_mat_q_prequant(int wtype, const void *w, int64_t K, int64_t M, cons
     const TiledDims d = tiled_dims(wtype, K, M);
     const ActDims a = act_dims(K, N);
     if (N <= 8) return launch_mmvq(wtype, d, w, a, act, dst, dst_row_stride_bytes, (cudaStream_t) stream);
-    return launch_mmq(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream);
+    if (act_layout_canonical(N)) return launch_mmq_tc(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream);
+    return launch_mmq(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream, false);
 }
 
 int b200_mul_mat_q(int wtype, const void *w, int64_t K, int64_t M, const float *x, int64_t x_row_stride_bytes, int64_t N,

@@ -1,5 +1,7 @@
 // Activation quantiser (quantize_row_q8_0), the tiled weight layout converters, GET_ROWS on tiled
 // weights and the exact block-dot debug kernel.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -7,7 +9,8 @@ namespace b200 {
 // ---------------------------------------------------------------------------------------------
 // quantize_row_q8_0 (cactus/ggml-cpu/ggml-cpu-quants.c:732-1045).  8 threads per 32-element block,
 // 4 elements each; the block maximum is reduced with three shuffles.  LAYOUT 0 writes the reference's
-// block_q8_0 stream, LAYOUT 1 the B8 scratch layout used by the mul_mat kernels.
+// block_q8_0 stream, LAYOUT 1 the B8 scratch layout (mma.sync fragment order), LAYOUT 2 the same tiles in the
+// canonical K-major core-matrix order the tcgen05 kernel's shared-memory descriptors expect.
 // ---------------------------------------------------------------------------------------------
 template <int LAYOUT>
 __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float *__restrict__ x, int64_t x_nb_row, int64_t K,
@@ -55,7 +58,12 @@ __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float *__restr
         const int g = (int) (n & 7);
         const int t = j & 3;
         uint8_t *tile = out + (nt * nbp + b) * 256;
-        *reinterpret_cast<uint32_t *>(tile + (g * 4 + t) * 8 + (j >= 4 ? 4 : 0)) = packed;
+        if (LAYOUT == 1) {
+            *reinterpret_cast<uint32_t *>(tile + (g * 4 + t) * 8 + (j >= 4 ? 4 : 0)) = packed;
+        } else {
+            // two 8-column x 16-byte core matrices: elements 0..15 of each column, then elements 16..31
+            *reinterpret_cast<uint32_t *>(tile + (j >> 2) * 128 + g * 16 + t * 4) = packed;
+        }
         if (j == 0) {
             float *dp = reinterpret_cast<float *>(out + d_offset) + (nt * (nbp >> 2) + (b >> 2)) * 64 + act_scale_index((int) (b & 3), g);
             const float df = real ? __half2float(d) : 0.0f;
@@ -232,13 +240,25 @@ static int check_wtype(int wtype) {
     return B200_OK;
 }
 
-int launch_quantize_b8(const float *x, int64_t x_nb_row, int64_t K, int64_t N, void *scratch, int variant, cudaStream_t st) {
+int launch_quantize_b8(const float *x, int64_t x_nb_row, int64_t K, int64_t N, void *scratch, int variant, bool canonical, cudaStream_t st) {
     const ActDims a = act_dims(K, N);
     const int64_t threads = a.n_nt * 8 * a.nbp * 8;
     const int64_t grid = (threads + 255) / 256;
-    quantize_q8_0_kernel<1><<<(unsigned) grid, 256, 0, st>>>(x, x_nb_row, K, N, a.n_nt * 8, a.nb, a.nbp, (uint8_t *) scratch,
-                                                            a.d_offset, variant);
-    return check_launch("quantize_q8_0 (B8)");
+    if (canonical) quantize_q8_0_kernel<2><<<(unsigned) grid, 256, 0, st>>>(x, x_nb_row, K, N, a.n_nt * 8, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
+    else quantize_q8_0_kernel<1><<<(unsigned) grid, 256, 0, st>>>(x, x_nb_row, K, N, a.n_nt * 8, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
+    return check_launch("quantize_q8_0 (activations)");
+}
+
+// Which order the quantised activations of an N-column product are kept in: the tcgen05 kernel (N > 8, only with
+// B200_MMQ_TC=1: it is correct but, at decode widths, still slower than the mma.sync kernel) reads canonical core
+// matrices, the dp4a kernel and the mma.sync kernel read fragment order.
+bool act_layout_canonical(int64_t N) {
+    static int mode = -1;
+    if (mode < 0) {
+        const char *e = getenv("B200_MMQ_TC");
+        mode = (e && atoi(e) == 1) ? 1 : 0;
+    }
+    return mode == 1 && N > 8;
 }
 
 }  // namespace b200
@@ -312,14 +332,15 @@ int b200_quantize_activations(const float *x, int64_t x_row_stride_bytes, int64_
     B200_REQUIRE(is_aligned(x, 4) && x_row_stride_bytes % 4 == 0, "misaligned activations");
     B200_REQUIRE(is_aligned(scratch, 256), "scratch must be 256-byte aligned");
     if (scratch_bytes < act_dims(K, N).total_bytes) return set_error(B200_E_SCRATCH, "scratch too small: %zu < %zu", scratch_bytes, act_dims(K, N).total_bytes);
-    return launch_quantize_b8(x, x_row_stride_bytes, K, N, scratch, variant, (cudaStream_t) stream);
+    return launch_quantize_b8(x, x_row_stride_bytes, K, N, scratch, variant, act_layout_canonical(N), (cudaStream_t) stream);
 }
 
 int b200_block_dots(int wtype, const void *w, int64_t K, int64_t M, const float *x, int64_t x_row_stride_bytes, int64_t N,
                     int32_t *out, void *scratch, size_t scratch_bytes, int variant, b200_stream_t stream) {
     if (int e = check_wtype(wtype)) return e;
     B200_REQUIRE(w && out && is_aligned(w, 16), "null or misaligned pointer");
-    if (int e = b200_quantize_activations(x, x_row_stride_bytes, K, N, scratch, scratch_bytes, variant, stream)) return e;
+    B200_REQUIRE(x && scratch && is_aligned(scratch, 256) && scratch_bytes >= act_dims(K, N).total_bytes, "bad activation scratch");
+    if (int e = launch_quantize_b8(x, x_row_stride_bytes, K, N, scratch, variant, false, (cudaStream_t) stream)) return e;
     const TiledDims d = tiled_dims(wtype, K, M);
     const ActDims a = act_dims(K, N);
     const int64_t total = N * M * d.nb;

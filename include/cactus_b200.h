@@ -58,6 +58,9 @@ B200_API int b200_device_count(void);
 B200_API int b200_device_info(int device, char *name, size_t name_len, size_t *free_bytes, size_t *total_bytes, int *sm_count);
 /* kernels launched by this library in the calling process since load (for launch accounting) */
 B200_API uint64_t b200_launch_count(void);
+/* 0, or non-zero once a kernel on the current device gave up a bounded wait on one of its own barriers (its result
+ * is then invalid; the context stays usable).  No reference counterpart: the CPU kernels have no such waits. */
+B200_API int b200_kernel_status(void);
 
 /* ------------------------------------------------------------------------------------------------
  * Weight storage.
