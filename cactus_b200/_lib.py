@@ -51,6 +51,12 @@ SIGNATURES = {
     "b200_scatter_i32": (_i32, [_vp, _vp, _vp, _i64, _vp]),
     "b200_set_rows_f16": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_argmax_rows": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp]),
+    "b200_peer_alloc": (_i32, [_sz, C.POINTER(_vp), C.c_char_p]),
+    "b200_peer_open": (_i32, [C.c_char_p, C.POINTER(_vp)]),
+    "b200_peer_close": (_i32, [_vp]),
+    "b200_peer_free": (_i32, [_vp]),
+    "b200_allgather_rows": (_i32, [_vp, _i64, _i64, _i64, _i32, _i32, C.POINTER(_vp), _i64, C.POINTER(_vp), _vp]),
+    "b200_peer_status": (_i32, [_vp]),
 }
 
 _lib = None

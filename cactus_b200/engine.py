@@ -104,6 +104,19 @@ class LlamaWeights:
             w.tensors[f"blk.{il}.ffn_norm.weight"] = torch.ones(d, device="cuda")
         return w
 
+    def shard(self, rank: int, g: int) -> "LlamaWeights":
+        """This rank's rows of every mul_mat weight (attention, feed-forward, output head); the embedding table and
+        the norm weights stay whole, as the replicated ops need them."""
+        from .rowsplit import row_bounds
+        out = LlamaWeights(self.cfg)
+        for name, t in self.tensors.items():
+            if isinstance(t, QWeight) and name != "token_embd.weight":
+                b = row_bounds(t.M, g)
+                out.tensors[name] = t.row_slice(b[rank], b[rank + 1])
+            else:
+                out.tensors[name] = t
+        return out
+
     @staticmethod
     def from_numpy(cfg: LlamaConfig, arrays: dict) -> "LlamaWeights":
         """arrays: name -> uint8 block stream [M, K/32*bb] for quantised tensors, f32 [d] for norms."""
@@ -132,10 +145,14 @@ class LlamaEngine:
     always spans the whole cache, masked) and replayed for every later ubatch of that size.
     """
 
-    def __init__(self, weights: LlamaWeights, n_cells: int, max_tokens: int = 512, variant: int = Q8_AVX2, use_graphs: bool = True):
+    def __init__(self, weights: LlamaWeights, n_cells: int, max_tokens: int = 512, variant: int = Q8_AVX2, use_graphs: bool = True, split=None):
         assert n_cells % 256 == 0, "the cache is padded to 256 cells for flash attention (cactus/llama-kv-cache.cpp:20-23)"
         self.w, self.cfg, self.n_cells, self.max_tokens, self.variant = weights, weights.cfg, n_cells, max_tokens, variant
         self.use_graphs = use_graphs
+        # row split (cactus_b200.rowsplit.RowSplit): ``weights`` then holds this rank's rows of every mul_mat weight,
+        # each product is joined into buffers the peers can write, everything else is replicated
+        self.split = split
+        g = split.world if split is not None else 1
         cfg, L = self.cfg, lib()
         dev = "cuda"
         kvd = cfg.n_kv_head * cfg.head_dim
@@ -152,17 +169,19 @@ class LlamaEngine:
         self.mask = torch.empty(((T + 63) // 64 * 64, n_cells), dtype=torch.float16, device=dev)
         self.index = u8(L.b200_mask_index_bytes(T, n_cells))
         self.x, self.h, self.attn = f32(T, cfg.d_model), f32(T, cfg.d_model), f32(T, cfg.d_model)
-        self.q, self.k, self.v = f32(T, cfg.d_model), f32(T, kvd), f32(T, kvd)
-        self.gate, self.up = f32(T, cfg.d_ff), f32(T, cfg.d_ff)
-        self.tmp = f32(T, cfg.d_model)
-        self.logits = f32(T, cfg.vocab)
+        out = split.carve if split is not None else f32   # mul_mat outputs: where the peers' slices land
+        self.q, self.k, self.v = out(T, cfg.d_model), out(T, kvd), out(T, kvd)
+        self.gate, self.up = out(T, cfg.d_ff), out(T, cfg.d_ff)
+        self.tmp = out(T, cfg.d_model)
+        self.logits = out(T, cfg.vocab)
+        self.local = f32(T * (max(cfg.d_ff, cfg.vocab) // g + 16)) if split is not None else None
         self.next_ids = torch.zeros(T, dtype=torch.int32, device=dev)
         self.logits_host = torch.empty((T, cfg.vocab), dtype=torch.float32).pin_memory()
         self.ids_host = torch.zeros(T, dtype=torch.int32).pin_memory()
         self.act_d = u8(L.b200_act_bytes(cfg.d_model, T))
         self.act_ff = u8(L.b200_act_bytes(cfg.d_ff, T))
-        ws = [L.b200_mul_mat_workspace_bytes(cfg.layer_type, K, M, t) for _, K, M in cfg.mul_mat_shapes() for t in (9, 16, 32, 64, T)]
-        ws.append(L.b200_mul_mat_workspace_bytes(cfg.head_type, cfg.d_model, cfg.vocab, T))
+        ws = [L.b200_mul_mat_workspace_bytes(cfg.layer_type, K, M // g, t) for _, K, M in cfg.mul_mat_shapes() for t in (9, 16, 32, 64, T)]
+        ws.append(L.b200_mul_mat_workspace_bytes(cfg.head_type, cfg.d_model, cfg.vocab // g, T))
         self.ws = u8(max(ws))
         self.fa_scratch = u8(max(L.b200_flash_attn_scratch_bytes(cfg.head_dim, cfg.n_head, cfg.n_kv_head, t, n_cells) for t in (1, 8, 64, T)))
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
@@ -171,8 +190,14 @@ class LlamaEngine:
     # ---- one ubatch worth of kernels on the current stream -------------------------------------
     def _mm(self, name: str, act: torch.Tensor, T: int, out: torch.Tensor):
         w: QWeight = self.w.tensors[name]
-        check(lib().b200_mul_mat_q_prequant(w.wtype, w.data.data_ptr(), w.K, w.M, act.data_ptr(), T, out.data_ptr(), out.stride(0) * 4,
+        if self.split is None:
+            check(lib().b200_mul_mat_q_prequant(w.wtype, w.data.data_ptr(), w.K, w.M, act.data_ptr(), T, out.data_ptr(), out.stride(0) * 4,
+                                                self.ws.data_ptr(), self.ws.numel(), self._st))
+            return
+        loc = self.local[:T * w.M].view(T, w.M)   # this rank's rows of the product, then the join
+        check(lib().b200_mul_mat_q_prequant(w.wtype, w.data.data_ptr(), w.K, w.M, act.data_ptr(), T, loc.data_ptr(), w.M * 4,
                                             self.ws.data_ptr(), self.ws.numel(), self._st))
+        self.split.allgather(loc, T, w.M, out, self._st)
 
     def _quant(self, x: torch.Tensor, K: int, T: int, act: torch.Tensor):
         check(lib().b200_quantize_activations(x.data_ptr(), x.stride(0) * 4, K, T, act.data_ptr(), act.numel(), self.variant, self._st))

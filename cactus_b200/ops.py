@@ -49,6 +49,17 @@ class QWeight:
         torch.cuda.current_stream().synchronize()  # src may be freed by the caller
         return QWeight(wtype, K, M, data)
 
+    def row_slice(self, r0: int, r1: int) -> "QWeight":
+        """Rows [r0, r1) as a weight of its own (a copy).  Tiles are stored row-tile-major, so a slice on 16-row
+        boundaries is one byte range of the quant plane plus one of the scale plane."""
+        assert 0 <= r0 < r1 <= self.M and r0 % 16 == 0 and (r1 % 16 == 0 or r1 == self.M), "row slices start and end on 16-row tiles"
+        n_rt, n_bg = (self.M + 15) // 16, (self.K // 32 + 3) // 4
+        tile = 1024 if self.wtype == Q4_0 else 2048
+        t0, t1 = r0 // 16, (r1 + 15) // 16
+        q = self.data[t0 * n_bg * tile:t1 * n_bg * tile]
+        d = self.data[n_rt * n_bg * tile + t0 * n_bg * 128:n_rt * n_bg * tile + t1 * n_bg * 128]
+        return QWeight(self.wtype, self.K, r1 - r0, torch.cat([q, d]))
+
     def to_blocks(self) -> torch.Tensor:
         L = lib()
         out = torch.empty((self.M, self.K // 32 * BLOCK_BYTES[self.wtype]), dtype=torch.uint8, device=self.data.device)

@@ -228,6 +228,32 @@ B200_API int b200_set_rows_f16(const float *x, int64_t x_nb_row, const int32_t *
  * cactus/cactus_completion.cpp:210); ties go to the lowest index */
 B200_API int b200_argmax_rows(const float *x, int64_t x_nb_row, int64_t d, int64_t rows, int32_t *out, b200_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Row-split mul_mat over the GPUs of one node (one process per GPU).
+ *
+ * The reference splits the rows of mul_mat weights over devices with a split buffer type
+ * (lm_ggml_backend_split_buffer_type, cactus/ggml-backend.h:188; requested by the loader for
+ * LLAMA_SPLIT_MODE_ROW, cactus/llama-model.cpp:339-351) and leaves the join to the backend.  Here each process
+ * computes its row range with b200_mul_mat_q* on a row slice of the weight (a slice on 16-row boundaries of a tiled
+ * weight is two byte ranges: quants, scales) and b200_allgather_rows joins the slices: it stores the caller's
+ * [T, M/g] slice at column rank*M/g of every rank's [T, M] buffer over NVLink and returns (in stream order) once
+ * every rank's slice has arrived in the caller's buffer.
+ *
+ * b200_peer_alloc allocates (zeroed) device memory that other processes can map: the 64-byte handle is passed to them
+ * by any host channel and opened with b200_peer_open.  Every rank allocates one dst region and one 64-byte flag block
+ * this way; dst_of_rank[r] / flags_of_rank[r] are rank r's dst buffer and flag block as mapped in the calling process
+ * (the caller's own allocation at index `rank`).  All ranks must issue the same sequence of b200_allgather_rows calls.
+ * The wait for the peers is bounded (seconds); b200_peer_status(own flag block) returns 0, or 1 + the first rank whose
+ * slice did not arrive.
+ * ------------------------------------------------------------------------------------------------ */
+B200_API int b200_peer_alloc(size_t bytes, void **ptr, unsigned char handle[64]);
+B200_API int b200_peer_open(const unsigned char handle[64], void **ptr);
+B200_API int b200_peer_close(void *ptr);
+B200_API int b200_peer_free(void *ptr);
+B200_API int b200_allgather_rows(const float *src, int64_t src_nb_row, int64_t T, int64_t Mg, int rank, int g, void *const *dst_of_rank,
+                                 int64_t dst_nb_row, void *const *flags_of_rank, b200_stream_t stream);
+B200_API int b200_peer_status(const void *flags);
+
 #ifdef __cplusplus
 }
 #endif

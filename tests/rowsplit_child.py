@@ -1,0 +1,81 @@
+"""One rank of the row-split tests (started by test_gpu_rowsplit.py with RANK / WORLD_SIZE / MASTER_* set).
+
+Part 1: the join alone -- every rank pushes a known slice, placement must be exact, repeated to exercise the
+collective counter.  Part 2: a small llama run row-split against the same model on one GPU (rank 0 holds both)."""
+import json
+import os
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+sys.path.insert(0, os.path.dirname(HERE))
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo")
+    from cactus_b200.engine import LlamaConfig, LlamaEngine, LlamaWeights
+    from cactus_b200.rowsplit import RowSplit
+    from llama_ref import tiny_model
+    from oracle.binding import Oracle, Q4_0
+
+    out = {"rank": rank}
+    rs = RowSplit(rank, world, 64 << 20)
+    # ---- part 1: the join ----
+    T, M = 5, 64 * world
+    Mg = M // world
+    dst = rs.carve(8, M)
+    st = torch.cuda.current_stream().cuda_stream
+    ok = True
+    for rep in range(3):
+        src = (torch.arange(T * Mg, device="cuda", dtype=torch.float32).view(T, Mg) + 1000 * rank + 100000 * rep)
+        rs.allgather(src, T, Mg, dst, st)
+        torch.cuda.synchronize()
+        want = torch.cat([torch.arange(T * Mg, dtype=torch.float32).view(T, Mg) + 1000 * r + 100000 * rep for r in range(world)], dim=1)
+        ok = ok and bool(torch.equal(dst[:T].cpu(), want))
+        dist.barrier()   # the next repetition overwrites dst: a one-buffer test needs what the model's buffer rotation gives
+    out["join_exact"] = ok
+    out["join_status"] = rs.status()
+    # ---- part 2: the model ----
+    oracle = Oracle()
+    cfg = LlamaConfig(n_layer=2, d_model=256, n_head=4, n_kv_head=2, d_ff=512, vocab=320, head_type=Q4_0)
+    arrays = tiny_model(oracle, cfg)
+    full = LlamaWeights.from_numpy(cfg, arrays)
+    eng = LlamaEngine(full.shard(rank, world), 256, max_tokens=32, use_graphs=True, split=rs)
+    rng = np.random.default_rng(1)
+    lens = [9, 4, 14]
+    tokens = rng.integers(0, cfg.vocab, sum(lens))
+    pos = np.concatenate([np.arange(n) for n in lens])
+    seq = np.concatenate([np.full(n, s) for s, n in enumerate(lens)])
+    slots = np.arange(sum(lens))
+    steps = [(tokens, pos, seq, slots)]
+    for step in range(2):
+        steps.append((rng.integers(0, cfg.vocab, 3), np.array(lens) + step, np.arange(3), sum(lens) + 3 * step + np.arange(3)))
+    got = [eng.decode(*s)[0].copy() for s in steps for _ in range(1)]
+    out["model_status"] = rs.status()
+    sums = torch.tensor([float(np.abs(g).sum()) for g in got], dtype=torch.float64)
+    gathered = [torch.zeros_like(sums) for _ in range(world)]
+    dist.all_gather(gathered, sums)
+    out["ranks_agree"] = all(bool(torch.equal(gathered[0], t)) for t in gathered)   # every rank ends with the same logits
+    if rank == 0:
+        single = LlamaEngine(full, 256, max_tokens=32, use_graphs=False)
+        errs, same_argmax = [], True
+        for s, g in zip(steps, got):
+            want, _ = single.decode(*s)
+            errs.append(float(np.abs(g - want).max() / np.abs(want).max()))
+            same_argmax = same_argmax and bool(np.array_equal(g.argmax(-1), want.argmax(-1)))
+        out["max_err_vs_single_gpu"] = max(errs)
+        out["same_argmax"] = same_argmax
+    dist.barrier()
+    rs.close()
+    print("RESULT " + json.dumps(out), flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,47 @@
+"""Row-split mul_mat over two GPUs: the peer-memory join places every slice exactly, and a small llama run row-split
+ends with the same logits on every rank and agrees with the one-GPU engine (the split changes which kernel variant
+and K split a product takes, so floats are compared with the model-level tolerance, greedy tokens exactly).
+Needs two GPUs; the single-GPU run skips it."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_row_split():
+    world, port = 2, free_port()
+    procs = []
+    for rank in range(world):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "rowsplit_child.py")], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.PIPE, text=True))
+    results = []
+    for p in procs:
+        try:
+            so, se = p.communicate(timeout=600)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        assert p.returncode == 0, se[-3000:]
+        line = [l for l in so.splitlines() if l.startswith("RESULT ")][-1]
+        results.append(json.loads(line[7:]))
+    for r in results:
+        assert r["join_exact"] and r["join_status"] == 0 and r["model_status"] == 0 and r["ranks_agree"], r
+    r0 = [r for r in results if r["rank"] == 0][0]
+    assert r0["same_argmax"] and r0["max_err_vs_single_gpu"] < 3e-2, r0
