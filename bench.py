@@ -194,7 +194,8 @@ def gpu_arm(args):
 
     from cactus_b200 import dist as bdist
     from cactus_b200 import lib
-    from cactus_b200.engine import LLAMA_3_8B, LlamaConfig, LlamaEngine, LlamaWeights
+    from cactus_b200.engine import LLAMA_3_8B, LLAMA_3_70B, LlamaConfig, LlamaEngine, LlamaWeights
+    from cactus_b200.rowsplit import RowSplit
 
     rank, world, local = bdist.env_rank()
     if not torch.cuda.is_available():
@@ -203,12 +204,20 @@ def gpu_arm(args):
     bdist.init("nccl", torch.device("cuda", local))
     L = lib()
 
-    cfg = LLAMA_3_8B if not args.small else LlamaConfig(4, 1024, 8, 2, 4096, 32000)
+    cfg = LlamaConfig(4, 1024, 8, 2, 4096, 32000) if args.small else (LLAMA_3_70B if args.model == "70b" else LLAMA_3_8B)
     lens, scale = prompt_lengths()
     cell_pos, cell_seq, head = prefilled_cells(lens)
-    weights = LlamaWeights.random(cfg, seed=rank)
-    eng = LlamaEngine(weights, N_CELLS, max_tokens=N_SEQ)
-    gen = torch.Generator(device="cuda").manual_seed(100 + rank)
+    rows = args.split == "rows" and world > 1
+    if rows:   # one job: every rank holds its rows of the weights and the whole (replicated) KV cache and activations
+        split = RowSplit(rank, world, 128 << 20)
+        weights = LlamaWeights.random(cfg, seed=0, rank=rank, world=world)
+        eng = LlamaEngine(weights, N_CELLS, max_tokens=N_SEQ, split=split)
+    else:
+        split = None
+        weights = LlamaWeights.random(cfg, seed=rank)
+        eng = LlamaEngine(weights, N_CELLS, max_tokens=N_SEQ)
+    jobs = 1 if rows else world
+    gen = torch.Generator(device="cuda").manual_seed(100 + (0 if rows else rank))
     for il in range(cfg.n_layer):      # the prefilled prompts: synthetic K/V ~ N(0, 1) in the cells the prompts own
         eng.k_cache[il][:head].copy_(torch.randn((head, eng.k_cache[il].shape[1]), device="cuda", generator=gen).half())
         eng.v_cache[il][:head].copy_(torch.randn((head, eng.v_cache[il].shape[1]), device="cuda", generator=gen).half())
@@ -249,7 +258,7 @@ def gpu_arm(args):
     ms = e0.elapsed_time(e1)
     clocks = sampler.stop()
     ms_max = bdist.max_over_ranks(ms, "cuda")
-    value = world * N_SEQ * K / (ms_max / 1e3)
+    value = jobs * N_SEQ * K / (ms_max / 1e3)
 
     # ---- e2e: the public call with host buffers, H2D of the inputs and D2H of the logits inside ---
     reset_state()
@@ -263,11 +272,12 @@ def gpu_arm(args):
         logits, tok = eng.decode(*decode_step_inputs(lens, head, s, tokens=tok))
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
-    e2e = bdist.job_throughput(N_SEQ * e2e_steps, dt, "cuda")
+    e2e = bdist.job_throughput(N_SEQ * e2e_steps, dt, "cuda") * jobs / world
     h2d = 4 * N_SEQ * 4
     d2h = N_SEQ * cfg.vocab * 4 + N_SEQ * 4
 
-    roof = mul_mat_roofline(eng, cfg) if rank == 0 else None
+    roof = mul_mat_roofline(eng, cfg) if (rank == 0 and not rows) else None
+    peer_status = split.status() if rows else 0
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_layer_sample(reps=2, warmup=1)
@@ -276,13 +286,17 @@ def gpu_arm(args):
         kv_bytes = int(lens.sum() + N_SEQ * (W + K / 2)) * cfg.n_layer * 2 * cfg.n_kv_head * cfg.head_dim * 2
         line = {
             "metric": METRIC, "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": round(ms_max / K, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": round(ms_max / K, 4), "higher_is_better": True, "scaling": "strong" if rows else "weak", "vs_baseline": None,
             "dtype": "int8 x int4/int8 block dots, f32 accumulate; f16 KV", "data": "synthetic",
-            "config": {"workload": "BASELINE configs[3]: Llama-3-8B architecture, random N(0,0.02) weights in Q4_0, 64 sequences, "
+            "config": {"workload": ("BASELINE configs[4] architecture (Llama-3-70B) on the configs[3] workload" if args.model == "70b" and not args.small
+                                    else "BASELINE configs[3]: Llama-3-8B architecture") + ", random N(0,0.02) weights in Q4_0, 64 sequences, "
                                    "unified f16 KV cache of 65536 cells, one decode ubatch of 64 tokens per step",
                        "prompt_lengths": f"U[16,2048] seed 0 scaled by {scale:.3f} to leave 128 decode cells per sequence; "
                                          f"{int(lens.sum())} prompt cells hold synthetic N(0,1) K/V",
-                       "parallelism": "one replica per GPU, no collective" if world > 1 else "single GPU",
+                       "parallelism": (f"row split over {world} GPUs: every mul_mat weight cut by rows, products joined by peer stores over NVLink "
+                                       f"(b200_allgather_rows), everything else replicated; peer_status {peer_status}") if rows
+                                      else ("one replica per GPU, no collective" if world > 1 else "single GPU"),
+                       "model": args.model if not args.small else "small",
                        "l2": "inputs larger than L2: 4.2 GB of weights and ~7 GB of KV are streamed every step"},
             "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
             "gpu_launches": int(launches0 * K), "launches_per_step": int(launches0),
@@ -290,6 +304,8 @@ def gpu_arm(args):
             "step_bytes": {"weights": cfg.weight_bytes_per_step(), "kv_read_about": kv_bytes},
         }
         print(json.dumps(line))
+    if rows:
+        split.close()
     bdist.shutdown()
 
 
@@ -321,6 +337,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--small", action="store_true", help="a small model for debugging the harness (not a bench number)")
+    ap.add_argument("--split", default="none", choices=["none", "rows"],
+                    help="rows: ONE job whose mul_mat weights are row-split over the GPUs and joined after every product (strong scaling); "
+                         "none: one replica per GPU (weak scaling, the default)")
+    ap.add_argument("--model", default="8b", choices=["8b", "70b"], help="70b: BASELINE configs[4] architecture on the same 64-sequence workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":

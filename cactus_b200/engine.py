@@ -89,17 +89,23 @@ class LlamaWeights:
         self.tensors: dict[str, object] = {}
 
     @staticmethod
-    def random(cfg: LlamaConfig, seed: int = 0) -> "LlamaWeights":
+    def random(cfg: LlamaConfig, seed: int = 0, rank: int = 0, world: int = 1) -> "LlamaWeights":
+        """Synthetic weights.  With ``world`` > 1 only this rank's rows of the mul_mat weights are generated (row
+        split); the embedding table, which every rank reads whole, comes from the shared seed."""
         w = LlamaWeights(cfg)
         gen = torch.Generator(device="cuda").manual_seed(seed)
         d = cfg.d_model
         w.tensors["token_embd.weight"] = QWeight.from_blocks(cfg.head_type, d, cfg.vocab, random_blocks(cfg.head_type, cfg.vocab, d, gen))
-        w.tensors["output.weight"] = QWeight.from_blocks(cfg.head_type, d, cfg.vocab, random_blocks(cfg.head_type, cfg.vocab, d, gen))
+        if world > 1:
+            from .rowsplit import row_bounds
+            gen = torch.Generator(device="cuda").manual_seed(seed * 1000 + 17 + rank)
+        rows = (lambda M: M) if world == 1 else (lambda M: row_bounds(M, world)[rank + 1] - row_bounds(M, world)[rank])
+        w.tensors["output.weight"] = QWeight.from_blocks(cfg.head_type, d, rows(cfg.vocab), random_blocks(cfg.head_type, rows(cfg.vocab), d, gen))
         w.tensors["output_norm.weight"] = torch.ones(d, device="cuda")
         names = {"wq": "attn_q", "wk": "attn_k", "wv": "attn_v", "wo": "attn_output", "gate": "ffn_gate", "up": "ffn_up", "down": "ffn_down"}
         for il in range(cfg.n_layer):
             for short, K, M in cfg.mul_mat_shapes():
-                w.tensors[f"blk.{il}.{names[short]}.weight"] = QWeight.from_blocks(cfg.layer_type, K, M, random_blocks(cfg.layer_type, M, K, gen))
+                w.tensors[f"blk.{il}.{names[short]}.weight"] = QWeight.from_blocks(cfg.layer_type, K, rows(M), random_blocks(cfg.layer_type, rows(M), K, gen))
             w.tensors[f"blk.{il}.attn_norm.weight"] = torch.ones(d, device="cuda")
             w.tensors[f"blk.{il}.ffn_norm.weight"] = torch.ones(d, device="cuda")
         return w
