@@ -17,6 +17,8 @@
 // flight per CTA to cover HBM latency) and the fragments are plain 128/64-bit shared loads.
 // grid = (row groups of 128, column chunks, K splits); with K splits > 1 partial tiles go to a workspace
 // and a second kernel adds them in a fixed order.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -128,7 +130,7 @@ struct MmqCfg {
 template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB>
 __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims, const uint8_t *__restrict__ w, ActDims act,
                                                           const uint8_t *__restrict__ aq, float *__restrict__ dst,
-                                                          int64_t dst_nb_row, float *__restrict__ partial, int ksplit, int canon) {
+                                                          int64_t dst_nb_row, float *__restrict__ partial, int ksplit, int canon, int cluster) {
     using S = MmqCfg<WTYPE, NTW, WN, MT, WM, STAGES>;
     constexpr int MMQ_STAGES = STAGES;
     constexpr int NT = NTW;              // n-tiles of this warp
@@ -303,6 +305,61 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
 
     // write back; Q4_0 quants were used as 16 * value
     constexpr float WS = (WTYPE == B200_TYPE_Q4_0) ? 0.0625f : 1.0f;
+    if (cluster) {
+        // The K splits of one output tile form a thread-block cluster (cluster dimension z = ksplit).  Every CTA parks its
+        // partial tile in its own shared memory; after a cluster barrier CTA r sums slice r of the tile over all CTAs,
+        // in split order, through distributed shared memory and writes it out.  No partial sums in global memory, no
+        // second kernel, and the summation order is fixed.
+        constexpr int ROWS = S::CTA_TILES * 16, COLS = S::NT * 8, TOTAL4 = ROWS * COLS / 4;
+        static_assert(ROWS * COLS * 4 <= S::TOTAL, "the partial tile reuses the copy ring");
+        __syncthreads();   // every warp is done with the ring
+        float *red = reinterpret_cast<float *>(smem);   // [col][row]
+#pragma unroll
+        for (int mt = 0; mt < MMQ_MT; ++mt) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float v0, v1;
+                    unpack2(y[mt][nt][h], v0, v1);
+                    const int r = (wm * MT + mt) * 16 + g + h * 8, c = (wn * NTW + nt) * 8 + 2 * t;
+                    red[c * ROWS + r] = v0 * WS;
+                    red[(c + 1) * ROWS + r] = v1 * WS;
+                }
+            }
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+        const int per4 = (TOTAL4 + ksplit - 1) / ksplit;   // float4 groups (4 consecutive rows of one column) per CTA
+        const uint32_t red_u32 = (uint32_t) __cvta_generic_to_shared(red);
+        for (int i = tid; i < per4; i += MMQ_THREADS) {
+            const int q4 = ks * per4 + i;
+            if (q4 >= TOTAL4) break;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int k = 0; k < ksplit; ++k) {
+                uint32_t remote;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(red_u32 + (uint32_t) q4 * 16u), "r"(k));
+                float4 v;
+                asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote));
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            const int c = (q4 * 4) / ROWS, r = (q4 * 4) % ROWS;
+            const int64_t col = cta_nt0 * 8 + c, row = cta_rt0 * 16 + r;
+            if (col < act.N) {
+                float *o = reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + col * dst_nb_row + row * 4);
+                if (row + 3 < dims.M && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+                    *reinterpret_cast<float4 *>(o) = acc;
+                } else {
+                    if (row < dims.M) o[0] = acc.x;
+                    if (row + 1 < dims.M) o[1] = acc.y;
+                    if (row + 2 < dims.M) o[2] = acc.z;
+                    if (row + 3 < dims.M) o[3] = acc.w;
+                }
+            }
+        }
+        // nobody leaves while a neighbour may still read its tile
+        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+        return;
+    }
 #pragma unroll
     for (int mt = 0; mt < MMQ_MT; ++mt) {
         const int64_t row_base = (rt0 + mt) * 16 + g;
@@ -358,16 +415,64 @@ struct MmqVariant {
     int cta_tiles;   // 16-row tiles per CTA
     int cta_nt;      // 8-column tiles per CTA
     int ctas_per_sm; // resident CTAs per SM (filled on first use)
-    int (*launch)(const TiledDims &, const uint8_t *, const ActDims &, const uint8_t *, float *, int64_t, float *, int, int, cudaStream_t);
+    int (*launch)(const TiledDims &, const uint8_t *, const ActDims &, const uint8_t *, float *, int64_t, float *, int, int, int, cudaStream_t);
+    int (*max_clusters)(int);   // resident clusters of `ksplit` CTAs on this device (0 = cannot be launched that way)
 };
 
 template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB>
 static int launch_variant(const TiledDims &d, const uint8_t *w, const ActDims &a, const uint8_t *aq, float *dst, int64_t dst_nb_row,
-                          float *partial, int ksplit, int canon, cudaStream_t st) {
+                          float *partial, int ksplit, int canon, int cluster, cudaStream_t st) {
     using S = MmqCfg<WTYPE, NTW, WN, MT, WM, STAGES>;
     dim3 grid((unsigned) ((d.n_rt + S::CTA_TILES - 1) / S::CTA_TILES), (unsigned) ((a.n_nt + S::NT - 1) / S::NT), (unsigned) ksplit);
-    mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB><<<grid, S::THREADS, S::TOTAL, st>>>(d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon);
-    return check_launch("mmq");
+    if (!cluster) {
+        mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB><<<grid, S::THREADS, S::TOTAL, st>>>(d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 0);
+        return check_launch("mmq");
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(S::THREADS);
+    cfg.dynamicSmemBytes = S::TOTAL;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = (unsigned) ksplit;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB>, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 1);
+    if (e != cudaSuccess) return set_error(B200_E_CUDA, "mmq cluster launch: %s", cudaGetErrorString(e));
+    count_launch();
+    return B200_OK;
+}
+
+template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB>
+static int max_clusters_variant(int ksplit) {
+    using S = MmqCfg<WTYPE, NTW, WN, MT, WM, STAGES>;
+    static int cache[64][9];   // per device and cluster size: 0 = not asked yet, -1 = none, else the count
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev &= 63;
+    if (ksplit < 2 || ksplit > 8) return 0;
+    if (cache[dev][ksplit] != 0) return cache[dev][ksplit] < 0 ? 0 : cache[dev][ksplit];
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, 1, (unsigned) ksplit);
+    cfg.blockDim = dim3(S::THREADS);
+    cfg.dynamicSmemBytes = S::TOTAL;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = (unsigned) ksplit;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+    }
+    cache[dev][ksplit] = n > 0 ? n : -1;
+    return n;
 }
 
 template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES = 4, int MINB = 1>
@@ -377,6 +482,7 @@ static MmqVariant make_variant() {
     v.cta_tiles = S::CTA_TILES;
     v.cta_nt = S::NT;
     v.launch = launch_variant<WTYPE, NTW, WN, MT, WM, STAGES, MINB>;
+    v.max_clusters = max_clusters_variant<WTYPE, NTW, WN, MT, WM, STAGES, MINB>;
     cudaFuncSetAttribute(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     int n = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB>, S::THREADS, S::TOTAL) != cudaSuccess || n <= 0) {
@@ -421,20 +527,41 @@ static const MmqVariant &pick_variant(int64_t N) {
 }
 
 // K splits: the CTA count is made to fit whole waves of resident CTAs; each split pays about three block
-// groups of fixed cost (pipeline fill, write-back, the later reduction)
-static int choose_ksplit(const MmqVariant &v, const TiledDims &d, int64_t n_nt) {
+// groups of fixed cost (pipeline fill, write-back).  Up to 8 splits can run as one thread-block cluster that sums
+// its partial tiles through distributed shared memory; more splits, or a device that cannot place such clusters,
+// write partial sums to the workspace for the reduction kernel (about two block groups' worth of time more).
+static int choose_ksplit(const MmqVariant &v, const TiledDims &d, int64_t n_nt, bool *cluster) {
+    static int allow = -1;
+    if (allow < 0) {
+        const char *e = getenv("B200_MMQ_CLUSTER");
+        allow = (e && atoi(e) == 0) ? 0 : 1;
+    }
     const int64_t ctas = ((d.n_rt + v.cta_tiles - 1) / v.cta_tiles) * ((n_nt + v.cta_nt - 1) / v.cta_nt);
     const int64_t slots = (int64_t) sm_count() * v.ctas_per_sm;
     int best = 1;
     int64_t best_cost = -1;
+    *cluster = false;
     for (int ks = 1; ks <= 16; ++ks) {
         const int64_t per = (d.n_bg + ks - 1) / ks;
         if (ks > 1 && per < 2) break;
         const int64_t waves = (ctas * ks + slots - 1) / slots;
-        const int64_t cost = waves * (per + 3) + (ks > 1 ? 2 : 0);
+        const int64_t cost = 2 * (waves * (per + 3) + (ks > 1 ? 2 : 0));
         if (best_cost < 0 || cost < best_cost) {
             best_cost = cost;
             best = ks;
+            *cluster = false;
+        }
+        if (allow && ks >= 2 && ks <= 8) {
+            const int64_t cslots = (int64_t) v.max_clusters(ks) * ks;
+            if (cslots > 0) {
+                const int64_t cwaves = (ctas * ks + cslots - 1) / cslots;
+                const int64_t ccost = 2 * cwaves * (per + 3) + 1;
+                if (ccost < best_cost) {
+                    best_cost = ccost;
+                    best = ks;
+                    *cluster = true;
+                }
+            }
         }
     }
     return best;
@@ -463,13 +590,14 @@ void launch_mmq_reduce(const float *partial, int ks, int64_t M, int64_t N, float
 int launch_mmq(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
                void *workspace, size_t workspace_bytes, cudaStream_t st, bool canon) {
     const MmqVariant &v = variant_for(wtype, a.N);
-    int ks = choose_ksplit(v, d, a.n_nt);
+    bool cluster = false;
+    int ks = choose_ksplit(v, d, a.n_nt, &cluster);
     const size_t per_split = (size_t) a.N * d.M * sizeof(float);
-    if (ks > 1 && (!workspace || workspace_bytes < per_split * ks)) {
+    if (ks > 1 && !cluster && (!workspace || workspace_bytes < per_split * ks)) {
         ks = workspace ? (int) std::max<size_t>(1, workspace_bytes / per_split) : 1;  // fewer splits fit: still correct, only slower
     }
-    if (int e = v.launch(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, (float *) workspace, ks, canon ? 1 : 0, st)) return e;
-    if (ks > 1) {
+    if (int e = v.launch(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, (float *) workspace, ks, canon ? 1 : 0, cluster ? 1 : 0, st)) return e;
+    if (ks > 1 && !cluster) {
         const int64_t total = d.M * a.N;
         mmq_reduce_kernel<<<(unsigned) ((total + 255) / 256), 256, 0, st>>>((const float *) workspace, ks, d.M, a.N, dst, dst_nb_row);
         return check_launch("mmq_reduce");
