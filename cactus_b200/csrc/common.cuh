@@ -104,4 +104,54 @@ __device__ __forceinline__ void q8_scales(float amax, int variant, __half *d_out
     }
 }
 
+// Stores one lane's share (4 quants, element group j of 8) of a quantised block (row n, block b).  LAYOUT 0: the
+// reference's block_q8_0 stream; 1: B8 tiles in mma.sync B-fragment order; 2: B8 tiles as K-major core matrices.
+// Lane j == 0 also stores the block scale (layouts 1/2: the f32 pair {d, -d * 12582912}; zero for padding).
+template <int LAYOUT>
+__device__ __forceinline__ void q8_store(uint8_t *__restrict__ out, size_t d_offset, int64_t nb, int64_t nbp, int64_t n, int64_t b, int j,
+                                         uint32_t packed, __half d, bool real) {
+    if (LAYOUT == 0) {
+        uint8_t *blkp = out + (n * nb + b) * 34;
+        if (j == 0) *reinterpret_cast<__half *>(blkp) = d;
+        uint16_t *q = reinterpret_cast<uint16_t *>(blkp + 2 + 4 * j);
+        q[0] = (uint16_t) (packed & 0xffffu);
+        q[1] = (uint16_t) (packed >> 16);
+    } else {
+        const int64_t nt = n >> 3;
+        const int g = (int) (n & 7);
+        const int t = j & 3;
+        uint8_t *tile = out + (nt * nbp + b) * 256;
+        if (LAYOUT == 1) {
+            *reinterpret_cast<uint32_t *>(tile + (g * 4 + t) * 8 + (j >= 4 ? 4 : 0)) = packed;
+        } else {
+            // two 8-column x 16-byte core matrices: elements 0..15 of each column, then elements 16..31
+            *reinterpret_cast<uint32_t *>(tile + (j >> 2) * 128 + g * 16 + t * 4) = packed;
+        }
+        if (j == 0) {
+            float *dp = reinterpret_cast<float *>(out + d_offset) + (nt * (nbp >> 2) + (b >> 2)) * 64 + act_scale_index((int) (b & 3), g);
+            const float df = real ? __half2float(d) : 0.0f;
+            dp[0] = df;
+            dp[2] = -df * ACT_MAGIC;
+        }
+    }
+}
+
+// quantises the 4 values of one lane of an 8-lane block group (all 8 lanes of the group must call it) and stores them
+template <int LAYOUT>
+__device__ __forceinline__ void q8_quantize_store(const float (&v)[4], uint8_t *__restrict__ out, size_t d_offset, int64_t nb, int64_t nbp,
+                                                  int64_t n, int64_t b, int j, bool real, int variant) {
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    const unsigned grp = 0xFFu << (threadIdx.x & 24);  // the 8 lanes that share this block
+    amax = fmaxf(amax, __shfl_xor_sync(grp, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(grp, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(grp, amax, 4));
+    __half d;
+    float id;
+    q8_scales(amax, variant, &d, &id);
+    uint32_t packed = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) packed |= ((uint32_t) (q8_round(v[i], id, variant) & 0xff)) << (8 * i);
+    q8_store<LAYOUT>(out, d_offset, nb, nbp, n, b, j, packed, d, real);
+}
+
 }  // namespace b200

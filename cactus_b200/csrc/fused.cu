@@ -1,0 +1,221 @@
+// Fused forms of the small ops between the mul_mats of a llama layer (llm_build_llama, cactus/llama-model.cpp:4517-4671).
+// Each one computes exactly what the chain of separate ops computes -- same float operations in the same order -- and
+// hands the result to the next mul_mat already quantised, so the intermediate f32 tensors need not be written:
+//   residual ADD (ops.cpp:1283-1300) + RMS_NORM (ops.cpp:3268-3316) + MUL by the norm weight + quantize_row_q8_0
+//   SILU (ops.cpp:2902-2981) * up + quantize_row_q8_0
+//   ROPE of q and k (ops.cpp:5080-5362) + the f32 -> f16 stores of k and v into the cache rows (cpy_k / cpy_v,
+//   cactus/llama-kv-cache.cpp:617-656)
+#include "common.cuh"
+
+namespace b200 {
+
+bool act_layout_canonical(int64_t N);
+
+// One CTA per (padded) token row.  The sum of squares is accumulated exactly as rms_norm_kernel does (per-thread
+// strided partial sums in double, shuffle tree, warps in order), so the scale -- and with it every quantised value --
+// is bit-identical to the unfused chain.
+template <int LAYOUT>
+__global__ void __launch_bounds__(256) add_rms_norm_quantize_kernel(float *__restrict__ x, int64_t x_nb_row, const float *__restrict__ res,
+                                                                   int64_t res_nb_row, const float *__restrict__ w, float *__restrict__ h,
+                                                                   int64_t h_nb_row, int64_t d, int64_t N, float eps, int64_t nb, int64_t nbp,
+                                                                   uint8_t *__restrict__ out, size_t d_offset, int variant) {
+    const int64_t n = blockIdx.x;
+    const bool row_real = n < N;
+    float sc = 0.0f;
+    float *xr = nullptr;
+    if (row_real) {
+        xr = reinterpret_cast<float *>(reinterpret_cast<char *>(x) + n * x_nb_row);
+        const float *rr = res ? reinterpret_cast<const float *>(reinterpret_cast<const char *>(res) + n * res_nb_row) : nullptr;
+        double sum = 0.0;
+        for (int64_t i = threadIdx.x; i < d; i += blockDim.x) {
+            float v = xr[i];
+            if (rr) {
+                v = v + rr[i];
+                xr[i] = v;
+            }
+            sum += (double) (v * v);
+        }
+        __shared__ double red[8];
+        for (int o2 = 16; o2 > 0; o2 >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o2);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+        __syncthreads();   // also orders this CTA's stores to xr before the reads below
+        double tot = 0.0;
+        for (int i = 0; i < (int) (blockDim.x >> 5); ++i) tot += red[i];
+        const float mean = (float) (tot / (double) d);
+        sc = 1.0f / sqrtf(mean + eps);
+    }
+    float *hr = (h && row_real) ? reinterpret_cast<float *>(reinterpret_cast<char *>(h) + n * h_nb_row) : nullptr;
+    // groups of 4 elements: 8 consecutive threads share a block of 32
+    for (int64_t grp4 = threadIdx.x; grp4 < nbp * 8; grp4 += blockDim.x) {
+        const int64_t b = grp4 >> 3;
+        const int j = (int) (grp4 & 7);
+        const bool real = row_real && b < nb;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (real) {
+            const int64_t e = b * 32 + j * 4;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float t = xr[e + i] * sc;
+                v[i] = w ? t * w[e + i] : t;
+            }
+            if (hr) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) hr[e + i] = v[i];
+            }
+        }
+        q8_quantize_store<LAYOUT>(v, out, d_offset, nb, nbp, n, b, j, real, variant);
+    }
+}
+
+// silu(gate) * up, quantised; the same index space as quantize_q8_0_kernel
+template <int LAYOUT>
+__global__ void __launch_bounds__(256) silu_mul_quantize_kernel(const float *__restrict__ gate, const float *__restrict__ up, int64_t nb_row,
+                                                               int64_t N, int64_t n_rows_padded, int64_t nb, int64_t nbp,
+                                                               uint8_t *__restrict__ out, size_t d_offset, int variant) {
+    const int64_t gid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    const int j = (int) (gid & 7);
+    const int64_t blk = gid >> 3;
+    const int64_t n = blk / nbp;
+    const int64_t b = blk - n * nbp;
+    if (n >= n_rows_padded) return;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    const bool real = (n < N) && (b < nb);
+    if (real) {
+        const float4 a = *reinterpret_cast<const float4 *>(reinterpret_cast<const char *>(gate) + n * nb_row + (b * 32 + j * 4) * 4);
+        const float4 u = *reinterpret_cast<const float4 *>(reinterpret_cast<const char *>(up) + n * nb_row + (b * 32 + j * 4) * 4);
+        const float ga[4] = {a.x, a.y, a.z, a.w}, ua[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float s = ga[i] / (1.0f + expf(-ga[i]));
+            v[i] = s * ua[i];
+        }
+    }
+    q8_quantize_store<LAYOUT>(v, out, d_offset, nb, nbp, n, b, j, real, variant);
+}
+
+// One CTA per token: the angles as rope_norm_kernel builds them, q rotated in place, k rotated and stored as f16 into
+// its cache row, v stored as f16 into its cache row.
+__global__ void __launch_bounds__(256) rope_store_kernel(float *__restrict__ q, int64_t q_nb_head, int64_t q_nb_tok, const float *__restrict__ k,
+                                                        int64_t k_nb_head, int64_t k_nb_tok, const float *__restrict__ v, int64_t v_nb_tok,
+                                                        int64_t D, int64_t H, int64_t Hkv, int n_dims, const int32_t *__restrict__ pos,
+                                                        const float *__restrict__ ff, float theta_scale, float freq_scale, float attn_factor,
+                                                        const int32_t *__restrict__ slots, __half *__restrict__ kc, int64_t kc_nb_row,
+                                                        __half *__restrict__ vc, int64_t vc_nb_row) {
+    extern __shared__ float cs[];   // [n_dims/2] cos, [n_dims/2] sin
+    const int64_t t = blockIdx.x;
+    const int half_dims = n_dims / 2;
+    if (threadIdx.x == 0) {
+        float theta = (float) pos[t];
+        for (int i = 0; i < half_dims; ++i) {
+            cs[i] = theta;
+            theta *= theta_scale;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < half_dims; i += blockDim.x) {
+        const float f = ff ? ff[i] : 1.0f;
+        const float th = freq_scale * (cs[i] / f);
+        cs[half_dims + i] = sinf(th) * attn_factor;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < half_dims; i += blockDim.x) {
+        const float f = ff ? ff[i] : 1.0f;
+        const float th = freq_scale * (cs[i] / f);
+        cs[i] = cosf(th) * attn_factor;
+    }
+    __syncthreads();
+    const int64_t pairs = D / 2;
+    const int64_t slot = slots[t];
+    __half *krow = reinterpret_cast<__half *>(reinterpret_cast<char *>(kc) + slot * kc_nb_row);
+    __half *vrow = reinterpret_cast<__half *>(reinterpret_cast<char *>(vc) + slot * vc_nb_row);
+    for (int64_t i = threadIdx.x; i < (H + 2 * Hkv) * pairs; i += blockDim.x) {
+        const int64_t hh = i / pairs, p = i - hh * pairs;
+        if (hh < H) {
+            float *s = reinterpret_cast<float *>(reinterpret_cast<char *>(q) + t * q_nb_tok + hh * q_nb_head) + 2 * p;
+            const float2 x = *reinterpret_cast<const float2 *>(s);
+            if (p < half_dims) {
+                const float c = cs[p], sn = cs[half_dims + p];
+                *reinterpret_cast<float2 *>(s) = make_float2(x.x * c - x.y * sn, x.x * sn + x.y * c);
+            }
+        } else if (hh < H + Hkv) {
+            const int64_t hk = hh - H;
+            const float2 x = *reinterpret_cast<const float2 *>(reinterpret_cast<const float *>(reinterpret_cast<const char *>(k) + t * k_nb_tok + hk * k_nb_head) + 2 * p);
+            float2 r = x;
+            if (p < half_dims) {
+                const float c = cs[p], sn = cs[half_dims + p];
+                r = make_float2(x.x * c - x.y * sn, x.x * sn + x.y * c);
+            }
+            *reinterpret_cast<__half2 *>(krow + hk * D + 2 * p) = __halves2half2(__float2half_rn(r.x), __float2half_rn(r.y));
+        } else {
+            const int64_t hv = hh - H - Hkv;
+            const float2 x = *reinterpret_cast<const float2 *>(reinterpret_cast<const float *>(reinterpret_cast<const char *>(v) + t * v_nb_tok) + hv * D + 2 * p);
+            *reinterpret_cast<__half2 *>(vrow + hv * D + 2 * p) = __halves2half2(__float2half_rn(x.x), __float2half_rn(x.y));
+        }
+    }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_add_rms_norm_quantize(float *x, int64_t x_nb_row, const float *residual, int64_t residual_nb_row, const float *w, float *h,
+                               int64_t h_nb_row, int64_t d, int64_t rows, float eps, void *scratch, size_t scratch_bytes, int variant,
+                               b200_stream_t stream) {
+    B200_REQUIRE(x && scratch && d > 0 && d % 32 == 0 && rows > 0, "bad arguments");
+    B200_REQUIRE(x_nb_row % 4 == 0 && residual_nb_row % 4 == 0 && h_nb_row % 4 == 0, "row strides must be multiples of 4 bytes");
+    B200_REQUIRE(variant == B200_Q8_AVX2 || variant == B200_Q8_SCALAR, "unknown quantiser variant %d", variant);
+    B200_REQUIRE(is_aligned(scratch, 256), "scratch must be 256-byte aligned");
+    const ActDims a = act_dims(d, rows);
+    if (scratch_bytes < a.total_bytes) return set_error(B200_E_SCRATCH, "scratch too small: %zu < %zu", scratch_bytes, a.total_bytes);
+    const unsigned grid = (unsigned) (a.n_nt * 8);
+    cudaStream_t st = (cudaStream_t) stream;
+    if (act_layout_canonical(rows)) {
+        add_rms_norm_quantize_kernel<2><<<grid, 256, 0, st>>>(x, x_nb_row, residual, residual_nb_row, w, h, h_nb_row, d, rows, eps, a.nb, a.nbp,
+                                                              (uint8_t *) scratch, a.d_offset, variant);
+    } else {
+        add_rms_norm_quantize_kernel<1><<<grid, 256, 0, st>>>(x, x_nb_row, residual, residual_nb_row, w, h, h_nb_row, d, rows, eps, a.nb, a.nbp,
+                                                              (uint8_t *) scratch, a.d_offset, variant);
+    }
+    return check_launch("add_rms_norm_quantize");
+}
+
+int b200_silu_mul_quantize(const float *gate, const float *up, int64_t nb_row, int64_t K, int64_t N, void *scratch, size_t scratch_bytes,
+                           int variant, b200_stream_t stream) {
+    B200_REQUIRE(gate && up && scratch && K > 0 && K % 32 == 0 && N > 0, "bad arguments");
+    B200_REQUIRE(nb_row % 16 == 0 && is_aligned(gate, 16) && is_aligned(up, 16), "rows must be 16-byte aligned");
+    B200_REQUIRE(variant == B200_Q8_AVX2 || variant == B200_Q8_SCALAR, "unknown quantiser variant %d", variant);
+    B200_REQUIRE(is_aligned(scratch, 256), "scratch must be 256-byte aligned");
+    const ActDims a = act_dims(K, N);
+    if (scratch_bytes < a.total_bytes) return set_error(B200_E_SCRATCH, "scratch too small: %zu < %zu", scratch_bytes, a.total_bytes);
+    const int64_t rows_padded = a.n_nt * 8;
+    const int64_t threads = rows_padded * a.nbp * 8;
+    const unsigned grid = (unsigned) ((threads + 255) / 256);
+    cudaStream_t st = (cudaStream_t) stream;
+    if (act_layout_canonical(N)) {
+        silu_mul_quantize_kernel<2><<<grid, 256, 0, st>>>(gate, up, nb_row, N, rows_padded, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
+    } else {
+        silu_mul_quantize_kernel<1><<<grid, 256, 0, st>>>(gate, up, nb_row, N, rows_padded, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
+    }
+    return check_launch("silu_mul_quantize");
+}
+
+int b200_rope_store(float *q, int64_t q_nb_head, int64_t q_nb_tok, const float *k, int64_t k_nb_head, int64_t k_nb_tok, const float *v,
+                    int64_t v_nb_tok, int64_t D, int64_t H, int64_t Hkv, int64_t T, int n_dims, const int32_t *pos, const float *freq_factors,
+                    float freq_base, float freq_scale, float attn_factor, const int32_t *slots, void *k_cache, int64_t k_cache_nb_row,
+                    void *v_cache, int64_t v_cache_nb_row, b200_stream_t stream) {
+    B200_REQUIRE(q && k && v && pos && slots && k_cache && v_cache, "null pointer");
+    B200_REQUIRE(D > 0 && D % 2 == 0 && H > 0 && Hkv > 0 && T >= 0 && n_dims > 0 && n_dims <= D && n_dims % 2 == 0, "bad rope arguments");
+    B200_REQUIRE(q_nb_head % 8 == 0 && q_nb_tok % 8 == 0 && k_nb_head % 8 == 0 && k_nb_tok % 8 == 0 && v_nb_tok % 8 == 0 && is_aligned(q, 8) &&
+                     is_aligned(k, 8) && is_aligned(v, 8) && k_cache_nb_row % 4 == 0 && v_cache_nb_row % 4 == 0 && is_aligned(k_cache, 4) && is_aligned(v_cache, 4),
+                 "pairs must be 8-byte aligned (f32) / 4-byte aligned (f16)");
+    if (T == 0) return B200_OK;
+    const float theta_scale = powf(freq_base, -2.0f / (float) n_dims);
+    rope_store_kernel<<<(unsigned) T, 256, (size_t) n_dims * sizeof(float), (cudaStream_t) stream>>>(
+        q, q_nb_head, q_nb_tok, k, k_nb_head, k_nb_tok, v, v_nb_tok, D, H, Hkv, n_dims, pos, freq_factors, theta_scale, freq_scale, attn_factor,
+        slots, (__half *) k_cache, k_cache_nb_row, (__half *) v_cache, v_cache_nb_row);
+    return check_launch("rope_store");
+}
+
+}  // extern "C"

@@ -35,42 +35,7 @@ __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float *__restr
             v[0] = row[0]; v[1] = row[1]; v[2] = row[2]; v[3] = row[3];
         }
     }
-    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-    const unsigned grp = 0xFFu << (threadIdx.x & 24);  // the 8 lanes that share this block
-    amax = fmaxf(amax, __shfl_xor_sync(grp, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(grp, amax, 2));
-    amax = fmaxf(amax, __shfl_xor_sync(grp, amax, 4));
-    __half d;
-    float id;
-    q8_scales(amax, variant, &d, &id);
-    uint32_t packed = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) packed |= ((uint32_t) (q8_round(v[i], id, variant) & 0xff)) << (8 * i);
-
-    if (LAYOUT == 0) {
-        uint8_t *blkp = out + (n * nb + b) * 34;
-        if (j == 0) *reinterpret_cast<__half *>(blkp) = d;
-        uint16_t *q = reinterpret_cast<uint16_t *>(blkp + 2 + 4 * j);
-        q[0] = (uint16_t) (packed & 0xffffu);
-        q[1] = (uint16_t) (packed >> 16);
-    } else {
-        const int64_t nt = n >> 3;
-        const int g = (int) (n & 7);
-        const int t = j & 3;
-        uint8_t *tile = out + (nt * nbp + b) * 256;
-        if (LAYOUT == 1) {
-            *reinterpret_cast<uint32_t *>(tile + (g * 4 + t) * 8 + (j >= 4 ? 4 : 0)) = packed;
-        } else {
-            // two 8-column x 16-byte core matrices: elements 0..15 of each column, then elements 16..31
-            *reinterpret_cast<uint32_t *>(tile + (j >> 2) * 128 + g * 16 + t * 4) = packed;
-        }
-        if (j == 0) {
-            float *dp = reinterpret_cast<float *>(out + d_offset) + (nt * (nbp >> 2) + (b >> 2)) * 64 + act_scale_index((int) (b & 3), g);
-            const float df = real ? __half2float(d) : 0.0f;
-            dp[0] = df;
-            dp[2] = -df * ACT_MAGIC;
-        }
-    }
+    q8_quantize_store<LAYOUT>(v, out, d_offset, nb, nbp, n, b, j, real, variant);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -178,7 +178,7 @@ class LlamaEngine:
         out = split.carve if split is not None else f32   # mul_mat outputs: where the peers' slices land
         self.q, self.k, self.v = out(T, cfg.d_model), out(T, kvd), out(T, kvd)
         self.gate, self.up = out(T, cfg.d_ff), out(T, cfg.d_ff)
-        self.tmp = out(T, cfg.d_model)
+        self.tmp, self.tmp2 = out(T, cfg.d_model), out(T, cfg.d_model)   # attention branch / feed-forward branch of the residual
         self.logits = out(T, cfg.vocab)
         self.local = f32(T * (max(cfg.d_ff, cfg.vocab) // g + 16)) if split is not None else None
         self.next_ids = torch.zeros(T, dtype=torch.int32, device=dev)
@@ -221,36 +221,39 @@ class LlamaEngine:
         check(L.b200_mask_index_build(self.mask.data_ptr(), nkv * 2, T, nkv, self.index.data_ptr(), self.index.numel(), st))
         emb: QWeight = self.w.tensors["token_embd.weight"]
         check(L.b200_get_rows_q(emb.wtype, emb.data.data_ptr(), emb.K, emb.M, tokens, self.x.data_ptr(), d * 4, T, st))
-        x, h = self.x, self.h
+        x = self.x
+        V = self.variant
+
+        def norm_quant(weight: str, residual):
+            """x (+= residual) -> rms_norm * weight -> quantised into act_d; one launch"""
+            check(L.b200_add_rms_norm_quantize(x.data_ptr(), d * 4, residual.data_ptr() if residual is not None else None, d * 4,
+                                               self.w.tensors[weight].data_ptr(), None, 0, d, T, cfg.eps, self.act_d.data_ptr(), self.act_d.numel(), V, st))
+
+        pending = None   # the residual branch not yet added to x: folded into the next norm
         for il in range(cfg.n_layer):
             p = f"blk.{il}."
-            check(L.b200_rms_norm(x.data_ptr(), d * 4, self.w.tensors[p + "attn_norm.weight"].data_ptr(), h.data_ptr(), d * 4, d, T, cfg.eps, st))
-            self._quant(h, d, T, self.act_d)
+            norm_quant(p + "attn_norm.weight", pending)
             self._mm(p + "attn_q.weight", self.act_d, T, self.q)
             self._mm(p + "attn_k.weight", self.act_d, T, self.k)
             self._mm(p + "attn_v.weight", self.act_d, T, self.v)
-            check(L.b200_rope_norm(self.q.data_ptr(), D * 4, d * 4, self.q.data_ptr(), D * 4, d * 4, D, H, T, D, pos, None, cfg.rope_theta, 1.0, 1.0, st))
-            check(L.b200_rope_norm(self.k.data_ptr(), D * 4, kvd * 4, self.k.data_ptr(), D * 4, kvd * 4, D, Hkv, T, D, pos, None, cfg.rope_theta, 1.0, 1.0, st))
             kc, vc = self.k_cache[il], self.v_cache[il]
-            check(L.b200_set_rows_f16(self.k.data_ptr(), kvd * 4, slots, kc.data_ptr(), kvd * 2, kvd, T, st))
-            check(L.b200_set_rows_f16(self.v.data_ptr(), kvd * 4, slots, vc.data_ptr(), kvd * 2, kvd, T, st))
+            check(L.b200_rope_store(self.q.data_ptr(), D * 4, d * 4, self.k.data_ptr(), D * 4, kvd * 4, self.v.data_ptr(), kvd * 4, D, H, Hkv, T, D,
+                                    pos, None, cfg.rope_theta, 1.0, 1.0, slots, kc.data_ptr(), kvd * 2, vc.data_ptr(), kvd * 2, st))
             check(L.b200_flash_attn_ext_indexed(D, H, Hkv, T, nkv, self.q.data_ptr(), d * 4, D * 4, kc.data_ptr(), kvd * 2, D * 2,
                                                 vc.data_ptr(), kvd * 2, D * 2, self.mask.data_ptr(), nkv * 2, self.index.data_ptr(),
                                                 D ** -0.5, 0.0, 0.0, self.attn.data_ptr(), self.fa_scratch.data_ptr(),
                                                 self.fa_scratch.numel(), st))
             self._quant(self.attn, d, T, self.act_d)
             self._mm(p + "attn_output.weight", self.act_d, T, self.tmp)
-            check(L.b200_add(x.data_ptr(), self.tmp.data_ptr(), x.data_ptr(), d, T, T, st))
-            check(L.b200_rms_norm(x.data_ptr(), d * 4, self.w.tensors[p + "ffn_norm.weight"].data_ptr(), h.data_ptr(), d * 4, d, T, cfg.eps, st))
-            self._quant(h, d, T, self.act_d)
+            norm_quant(p + "ffn_norm.weight", self.tmp)
             self._mm(p + "ffn_gate.weight", self.act_d, T, self.gate)
             self._mm(p + "ffn_up.weight", self.act_d, T, self.up)
-            check(L.b200_silu(self.gate.data_ptr(), self.up.data_ptr(), self.gate.data_ptr(), T * cfg.d_ff, st))
-            self._quant(self.gate, cfg.d_ff, T, self.act_ff)
-            self._mm(p + "ffn_down.weight", self.act_ff, T, self.tmp)
-            check(L.b200_add(x.data_ptr(), self.tmp.data_ptr(), x.data_ptr(), d, T, T, st))
-        check(L.b200_rms_norm(x.data_ptr(), d * 4, self.w.tensors["output_norm.weight"].data_ptr(), h.data_ptr(), d * 4, d, T, cfg.eps, st))
-        self._quant(h, d, T, self.act_d)
+            check(L.b200_silu_mul_quantize(self.gate.data_ptr(), self.up.data_ptr(), cfg.d_ff * 4, cfg.d_ff, T, self.act_ff.data_ptr(),
+                                           self.act_ff.numel(), V, st))
+            self._mm(p + "ffn_down.weight", self.act_ff, T, self.tmp2)
+            pending = self.tmp2
+        check(L.b200_add_rms_norm_quantize(x.data_ptr(), d * 4, pending.data_ptr(), d * 4, self.w.tensors["output_norm.weight"].data_ptr(), None, 0,
+                                           d, T, cfg.eps, self.act_d.data_ptr(), self.act_d.numel(), V, st))
         self._mm("output.weight", self.act_d, T, self.logits)
         check(L.b200_argmax_rows(self.logits.data_ptr(), cfg.vocab * 4, cfg.vocab, T, self.next_ids.data_ptr(), st))
 

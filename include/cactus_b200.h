@@ -229,6 +229,28 @@ B200_API int b200_set_rows_f16(const float *x, int64_t x_nb_row, const int32_t *
 B200_API int b200_argmax_rows(const float *x, int64_t x_nb_row, int64_t d, int64_t rows, int32_t *out, b200_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Fused forms of the ops between the mul_mats of a llama layer (llm_build_llama, cactus/llama-model.cpp:4517-4671).
+ * Each computes bit for bit what the chain of the separate entry points computes; the f32 intermediates that only the
+ * next mul_mat would read are not written.
+ *
+ * b200_add_rms_norm_quantize: x += residual (ADD, cactus/ggml-cpu/ops.cpp:1283-1300; skipped when residual is NULL),
+ *   h = rms_norm(x) * w (ops.cpp:3268-3316 + MUL; w may be NULL), h quantised into `scratch` as
+ *   b200_quantize_activations would; h itself is stored only when `h` is not NULL.
+ * b200_silu_mul_quantize: silu(gate) * up (ops.cpp:2902-2981 + MUL) quantised into `scratch`.
+ * b200_rope_store: ROPE (mode 0, as b200_rope_norm) of q in place and of k, with k and v stored as f16 into the cache
+ *   rows slots[t] (cpy_k / cpy_v, cactus/llama-kv-cache.cpp:617-656); the f32 k is left as it was.
+ * ------------------------------------------------------------------------------------------------ */
+B200_API int b200_add_rms_norm_quantize(float *x, int64_t x_nb_row, const float *residual, int64_t residual_nb_row, const float *w, float *h,
+                                        int64_t h_nb_row, int64_t d, int64_t rows, float eps, void *scratch, size_t scratch_bytes,
+                                        int variant, b200_stream_t stream);
+B200_API int b200_silu_mul_quantize(const float *gate, const float *up, int64_t nb_row, int64_t K, int64_t N, void *scratch,
+                                    size_t scratch_bytes, int variant, b200_stream_t stream);
+B200_API int b200_rope_store(float *q, int64_t q_nb_head, int64_t q_nb_tok, const float *k, int64_t k_nb_head, int64_t k_nb_tok,
+                             const float *v, int64_t v_nb_tok, int64_t D, int64_t H, int64_t Hkv, int64_t T, int n_dims, const int32_t *pos,
+                             const float *freq_factors, float freq_base, float freq_scale, float attn_factor, const int32_t *slots,
+                             void *k_cache, int64_t k_cache_nb_row, void *v_cache, int64_t v_cache_nb_row, b200_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Row-split mul_mat over the GPUs of one node (one process per GPU).
  *
  * The reference splits the rows of mul_mat weights over devices with a split buffer type
