@@ -13,11 +13,16 @@
 // sequence for validation (fattn_parity_kernel).
 #include <math_constants.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace b200 {
 
 constexpr int FA_THREADS = 128;
+#ifndef FA_MIN_CTAS
+#define FA_MIN_CTAS 3
+#endif
 constexpr int FA_SUPER_WORDS = 32;  // 2048 cells listed per round
 
 // ---- mask scan: one warp per 64 cells of one token row ------------------------------------------
@@ -70,6 +75,7 @@ struct FattnParams {
     float *dst;
     float *partial;  // [Nq][H][nsplit][D + 2]
     int nsplit, hgroups;
+    int w0;          // > 0: a token gets ceil(words / w0) KV splits (at most nsplit), so long sequences are cut, short ones are not
 };
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -95,7 +101,7 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 //               probabilities at fp32 accuracy.
 // Every warp keeps its own (max, sum, accumulator) state; the states are merged through shared memory at the end.
 template <int D>
-__global__ void __launch_bounds__(FA_THREADS) fattn_mma_kernel(FattnParams p) {
+__global__ void __launch_bounds__(FA_THREADS, FA_MIN_CTAS) fattn_mma_kernel(FattnParams p) {
     constexpr int KS = D / 16;   // k-steps of the S MMA
     constexpr int NU = D / 32;   // 16-byte K pieces per lane and cell
     constexpr int NR = D / 64;   // 64-wide d ranges of V
@@ -141,7 +147,12 @@ __global__ void __launch_bounds__(FA_THREADS) fattn_mma_kernel(FattnParams p) {
     const unsigned long long *wrow = p.words ? p.words + j * p.nw : nullptr;
     const int32_t *wl = p.words ? p.wlist + j * p.nw : nullptr;
     const int64_t n_words = p.words ? (int64_t) p.wcount[j] : p.nw;
-    const int64_t per_split = (n_words + p.nsplit - 1) / p.nsplit;
+    int ns_j = p.nsplit;   // KV splits of this token
+    if (p.w0 > 0) {
+        ns_j = (int) min((int64_t) p.nsplit, max((int64_t) 1, (n_words + p.w0 - 1) / p.w0));
+        if (split >= ns_j) return;   // the whole CTA: nothing has been synchronised yet
+    }
+    const int64_t per_split = (n_words + ns_j - 1) / ns_j;
     const int64_t w_begin = (int64_t) split * per_split;
     const int64_t w_end = min(n_words, w_begin + per_split);
     const __half *mrow = p.mask ? reinterpret_cast<const __half *>(p.mask + j * p.mask_nb_row) : nullptr;
@@ -181,23 +192,29 @@ __global__ void __launch_bounds__(FA_THREADS) fattn_mma_kernel(FattnParams p) {
         __syncthreads();
         const int count = list_count;
         const int n_chunks = (count + 15) >> 4;
+        const int last = count - 1;
+        uint4 kr[2][NU];   // K rows of the two 8-cell tiles of a chunk: 16-byte pieces t, t+4, ... of cell g
+        auto load_k = [&](int chunk) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int64_t cell = cell_list[min((chunk << 4) + 8 * c + g, last)];
+                const uint4 *kp = reinterpret_cast<const uint4 *>(kbase + cell * p.k_nb_cell) + t;
+#pragma unroll
+                for (int u = 0; u < NU; ++u) kr[c][u] = __ldg(kp + 4 * u);
+            }
+        };
+        if (warp < n_chunks) load_k(warp);
         for (int ch = warp; ch < n_chunks; ch += 4) {
             const int base = ch << 4;
-            const int last = count - 1;
             // ---- S = Q K^T for the two 8-cell tiles ----
             float sacc[2][4];
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                const int64_t cell = cell_list[min(base + 8 * c + g, last)];
-                const uint4 *kp = reinterpret_cast<const uint4 *>(kbase + cell * p.k_nb_cell) + t;
-                uint4 kr[NU];
-#pragma unroll
-                for (int u = 0; u < NU; ++u) kr[u] = __ldg(kp + 4 * u);
                 sacc[c][0] = sacc[c][1] = sacc[c][2] = sacc[c][3] = 0.0f;
 #pragma unroll
                 for (int u = 0; u < NU; ++u) {
-                    mma_f16(sacc[c], qa0[2 * u], 0u, qa2[2 * u], 0u, kr[u].x, kr[u].y);
-                    mma_f16(sacc[c], qa0[2 * u + 1], 0u, qa2[2 * u + 1], 0u, kr[u].z, kr[u].w);
+                    mma_f16(sacc[c], qa0[2 * u], 0u, qa2[2 * u], 0u, kr[c][u].x, kr[c][u].y);
+                    mma_f16(sacc[c], qa0[2 * u + 1], 0u, qa2[2 * u + 1], 0u, kr[c][u].z, kr[c][u].w);
                 }
             }
             // V rows of cells 2t, 2t+1, 2t+8, 2t+9: issue the loads before the softmax arithmetic
@@ -209,6 +226,8 @@ __global__ void __launch_bounds__(FA_THREADS) fattn_mma_kernel(FattnParams p) {
 #pragma unroll
                 for (int r = 0; r < NR; ++r) vr[i][r] = __ldg(vp + 8 * r);
             }
+            // the next chunk's K rows travel during the softmax and the P V MMAs of this one
+            if (ch + 4 < n_chunks) load_k(ch + 4);
             // ---- scores of head g for cells base + {2t, 2t+1, 8+2t, 9+2t} ----
             float sc[4];
 #pragma unroll
@@ -299,7 +318,7 @@ __global__ void __launch_bounds__(FA_THREADS) fattn_mma_kernel(FattnParams p) {
             ls += merge_l[wv][h] * scl;
         }
         const int64_t head = h0 + h;
-        if (p.nsplit == 1) {
+        if (ns_j == 1) {
             p.dst[(j * p.H + head) * D + d] = a * (1.0f / ls);
         } else {
             float *pp = p.partial + ((j * p.H + head) * p.nsplit + split) * (D + 2);
@@ -392,10 +411,16 @@ __global__ void __launch_bounds__(128) fattn_parity_kernel(FattnParams p) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(D) fattn_combine_kernel(const float *__restrict__ partial, int nsplit, float *__restrict__ dst) {
+__global__ void __launch_bounds__(D) fattn_combine_kernel(const float *__restrict__ partial, int nsplit, float *__restrict__ dst, int64_t H,
+                                                          const int32_t *__restrict__ wcount, int64_t nw, int w0) {
     const int64_t row = blockIdx.x;  // token * H + head
     const int d = threadIdx.x;
     const float *pp = partial + row * nsplit * (D + 2);
+    if (w0 > 0) {   // the splits this token really has; a token with one split was written directly
+        const int64_t n_words = wcount ? (int64_t) wcount[row / H] : nw;
+        nsplit = (int) min((int64_t) nsplit, max((int64_t) 1, (n_words + w0 - 1) / w0));
+        if (nsplit == 1) return;
+    }
     float mn = -CUDART_INF_F;
     for (int s = 0; s < nsplit; ++s) mn = fmaxf(mn, pp[s * (D + 2) + D]);
     float a = 0.0f, ls = 0.0f;
@@ -408,6 +433,9 @@ __global__ void __launch_bounds__(D) fattn_combine_kernel(const float *__restric
     dst[row * D + d] = a * (1.0f / ls);
 }
 
+
+static int fattn_hgroups(int gqa) { return (gqa + 7) / 8; }   // a CTA takes up to 8 query heads of one KV head
+
 static int fa_sm_count() {
     static int n = 0;
     if (!n) {
@@ -419,9 +447,27 @@ static int fa_sm_count() {
     return n;
 }
 
-static int fattn_hgroups(int gqa) { return (gqa + 7) / 8; }   // a CTA takes up to 8 query heads of one KV head
+// Decode-sized batches over ragged sequences: one CTA per (token, kv head) makes the longest sequence the kernel's
+// duration.  When the grid is small enough for spare CTAs to be cheap, tokens whose mask has more than w0 non-empty
+// 64-cell words are cut into up to 4 KV splits; w0 is 1.25 x the mean words per token if the tokens shared the cache.
+static int fattn_adaptive_w0(int64_t Nq, int64_t Hkv, int hgroups, int64_t n_kv, bool have_index) {
+    static int allow = -1;
+    if (allow < 0) {
+        const char *e = getenv("B200_FA_ADAPTIVE");   // opt-in: measured a gain only without the K prefetch (4 CTAs per SM)
+        allow = (e && atoi(e) == 1) ? 1 : 0;
+    }
+    if (!allow || !have_index || Nq * Hkv * hgroups > 2 * 4 * (int64_t) fa_sm_count() / 2) return 0;
+    const int64_t mean_words = (n_kv / 64 + Nq - 1) / Nq;
+    return (int) std::max<int64_t>(4, (mean_words * 5 + 3) / 4);
+}
 
 static int fattn_nsplit(int64_t Nq, int64_t Hkv, int hgroups, int64_t n_kv) {
+    static int forced = -1;
+    if (forced < 0) {
+        const char *e = getenv("B200_FA_NSPLIT");
+        forced = e ? atoi(e) : 0;
+    }
+    if (forced > 0) return (int) std::min<int64_t>(forced, 64);
     const int64_t ctas = Nq * Hkv * hgroups;
     const int64_t want = 2 * fa_sm_count();
     if (ctas >= want) return 1;
@@ -465,7 +511,8 @@ int b200_mask_index_build(const void *mask, int64_t mask_nb_row, int64_t Nq, int
 size_t b200_flash_attn_scratch_bytes(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, int64_t n_kv) {
     if (D <= 0 || H <= 0 || Hkv <= 0 || Nq <= 0 || n_kv <= 0 || H % Hkv) return 0;
     const int hgroups = fattn_hgroups((int) (H / Hkv));
-    const int ns = fattn_nsplit(Nq, Hkv, hgroups, n_kv);
+    int ns = fattn_nsplit(Nq, Hkv, hgroups, n_kv);
+    if (ns == 1 && fattn_adaptive_w0(Nq, Hkv, hgroups, n_kv, true) > 0) ns = 4;
     const size_t part = ns > 1 ? align_up((size_t) Nq * H * ns * (D + 2) * sizeof(float), 256) : 0;
     return b200_mask_index_bytes(Nq, n_kv) + part;
 }
@@ -485,7 +532,9 @@ static int flash_attn_impl(bool parity, int64_t D, int64_t H, int64_t Hkv, int64
     B200_REQUIRE(!mask || (is_aligned(mask, 2) && mask_nb_row % 2 == 0), "misaligned mask");
     const int gqa = (int) (H / Hkv);
     const int hgroups = fattn_hgroups(gqa);
-    const int ns = parity ? 1 : fattn_nsplit(Nq, Hkv, hgroups, n_kv);
+    int ns = parity ? 1 : fattn_nsplit(Nq, Hkv, hgroups, n_kv);
+    int w0 = 0;
+    if (!parity && ns == 1 && (w0 = fattn_adaptive_w0(Nq, Hkv, hgroups, n_kv, index != nullptr)) > 0) ns = 4;
     const size_t part = ns > 1 ? (size_t) Nq * H * ns * (D + 2) * sizeof(float) : 0;
     if (part && (!scratch || scratch_bytes < part)) return set_error(B200_E_SCRATCH, "flash_attn scratch too small: %zu < %zu", scratch_bytes, part);
     B200_REQUIRE(!part || is_aligned(scratch, 16), "scratch must be 16-byte aligned");
@@ -504,7 +553,7 @@ static int flash_attn_impl(bool parity, int64_t D, int64_t H, int64_t Hkv, int64
     p.n_head_log2 = 1u << (uint32_t) floor(log2((double) H));
     p.m0 = powf(2.0f, -(max_bias) / p.n_head_log2);
     p.m1 = powf(2.0f, -(max_bias / 2.0f) / p.n_head_log2);
-    p.dst = dst; p.partial = (float *) scratch; p.nsplit = ns; p.hgroups = hgroups;
+    p.dst = dst; p.partial = (float *) scratch; p.nsplit = ns; p.hgroups = hgroups; p.w0 = w0;
 
     cudaStream_t st = (cudaStream_t) stream;
     if (parity) {
@@ -518,8 +567,8 @@ static int flash_attn_impl(bool parity, int64_t D, int64_t H, int64_t Hkv, int64
     else fattn_mma_kernel<64><<<grid, FA_THREADS, 0, st>>>(p);
     if (int e = check_launch("fattn_mma")) return e;
     if (ns > 1) {
-        if (D == 128) fattn_combine_kernel<128><<<(unsigned) (Nq * H), 128, 0, st>>>(p.partial, ns, dst);
-        else fattn_combine_kernel<64><<<(unsigned) (Nq * H), 64, 0, st>>>(p.partial, ns, dst);
+        if (D == 128) fattn_combine_kernel<128><<<(unsigned) (Nq * H), 128, 0, st>>>(p.partial, ns, dst, H, p.wcount, p.nw, w0);
+        else fattn_combine_kernel<64><<<(unsigned) (Nq * H), 64, 0, st>>>(p.partial, ns, dst, H, p.wcount, p.nw, w0);
         return check_launch("fattn_combine");
     }
     return B200_OK;

@@ -189,7 +189,7 @@ class LlamaEngine:
         ws = [L.b200_mul_mat_workspace_bytes(cfg.layer_type, K, M // g, t) for _, K, M in cfg.mul_mat_shapes() for t in (9, 16, 32, 64, T)]
         ws.append(L.b200_mul_mat_workspace_bytes(cfg.head_type, cfg.d_model, cfg.vocab // g, T))
         self.ws = u8(max(ws))
-        self.fa_scratch = u8(max(L.b200_flash_attn_scratch_bytes(cfg.head_dim, cfg.n_head, cfg.n_kv_head, t, n_cells) for t in (1, 8, 64, T)))
+        self.fa_scratch = u8(max(L.b200_flash_attn_scratch_bytes(cfg.head_dim, cfg.n_head, cfg.n_kv_head, t, n_cells) for t in range(1, T + 1)))
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
         self.launches_per_step: dict[int, int] = {}
 
