@@ -148,13 +148,21 @@ def mul_mat_roofline(eng, cfg, reps: int = 3):
     names = {"wq": "attn_q", "wk": "attn_k", "wv": "attn_v", "wo": "attn_output", "gate": "ffn_gate", "up": "ffn_up", "down": "ffn_down"}
     T = N_SEQ
     per_shape, total_bytes, total_ms, launches = {}, 0.0, 0.0, 0
-    shapes = [(s, K, M, [f"blk.{il}.{names[s]}.weight" for il in range(cfg.n_layer)], cfg.layer_type) for s, K, M in cfg.mul_mat_shapes()]
+    per_layer = cfg.mul_mat_shapes()
+    if eng.fused:   # the engine runs wq/wk/wv and gate/up as one stacked mul_mat each
+        d, kvd, ff = cfg.d_model, cfg.n_kv_head * cfg.head_dim, cfg.d_ff
+        names.update(qkv="attn_qkv", gate_up="ffn_gate_up")
+        per_layer = [("qkv", d, d + 2 * kvd), ("wo", d, d), ("gate_up", d, 2 * ff), ("down", ff, d)]
+    shapes = [(s, K, M, [f"blk.{il}.{names[s]}.weight" for il in range(cfg.n_layer)], cfg.layer_type) for s, K, M in per_layer]
     shapes.append(("output", cfg.d_model, cfg.vocab, ["output.weight"], cfg.head_type))
     for short, K, M, tensors, wtype in shapes:
         act = eng.act_ff if K == cfg.d_ff else eng.act_d
-        out = {cfg.d_model: eng.tmp, cfg.d_ff: eng.gate, cfg.vocab: eng.logits}.get(M, eng.k)
+        out = {"qkv": getattr(eng, "qkv", None), "gate_up": getattr(eng, "gu", None), "output": eng.logits}.get(short)
+        if out is None:
+            out = {cfg.d_model: eng.tmp, cfg.d_ff: eng.gate, cfg.vocab: eng.logits}.get(M, eng.k)
         bb = 18 if wtype == 2 else 34
-        alg = M * (K // 32) * bb + T * K * 4 + T * M * 4      # weights + f32 activations in + f32 out
+        n_products = {"qkv": 3, "gate_up": 2}.get(short, 1)       # the reference's mul_mats behind this launch: each reads the activations
+        alg = M * (K // 32) * bb + n_products * T * K * 4 + T * M * 4      # weights + f32 activations in + f32 out
         def launch_all():
             stq = torch.cuda.current_stream().cuda_stream
             for name in tensors:

@@ -151,7 +151,8 @@ class LlamaEngine:
     always spans the whole cache, masked) and replayed for every later ubatch of that size.
     """
 
-    def __init__(self, weights: LlamaWeights, n_cells: int, max_tokens: int = 512, variant: int = Q8_AVX2, use_graphs: bool = True, split=None):
+    def __init__(self, weights: LlamaWeights, n_cells: int, max_tokens: int = 512, variant: int = Q8_AVX2, use_graphs: bool = True, split=None,
+                 fuse_weights: bool = True):
         assert n_cells % 256 == 0, "the cache is padded to 256 cells for flash attention (cactus/llama-kv-cache.cpp:20-23)"
         self.w, self.cfg, self.n_cells, self.max_tokens, self.variant = weights, weights.cfg, n_cells, max_tokens, variant
         self.use_graphs = use_graphs
@@ -160,6 +161,16 @@ class LlamaEngine:
         self.split = split
         g = split.world if split is not None else 1
         cfg, L = self.cfg, lib()
+        # wq/wk/wv and gate/up read the same activations: stacked into one weight each, they are one mul_mat each (the
+        # engine takes the stacked copies and drops the separate tensors).  Not with a row split, whose slices are per tensor.
+        self.fused = bool(fuse_weights) and split is None
+        if self.fused:
+            t = self.w.tensors
+            for il in range(cfg.n_layer):
+                p = f"blk.{il}."
+                if p + "attn_qkv.weight" not in t:
+                    t[p + "attn_qkv.weight"] = QWeight.cat([t.pop(p + "attn_q.weight"), t.pop(p + "attn_k.weight"), t.pop(p + "attn_v.weight")])
+                    t[p + "ffn_gate_up.weight"] = QWeight.cat([t.pop(p + "ffn_gate.weight"), t.pop(p + "ffn_up.weight")])
         dev = "cuda"
         kvd = cfg.n_kv_head * cfg.head_dim
         T = max_tokens
@@ -176,8 +187,13 @@ class LlamaEngine:
         self.index = u8(L.b200_mask_index_bytes(T, n_cells))
         self.x, self.h, self.attn = f32(T, cfg.d_model), f32(T, cfg.d_model), f32(T, cfg.d_model)
         out = split.carve if split is not None else f32   # mul_mat outputs: where the peers' slices land
-        self.q, self.k, self.v = out(T, cfg.d_model), out(T, kvd), out(T, kvd)
-        self.gate, self.up = out(T, cfg.d_ff), out(T, cfg.d_ff)
+        if self.fused:   # the stacked products, and the reference's q/k/v and gate/up as column ranges of them
+            self.qkv, self.gu = f32(T, cfg.d_model + 2 * kvd), f32(T, 2 * cfg.d_ff)
+            self.q, self.k, self.v = self.qkv[:, :cfg.d_model], self.qkv[:, cfg.d_model:cfg.d_model + kvd], self.qkv[:, cfg.d_model + kvd:]
+            self.gate, self.up = self.gu[:, :cfg.d_ff], self.gu[:, cfg.d_ff:]
+        else:
+            self.q, self.k, self.v = out(T, cfg.d_model), out(T, kvd), out(T, kvd)
+            self.gate, self.up = out(T, cfg.d_ff), out(T, cfg.d_ff)
         self.tmp, self.tmp2 = out(T, cfg.d_model), out(T, cfg.d_model)   # attention branch / feed-forward branch of the residual
         self.logits = out(T, cfg.vocab)
         self.local = f32(T * (max(cfg.d_ff, cfg.vocab) // g + 16)) if split is not None else None
@@ -186,7 +202,8 @@ class LlamaEngine:
         self.ids_host = torch.zeros(T, dtype=torch.int32).pin_memory()
         self.act_d = u8(L.b200_act_bytes(cfg.d_model, T))
         self.act_ff = u8(L.b200_act_bytes(cfg.d_ff, T))
-        ws = [L.b200_mul_mat_workspace_bytes(cfg.layer_type, K, M // g, t) for _, K, M in cfg.mul_mat_shapes() for t in (9, 16, 32, 64, T)]
+        shapes = [(K, M // g) for _, K, M in cfg.mul_mat_shapes()] + [(cfg.d_model, cfg.d_model + 2 * kvd), (cfg.d_model, 2 * cfg.d_ff)]
+        ws = [L.b200_mul_mat_workspace_bytes(cfg.layer_type, K, M, t) for K, M in shapes for t in (9, 16, 32, 64, T)]
         ws.append(L.b200_mul_mat_workspace_bytes(cfg.head_type, cfg.d_model, cfg.vocab // g, T))
         self.ws = u8(max(ws))
         self.fa_scratch = u8(max(L.b200_flash_attn_scratch_bytes(cfg.head_dim, cfg.n_head, cfg.n_kv_head, t, n_cells) for t in range(1, T + 1)))
@@ -233,22 +250,29 @@ class LlamaEngine:
         for il in range(cfg.n_layer):
             p = f"blk.{il}."
             norm_quant(p + "attn_norm.weight", pending)
-            self._mm(p + "attn_q.weight", self.act_d, T, self.q)
-            self._mm(p + "attn_k.weight", self.act_d, T, self.k)
-            self._mm(p + "attn_v.weight", self.act_d, T, self.v)
+            if self.fused:
+                self._mm(p + "attn_qkv.weight", self.act_d, T, self.qkv)
+            else:
+                self._mm(p + "attn_q.weight", self.act_d, T, self.q)
+                self._mm(p + "attn_k.weight", self.act_d, T, self.k)
+                self._mm(p + "attn_v.weight", self.act_d, T, self.v)
             kc, vc = self.k_cache[il], self.v_cache[il]
-            check(L.b200_rope_store(self.q.data_ptr(), D * 4, d * 4, self.k.data_ptr(), D * 4, kvd * 4, self.v.data_ptr(), kvd * 4, D, H, Hkv, T, D,
+            qs, kst, vst = self.q.stride(0) * 4, self.k.stride(0) * 4, self.v.stride(0) * 4
+            check(L.b200_rope_store(self.q.data_ptr(), D * 4, qs, self.k.data_ptr(), D * 4, kst, self.v.data_ptr(), vst, D, H, Hkv, T, D,
                                     pos, None, cfg.rope_theta, 1.0, 1.0, slots, kc.data_ptr(), kvd * 2, vc.data_ptr(), kvd * 2, st))
-            check(L.b200_flash_attn_ext_indexed(D, H, Hkv, T, nkv, self.q.data_ptr(), d * 4, D * 4, kc.data_ptr(), kvd * 2, D * 2,
+            check(L.b200_flash_attn_ext_indexed(D, H, Hkv, T, nkv, self.q.data_ptr(), qs, D * 4, kc.data_ptr(), kvd * 2, D * 2,
                                                 vc.data_ptr(), kvd * 2, D * 2, self.mask.data_ptr(), nkv * 2, self.index.data_ptr(),
                                                 D ** -0.5, 0.0, 0.0, self.attn.data_ptr(), self.fa_scratch.data_ptr(),
                                                 self.fa_scratch.numel(), st))
             self._quant(self.attn, d, T, self.act_d)
             self._mm(p + "attn_output.weight", self.act_d, T, self.tmp)
             norm_quant(p + "ffn_norm.weight", self.tmp)
-            self._mm(p + "ffn_gate.weight", self.act_d, T, self.gate)
-            self._mm(p + "ffn_up.weight", self.act_d, T, self.up)
-            check(L.b200_silu_mul_quantize(self.gate.data_ptr(), self.up.data_ptr(), cfg.d_ff * 4, cfg.d_ff, T, self.act_ff.data_ptr(),
+            if self.fused:
+                self._mm(p + "ffn_gate_up.weight", self.act_d, T, self.gu)
+            else:
+                self._mm(p + "ffn_gate.weight", self.act_d, T, self.gate)
+                self._mm(p + "ffn_up.weight", self.act_d, T, self.up)
+            check(L.b200_silu_mul_quantize(self.gate.data_ptr(), self.up.data_ptr(), self.gate.stride(0) * 4, cfg.d_ff, T, self.act_ff.data_ptr(),
                                            self.act_ff.numel(), V, st))
             self._mm(p + "ffn_down.weight", self.act_ff, T, self.tmp2)
             pending = self.tmp2

@@ -60,6 +60,18 @@ class QWeight:
         d = self.data[n_rt * n_bg * tile + t0 * n_bg * 128:n_rt * n_bg * tile + t1 * n_bg * 128]
         return QWeight(self.wtype, self.K, r1 - r0, torch.cat([q, d]))
 
+    @staticmethod
+    def cat(parts: list) -> "QWeight":
+        """The rows of several weights with the same K and type stacked into one weight (a copy): one mul_mat then
+        yields all their products side by side.  Every part but the last must have a multiple of 16 rows."""
+        w0 = parts[0]
+        assert all(p.K == w0.K and p.wtype == w0.wtype for p in parts) and all(p.M % 16 == 0 for p in parts[:-1])
+        n_bg = (w0.K // 32 + 3) // 4
+        tile = 1024 if w0.wtype == Q4_0 else 2048
+        qs = [p.data[:((p.M + 15) // 16) * n_bg * tile] for p in parts]
+        ds = [p.data[((p.M + 15) // 16) * n_bg * tile:] for p in parts]
+        return QWeight(w0.wtype, w0.K, sum(p.M for p in parts), torch.cat(qs + ds))
+
     def to_blocks(self) -> torch.Tensor:
         L = lib()
         out = torch.empty((self.M, self.K // 32 * BLOCK_BYTES[self.wtype]), dtype=torch.uint8, device=self.data.device)
