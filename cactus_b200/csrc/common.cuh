@@ -104,6 +104,23 @@ __device__ __forceinline__ void q8_scales(float amax, int variant, __half *d_out
     }
 }
 
+// RMS_NORM's sum of squares (ops.cpp:3268-3316 accumulates in double).  The order both kernels that need it use: a
+// row is cut into groups of 4 elements, thread i takes groups i, i + blockDim, ...; then a shuffle tree per warp, then
+// the warps in order.  rms_threads(d) threads per row: one group per thread up to 4096 elements.
+static inline unsigned rms_threads(int64_t d) {
+    const int64_t g = (d / 4 + 31) / 32 * 32;
+    return (unsigned) (g < 32 ? 32 : (g > 1024 ? 1024 : g));
+}
+__device__ __forceinline__ double rms_block_sum(double sum) {
+    __shared__ double red[32];
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    double tot = 0.0;
+    for (int i = 0; i < (int) ((blockDim.x + 31) >> 5); ++i) tot += red[i];
+    return tot;
+}
+
 // Stores one lane's share (4 quants, element group j of 8) of a quantised block (row n, block b).  LAYOUT 0: the
 // reference's block_q8_0 stream; 1: B8 tiles in mma.sync B-fragment order; 2: B8 tiles as K-major core matrices.
 // Lane j == 0 also stores the block scale (layouts 1/2: the f32 pair {d, -d * 12582912}; zero for padding).

@@ -11,59 +11,57 @@ namespace b200 {
 
 bool act_layout_canonical(int64_t N);
 
-// One CTA per (padded) token row.  The sum of squares is accumulated exactly as rms_norm_kernel does (per-thread
-// strided partial sums in double, shuffle tree, warps in order), so the scale -- and with it every quantised value --
-// is bit-identical to the unfused chain.
+// One CTA per (padded) token row, one pass: a thread keeps its groups of 4 elements in registers from the load to the
+// quantised store.  The sum of squares is accumulated in the order rms_norm_kernel uses (rms_block_sum), so the
+// scale -- and with it every quantised value -- is bit-identical to the unfused chain.
 template <int LAYOUT>
-__global__ void __launch_bounds__(256) add_rms_norm_quantize_kernel(float *__restrict__ x, int64_t x_nb_row, const float *__restrict__ res,
-                                                                   int64_t res_nb_row, const float *__restrict__ w, float *__restrict__ h,
-                                                                   int64_t h_nb_row, int64_t d, int64_t N, float eps, int64_t nb, int64_t nbp,
-                                                                   uint8_t *__restrict__ out, size_t d_offset, int variant) {
+__global__ void __launch_bounds__(1024) add_rms_norm_quantize_kernel(float *__restrict__ x, int64_t x_nb_row, const float *__restrict__ res,
+                                                                    int64_t res_nb_row, const float *__restrict__ w, float *__restrict__ h,
+                                                                    int64_t h_nb_row, int64_t d, int64_t N, float eps, int64_t nb, int64_t nbp,
+                                                                    uint8_t *__restrict__ out, size_t d_offset, int variant) {
+    constexpr int GMAX = 4;   // groups of 4 elements per thread: d <= 16 * blockDim.x
     const int64_t n = blockIdx.x;
     const bool row_real = n < N;
-    float sc = 0.0f;
-    float *xr = nullptr;
-    if (row_real) {
-        xr = reinterpret_cast<float *>(reinterpret_cast<char *>(x) + n * x_nb_row);
-        const float *rr = res ? reinterpret_cast<const float *>(reinterpret_cast<const char *>(res) + n * res_nb_row) : nullptr;
-        double sum = 0.0;
-        for (int64_t i = threadIdx.x; i < d; i += blockDim.x) {
-            float v = xr[i];
+    const int64_t groups = d / 4, groups_padded = nbp * 8;
+    float v[GMAX][4];
+    double sum = 0.0;
+    float *xr = row_real ? reinterpret_cast<float *>(reinterpret_cast<char *>(x) + n * x_nb_row) : nullptr;
+    const float *rr = (row_real && res) ? reinterpret_cast<const float *>(reinterpret_cast<const char *>(res) + n * res_nb_row) : nullptr;
+#pragma unroll
+    for (int k = 0; k < GMAX; ++k) {
+        const int64_t gi = threadIdx.x + (int64_t) k * blockDim.x;
+        v[k][0] = v[k][1] = v[k][2] = v[k][3] = 0.0f;
+        if (row_real && gi < groups) {
+            const float4 a = *reinterpret_cast<const float4 *>(xr + gi * 4);
+            v[k][0] = a.x; v[k][1] = a.y; v[k][2] = a.z; v[k][3] = a.w;
             if (rr) {
-                v = v + rr[i];
-                xr[i] = v;
+                const float4 b = *reinterpret_cast<const float4 *>(rr + gi * 4);
+                v[k][0] = v[k][0] + b.x; v[k][1] = v[k][1] + b.y; v[k][2] = v[k][2] + b.z; v[k][3] = v[k][3] + b.w;
+                *reinterpret_cast<float4 *>(xr + gi * 4) = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
             }
-            sum += (double) (v * v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sum += (double) (v[k][i] * v[k][i]);
         }
-        __shared__ double red[8];
-        for (int o2 = 16; o2 > 0; o2 >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o2);
-        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
-        __syncthreads();   // also orders this CTA's stores to xr before the reads below
-        double tot = 0.0;
-        for (int i = 0; i < (int) (blockDim.x >> 5); ++i) tot += red[i];
-        const float mean = (float) (tot / (double) d);
-        sc = 1.0f / sqrtf(mean + eps);
     }
+    const double tot = rms_block_sum(sum);
+    const float mean = (float) (tot / (double) d);
+    const float sc = 1.0f / sqrtf(mean + eps);
     float *hr = (h && row_real) ? reinterpret_cast<float *>(reinterpret_cast<char *>(h) + n * h_nb_row) : nullptr;
-    // groups of 4 elements: 8 consecutive threads share a block of 32
-    for (int64_t grp4 = threadIdx.x; grp4 < nbp * 8; grp4 += blockDim.x) {
-        const int64_t b = grp4 >> 3;
-        const int j = (int) (grp4 & 7);
-        const bool real = row_real && b < nb;
-        float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int k = 0; k < GMAX; ++k) {
+        const int64_t gi = threadIdx.x + (int64_t) k * blockDim.x;
+        if (gi >= groups_padded) continue;   // whole 8-lane block groups leave together
+        const bool real = row_real && gi < groups;
+        float o[4] = {0.f, 0.f, 0.f, 0.f};
         if (real) {
-            const int64_t e = b * 32 + j * 4;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const float t = xr[e + i] * sc;
-                v[i] = w ? t * w[e + i] : t;
+                const float t = v[k][i] * sc;
+                o[i] = w ? t * w[gi * 4 + i] : t;
             }
-            if (hr) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) hr[e + i] = v[i];
-            }
+            if (hr) *reinterpret_cast<float4 *>(hr + gi * 4) = make_float4(o[0], o[1], o[2], o[3]);
         }
-        q8_quantize_store<LAYOUT>(v, out, d_offset, nb, nbp, n, b, j, real, variant);
+        q8_quantize_store<LAYOUT>(o, out, d_offset, nb, nbp, n, gi >> 3, (int) (gi & 7), real, variant);
     }
 }
 
@@ -169,14 +167,18 @@ int b200_add_rms_norm_quantize(float *x, int64_t x_nb_row, const float *residual
     B200_REQUIRE(is_aligned(scratch, 256), "scratch must be 256-byte aligned");
     const ActDims a = act_dims(d, rows);
     if (scratch_bytes < a.total_bytes) return set_error(B200_E_SCRATCH, "scratch too small: %zu < %zu", scratch_bytes, a.total_bytes);
+    B200_REQUIRE(d <= 16384, "rows of more than 16384 elements are not supported");
+    B200_REQUIRE(x_nb_row % 16 == 0 && residual_nb_row % 16 == 0 && h_nb_row % 16 == 0 && is_aligned(x, 16) && (!residual || is_aligned(residual, 16)) &&
+                     (!h || is_aligned(h, 16)) && (!w || is_aligned(w, 4)), "rows must be 16-byte aligned");
     const unsigned grid = (unsigned) (a.n_nt * 8);
+    const unsigned threads = rms_threads(d);
     cudaStream_t st = (cudaStream_t) stream;
     if (act_layout_canonical(rows)) {
-        add_rms_norm_quantize_kernel<2><<<grid, 256, 0, st>>>(x, x_nb_row, residual, residual_nb_row, w, h, h_nb_row, d, rows, eps, a.nb, a.nbp,
-                                                              (uint8_t *) scratch, a.d_offset, variant);
+        add_rms_norm_quantize_kernel<2><<<grid, threads, 0, st>>>(x, x_nb_row, residual, residual_nb_row, w, h, h_nb_row, d, rows, eps, a.nb, a.nbp,
+                                                                  (uint8_t *) scratch, a.d_offset, variant);
     } else {
-        add_rms_norm_quantize_kernel<1><<<grid, 256, 0, st>>>(x, x_nb_row, residual, residual_nb_row, w, h, h_nb_row, d, rows, eps, a.nb, a.nbp,
-                                                              (uint8_t *) scratch, a.d_offset, variant);
+        add_rms_norm_quantize_kernel<1><<<grid, threads, 0, st>>>(x, x_nb_row, residual, residual_nb_row, w, h, h_nb_row, d, rows, eps, a.nb, a.nbp,
+                                                                  (uint8_t *) scratch, a.d_offset, variant);
     }
     return check_launch("add_rms_norm_quantize");
 }

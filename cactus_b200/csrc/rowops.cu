@@ -6,22 +6,23 @@ namespace b200 {
 
 // RMS_NORM: ops.cpp:3268-3316.  The reference sums squares in double and scales by 1/sqrtf(mean + eps);
 // a following MUL by the weight row (binary-ops.cpp:152-154) is fused when w != NULL.
-__global__ void __launch_bounds__(256) rms_norm_kernel(const float *__restrict__ x, int64_t x_nb_row, const float *__restrict__ w,
-                                                      float *__restrict__ dst, int64_t dst_nb_row, int64_t d, float eps) {
+__global__ void __launch_bounds__(1024) rms_norm_kernel(const float *__restrict__ x, int64_t x_nb_row, const float *__restrict__ w,
+                                                       float *__restrict__ dst, int64_t dst_nb_row, int64_t d, float eps) {
     const int64_t r = blockIdx.x;
     const float *xr = reinterpret_cast<const float *>(reinterpret_cast<const char *>(x) + r * x_nb_row);
     float *o = reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + r * dst_nb_row);
     double sum = 0.0;
-    for (int64_t i = threadIdx.x; i < d; i += blockDim.x) {
-        const float v = xr[i];
-        sum += (double) (v * v);
+    const int64_t groups = (d + 3) / 4;
+    for (int64_t gi = threadIdx.x; gi < groups; gi += blockDim.x) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (gi * 4 + i < d) {
+                const float v = xr[gi * 4 + i];
+                sum += (double) (v * v);
+            }
+        }
     }
-    __shared__ double red[8];
-    for (int o2 = 16; o2 > 0; o2 >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o2);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
-    __syncthreads();
-    double tot = 0.0;
-    for (int i = 0; i < (int) (blockDim.x >> 5); ++i) tot += red[i];
+    const double tot = rms_block_sum(sum);
     const float mean = (float) (tot / (double) d);
     const float sc = 1.0f / sqrtf(mean + eps);
     for (int64_t i = threadIdx.x; i < d; i += blockDim.x) {
@@ -129,7 +130,7 @@ int b200_rms_norm(const float *x, int64_t x_nb_row, const float *w, float *dst, 
                   float eps, b200_stream_t stream) {
     B200_REQUIRE(x && dst && d > 0 && rows >= 0 && x_nb_row % 4 == 0 && dst_nb_row % 4 == 0, "bad rms_norm arguments");
     if (rows == 0) return B200_OK;
-    rms_norm_kernel<<<(unsigned) rows, 256, 0, (cudaStream_t) stream>>>(x, x_nb_row, w, dst, dst_nb_row, d, eps);
+    rms_norm_kernel<<<(unsigned) rows, rms_threads(d), 0, (cudaStream_t) stream>>>(x, x_nb_row, w, dst, dst_nb_row, d, eps);
     return check_launch("rms_norm");
 }
 
