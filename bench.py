@@ -134,7 +134,8 @@ def cpu_layer_sample(reps: int, warmup: int):
 # DRAM bytes (read + write) per launch of the tensor-core mul_mat at 64 columns, from `ncu --metrics
 # dram__bytes_read.sum,dram__bytes_write.sum` captures of `python -m cactus_b200.microbench mul_mat` on each of the
 # step's shapes (profiles/mul_mat_q4_0_n64.md).  Keyed by (K, M).
-NCU_DRAM_BYTES_PER_LAUNCH: dict = {(4096, 4096): 9.81e6, (4096, 1024): 2.73e6, (4096, 14336): 33.40e6, (14336, 4096): 34.22e6,
+NCU_DRAM_BYTES_PER_LAUNCH: dict = {(4096, 4096): 9.82e6, (4096, 1024): 2.73e6, (4096, 14336): 33.40e6, (14336, 4096): 34.23e6,
+                                   (4096, 6144): 14.53e6, (4096, 28672): 66.9e6,   # the stacked wq/wk/wv and gate/up products
                                    (4096, 128256): 296.6e6}   # output head: weight bytes + 1 MB of activations, not captured (1002 CTAs, no K split)
 
 

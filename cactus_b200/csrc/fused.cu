@@ -93,33 +93,29 @@ __global__ void __launch_bounds__(256) silu_mul_quantize_kernel(const float *__r
 
 // One CTA per token: the angles as rope_norm_kernel builds them, q rotated in place, k rotated and stored as f16 into
 // its cache row, v stored as f16 into its cache row.
-__global__ void __launch_bounds__(256) rope_store_kernel(float *__restrict__ q, int64_t q_nb_head, int64_t q_nb_tok, const float *__restrict__ k,
+__global__ void __launch_bounds__(512) rope_store_kernel(float *__restrict__ q, int64_t q_nb_head, int64_t q_nb_tok, const float *__restrict__ k,
                                                         int64_t k_nb_head, int64_t k_nb_tok, const float *__restrict__ v, int64_t v_nb_tok,
                                                         int64_t D, int64_t H, int64_t Hkv, int n_dims, const int32_t *__restrict__ pos,
                                                         const float *__restrict__ ff, float theta_scale, float freq_scale, float attn_factor,
                                                         const int32_t *__restrict__ slots, __half *__restrict__ kc, int64_t kc_nb_row,
                                                         __half *__restrict__ vc, int64_t vc_nb_row) {
-    extern __shared__ float cs[];   // [n_dims/2] cos, [n_dims/2] sin
+    extern __shared__ float cs[];   // [n_dims/2] cos, [n_dims/2] sin, [n_dims/2] theta
     const int64_t t = blockIdx.x;
     const int half_dims = n_dims / 2;
+    float *th_s = cs + 2 * half_dims;
     if (threadIdx.x == 0) {
         float theta = (float) pos[t];
         for (int i = 0; i < half_dims; ++i) {
-            cs[i] = theta;
+            th_s[i] = theta;
             theta *= theta_scale;
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < half_dims; i += blockDim.x) {
-        const float f = ff ? ff[i] : 1.0f;
-        const float th = freq_scale * (cs[i] / f);
-        cs[half_dims + i] = sinf(th) * attn_factor;
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < half_dims; i += blockDim.x) {
-        const float f = ff ? ff[i] : 1.0f;
-        const float th = freq_scale * (cs[i] / f);
-        cs[i] = cosf(th) * attn_factor;
+    for (int i = threadIdx.x; i < 2 * half_dims; i += blockDim.x) {   // first half of the threads: cosines, second half: sines
+        const int a = i < half_dims ? i : i - half_dims;
+        const float f = ff ? ff[a] : 1.0f;
+        const float th = freq_scale * (th_s[a] / f);
+        cs[i] = (i < half_dims ? cosf(th) : sinf(th)) * attn_factor;
     }
     __syncthreads();
     const int64_t pairs = D / 2;
@@ -214,7 +210,7 @@ int b200_rope_store(float *q, int64_t q_nb_head, int64_t q_nb_tok, const float *
                  "pairs must be 8-byte aligned (f32) / 4-byte aligned (f16)");
     if (T == 0) return B200_OK;
     const float theta_scale = powf(freq_base, -2.0f / (float) n_dims);
-    rope_store_kernel<<<(unsigned) T, 256, (size_t) n_dims * sizeof(float), (cudaStream_t) stream>>>(
+    rope_store_kernel<<<(unsigned) T, 512, (size_t) (n_dims + n_dims / 2) * sizeof(float), (cudaStream_t) stream>>>(
         q, q_nb_head, q_nb_tok, k, k_nb_head, k_nb_tok, v, v_nb_tok, D, H, Hkv, n_dims, pos, freq_factors, theta_scale, freq_scale, attn_factor,
         slots, (__half *) k_cache, k_cache_nb_row, (__half *) v_cache, v_cache_nb_row);
     return check_launch("rope_store");

@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
         uint32_t a0[MMQ_MT], a1[MMQ_MT], a2[MMQ_MT], a3[MMQ_MT];
         uint64_t dwa[2][MMQ_MT], dwb[2][MMQ_MT];   // weight scales of the block of the step in flight / the step being finished
         uint64_t p01[2][2][MMQ_MT], p23[2][2][MMQ_MT];
-        uint4 sc[2][2];                              // {d0, d1, nd0, nd1} of the two column tiles of a step
+        uint2 sc[2][2];                              // {d0, d1} of the two column tiles of a step (-d * 12582912 is recomputed: half the shared-memory traffic)
         auto start = [&](int step, int buf) {
             const int j = step / NP, np = step % NP;
             if (np == 0) {
@@ -273,8 +273,8 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
                 b0 = reinterpret_cast<const uint2 *>(Bs + ntl * 1024 + j * 256)[lane];
                 b1 = reinterpret_cast<const uint2 *>(Bs + (ntl + 1) * 1024 + j * 256)[lane];
             }
-            sc[buf][0] = reinterpret_cast<const uint4 *>(Ss + ntl * 256)[j * 4 + t];
-            sc[buf][1] = reinterpret_cast<const uint4 *>(Ss + (ntl + 1) * 256)[j * 4 + t];
+            sc[buf][0] = *reinterpret_cast<const uint2 *>(Ss + ntl * 256 + (j * 4 + t) * 16);
+            sc[buf][1] = *reinterpret_cast<const uint2 *>(Ss + (ntl + 1) * 256 + (j * 4 + t) * 16);
 #pragma unroll
             for (int mt = 0; mt < MMQ_MT; ++mt) {
                 mma_s8_magic2(p01[buf][0][mt], p23[buf][0][mt], a0[mt], a1[mt], a2[mt], a3[mt], b0.x, b0.y);
@@ -285,7 +285,8 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
             const int j = step / NP, np = step % NP;
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                const uint64_t da = pack2(sc[buf][i].x, sc[buf][i].y), nda = pack2(sc[buf][i].z, sc[buf][i].w);
+                const uint64_t da = pack2(sc[buf][i].x, sc[buf][i].y);
+                const uint64_t nda = fma2(da, pack2(0xCB400000u, 0xCB400000u), 0ull);   // -d * 12582912, exact (d is an fp16 value)
 #pragma unroll
                 for (int mt = 0; mt < MMQ_MT; ++mt) {
                     const uint64_t t01 = fma2(p01[buf][i][mt], da, nda), t23 = fma2(p23[buf][i][mt], da, nda);
