@@ -43,6 +43,8 @@ SIGNATURES = {
     "b200_mul": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_silu": (_i32, [_vp, _vp, _vp, _i64, _vp]),
     "b200_rope_norm": (_i32, [_vp, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _f32, _f32, _f32, _vp]),
+    "b200_rope_norm_f16": (_i32, [_vp, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _f32, _f32, _f32, _vp]),
+    "b200_cpy_f16_f16": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "b200_cpy_f32_f16": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "b200_cpy_f32_f32": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "b200_get_rows_f32": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _vp]),
@@ -52,7 +54,7 @@ SIGNATURES = {
     "b200_set_rows_f16": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _vp]),
     "b200_argmax_rows": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp]),
     "b200_add_rms_norm_quantize": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _f32, _vp, _sz, _i32, _vp]),
-    "b200_silu_mul_quantize": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _sz, _i32, _vp]),
+    "b200_silu_mul_quantize": (_i32, [_vp, _vp, _i64, _vp, _i64, _i64, _i64, _vp, _sz, _i32, _vp]),
     "b200_rope_store": (_i32, [_vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _f32, _f32, _f32, _vp,
                                _vp, _i64, _vp, _i64, _vp]),
     "b200_peer_alloc": (_i32, [_sz, C.POINTER(_vp), C.c_char_p]),

@@ -455,6 +455,11 @@ bool supports_flash_attn(const lm_ggml_tensor * op) {
 }
 
 bool supports_cpy(const lm_ggml_tensor * src, const lm_ggml_tensor * dst) {
+    if (src && src->type == LM_GGML_TYPE_F16 && dst->type == LM_GGML_TYPE_F16) {   // cache defragmentation moves
+        if (lm_ggml_nelements(src) != lm_ggml_nelements(dst)) return false;
+        if (lm_ggml_is_contiguous(src) && lm_ggml_is_contiguous(dst)) return true;
+        return lm_ggml_are_same_shape(src, dst) && src->nb[0] == 2 && dst->nb[0] == 2;
+    }
     if (!src || src->type != LM_GGML_TYPE_F32) return false;
     if (dst->type != LM_GGML_TYPE_F32 && dst->type != LM_GGML_TYPE_F16) return false;
     if (lm_ggml_nelements(src) != lm_ggml_nelements(dst)) return false;
@@ -471,7 +476,12 @@ bool supports_binary(const lm_ggml_tensor * op) {
 
 bool supports_rope(const lm_ggml_tensor * op) {
     const lm_ggml_tensor * a = op->src[0], * pos = op->src[1], * ff = op->src[2];
-    if (!a || !pos || !f32_rows(a) || op->type != LM_GGML_TYPE_F32 || op->nb[0] != 4 || pos->type != LM_GGML_TYPE_I32) return false;
+    if (!a || !pos || pos->type != LM_GGML_TYPE_I32) return false;
+    const bool f32 = f32_rows(a) && op->type == LM_GGML_TYPE_F32 && op->nb[0] == 4;
+    // f16 in, f16 out: the K-shift of the cache (llama_kv_cache_unified::build_rope_shift)
+    const bool f16 = a->type == LM_GGML_TYPE_F16 && op->type == LM_GGML_TYPE_F16 && a->nb[0] == 2 && op->nb[0] == 2 && a->nb[1] % 4 == 0 &&
+                     a->nb[2] % 4 == 0 && op->nb[1] % 4 == 0 && op->nb[2] % 4 == 0;
+    if (!f32 && !f16) return false;
     const int32_t * p = (const int32_t *) op->op_params;
     const int n_dims = p[1], mode = p[2];
     float ext_factor;
@@ -541,14 +551,15 @@ bool only_user_is(const lm_ggml_cgraph * g, const lm_ggml_tensor * t, const lm_g
 }
 
 lm_ggml_status compute_cpy(b200_backend_ctx * ctx, const lm_ggml_tensor * node, const lm_ggml_tensor * src, const lm_ggml_tensor * dst) {
-    const bool to_f16 = dst->type == LM_GGML_TYPE_F16;
+    const bool to_f16 = dst->type == LM_GGML_TYPE_F16, from_f16 = src->type == LM_GGML_TYPE_F16;
     auto run = [&](const void * s, int64_t snb, void * d, int64_t dnb, int64_t n, int64_t rows) {
+        if (from_f16) return b200_cpy_f16_f16(s, snb, d, dnb, n, rows, ctx->stream);
         return to_f16 ? b200_cpy_f32_f16((const float *) s, snb, d, dnb, n, rows, ctx->stream)
                       : b200_cpy_f32_f32((const float *) s, snb, (float *) d, dnb, n, rows, ctx->stream);
     };
     if (lm_ggml_is_contiguous(src) && lm_ggml_is_contiguous(dst)) {
         const int64_t n = lm_ggml_nelements(src);
-        B200_CHECK(run(src->data, n * 4, dst->data, n * (int64_t) lm_ggml_type_size(dst->type), n, 1));
+        B200_CHECK(run(src->data, n * (int64_t) lm_ggml_type_size(src->type), dst->data, n * (int64_t) lm_ggml_type_size(dst->type), n, 1));
         return LM_GGML_STATUS_SUCCESS;
     }
     for (int64_t i3 = 0; i3 < src->ne[3]; ++i3)
@@ -643,7 +654,20 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
                 if (next && next->op == LM_GGML_OP_MUL && next->src[0] == node && next->src[1] && next->src[1]->type == LM_GGML_TYPE_F32 &&
                     next->src[1]->ne[0] == d && lm_ggml_nelements(next->src[1]) == d && lm_ggml_is_contiguous(next->src[1]) &&
                     lm_ggml_is_contiguous(next) && only_user_is(cgraph, node, next)) {
-                    B200_CHECK(b200_rms_norm((const float *) s0->data, s0->nb[1], (const float *) next->src[1]->data, (float *) next->data, d * 4, d, rows, eps, st));
+                    // ... and when the next node multiplies a quantised weight by the result, the same kernel also
+                    // leaves it quantised for that mul_mat (and the ones after it that read the same tensor)
+                    lm_ggml_tensor * mm = i + 2 < cgraph->n_nodes ? cgraph->nodes[i + 2] : nullptr;
+                    const bool feeds_mul_mat = mm && mm->op == LM_GGML_OP_MUL_MAT && mm->src[1] == next && d % 32 == 0 && d <= 16384 &&
+                                               s0->nb[1] % 16 == 0 && ((uintptr_t) s0->data % 16) == 0 && ((uintptr_t) next->data % 16) == 0;
+                    void * act = feeds_mul_mat ? ctx->act.get(b200_act_bytes(d, rows), st) : nullptr;
+                    if (act) {
+                        B200_CHECK(b200_add_rms_norm_quantize((float *) s0->data, s0->nb[1], nullptr, 0, (const float *) next->src[1]->data, (float *) next->data,
+                                                              d * 4, d, rows, eps, act, ctx->act.bytes, ctx->q8_variant, st));
+                        ctx->act_src = next;
+                        ctx->stats.act_quantized++;
+                    } else {
+                        B200_CHECK(b200_rms_norm((const float *) s0->data, s0->nb[1], (const float *) next->src[1]->data, (float *) next->data, d * 4, d, rows, eps, st));
+                    }
                     ++i;
                 } else {
                     B200_CHECK(b200_rms_norm((const float *) s0->data, s0->nb[1], nullptr, (float *) node->data, d * 4, d, rows, eps, st));
@@ -662,7 +686,21 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
                 if (next && next->op == LM_GGML_OP_MUL && (next->src[0] == node || next->src[1] == node) && supports_binary(next) &&
                     lm_ggml_are_same_shape(next->src[0], next->src[1]) && only_user_is(cgraph, node, next)) {
                     const lm_ggml_tensor * other = next->src[0] == node ? next->src[1] : next->src[0];
-                    B200_CHECK(b200_silu((const float *) s0->data, (const float *) other->data, (float *) next->data, lm_ggml_nelements(s0), st));
+                    // the product is the input of ffn_down: the same kernel leaves it quantised for that mul_mat
+                    lm_ggml_tensor * mm = i + 2 < cgraph->n_nodes ? cgraph->nodes[i + 2] : nullptr;
+                    const int64_t d = s0->ne[0], rows = lm_ggml_nrows(s0);
+                    const bool feeds_mul_mat = mm && mm->op == LM_GGML_OP_MUL_MAT && mm->src[1] == next && d % 32 == 0 && lm_ggml_is_contiguous(s0) &&
+                                               lm_ggml_is_contiguous(other) && lm_ggml_is_contiguous(next) && ((uintptr_t) s0->data % 16) == 0 &&
+                                               ((uintptr_t) other->data % 16) == 0 && ((uintptr_t) next->data % 16) == 0;
+                    void * act = feeds_mul_mat ? ctx->act.get(b200_act_bytes(d, rows), st) : nullptr;
+                    if (act) {
+                        B200_CHECK(b200_silu_mul_quantize((const float *) s0->data, (const float *) other->data, d * 4, (float *) next->data, d * 4, d, rows,
+                                                          act, ctx->act.bytes, ctx->q8_variant, st));
+                        ctx->act_src = next;
+                        ctx->stats.act_quantized++;
+                    } else {
+                        B200_CHECK(b200_silu((const float *) s0->data, (const float *) other->data, (float *) next->data, lm_ggml_nelements(s0), st));
+                    }
                     ++i;
                 } else {
                     B200_CHECK(b200_silu((const float *) s0->data, nullptr, (float *) node->data, lm_ggml_nelements(s0), st));
@@ -674,6 +712,12 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
                 memcpy(&freq_base, p + 5, sizeof(float));
                 memcpy(&freq_scale, p + 6, sizeof(float));
                 memcpy(&attn_factor, p + 8, sizeof(float));
+                if (s0->type == LM_GGML_TYPE_F16) {
+                    B200_CHECK(b200_rope_norm_f16(s0->data, s0->nb[1], s0->nb[2], node->data, node->nb[1], node->nb[2], s0->ne[0], s0->ne[1], s0->ne[2], p[1],
+                                                  (const int32_t *) s1->data, node->src[2] ? (const float *) node->src[2]->data : nullptr, freq_base,
+                                                  freq_scale, attn_factor, st));
+                    break;
+                }
                 B200_CHECK(b200_rope_norm((const float *) s0->data, s0->nb[1], s0->nb[2], (float *) node->data, node->nb[1], node->nb[2], s0->ne[0],
                                           s0->ne[1], s0->ne[2], p[1], (const int32_t *) s1->data, node->src[2] ? (const float *) node->src[2]->data : nullptr,
                                           freq_base, freq_scale, attn_factor, st));

@@ -68,6 +68,7 @@ __global__ void __launch_bounds__(1024) add_rms_norm_quantize_kernel(float *__re
 // silu(gate) * up, quantised; the same index space as quantize_q8_0_kernel
 template <int LAYOUT>
 __global__ void __launch_bounds__(256) silu_mul_quantize_kernel(const float *__restrict__ gate, const float *__restrict__ up, int64_t nb_row,
+                                                               float *__restrict__ dst, int64_t dst_nb_row,
                                                                int64_t N, int64_t n_rows_padded, int64_t nb, int64_t nbp,
                                                                uint8_t *__restrict__ out, size_t d_offset, int variant) {
     const int64_t gid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
@@ -87,6 +88,7 @@ __global__ void __launch_bounds__(256) silu_mul_quantize_kernel(const float *__r
             const float s = ga[i] / (1.0f + expf(-ga[i]));
             v[i] = s * ua[i];
         }
+        if (dst) *reinterpret_cast<float4 *>(reinterpret_cast<char *>(dst) + n * dst_nb_row + (b * 32 + j * 4) * 4) = make_float4(v[0], v[1], v[2], v[3]);
     }
     q8_quantize_store<LAYOUT>(v, out, d_offset, nb, nbp, n, b, j, real, variant);
 }
@@ -179,10 +181,11 @@ int b200_add_rms_norm_quantize(float *x, int64_t x_nb_row, const float *residual
     return check_launch("add_rms_norm_quantize");
 }
 
-int b200_silu_mul_quantize(const float *gate, const float *up, int64_t nb_row, int64_t K, int64_t N, void *scratch, size_t scratch_bytes,
-                           int variant, b200_stream_t stream) {
+int b200_silu_mul_quantize(const float *gate, const float *up, int64_t nb_row, float *dst, int64_t dst_nb_row, int64_t K, int64_t N,
+                           void *scratch, size_t scratch_bytes, int variant, b200_stream_t stream) {
     B200_REQUIRE(gate && up && scratch && K > 0 && K % 32 == 0 && N > 0, "bad arguments");
-    B200_REQUIRE(nb_row % 16 == 0 && is_aligned(gate, 16) && is_aligned(up, 16), "rows must be 16-byte aligned");
+    B200_REQUIRE(nb_row % 16 == 0 && is_aligned(gate, 16) && is_aligned(up, 16) && (!dst || (is_aligned(dst, 16) && dst_nb_row % 16 == 0)),
+                 "rows must be 16-byte aligned");
     B200_REQUIRE(variant == B200_Q8_AVX2 || variant == B200_Q8_SCALAR, "unknown quantiser variant %d", variant);
     B200_REQUIRE(is_aligned(scratch, 256), "scratch must be 256-byte aligned");
     const ActDims a = act_dims(K, N);
@@ -192,9 +195,9 @@ int b200_silu_mul_quantize(const float *gate, const float *up, int64_t nb_row, i
     const unsigned grid = (unsigned) ((threads + 255) / 256);
     cudaStream_t st = (cudaStream_t) stream;
     if (act_layout_canonical(N)) {
-        silu_mul_quantize_kernel<2><<<grid, 256, 0, st>>>(gate, up, nb_row, N, rows_padded, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
+        silu_mul_quantize_kernel<2><<<grid, 256, 0, st>>>(gate, up, nb_row, dst, dst_nb_row, N, rows_padded, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
     } else {
-        silu_mul_quantize_kernel<1><<<grid, 256, 0, st>>>(gate, up, nb_row, N, rows_padded, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
+        silu_mul_quantize_kernel<1><<<grid, 256, 0, st>>>(gate, up, nb_row, dst, dst_nb_row, N, rows_padded, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
     }
     return check_launch("silu_mul_quantize");
 }

@@ -96,6 +96,57 @@ __global__ void __launch_bounds__(128) rope_norm_kernel(const float *__restrict_
     }
 }
 
+// The same rotation on f16 rows, as the K-shift graph applies it in place to the cached keys
+// (lm_ggml_compute_forward_rope_f16, ops.cpp:5364-5520): values widened to f32, rotated, rounded back to f16.
+// pos[t] is the shift of cell t; a zero shift returns the row unchanged bit for bit (cos 1, sin 0).
+__global__ void __launch_bounds__(128) rope_norm_f16_kernel(const __half *__restrict__ x, int64_t x_nb_head, int64_t x_nb_tok,
+                                                           __half *__restrict__ dst, int64_t dst_nb_head, int64_t dst_nb_tok, int64_t D,
+                                                           int64_t H, int n_dims, const int32_t *__restrict__ pos,
+                                                           const float *__restrict__ ff, float theta_scale, float freq_scale, float attn_factor) {
+    extern __shared__ float cs[];   // [n_dims/2] cos, [n_dims/2] sin, [n_dims/2] theta
+    const int64_t t = blockIdx.x;
+    const int half_dims = n_dims / 2;
+    float *th_s = cs + 2 * half_dims;
+    if (threadIdx.x == 0) {
+        float theta = (float) pos[t];
+        for (int k = 0; k < half_dims; ++k) {
+            th_s[k] = theta;
+            theta *= theta_scale;
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 2 * half_dims; i += blockDim.x) {
+        const int a = i < half_dims ? i : i - half_dims;
+        const float f = ff ? ff[a] : 1.0f;
+        const float th = freq_scale * (th_s[a] / f);
+        cs[i] = (i < half_dims ? cosf(th) : sinf(th)) * attn_factor;
+    }
+    __syncthreads();
+    const int64_t pairs = D / 2;
+    for (int64_t i = threadIdx.x; i < H * pairs; i += blockDim.x) {
+        const int64_t h = i / pairs, k = i - h * pairs;
+        const __half2 v = *reinterpret_cast<const __half2 *>(reinterpret_cast<const char *>(x) + t * x_nb_tok + h * x_nb_head + 4 * k);
+        __half2 *o = reinterpret_cast<__half2 *>(reinterpret_cast<char *>(dst) + t * dst_nb_tok + h * dst_nb_head + 4 * k);
+        if (k < half_dims) {
+            const float c = cs[k], sn = cs[half_dims + k];
+            const float x0 = __low2float(v), x1 = __high2float(v);
+            *o = __halves2half2(__float2half_rn(x0 * c - x1 * sn), __float2half_rn(x0 * sn + x1 * c));
+        } else {
+            *o = v;
+        }
+    }
+}
+
+// rows of 2-byte elements copied as they are (f16 -> f16: the moves of a cache defragmentation)
+__global__ void __launch_bounds__(256) cpy_b16_kernel(const uint16_t *__restrict__ x, int64_t x_nb_row, uint16_t *__restrict__ dst,
+                                                     int64_t dst_nb_row, int64_t d, int64_t rows) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= d * rows) return;
+    const int64_t r = i / d, c = i - r * d;
+    reinterpret_cast<uint16_t *>(reinterpret_cast<char *>(dst) + r * dst_nb_row)[c] =
+        reinterpret_cast<const uint16_t *>(reinterpret_cast<const char *>(x) + r * x_nb_row)[c];
+}
+
 template <typename TO>
 __global__ void __launch_bounds__(256) cpy_kernel(const float *__restrict__ x, int64_t x_nb_row, TO *__restrict__ dst, int64_t dst_nb_row,
                                                  int64_t d, int64_t rows) {
@@ -166,6 +217,26 @@ int b200_rope_norm(const float *x, int64_t x_nb_head, int64_t x_nb_tok, float *d
     rope_norm_kernel<<<(unsigned) T, 128, (size_t) n_dims * sizeof(float), (cudaStream_t) stream>>>(x, x_nb_head, x_nb_tok, dst, dst_nb_head, dst_nb_tok, D, H, T,
                                                                               n_dims, pos, freq_factors, theta_scale, freq_scale, attn_factor);
     return check_launch("rope_norm");
+}
+
+int b200_rope_norm_f16(const void *x, int64_t x_nb_head, int64_t x_nb_tok, void *dst, int64_t dst_nb_head, int64_t dst_nb_tok, int64_t D,
+                       int64_t H, int64_t T, int n_dims, const int32_t *pos, const float *freq_factors, float freq_base, float freq_scale,
+                       float attn_factor, b200_stream_t stream) {
+    B200_REQUIRE(x && dst && pos && D > 0 && D % 2 == 0 && H > 0 && T >= 0 && n_dims > 0 && n_dims <= D && n_dims % 2 == 0, "bad rope arguments");
+    B200_REQUIRE(n_dims <= 8192 && is_aligned(x, 4) && is_aligned(dst, 4) && x_nb_head % 4 == 0 && x_nb_tok % 4 == 0 && dst_nb_head % 4 == 0 && dst_nb_tok % 4 == 0,
+                 "f16 rope rows must be 4-byte aligned");
+    if (T == 0) return B200_OK;
+    const float theta_scale = powf(freq_base, -2.0f / (float) n_dims);
+    rope_norm_f16_kernel<<<(unsigned) T, 128, (size_t) (n_dims + n_dims / 2) * sizeof(float), (cudaStream_t) stream>>>(
+        (const __half *) x, x_nb_head, x_nb_tok, (__half *) dst, dst_nb_head, dst_nb_tok, D, H, n_dims, pos, freq_factors, theta_scale, freq_scale, attn_factor);
+    return check_launch("rope_norm_f16");
+}
+
+int b200_cpy_f16_f16(const void *x, int64_t x_nb_row, void *dst, int64_t dst_nb_row, int64_t d, int64_t rows, b200_stream_t stream) {
+    B200_REQUIRE(x && dst && d > 0 && rows >= 0 && x_nb_row % 2 == 0 && dst_nb_row % 2 == 0, "bad cpy arguments");
+    if (rows == 0) return B200_OK;
+    cpy_b16_kernel<<<blocks_for(d * rows), 256, 0, (cudaStream_t) stream>>>((const uint16_t *) x, x_nb_row, (uint16_t *) dst, dst_nb_row, d, rows);
+    return check_launch("cpy_f16_f16");
 }
 
 int b200_cpy_f32_f16(const float *x, int64_t x_nb_row, void *dst, int64_t dst_nb_row, int64_t d, int64_t rows, b200_stream_t stream) {

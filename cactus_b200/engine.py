@@ -272,7 +272,7 @@ class LlamaEngine:
             else:
                 self._mm(p + "ffn_gate.weight", self.act_d, T, self.gate)
                 self._mm(p + "ffn_up.weight", self.act_d, T, self.up)
-            check(L.b200_silu_mul_quantize(self.gate.data_ptr(), self.up.data_ptr(), self.gate.stride(0) * 4, cfg.d_ff, T, self.act_ff.data_ptr(),
+            check(L.b200_silu_mul_quantize(self.gate.data_ptr(), self.up.data_ptr(), self.gate.stride(0) * 4, None, 0, cfg.d_ff, T, self.act_ff.data_ptr(),
                                            self.act_ff.numel(), V, st))
             self._mm(p + "ffn_down.weight", self.act_ff, T, self.tmp2)
             pending = self.tmp2

@@ -200,6 +200,14 @@ B200_API int b200_rope_norm(const float *x, int64_t x_nb_head, int64_t x_nb_tok,
                             int64_t dst_nb_tok, int64_t D, int64_t H, int64_t T, int n_dims, const int32_t *pos,
                             const float *freq_factors, float freq_base, float freq_scale, float attn_factor,
                             b200_stream_t stream);
+/* KV-cache maintenance graphs (cactus/llama-kv-cache.cpp:822-926, :928-1210).
+ * K-shift: ROPE mode 0 applied in place to the cached f16 keys viewed as [D, Hkv, cells], with the per-cell position
+ * shift as `pos` (lm_ggml_compute_forward_rope_f16, cactus/ggml-cpu/ops.cpp:5364-5520: widen to f32, rotate, round to f16).
+ * Defragmentation: CPY f16 -> f16 of row ranges of the cache from one run of cells to another. */
+B200_API int b200_rope_norm_f16(const void *x, int64_t x_nb_head, int64_t x_nb_tok, void *dst, int64_t dst_nb_head, int64_t dst_nb_tok,
+                                int64_t D, int64_t H, int64_t T, int n_dims, const int32_t *pos, const float *freq_factors, float freq_base,
+                                float freq_scale, float attn_factor, b200_stream_t stream);
+B200_API int b200_cpy_f16_f16(const void *x, int64_t x_nb_row, void *dst, int64_t dst_nb_row, int64_t d, int64_t rows, b200_stream_t stream);
 /* CPY f32 -> f16 / f32 -> f32 (ops.cpp:657, :4180): rows of d elements with byte strides on both sides */
 B200_API int b200_cpy_f32_f16(const float *x, int64_t x_nb_row, void *dst, int64_t dst_nb_row, int64_t d, int64_t rows,
                               b200_stream_t stream);
@@ -236,15 +244,16 @@ B200_API int b200_argmax_rows(const float *x, int64_t x_nb_row, int64_t d, int64
  * b200_add_rms_norm_quantize: x += residual (ADD, cactus/ggml-cpu/ops.cpp:1283-1300; skipped when residual is NULL),
  *   h = rms_norm(x) * w (ops.cpp:3268-3316 + MUL; w may be NULL), h quantised into `scratch` as
  *   b200_quantize_activations would; h itself is stored only when `h` is not NULL.
- * b200_silu_mul_quantize: silu(gate) * up (ops.cpp:2902-2981 + MUL) quantised into `scratch`.
+ * b200_silu_mul_quantize: silu(gate) * up (ops.cpp:2902-2981 + MUL) quantised into `scratch`; the f32 product is stored
+ *   only when `dst` is not NULL.
  * b200_rope_store: ROPE (mode 0, as b200_rope_norm) of q in place and of k, with k and v stored as f16 into the cache
  *   rows slots[t] (cpy_k / cpy_v, cactus/llama-kv-cache.cpp:617-656); the f32 k is left as it was.
  * ------------------------------------------------------------------------------------------------ */
 B200_API int b200_add_rms_norm_quantize(float *x, int64_t x_nb_row, const float *residual, int64_t residual_nb_row, const float *w, float *h,
                                         int64_t h_nb_row, int64_t d, int64_t rows, float eps, void *scratch, size_t scratch_bytes,
                                         int variant, b200_stream_t stream);
-B200_API int b200_silu_mul_quantize(const float *gate, const float *up, int64_t nb_row, int64_t K, int64_t N, void *scratch,
-                                    size_t scratch_bytes, int variant, b200_stream_t stream);
+B200_API int b200_silu_mul_quantize(const float *gate, const float *up, int64_t nb_row, float *dst, int64_t dst_nb_row, int64_t K, int64_t N,
+                                    void *scratch, size_t scratch_bytes, int variant, b200_stream_t stream);
 B200_API int b200_rope_store(float *q, int64_t q_nb_head, int64_t q_nb_tok, const float *k, int64_t k_nb_head, int64_t k_nb_tok,
                              const float *v, int64_t v_nb_tok, int64_t D, int64_t H, int64_t Hkv, int64_t T, int n_dims, const int32_t *pos,
                              const float *freq_factors, float freq_base, float freq_scale, float attn_factor, const int32_t *slots,

@@ -67,6 +67,7 @@ class Oracle:
         L.orc_add.argtypes = [i64, _f32p, _f32p, _f32p]
         L.orc_rope_norm.argtypes = [i64, i64, i64, _f32p, _i32p, f32, _f32p]
         L.orc_cpy_f32_f16.argtypes = [i64, _f32p, _u16p]
+        L.orc_rope_norm_f16.argtypes = [i64, i64, i64, _u16p, _i32p, f32, _u16p]
         L.orc_get_rows.argtypes = [i32, i64, i64, _u8p, _i32p, _f32p]
 
     # ---- quantisers -------------------------------------------------------------------------
@@ -161,6 +162,13 @@ class Oracle:
         self.L.orc_rope_norm(D, H, T, np.ascontiguousarray(x), np.ascontiguousarray(pos, np.int32), freq_base, dst)
         return dst
 
+    def rope_norm_f16(self, x, pos, freq_base):
+        """x uint16 (f16 bits) [T, H, D], pos int32 [T] -> uint16 [T, H, D]"""
+        T, H, D = x.shape
+        dst = np.empty_like(x)
+        self.L.orc_rope_norm_f16(D, H, T, np.ascontiguousarray(x, np.uint16), np.ascontiguousarray(pos, np.int32), freq_base, dst)
+        return dst
+
     def cpy_f32_f16(self, x):
         dst = np.empty(x.shape, np.uint16)
         self.L.orc_cpy_f32_f16(x.size, np.ascontiguousarray(x), dst)
@@ -198,7 +206,7 @@ class Reference:
         L.ref_mul_mat.argtypes = [i32, i64, i64, i64, _u8p, C.c_void_p, i64, _f32p, i32, i32, i32]
         L.ref_flash_attn_ext.restype = dbl
         L.ref_flash_attn_ext.argtypes = [i64, i64, i64, i64, i64, _f32p, _u16p, _u16p, _u16p, f32, f32, f32, _f32p, i32, i32, i32]
-        L.ref_row_op.argtypes = [i32, i64, i64, i64, _f32p, C.c_void_p, f32, C.c_void_p, i32]
+        L.ref_row_op.argtypes = [i32, i64, i64, i64, C.c_void_p, C.c_void_p, f32, C.c_void_p, i32]
 
     def quantize_weights(self, wtype, w):
         w = np.ascontiguousarray(w, np.float32)
@@ -241,13 +249,13 @@ class Reference:
         return dst, t
 
     def row_op(self, op, a, b, p0=0.0, out_dtype=np.float32):
-        a = np.ascontiguousarray(a, np.float32)
+        a = np.ascontiguousarray(a, np.uint16 if op == 5 else np.float32)   # op 5 takes f16 bits
         if a.ndim == 3:
             T, h, d = a.shape
         else:
             (T, d), h = a.shape, 1
         dst = np.empty(a.shape, out_dtype)
         b = np.ascontiguousarray(b) if b is not None else None
-        rc = self.L.ref_row_op(op, d, h, T, a, b.ctypes.data if b is not None else None, p0, dst.ctypes.data, 1)
+        rc = self.L.ref_row_op(op, d, h, T, a.ctypes.data, b.ctypes.data if b is not None else None, p0, dst.ctypes.data, 1)
         assert rc == 0
         return dst

@@ -386,6 +386,26 @@ void orc_rope_norm(int64_t D, int64_t H, int64_t T, const float *x, const int32_
         }
     }
 }
+/* the same on an f16 tensor, as the K-shift graph applies it in place to the cached keys
+ * (cactus/llama-kv-cache.cpp:822-860 -> lm_ggml_compute_forward_rope_f16, cactus/ggml-cpu/ops.cpp:5364-5520):
+ * values widened to f32, rotated, rounded back to f16; pos holds the per-cell position shift (may be negative) */
+void orc_rope_norm_f16(int64_t D, int64_t H, int64_t T, const uint16_t *x, const int32_t *pos, float freq_base, uint16_t *dst) {
+    const float theta_scale = powf(freq_base, -2.0f / (float) D);
+    for (int64_t t = 0; t < T; ++t) {
+        for (int64_t h = 0; h < H; ++h) {
+            float theta = (float) pos[t];
+            const uint16_t *s = x + (t * H + h) * D;
+            uint16_t *o = dst + (t * H + h) * D;
+            for (int64_t i = 0; i < D; i += 2) {
+                const float c = cosf(theta), sn = sinf(theta);
+                const float x0 = orc_fp16_to_fp32(s[i]), x1 = orc_fp16_to_fp32(s[i + 1]);
+                o[i] = orc_fp32_to_fp16(fmaf(x0, c, -(x1 * sn)));
+                o[i + 1] = orc_fp32_to_fp16(fmaf(x0, sn, x1 * c));
+                theta *= theta_scale;
+            }
+        }
+    }
+}
 void orc_cpy_f32_f16(int64_t n, const float *x, uint16_t *dst) {
     for (int64_t i = 0; i < n; ++i) dst[i] = orc_fp32_to_fp16(x[i]);
 }

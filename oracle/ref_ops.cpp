@@ -150,6 +150,7 @@ double ref_flash_attn_ext(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, int64_t
 //   op 2: ADD(a, b)                 a,b [d,T]
 //   op 3: ROPE mode 0 on a [D,H,T] with int32 positions in b, freq_base in p0, n_dims = D
 //   op 4: CPY f32 -> f16            a [d,T] -> dst f16
+//   op 5: ROPE mode 0 on an f16 a [D,H,T] (passed through the float pointer) -> dst f16: the K-shift of the cache
 int ref_row_op(int op, int64_t d, int64_t h, int64_t T, const float * a, const void * b, float p0, void * dst, int n_threads) {
     ctx_guard g(16 * 1024 * 1024);
     lm_ggml_tensor * out = nullptr;
@@ -192,6 +193,13 @@ int ref_row_op(int op, int64_t d, int64_t h, int64_t T, const float * a, const v
             lm_ggml_tensor * y = lm_ggml_new_tensor(g.ctx, LM_GGML_TYPE_F16, 2, ne2);
             y->data = dst;
             out = lm_ggml_cpy(g.ctx, x, y);
+        } break;
+        case 5: {   // ROPE on an f16 tensor (the K-shift of the cache); a is f16 here
+            const int64_t ne3[3] = { d, h, T };
+            lm_ggml_tensor * x = wrap(g.ctx, LM_GGML_TYPE_F16, 3, ne3, a);
+            const int64_t nep[1] = { T };
+            lm_ggml_tensor * pos = wrap(g.ctx, LM_GGML_TYPE_I32, 1, nep, b);
+            out = lm_ggml_rope_ext(g.ctx, x, pos, nullptr, (int) d, 0, 0, p0, 1.0f, 0.0f, 1.0f, 0.0f, 0.0f);
         } break;
         default: return -1;
     }

@@ -197,6 +197,58 @@ static int run_ops(int n_tokens, lm_ggml_type wtype) {
     return rc;
 }
 
+// The two KV-cache maintenance graphs of the reference on single nodes: the K-shift (ROPE in place on the cached f16
+// keys with a per-cell shift, llama_kv_cache_unified::build_graph_shift) and a defragmentation move (CPY f16 -> f16 of a
+// run of cells, build_graph_defrag), CPU backend against the B200 backend.
+static int run_kv_ops() {
+    lm_ggml_backend_t cpu = lm_ggml_backend_cpu_init();
+    lm_ggml_backend_t gpu = lm_ggml_backend_b200_init(0);
+    if (!gpu) { printf("{\"error\": \"no B200 backend\"}\n"); return 2; }
+    const int64_t Hkv = 2, D = 64, n_kv = 256;
+    lm_ggml_init_params ip = { 16 * 1024 * 1024, nullptr, true };
+    lm_ggml_context * ctx = lm_ggml_init(ip);
+    std::mt19937 rng(11);
+    lm_ggml_tensor * kc = lm_ggml_new_tensor_2d(ctx, LM_GGML_TYPE_F16, Hkv * D, n_kv);
+    lm_ggml_tensor * vc = lm_ggml_new_tensor_2d(ctx, LM_GGML_TYPE_F16, Hkv * D, n_kv);
+    lm_ggml_tensor * shift = lm_ggml_new_tensor_1d(ctx, LM_GGML_TYPE_I32, n_kv);
+    for (lm_ggml_tensor * t : {kc, vc, shift}) lm_ggml_set_input(t);
+    lm_ggml_tensor * k3 = lm_ggml_view_3d(ctx, kc, D, Hkv, n_kv, lm_ggml_row_size(kc->type, D), lm_ggml_row_size(kc->type, Hkv * D), 0);
+    lm_ggml_tensor * shifted = lm_ggml_rope_ext_inplace(ctx, k3, shift, nullptr, D, 0, 0, 500000.0f, 1.0f, 0.0f, 1.0f, 0.0f, 0.0f);
+    const int64_t from = 200, to = 40, nm = 17;   // cells [200, 217) move to [40, 57)
+    lm_ggml_tensor * src = lm_ggml_view_2d(ctx, vc, Hkv * D, nm, lm_ggml_row_size(vc->type, Hkv * D), lm_ggml_row_size(vc->type, Hkv * D * from));
+    lm_ggml_tensor * dst = lm_ggml_view_2d(ctx, vc, Hkv * D, nm, lm_ggml_row_size(vc->type, Hkv * D), lm_ggml_row_size(vc->type, Hkv * D * to));
+    lm_ggml_tensor * moved = lm_ggml_cpy(ctx, src, dst);
+    lm_ggml_cgraph * gf = lm_ggml_new_graph(ctx);
+    lm_ggml_build_forward_expand(gf, shifted);
+    lm_ggml_build_forward_expand(gf, moved);
+    lm_ggml_backend_buffer_t buf = lm_ggml_backend_alloc_ctx_tensors(ctx, cpu);
+    if (!buf) { printf("{\"error\": \"alloc failed\"}\n"); return 2; }
+    std::vector<float> tmp((size_t) Hkv * D * n_kv);
+    std::vector<lm_ggml_fp16_t> kv(tmp.size());
+    for (lm_ggml_tensor * t : {kc, vc}) {
+        fill_normal(tmp, rng, 1.0f);
+        lm_ggml_fp32_to_fp16_row(tmp.data(), kv.data(), tmp.size());
+        lm_ggml_backend_tensor_set(t, kv.data(), 0, kv.size() * 2);
+    }
+    std::vector<int32_t> sh(n_kv);
+    for (int i = 0; i < n_kv; ++i) sh[i] = (i % 4 == 0) ? 0 : (int32_t) (rng() % 4096) - 2048;
+    lm_ggml_backend_tensor_set(shift, sh.data(), 0, sh.size() * 4);
+    cmp_state st;
+    memset(&st, 0, sizeof(st));
+    const bool ok = lm_ggml_backend_compare_graph_backend(cpu, gpu, gf, cmp_cb, &st);
+    printf("{\"case\": \"kv maintenance\", \"compared\": %s, \"nan_mismatch\": %s, \"ROPE\": %.3g, \"CPY\": %.3g, \"rope_nodes\": %d, \"cpy_nodes\": %d}\n",
+           ok ? "true" : "false", st.nan_seen ? "true" : "false", st.worst[LM_GGML_OP_ROPE], st.worst[LM_GGML_OP_CPY], st.count[LM_GGML_OP_ROPE],
+           st.count[LM_GGML_OP_CPY]);
+    // f16 results: at most one f16 step apart where the f32 rotation differs in its last bits; copies are exact
+    int rc = (ok && !st.nan_seen && st.count[LM_GGML_OP_ROPE] == 1 && st.count[LM_GGML_OP_CPY] == 1 && st.worst[LM_GGML_OP_ROPE] < 2e-3 &&
+              st.worst[LM_GGML_OP_CPY] == 0.0) ? 0 : 1;
+    lm_ggml_backend_buffer_free(buf);
+    lm_ggml_free(ctx);
+    lm_ggml_backend_free(gpu);
+    lm_ggml_backend_free(cpu);
+    return rc;
+}
+
 // ------------------------------------------------------------------------------------------------------
 // model
 // ------------------------------------------------------------------------------------------------------
@@ -454,6 +506,7 @@ int main(int argc, char ** argv) {
         int rc = 0;
         for (lm_ggml_type t : {LM_GGML_TYPE_Q4_0, LM_GGML_TYPE_Q8_0})
             for (int n : {1, 5, 24, 70}) rc |= run_ops(n, t);
+        rc |= run_kv_ops();
         return rc;
     }
     if (argc >= 2 && strcmp(argv[1], "model") == 0) return run_model(argc, argv);

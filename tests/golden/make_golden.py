@@ -92,6 +92,7 @@ def main():
     out["add"] = ref.row_op(2, r["x"], r["y"])
     out["rope"] = ref.row_op(3, r["xr"], r["pos"], 500000.0)
     out["cpy_f16"] = ref.row_op(4, r["x"], None, out_dtype=np.uint16)
+    out["rope_f16"] = ref.row_op(5, r["kf16"], r["shift"], 500000.0, out_dtype=np.uint16)
 
     path = os.path.join(HERE, "golden.npz")
     np.savez_compressed(path, **out)

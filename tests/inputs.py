@@ -137,4 +137,7 @@ def row_op_inputs():
         w=(1.0 + 0.1 * rng.standard_normal(2048)).astype(np.float32),
         xr=rng.standard_normal((7, 4, 128)).astype(np.float32),
         pos=np.array([0, 1, 5, 100, 4095, 70000, 3], np.int32),
+        # K-shift of cached keys: f16 rows [cells, kv heads, D] and a per-cell position shift (zero, negative, large)
+        kf16=rng.standard_normal((9, 2, 128)).astype(np.float16).view(np.uint16),
+        shift=np.array([0, -1, 7, -512, 0, 2048, -33000, 1, 0], np.int32),
     )

@@ -58,7 +58,13 @@ def test_silu_mul_quantize(N, K):
     check(L.b200_silu(gate.data_ptr(), up.data_ptr(), act.data_ptr(), N * K, _st()))
     sa, sb = _scratch(L, K, N)
     check(L.b200_quantize_activations(act.data_ptr(), K * 4, K, N, sa.data_ptr(), sa.numel(), 0, _st()))
-    check(L.b200_silu_mul_quantize(gate.data_ptr(), up.data_ptr(), K * 4, K, N, sb.data_ptr(), sb.numel(), 0, _st()))
+    out = torch.empty_like(gate)
+    check(L.b200_silu_mul_quantize(gate.data_ptr(), up.data_ptr(), K * 4, out.data_ptr(), K * 4, K, N, sb.data_ptr(), sb.numel(), 0, _st()))
+    torch.cuda.synchronize()
+    assert torch.equal(sa, sb)
+    assert torch.equal(act.view(torch.int32), out.view(torch.int32))
+    sb.fill_(0xAB)
+    check(L.b200_silu_mul_quantize(gate.data_ptr(), up.data_ptr(), K * 4, None, 0, K, N, sb.data_ptr(), sb.numel(), 0, _st()))
     torch.cuda.synchronize()
     assert torch.equal(sa, sb)
 

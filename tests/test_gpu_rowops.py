@@ -37,3 +37,31 @@ def test_mul_broadcast_and_views(oracle):
     # GET_ROWS on an f32 table
     ids = np.array([4, 0, 4], np.int32)
     assert np.array_equal(host(ops.get_rows(dev(a), dev(ids))), a[ids])
+
+
+def test_k_shift_rope_f16_and_f16_copy(golden):
+    """K-shift (ROPE in place on cached f16 keys) against the reference's golden vector, and the f16 row copies a cache
+    defragmentation issues.  sinf/cosf of the device differ from glibc's in the last bit, so a result may land one f16
+    step away; rows with a zero shift must come back bit for bit."""
+    from cactus_b200._lib import check, lib
+    L = lib()
+    r = inputs.row_op_inputs()
+    k = torch.from_numpy(r["kf16"].view(np.int16)).cuda()          # [cells, kv heads, D] f16 bits
+    shift = torch.from_numpy(r["shift"]).cuda()
+    T, H, D = k.shape
+    st = torch.cuda.current_stream().cuda_stream
+    check(L.b200_rope_norm_f16(k.data_ptr(), D * 2, H * D * 2, k.data_ptr(), D * 2, H * D * 2, D, H, T, D, shift.data_ptr(), None, 500000.0, 1.0, 1.0, st))
+    torch.cuda.synchronize()
+    got = k.cpu().numpy().view(np.uint16)
+    want = golden["rope_f16"]
+    gf, wf = got.view(np.float16).astype(np.float32), want.view(np.float16).astype(np.float32)
+    assert (got == want).mean() > 0.995
+    assert np.all(np.abs(gf - wf) <= np.spacing(np.abs(wf).astype(np.float16)).astype(np.float32))
+    assert np.array_equal(got[r["shift"] == 0], r["kf16"][r["shift"] == 0])
+    # defragmentation move: rows [5, 9) of a strided cache view to rows [0, 4)
+    cache = torch.arange(12 * 64, dtype=torch.int16, device="cuda").view(12, 64)
+    before = cache.cpu().numpy().copy()
+    check(L.b200_cpy_f16_f16(cache[5:].data_ptr(), 128, cache.data_ptr(), 128, 64, 4, st))
+    torch.cuda.synchronize()
+    after = cache.cpu().numpy()
+    assert np.array_equal(after[:4], before[5:9]) and np.array_equal(after[4:], before[4:])

@@ -92,6 +92,14 @@ def test_row_ops(oracle, golden):
     assert np.array_equal(bits(oracle.add(r["x"], r["y"])), bits(golden["add"]))
     np.testing.assert_allclose(oracle.rope_norm(r["xr"], r["pos"], 500000.0), golden["rope"], rtol=0, atol=1e-6)
     assert np.array_equal(oracle.cpy_f32_f16(r["x"]), golden["cpy_f16"])
+    # K-shift of cached f16 keys: the f32 rotation differs from the reference's by at most the last bit before rounding to
+    # f16, so nearly every f16 result is identical and none is more than one f16 step away
+    got, want = oracle.rope_norm_f16(r["kf16"], r["shift"], 500000.0), golden["rope_f16"]
+    gf, wf = got.view(np.float16).astype(np.float32), want.view(np.float16).astype(np.float32)
+    assert (got == want).mean() > 0.999
+    assert np.all(np.abs(gf - wf) <= np.spacing(np.abs(wf).astype(np.float16)).astype(np.float32))
+    unshifted = r["shift"] == 0
+    assert np.array_equal(want[unshifted], r["kf16"][unshifted])   # a zero shift leaves the row as it was
     # the reference's SIMD silu uses a polynomial exp: tolerance only
     np.testing.assert_allclose(oracle.silu_mul(r["x"], r["y"]), golden["silu_mul"], rtol=0, atol=1e-5)
 
