@@ -27,9 +27,13 @@ def run(*args, timeout=600):
 def test_layer_ops_node_by_node_against_reference_cpu():
     rc, lines, err = run("ops")
     assert lines, err
+    kv = [r for r in lines if r.get("case") == "kv maintenance"]
+    assert len(kv) == 1 and kv[0]["compared"] and kv[0]["ROPE"] < 2e-3 and kv[0]["CPY"] == 0 and kv[0]["rope_nodes"] == 1 and kv[0]["cpy_nodes"] == 1, kv
     for r in lines:
         assert "error" not in r, r
         assert r["compared"] and not r["nan_mismatch"], r
+        if r.get("case") == "kv maintenance":   # K-shift and defragmentation nodes, checked above
+            continue
         # the graph is not teacher-forced: the reference accumulates the attention output in fp16 and is itself
         # ~3e-3 from the exact result, and that difference flows into the mul_mats after it
         assert r["MUL_MAT"] < 3e-2, r
@@ -62,6 +66,8 @@ def test_layer_ops_with_reference_order_attention():
     lines = [json.loads(line) for line in p.stdout.splitlines() if line.startswith("{")]
     assert lines
     for r in lines:
+        if r.get("case") == "kv maintenance":
+            continue
         if r["tokens"] == 1:
             assert r["MUL_MAT"] < 1e-5 and r["FLASH_ATTN_EXT"] < 1e-5 and r["ADD"] < 1e-5, r
         assert r["FLASH_ATTN_EXT"] < 6e-4, r
