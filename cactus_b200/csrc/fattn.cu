@@ -24,6 +24,7 @@ constexpr int FA_THREADS = 128;
 #define FA_MIN_CTAS 3
 #endif
 constexpr int FA_SUPER_WORDS = 32;  // 2048 cells listed per round
+constexpr int FA_ADAPTIVE_SPLITS = 2;   // most KV splits a long sequence is cut into when the batch is small
 
 // ---- mask scan: one warp per 64 cells of one token row ------------------------------------------
 __global__ void __launch_bounds__(256) mask_index_kernel(const __half *__restrict__ mask, int64_t mask_nb_row, int64_t Nq,
@@ -62,6 +63,30 @@ __global__ void __launch_bounds__(256) mask_words_compact_kernel(const unsigned 
     if (lane == 0) wcount[j] = base;
 }
 
+// Third pass: the tokens ordered by decreasing word count (longest sequence first, so the scheduler hands the long
+// walks out first and the short ones fill the gaps), and the total number of words, from which the attention kernel
+// derives how many words one CTA should walk.
+__global__ void __launch_bounds__(1024) fattn_plan_kernel(const int32_t *__restrict__ wcount, int64_t Nq, int32_t *__restrict__ order,
+                                                         int32_t *__restrict__ plan) {
+    __shared__ long long total_s;
+    if (threadIdx.x == 0) total_s = 0;
+    __syncthreads();
+    long long part = 0;
+    for (int64_t j = threadIdx.x; j < Nq; j += blockDim.x) {
+        const int32_t c = wcount[j];
+        part += c;
+        int64_t rank = 0;   // tokens with more words, or as many and a lower index, come first
+        for (int64_t i = 0; i < Nq; ++i) {
+            const int32_t ci = wcount[i];
+            rank += (ci > c || (ci == c && i < j)) ? 1 : 0;
+        }
+        order[rank] = (int32_t) j;
+    }
+    atomicAdd((unsigned long long *) &total_s, (unsigned long long) part);
+    __syncthreads();
+    if (threadIdx.x == 0) plan[0] = (int32_t) min(total_s, (long long) 0x7fffffff);
+}
+
 struct FattnParams {
     int64_t H, Hkv, Nq, n_kv, nw;
     const float *q; int64_t q_nb_tok, q_nb_head;
@@ -75,7 +100,10 @@ struct FattnParams {
     float *dst;
     float *partial;  // [Nq][H][nsplit][D + 2]
     int nsplit, hgroups;
-    int w0;          // > 0: a token gets ceil(words / w0) KV splits (at most nsplit), so long sequences are cut, short ones are not
+    int w0;          // > 0: a token gets ceil(words / w0) KV splits (at most nsplit), so long sequences are cut, short ones are not;
+                     // < 0: w0 is derived on the device from the mask's total word count (fattn_target_words)
+    const int32_t *order, *plan;   // tokens by decreasing word count; plan[0] = total words (NULL without a mask index)
+    int slots;       // CTAs of this kernel the device holds at once
 };
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -100,6 +128,14 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 //               two cells with byte permutes; P goes in as fp16 hi + lo parts (two MMAs), which keeps the
 //               probabilities at fp32 accuracy.
 // Every warp keeps its own (max, sum, accumulator) state; the states are merged through shared memory at the end.
+// words one CTA should walk: 1.15 x the mean load of a CTA slot if the whole mask were spread evenly (at least 4 words)
+__device__ __forceinline__ int fattn_target_words(const FattnParams &p, int ctas_per_token) {
+    if (p.w0 >= 0) return p.w0;
+    const long long total = p.plan ? p.plan[0] : p.Nq * p.nw;
+    const long long w = (115ll * total * ctas_per_token + 100ll * p.slots - 1) / (100ll * p.slots);
+    return (int) max(4ll, min(w, 0x7fffffffll));
+}
+
 template <int D>
 __global__ void __launch_bounds__(FA_THREADS, FA_MIN_CTAS) fattn_mma_kernel(FattnParams p) {
     constexpr int KS = D / 16;   // k-steps of the S MMA
@@ -107,8 +143,9 @@ __global__ void __launch_bounds__(FA_THREADS, FA_MIN_CTAS) fattn_mma_kernel(Fatt
     constexpr int NR = D / 64;   // 64-wide d ranges of V
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int64_t j = blockIdx.x;
-    const int hk = blockIdx.y / p.hgroups, hg = blockIdx.y % p.hgroups;
+    // blocks are handed out heads first, then tokens in the order of the plan: the longest sequences start first
+    const int64_t j = p.order ? p.order[blockIdx.y] : blockIdx.y;
+    const int hk = blockIdx.x / p.hgroups, hg = blockIdx.x % p.hgroups;
     const int split = blockIdx.z;
     const int gqa = (int) (p.H / p.Hkv);
     const int G = min(8, gqa - hg * 8);        // query heads of this CTA
@@ -148,8 +185,9 @@ __global__ void __launch_bounds__(FA_THREADS, FA_MIN_CTAS) fattn_mma_kernel(Fatt
     const int32_t *wl = p.words ? p.wlist + j * p.nw : nullptr;
     const int64_t n_words = p.words ? (int64_t) p.wcount[j] : p.nw;
     int ns_j = p.nsplit;   // KV splits of this token
-    if (p.w0 > 0) {
-        ns_j = (int) min((int64_t) p.nsplit, max((int64_t) 1, (n_words + p.w0 - 1) / p.w0));
+    if (p.w0 != 0) {
+        const int w0 = fattn_target_words(p, (int) gridDim.x);
+        ns_j = (int) min((int64_t) p.nsplit, max((int64_t) 1, (n_words + w0 - 1) / w0));
         if (split >= ns_j) return;   // the whole CTA: nothing has been synchronised yet
     }
     const int64_t per_split = (n_words + ns_j - 1) / ns_j;
@@ -411,13 +449,16 @@ __global__ void __launch_bounds__(128) fattn_parity_kernel(FattnParams p) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(D) fattn_combine_kernel(const float *__restrict__ partial, int nsplit, float *__restrict__ dst, int64_t H,
-                                                          const int32_t *__restrict__ wcount, int64_t nw, int w0) {
+__global__ void __launch_bounds__(D) fattn_combine_kernel(FattnParams p, int ctas_per_token) {
+    const float *__restrict__ partial = p.partial;
+    float *__restrict__ dst = p.dst;
+    int nsplit = p.nsplit;
     const int64_t row = blockIdx.x;  // token * H + head
     const int d = threadIdx.x;
     const float *pp = partial + row * nsplit * (D + 2);
-    if (w0 > 0) {   // the splits this token really has; a token with one split was written directly
-        const int64_t n_words = wcount ? (int64_t) wcount[row / H] : nw;
+    if (p.w0 != 0) {   // the splits this token really has; a token with one split was written directly
+        const int w0 = fattn_target_words(p, ctas_per_token);
+        const int64_t n_words = p.wcount ? (int64_t) p.wcount[row / p.H] : p.nw;
         nsplit = (int) min((int64_t) nsplit, max((int64_t) 1, (n_words + w0 - 1) / w0));
         if (nsplit == 1) return;
     }
@@ -448,17 +489,15 @@ static int fa_sm_count() {
 }
 
 // Decode-sized batches over ragged sequences: one CTA per (token, kv head) makes the longest sequence the kernel's
-// duration.  When the grid is small enough for spare CTAs to be cheap, tokens whose mask has more than w0 non-empty
-// 64-cell words are cut into up to 4 KV splits; w0 is 1.25 x the mean words per token if the tokens shared the cache.
-static int fattn_adaptive_w0(int64_t Nq, int64_t Hkv, int hgroups, int64_t n_kv, bool have_index) {
+// duration.  When the grid is small enough for spare CTAs to be cheap (at most two waves), a token whose mask has more
+// words than fattn_target_words is cut into up to FA_ADAPTIVE_SPLITS KV splits; the rest are written directly.
+static bool fattn_adaptive(int64_t Nq, int64_t Hkv, int hgroups, bool have_index) {
     static int allow = -1;
     if (allow < 0) {
-        const char *e = getenv("B200_FA_ADAPTIVE");   // opt-in: measured a gain only without the K prefetch (4 CTAs per SM)
+        const char *e = getenv("B200_FA_ADAPTIVE");   // opt-in: on the 64-sequence decode batch the cuts cost more than they save
         allow = (e && atoi(e) == 1) ? 1 : 0;
     }
-    if (!allow || !have_index || Nq * Hkv * hgroups > 2 * 4 * (int64_t) fa_sm_count() / 2) return 0;
-    const int64_t mean_words = (n_kv / 64 + Nq - 1) / Nq;
-    return (int) std::max<int64_t>(4, (mean_words * 5 + 3) / 4);
+    return allow && have_index && Nq * Hkv * hgroups <= 2 * (int64_t) FA_MIN_CTAS * fa_sm_count();
 }
 
 static int fattn_nsplit(int64_t Nq, int64_t Hkv, int hgroups, int64_t n_kv) {
@@ -482,14 +521,18 @@ using namespace b200;
 
 extern "C" {
 
-// index layout: words [Nq][nw] u64 | list of non-empty word indices [Nq][nw] i32 | their counts [Nq] i32
+// index layout: words [Nq][nw] u64 | list of non-empty word indices [Nq][nw] i32 | their counts [Nq] i32 |
+// tokens by decreasing count [Nq] i32 | plan: total words i32
 static size_t index_list_offset(int64_t Nq, int64_t nw) { return align_up((size_t) Nq * nw * 8, 256); }
 static size_t index_count_offset(int64_t Nq, int64_t nw) { return index_list_offset(Nq, nw) + align_up((size_t) Nq * nw * 4, 256); }
+
+static size_t index_order_offset(int64_t Nq, int64_t nw) { return index_count_offset(Nq, nw) + align_up((size_t) Nq * 4, 256); }
+static size_t index_plan_offset(int64_t Nq, int64_t nw) { return index_order_offset(Nq, nw) + align_up((size_t) Nq * 4, 256); }
 
 size_t b200_mask_index_bytes(int64_t Nq, int64_t n_kv) {
     if (Nq <= 0 || n_kv <= 0) return 0;
     const int64_t nw = (n_kv + 63) / 64;
-    return index_count_offset(Nq, nw) + align_up((size_t) Nq * 4, 256);
+    return index_plan_offset(Nq, nw) + 256;
 }
 
 int b200_mask_index_build(const void *mask, int64_t mask_nb_row, int64_t Nq, int64_t n_kv, void *index, size_t index_bytes,
@@ -505,14 +548,18 @@ int b200_mask_index_build(const void *mask, int64_t mask_nb_row, int64_t Nq, int
     mask_words_compact_kernel<<<(unsigned) ((Nq * 32 + 255) / 256), 256, 0, (cudaStream_t) stream>>>(
         (const unsigned long long *) index, Nq, nw, (int32_t *) ((char *) index + index_list_offset(Nq, nw)),
         (int32_t *) ((char *) index + index_count_offset(Nq, nw)));
-    return check_launch("mask_words_compact");
+    if (int e = check_launch("mask_words_compact")) return e;
+    fattn_plan_kernel<<<1, 1024, 0, (cudaStream_t) stream>>>((const int32_t *) ((char *) index + index_count_offset(Nq, nw)), Nq,
+                                                             (int32_t *) ((char *) index + index_order_offset(Nq, nw)),
+                                                             (int32_t *) ((char *) index + index_plan_offset(Nq, nw)));
+    return check_launch("fattn_plan");
 }
 
 size_t b200_flash_attn_scratch_bytes(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, int64_t n_kv) {
     if (D <= 0 || H <= 0 || Hkv <= 0 || Nq <= 0 || n_kv <= 0 || H % Hkv) return 0;
     const int hgroups = fattn_hgroups((int) (H / Hkv));
     int ns = fattn_nsplit(Nq, Hkv, hgroups, n_kv);
-    if (ns == 1 && fattn_adaptive_w0(Nq, Hkv, hgroups, n_kv, true) > 0) ns = 4;
+    if (ns == 1 && fattn_adaptive(Nq, Hkv, hgroups, true)) ns = FA_ADAPTIVE_SPLITS;
     const size_t part = ns > 1 ? align_up((size_t) Nq * H * ns * (D + 2) * sizeof(float), 256) : 0;
     return b200_mask_index_bytes(Nq, n_kv) + part;
 }
@@ -534,7 +581,10 @@ static int flash_attn_impl(bool parity, int64_t D, int64_t H, int64_t Hkv, int64
     const int hgroups = fattn_hgroups(gqa);
     int ns = parity ? 1 : fattn_nsplit(Nq, Hkv, hgroups, n_kv);
     int w0 = 0;
-    if (!parity && ns == 1 && (w0 = fattn_adaptive_w0(Nq, Hkv, hgroups, n_kv, index != nullptr)) > 0) ns = 4;
+    if (!parity && ns == 1 && fattn_adaptive(Nq, Hkv, hgroups, index != nullptr)) {
+        ns = FA_ADAPTIVE_SPLITS;
+        w0 = -1;
+    }
     const size_t part = ns > 1 ? (size_t) Nq * H * ns * (D + 2) * sizeof(float) : 0;
     if (part && (!scratch || scratch_bytes < part)) return set_error(B200_E_SCRATCH, "flash_attn scratch too small: %zu < %zu", scratch_bytes, part);
     B200_REQUIRE(!part || is_aligned(scratch, 16), "scratch must be 16-byte aligned");
@@ -554,6 +604,10 @@ static int flash_attn_impl(bool parity, int64_t D, int64_t H, int64_t Hkv, int64
     p.m0 = powf(2.0f, -(max_bias) / p.n_head_log2);
     p.m1 = powf(2.0f, -(max_bias / 2.0f) / p.n_head_log2);
     p.dst = dst; p.partial = (float *) scratch; p.nsplit = ns; p.hgroups = hgroups; p.w0 = w0;
+    p.order = index ? (const int32_t *) ((const char *) index + index_order_offset(Nq, p.nw)) : nullptr;
+    p.plan = index ? (const int32_t *) ((const char *) index + index_plan_offset(Nq, p.nw)) : nullptr;
+    p.slots = FA_MIN_CTAS * fa_sm_count();
+    B200_REQUIRE(Nq <= 65535, "at most 65535 tokens per call");
 
     cudaStream_t st = (cudaStream_t) stream;
     if (parity) {
@@ -562,13 +616,13 @@ static int flash_attn_impl(bool parity, int64_t D, int64_t H, int64_t Hkv, int64
         else fattn_parity_kernel<64><<<blocks, 128, 0, st>>>(p);
         return check_launch("fattn_parity");
     }
-    dim3 grid((unsigned) Nq, (unsigned) (Hkv * hgroups), (unsigned) ns);
+    dim3 grid((unsigned) (Hkv * hgroups), (unsigned) Nq, (unsigned) ns);
     if (D == 128) fattn_mma_kernel<128><<<grid, FA_THREADS, 0, st>>>(p);
     else fattn_mma_kernel<64><<<grid, FA_THREADS, 0, st>>>(p);
     if (int e = check_launch("fattn_mma")) return e;
     if (ns > 1) {
-        if (D == 128) fattn_combine_kernel<128><<<(unsigned) (Nq * H), 128, 0, st>>>(p.partial, ns, dst, H, p.wcount, p.nw, w0);
-        else fattn_combine_kernel<64><<<(unsigned) (Nq * H), 64, 0, st>>>(p.partial, ns, dst, H, p.wcount, p.nw, w0);
+        if (D == 128) fattn_combine_kernel<128><<<(unsigned) (Nq * H), 128, 0, st>>>(p, (int) (Hkv * hgroups));
+        else fattn_combine_kernel<64><<<(unsigned) (Nq * H), 64, 0, st>>>(p, (int) (Hkv * hgroups));
         return check_launch("fattn_combine");
     }
     return B200_OK;

@@ -42,7 +42,8 @@ def test_size_queries_and_argument_checks_without_a_gpu():
     assert L.b200_weight_bytes(3, 128, 16) == 0      # unsupported type
     assert L.b200_act_bytes(4096, 1) == 128 * 256 + 32 * 256
     assert L.b200_mul_mat_scratch_bytes(2, 4096, 4096, 8) == L.b200_act_bytes(4096, 8)
-    assert L.b200_mask_index_bytes(64, 65536) == 64 * 1024 * 8 + 64 * 1024 * 4 + 256
+    # words, word list, counts, token order, plan
+    assert L.b200_mask_index_bytes(64, 65536) == 64 * 1024 * 8 + 64 * 1024 * 4 + 256 + 256 + 256
     # invalid arguments are rejected before any CUDA call
     rc = L.b200_mul_mat_q(5, None, 64, 16, None, 256, 1, None, 64, None, 0, 0, None)
     assert rc == -1 and b"bad mul_mat" in L.b200_last_error()
