@@ -23,6 +23,9 @@ constexpr int FA_THREADS = 128;
 #ifndef FA_MIN_CTAS
 #define FA_MIN_CTAS 3
 #endif
+#ifndef FA_PREFETCH_K
+#define FA_PREFETCH_K 1   // the next chunk's K rows are loaded during the softmax and P V MMAs of the current one (32 more registers)
+#endif
 constexpr int FA_SUPER_WORDS = 32;  // 2048 cells listed per round
 constexpr int FA_ADAPTIVE_SPLITS = 2;   // most KV splits a long sequence is cut into when the batch is small
 
@@ -241,9 +244,10 @@ __global__ void __launch_bounds__(FA_THREADS, FA_MIN_CTAS) fattn_mma_kernel(Fatt
                 for (int u = 0; u < NU; ++u) kr[c][u] = __ldg(kp + 4 * u);
             }
         };
-        if (warp < n_chunks) load_k(warp);
+        if (FA_PREFETCH_K && warp < n_chunks) load_k(warp);
         for (int ch = warp; ch < n_chunks; ch += 4) {
             const int base = ch << 4;
+            if (!FA_PREFETCH_K) load_k(ch);
             // ---- S = Q K^T for the two 8-cell tiles ----
             float sacc[2][4];
 #pragma unroll
@@ -265,7 +269,7 @@ __global__ void __launch_bounds__(FA_THREADS, FA_MIN_CTAS) fattn_mma_kernel(Fatt
                 for (int r = 0; r < NR; ++r) vr[i][r] = __ldg(vp + 8 * r);
             }
             // the next chunk's K rows travel during the softmax and the P V MMAs of this one
-            if (ch + 4 < n_chunks) load_k(ch + 4);
+            if (FA_PREFETCH_K && ch + 4 < n_chunks) load_k(ch + 4);
             // ---- scores of head g for cells base + {2t, 2t+1, 8+2t, 9+2t} ----
             float sc[4];
 #pragma unroll

@@ -293,7 +293,8 @@ static bool write_gguf(const model_cfg & c, const std::string & path, uint32_t s
             const int64_t rows = std::min(chunk, m - r0);
             tmp.resize((size_t) rows * k);
             fill_normal(tmp, rng, std_);
-            lm_ggml_quantize_chunk(t, tmp.data(), w->data, r0 * k, rows, k, nullptr);
+            // (the chunk API offsets both source and destination by `start`: quantise chunk-local rows at offset 0)
+            lm_ggml_quantize_chunk(t, tmp.data(), (char *) w->data + r0 * lm_ggml_row_size(t, k), 0, rows, k, nullptr);
         }
         lm_gguf_add_tensor(g, w);
     };
