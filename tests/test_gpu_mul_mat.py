@@ -132,3 +132,25 @@ def test_kernels_agree_column_by_column():
         assert rel_max_err(host(big[n:n + 1]), host(one)) < 1e-4
     eight = ops.mul_mat(w, x[8:16])
     assert rel_max_err(host(big[8:16]), host(eight)) < 1e-4
+
+
+@pytest.mark.parametrize("wtype", [Q4_0, Q8_0])
+def test_weight_cat_and_row_slice(oracle, wtype):
+    """Stacking weights row-wise (wq/wk/wv, gate/up as one mul_mat) and cutting row ranges (row split) are byte-range
+    operations on the tiled layout: both must reproduce the reference block streams exactly."""
+    from cactus_b200 import ops
+    K = 288   # 9 blocks: not a multiple of the 4-block tile
+    rng = np.random.default_rng(77)
+    parts = [np.asarray(oracle.quantize_weights(wtype, (rng.standard_normal((M, K)) * 0.02).astype(np.float32))) for M in (48, 32, 20)]
+    ws = [ops.QWeight.from_blocks(wtype, K, p.shape[0], p) for p in parts]
+    cat = ops.QWeight.cat(ws)
+    assert cat.M == 100
+    assert np.array_equal(host(cat.to_blocks()), np.concatenate([p.reshape(p.shape[0], -1) for p in parts]))
+    mid = cat.row_slice(48, 80)
+    assert np.array_equal(host(mid.to_blocks()), parts[1].reshape(32, -1))
+    tail = cat.row_slice(80, 100)
+    assert np.array_equal(host(tail.to_blocks()), parts[2].reshape(20, -1))
+    x = rng.standard_normal((5, K)).astype(np.float32)
+    whole = host(ops.mul_mat(cat, dev(x)))
+    for w, lo in zip(ws, (0, 48, 80)):
+        assert rel_max_err(whole[:, lo:lo + w.M], host(ops.mul_mat(w, dev(x)))) < 1e-6
