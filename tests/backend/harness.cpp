@@ -292,7 +292,16 @@ static bool write_gguf(const model_cfg & c, const std::string & path, uint32_t s
         for (int64_t r0 = 0; r0 < m; r0 += chunk) {
             const int64_t rows = std::min(chunk, m - r0);
             tmp.resize((size_t) rows * k);
-            fill_normal(tmp, rng, std_);
+            if (m * k <= (1 << 24)) {
+                fill_normal(tmp, rng, std_);
+            } else {   // big (benchmark-sized) tensors: rows cut out of one table of normal values at random offsets, a hundred times faster
+                static std::vector<float> table;
+                if (table.empty()) { table.resize(1 << 22); fill_normal(table, rng, 1.0f); }
+                for (int64_t r = 0; r < rows; ++r) {
+                    const size_t off = rng() % (table.size() - (size_t) k);
+                    for (int64_t i = 0; i < k; ++i) tmp[(size_t) r * k + i] = table[off + i] * std_;
+                }
+            }
             // (the chunk API offsets both source and destination by `start`: quantise chunk-local rows at offset 0)
             lm_ggml_quantize_chunk(t, tmp.data(), (char *) w->data + r0 * lm_ggml_row_size(t, k), 0, rows, k, nullptr);
         }
@@ -368,29 +377,35 @@ static bool open_runner(runner & r, const std::string & path, bool gpu, const mo
     return r.ctx != nullptr;
 }
 
+// One logical batch, submitted in pieces of at most n_batch tokens (llama_decode asserts n_tokens <= n_batch,
+// cactus/llama-context.cpp:895), the way a serving loop feeds long prompts; the logits of the wanted tokens are collected in order.
 static int decode_batch(runner & r, const std::vector<int32_t> & tok, const std::vector<int32_t> & pos, const std::vector<int32_t> & seq,
                         const std::vector<int8_t> & want, std::vector<float> & logits_out) {
-    const int n = (int) tok.size();
-    llama_batch b = llama_batch_init(n, 0, 1);
-    b.n_tokens = n;
-    for (int i = 0; i < n; ++i) {
-        b.token[i] = tok[i];
-        b.pos[i] = pos[i];
-        b.n_seq_id[i] = 1;
-        b.seq_id[i][0] = seq[i];
-        b.logits[i] = want[i];
+    const int n_all = (int) tok.size(), n_batch = 2048;
+    logits_out.clear();
+    for (int i0 = 0; i0 < n_all; i0 += n_batch) {
+        const int n = std::min(n_batch, n_all - i0);
+        llama_batch b = llama_batch_init(n, 0, 1);
+        b.n_tokens = n;
+        for (int i = 0; i < n; ++i) {
+            b.token[i] = tok[i0 + i];
+            b.pos[i] = pos[i0 + i];
+            b.n_seq_id[i] = 1;
+            b.seq_id[i][0] = seq[i0 + i];
+            b.logits[i] = want[i0 + i];
+        }
+        const int rc = llama_decode(r.ctx, b);
+        if (rc == 0) {
+            for (int i = 0; i < n; ++i)
+                if (want[i0 + i]) {
+                    const float * l = llama_get_logits_ith(r.ctx, i);
+                    logits_out.insert(logits_out.end(), l, l + r.vocab);
+                }
+        }
+        llama_batch_free(b);
+        if (rc != 0) return rc;
     }
-    const int rc = llama_decode(r.ctx, b);
-    if (rc == 0) {
-        logits_out.clear();
-        for (int i = 0; i < n; ++i)
-            if (want[i]) {
-                const float * l = llama_get_logits_ith(r.ctx, i);
-                logits_out.insert(logits_out.end(), l, l + r.vocab);
-            }
-    }
-    llama_batch_free(b);
-    return rc;
+    return 0;
 }
 
 static int run_model(int argc, char ** argv) {
