@@ -4,6 +4,8 @@
 #include <cstdio>
 #include <cstring>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -17,6 +19,15 @@ int set_error(int code, const char *fmt, ...) {
     vsnprintf(g_err, sizeof(g_err), fmt, ap);
     va_end(ap);
     return code;
+}
+
+bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_PDL");
+        v = (e && atoi(e) == 0) ? 0 : 1;
+    }
+    return v == 1;
 }
 
 void count_launch(int n) { g_launches.fetch_add((uint64_t) n, std::memory_order_relaxed); }

@@ -21,6 +21,38 @@ int check_launch(const char *what);  // cudaGetLastError after a launch -> B200_
     } while (0)
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// The kernels of a decode step run back to back on one stream, each a few to a few dozen microseconds long.  A kernel
+// launched with launch_pdl may have its CTAs placed on the SMs while the previous kernel's last CTAs are still running;
+// its first statement (pdl_prologue) waits until the previous kernel has completed and its writes are visible, so only
+// the launch itself and the CTA start-up overlap.  B200_PDL=0 turns the launch attribute off.
+bool pdl_enabled();
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_prologue() {
+#ifdef B200_PDL_EARLY_TRIGGER   // lets the next kernel's CTAs take their places for the whole run of this one: measured slower
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+#endif
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+}
+// placed where a long kernel's CTA has only its write-back left: once every CTA of the grid is there (or gone), the next
+// kernel's CTAs may be placed
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+template <typename... P, typename... A>
+static inline cudaError_t launch_pdl(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
+#endif
 static inline bool is_aligned(const void *p, size_t a) { return ((uintptr_t) p % a) == 0; }
 
 // ---- T16: tiled quantised weights ---------------------------------------------------------------

@@ -141,6 +141,7 @@ __device__ __forceinline__ int fattn_target_words(const FattnParams &p, int ctas
 
 template <int D>
 __global__ void __launch_bounds__(FA_THREADS, FA_MIN_CTAS) fattn_mma_kernel(FattnParams p) {
+    pdl_prologue();
     constexpr int KS = D / 16;   // k-steps of the S MMA
     constexpr int NU = D / 32;   // 16-byte K pieces per lane and cell
     constexpr int NR = D / 64;   // 64-wide d ranges of V
@@ -330,6 +331,7 @@ __global__ void __launch_bounds__(FA_THREADS, FA_MIN_CTAS) fattn_mma_kernel(Fatt
         __syncthreads();
     }
 
+    pdl_trigger();
     // ---- merge the four warps ----
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
@@ -454,6 +456,7 @@ __global__ void __launch_bounds__(128) fattn_parity_kernel(FattnParams p) {
 
 template <int D>
 __global__ void __launch_bounds__(D) fattn_combine_kernel(FattnParams p, int ctas_per_token) {
+    pdl_prologue();
     const float *__restrict__ partial = p.partial;
     float *__restrict__ dst = p.dst;
     int nsplit = p.nsplit;
@@ -621,12 +624,12 @@ static int flash_attn_impl(bool parity, int64_t D, int64_t H, int64_t Hkv, int64
         return check_launch("fattn_parity");
     }
     dim3 grid((unsigned) (Hkv * hgroups), (unsigned) Nq, (unsigned) ns);
-    if (D == 128) fattn_mma_kernel<128><<<grid, FA_THREADS, 0, st>>>(p);
-    else fattn_mma_kernel<64><<<grid, FA_THREADS, 0, st>>>(p);
+    if (D == 128) launch_pdl(fattn_mma_kernel<128>, grid, dim3(FA_THREADS), 0, st, p);
+    else launch_pdl(fattn_mma_kernel<64>, grid, dim3(FA_THREADS), 0, st, p);
     if (int e = check_launch("fattn_mma")) return e;
     if (ns > 1) {
-        if (D == 128) fattn_combine_kernel<128><<<(unsigned) (Nq * H), 128, 0, st>>>(p, (int) (Hkv * hgroups));
-        else fattn_combine_kernel<64><<<(unsigned) (Nq * H), 64, 0, st>>>(p, (int) (Hkv * hgroups));
+        if (D == 128) launch_pdl(fattn_combine_kernel<128>, dim3((unsigned) (Nq * H)), dim3(128), 0, st, p, (int) (Hkv * hgroups));
+        else launch_pdl(fattn_combine_kernel<64>, dim3((unsigned) (Nq * H)), dim3(64), 0, st, p, (int) (Hkv * hgroups));
         return check_launch("fattn_combine");
     }
     return B200_OK;

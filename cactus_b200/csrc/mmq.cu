@@ -131,6 +131,7 @@ template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB>
 __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims, const uint8_t *__restrict__ w, ActDims act,
                                                           const uint8_t *__restrict__ aq, float *__restrict__ dst,
                                                           int64_t dst_nb_row, float *__restrict__ partial, int ksplit, int canon, int cluster) {
+    pdl_prologue();
     using S = MmqCfg<WTYPE, NTW, WN, MT, WM, STAGES>;
     constexpr int MMQ_STAGES = STAGES;
     constexpr int NT = NTW;              // n-tiles of this warp
@@ -303,6 +304,7 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
         }
     }
     cp_async_wait<0>();
+    pdl_trigger();
 
     // write back; Q4_0 quants were used as 16 * value
     constexpr float WS = (WTYPE == B200_TYPE_Q4_0) ? 0.0625f : 1.0f;
@@ -391,6 +393,7 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
 // dst[n][m] = sum over splits of partial[s][n][m], in split order
 __global__ void __launch_bounds__(256) mmq_reduce_kernel(const float *__restrict__ partial, int ksplit, int64_t M, int64_t N,
                                                         float *__restrict__ dst, int64_t dst_nb_row) {
+    pdl_prologue();
     const int64_t gid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
     if (gid >= M * N) return;
     const int64_t n = gid / M, m = gid - n * M;
@@ -426,7 +429,7 @@ static int launch_variant(const TiledDims &d, const uint8_t *w, const ActDims &a
     using S = MmqCfg<WTYPE, NTW, WN, MT, WM, STAGES>;
     dim3 grid((unsigned) ((d.n_rt + S::CTA_TILES - 1) / S::CTA_TILES), (unsigned) ((a.n_nt + S::NT - 1) / S::NT), (unsigned) ksplit);
     if (!cluster) {
-        mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB><<<grid, S::THREADS, S::TOTAL, st>>>(d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 0);
+        launch_pdl(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB>, grid, dim3(S::THREADS), S::TOTAL, st, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 0);
         return check_launch("mmq");
     }
     cudaLaunchConfig_t cfg = {};
@@ -434,13 +437,15 @@ static int launch_variant(const TiledDims &d, const uint8_t *w, const ActDims &a
     cfg.blockDim = dim3(S::THREADS);
     cfg.dynamicSmemBytes = S::TOTAL;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = (unsigned) ksplit;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB>, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 1);
     if (e != cudaSuccess) return set_error(B200_E_CUDA, "mmq cluster launch: %s", cudaGetErrorString(e));
     count_launch();
@@ -585,7 +590,7 @@ size_t mmq_workspace_bytes(int wtype, int64_t K, int64_t M, int64_t N) {
 
 void launch_mmq_reduce(const float *partial, int ks, int64_t M, int64_t N, float *dst, int64_t dst_nb_row, cudaStream_t st) {
     const int64_t total = M * N;
-    mmq_reduce_kernel<<<(unsigned) ((total + 255) / 256), 256, 0, st>>>(partial, ks, M, N, dst, dst_nb_row);
+    launch_pdl(mmq_reduce_kernel, dim3((unsigned) ((total + 255) / 256)), dim3(256), 0, st, partial, ks, M, N, dst, dst_nb_row);
 }
 
 int launch_mmq(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
@@ -600,7 +605,7 @@ int launch_mmq(int wtype, const TiledDims &d, const void *w, const ActDims &a, c
     if (int e = v.launch(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, (float *) workspace, ks, canon ? 1 : 0, cluster ? 1 : 0, st)) return e;
     if (ks > 1 && !cluster) {
         const int64_t total = d.M * a.N;
-        mmq_reduce_kernel<<<(unsigned) ((total + 255) / 256), 256, 0, st>>>((const float *) workspace, ks, d.M, a.N, dst, dst_nb_row);
+        launch_pdl(mmq_reduce_kernel, dim3((unsigned) ((total + 255) / 256)), dim3(256), 0, st, (const float *) workspace, ks, d.M, a.N, dst, dst_nb_row);
         return check_launch("mmq_reduce");
     }
     return B200_OK;

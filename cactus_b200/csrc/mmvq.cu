@@ -19,6 +19,7 @@ template <int WTYPE, int NC>
 __global__ void __launch_bounds__(MMVQ_WARPS * 32) mmvq_kernel(TiledDims dims, const uint8_t *__restrict__ w, ActDims act,
                                                               const uint8_t *__restrict__ aq, float *__restrict__ dst,
                                                               int64_t dst_nb_row) {
+    pdl_prologue();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int64_t rt = blockIdx.x;
@@ -116,14 +117,14 @@ static int launch_mmvq_t(const TiledDims &d, const uint8_t *w, const ActDims &a,
     const unsigned grid = (unsigned) d.n_rt;
     const unsigned block = MMVQ_WARPS * 32;
     switch (a.N) {
-        case 1: mmvq_kernel<WTYPE, 1><<<grid, block, 0, st>>>(d, w, a, aq, dst, dst_nb_row); break;
-        case 2: mmvq_kernel<WTYPE, 2><<<grid, block, 0, st>>>(d, w, a, aq, dst, dst_nb_row); break;
-        case 3: mmvq_kernel<WTYPE, 3><<<grid, block, 0, st>>>(d, w, a, aq, dst, dst_nb_row); break;
-        case 4: mmvq_kernel<WTYPE, 4><<<grid, block, 0, st>>>(d, w, a, aq, dst, dst_nb_row); break;
-        case 5: mmvq_kernel<WTYPE, 5><<<grid, block, 0, st>>>(d, w, a, aq, dst, dst_nb_row); break;
-        case 6: mmvq_kernel<WTYPE, 6><<<grid, block, 0, st>>>(d, w, a, aq, dst, dst_nb_row); break;
-        case 7: mmvq_kernel<WTYPE, 7><<<grid, block, 0, st>>>(d, w, a, aq, dst, dst_nb_row); break;
-        case 8: mmvq_kernel<WTYPE, 8><<<grid, block, 0, st>>>(d, w, a, aq, dst, dst_nb_row); break;
+        case 1: launch_pdl(mmvq_kernel<WTYPE, 1>, dim3(grid), dim3(block), 0, st, d, w, a, aq, dst, dst_nb_row); break;
+        case 2: launch_pdl(mmvq_kernel<WTYPE, 2>, dim3(grid), dim3(block), 0, st, d, w, a, aq, dst, dst_nb_row); break;
+        case 3: launch_pdl(mmvq_kernel<WTYPE, 3>, dim3(grid), dim3(block), 0, st, d, w, a, aq, dst, dst_nb_row); break;
+        case 4: launch_pdl(mmvq_kernel<WTYPE, 4>, dim3(grid), dim3(block), 0, st, d, w, a, aq, dst, dst_nb_row); break;
+        case 5: launch_pdl(mmvq_kernel<WTYPE, 5>, dim3(grid), dim3(block), 0, st, d, w, a, aq, dst, dst_nb_row); break;
+        case 6: launch_pdl(mmvq_kernel<WTYPE, 6>, dim3(grid), dim3(block), 0, st, d, w, a, aq, dst, dst_nb_row); break;
+        case 7: launch_pdl(mmvq_kernel<WTYPE, 7>, dim3(grid), dim3(block), 0, st, d, w, a, aq, dst, dst_nb_row); break;
+        case 8: launch_pdl(mmvq_kernel<WTYPE, 8>, dim3(grid), dim3(block), 0, st, d, w, a, aq, dst, dst_nb_row); break;
         default: return set_error(B200_E_INVALID, "mmvq handles 1..8 columns, got %lld", (long long) a.N);
     }
     return check_launch("mmvq");

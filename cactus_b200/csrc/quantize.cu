@@ -16,6 +16,7 @@ template <int LAYOUT>
 __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float *__restrict__ x, int64_t x_nb_row, int64_t K,
                                                            int64_t N, int64_t n_rows_padded, int64_t nb, int64_t nbp,
                                                            uint8_t *__restrict__ out, size_t d_offset, int variant) {
+    pdl_prologue();
     const int64_t gid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
     const int j = (int) (gid & 7);             // which group of 4 elements inside the block
     const int64_t blk = gid >> 3;              // (row, block) index
@@ -209,8 +210,8 @@ int launch_quantize_b8(const float *x, int64_t x_nb_row, int64_t K, int64_t N, v
     const ActDims a = act_dims(K, N);
     const int64_t threads = a.n_nt * 8 * a.nbp * 8;
     const int64_t grid = (threads + 255) / 256;
-    if (canonical) quantize_q8_0_kernel<2><<<(unsigned) grid, 256, 0, st>>>(x, x_nb_row, K, N, a.n_nt * 8, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
-    else quantize_q8_0_kernel<1><<<(unsigned) grid, 256, 0, st>>>(x, x_nb_row, K, N, a.n_nt * 8, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
+    if (canonical) launch_pdl(quantize_q8_0_kernel<2>, dim3((unsigned) grid), dim3(256), 0, st, x, x_nb_row, K, N, a.n_nt * 8, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
+    else launch_pdl(quantize_q8_0_kernel<1>, dim3((unsigned) grid), dim3(256), 0, st, x, x_nb_row, K, N, a.n_nt * 8, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
     return check_launch("quantize_q8_0 (activations)");
 }
 
