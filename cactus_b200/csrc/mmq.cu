@@ -1,4 +1,4 @@
-// MUL_MAT for many activation columns (N > 8): int8 tensor-core kernel with per-block fp16 scales.
+// MUL_MAT for more than a couple of activation columns: int8 tensor-core kernel with per-block fp16 scales.
 //
 // Replaces the chunked vec_dot loop of lm_ggml_compute_forward_mul_mat
 // (cactus/ggml-cpu/ggml-cpu.c:1257-1449).  Every 32-element block has its own pair of scales, so each
@@ -577,8 +577,20 @@ static const MmqVariant &variant_for(int wtype, int64_t N) {
     return wtype == B200_TYPE_Q4_0 ? pick_variant<B200_TYPE_Q4_0>(N) : pick_variant<B200_TYPE_Q8_0>(N);
 }
 
+// Up to this many activation columns the dp4a kernel (mmvq.cu) runs; its time grows with the columns (9.9, 10.9, 14.9,
+// 17.0 us for 1..4 columns of a 14336 x 4096 Q4_0 weight on B200), where the tensor-core kernel's 16-column tile costs
+// 13.4 us for any count up to 16.
+int mmvq_max_n() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_MMVQ_MAX_N");
+        v = e ? std::max(2, std::min(8, atoi(e))) : 2;
+    }
+    return v;
+}
+
 size_t mmq_workspace_bytes(int wtype, int64_t K, int64_t M, int64_t N) {
-    if (N <= 8) return 0;
+    if (N <= 2) return 0;   // never the tensor-core kernel (mmvq_max_n() is 2 ... 8: columns 3..8 may need it)
     // upper bound over every K split the launcher may choose (the choice depends on the device): never more
     // than 16, than half the block groups, or than what two waves of the largest plausible device need
     const TiledDims d = tiled_dims(wtype, K, M);

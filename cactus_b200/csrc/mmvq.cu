@@ -1,4 +1,4 @@
-// MUL_MAT for few activation columns (N <= 8): the HBM-bound decode kernel.
+// MUL_MAT for few activation columns (1 or 2 by default, at most 8): the HBM-bound decode kernel.
 //
 // Replaces lm_ggml_vec_dot_q4_0_q8_0 / lm_ggml_vec_dot_q8_0_q8_0 under mul_mat
 // (cactus/ggml-cpu/ggml-cpu-quants.c:1906, :3591; cactus/ggml-cpu/ggml-cpu.c:1167-1255).
@@ -32,22 +32,42 @@ __global__ void __launch_bounds__(MMVQ_WARPS * 32) mmvq_kernel(TiledDims dims, c
     const float *ad = reinterpret_cast<const float *>(aq + act.d_offset);
     constexpr float WS = (WTYPE == B200_TYPE_Q4_0) ? 0.0625f : 1.0f;  // Q4_0 nibbles sit in the high half of each byte: x16
 
+    // the weight tile and its scales of one block group, as loaded: the next group's are requested before this one's are used
+    struct Tile {
+        uint4 q[WTYPE == B200_TYPE_Q4_0 ? 2 : 4];
+        uint2 sa, sb;
+    };
+    auto load_tile = [&](int64_t bg, Tile &tl) {
+        if (WTYPE == B200_TYPE_Q4_0) {
+            const uint4 *p = reinterpret_cast<const uint4 *>(wq + bg * 1024) + lane * 2;
+            tl.q[0] = __ldg(p);
+            tl.q[1] = __ldg(p + 1);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tl.q[j] = __ldg(reinterpret_cast<const uint4 *>(wq + bg * 2048 + j * 512) + lane);
+        }
+        tl.sa = __ldg(wd + bg * 16 + g);
+        tl.sb = __ldg(wd + bg * 16 + g + 8);
+    };
+    Tile nxt;
+    if (warp < dims.n_bg) load_tile(warp, nxt);
     for (int64_t bg = warp; bg < dims.n_bg; bg += MMVQ_WARPS) {
+        const Tile cur = nxt;
+        if (bg + MMVQ_WARPS < dims.n_bg) load_tile(bg + MMVQ_WARPS, nxt);
         // weights of this tile
         uint32_t wa[8], wb[8];  // row g / row g+8: Q4_0 uses [0..3] (blocks), Q8_0 [2*j], [2*j+1] (word t, word 4+t)
         if (WTYPE == B200_TYPE_Q4_0) {
-            const uint4 *p = reinterpret_cast<const uint4 *>(wq + bg * 1024) + lane * 2;
-            const uint4 u0 = __ldg(p), u1 = __ldg(p + 1);
+            const uint4 u0 = cur.q[0], u1 = cur.q[1];
             wa[0] = u0.x; wa[1] = u0.y; wa[2] = u0.z; wa[3] = u0.w;
             wb[0] = u1.x; wb[1] = u1.y; wb[2] = u1.z; wb[3] = u1.w;
         } else {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const uint4 u = __ldg(reinterpret_cast<const uint4 *>(wq + bg * 2048 + j * 512) + lane);
+                const uint4 u = cur.q[j];
                 wa[2 * j] = u.x; wb[2 * j] = u.y; wa[2 * j + 1] = u.z; wb[2 * j + 1] = u.w;
             }
         }
-        const uint2 sa = __ldg(wd + bg * 16 + g), sb = __ldg(wd + bg * 16 + g + 8);
+        const uint2 sa = cur.sa, sb = cur.sb;
         float dwa[4], dwb[4];
         {
             const __half2 a01 = *reinterpret_cast<const __half2 *>(&sa.x), a23 = *reinterpret_cast<const __half2 *>(&sa.y);

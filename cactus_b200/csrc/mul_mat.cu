@@ -1,5 +1,5 @@
-// C ABI of MUL_MAT: argument checks and the choice between the dp4a kernel (N <= 8) and the
-// tensor-core kernel (N > 8).
+// C ABI of MUL_MAT: argument checks and the choice between the dp4a kernel (few columns, mmvq_max_n()) and the
+// tensor-core kernels.
 #include <mutex>
 
 #include "common.cuh"
@@ -9,6 +9,7 @@ int launch_quantize_b8(const float *x, int64_t x_nb_row, int64_t K, int64_t N, v
 bool act_layout_canonical(int64_t N);
 int launch_mmq_tc(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
                   void *workspace, size_t workspace_bytes, cudaStream_t st);
+int mmvq_max_n();
 int launch_mmvq(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row, cudaStream_t st);
 int launch_mmq(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
                void *workspace, size_t workspace_bytes, cudaStream_t st, bool canon);
@@ -70,7 +71,7 @@ int b200_mul_mat_q_prequant(int wtype, const void *w, int64_t K, int64_t M, cons
     B200_REQUIRE(!workspace || is_aligned(workspace, 256), "workspace must be 256-byte aligned");
     const TiledDims d = tiled_dims(wtype, K, M);
     const ActDims a = act_dims(K, N);
-    if (N <= 8) return launch_mmvq(wtype, d, w, a, act, dst, dst_row_stride_bytes, (cudaStream_t) stream);
+    if (N <= mmvq_max_n()) return launch_mmvq(wtype, d, w, a, act, dst, dst_row_stride_bytes, (cudaStream_t) stream);
     if (act_layout_canonical(N)) return launch_mmq_tc(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream);
     return launch_mmq(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream, false);
 }

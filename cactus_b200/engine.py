@@ -203,8 +203,8 @@ class LlamaEngine:
         self.act_d = u8(L.b200_act_bytes(cfg.d_model, T))
         self.act_ff = u8(L.b200_act_bytes(cfg.d_ff, T))
         shapes = [(K, M // g) for _, K, M in cfg.mul_mat_shapes()] + [(cfg.d_model, cfg.d_model + 2 * kvd), (cfg.d_model, 2 * cfg.d_ff)]
-        ws = [L.b200_mul_mat_workspace_bytes(cfg.layer_type, K, M, t) for K, M in shapes for t in (9, 16, 32, 64, T)]
-        ws.append(L.b200_mul_mat_workspace_bytes(cfg.head_type, cfg.d_model, cfg.vocab // g, T))
+        ws = [L.b200_mul_mat_workspace_bytes(cfg.layer_type, K, M, t) for K, M in shapes for t in range(1, T + 1)]
+        ws += [L.b200_mul_mat_workspace_bytes(cfg.head_type, cfg.d_model, cfg.vocab // g, t) for t in range(1, T + 1)]
         self.ws = u8(max(ws))
         self.fa_scratch = u8(max(L.b200_flash_attn_scratch_bytes(cfg.head_dim, cfg.n_head, cfg.n_kv_head, t, n_cells) for t in range(1, T + 1)))
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
