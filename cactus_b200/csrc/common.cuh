@@ -55,6 +55,21 @@ static inline cudaError_t launch_pdl(void (*kernel)(P...), dim3 grid, dim3 block
 #endif
 static inline bool is_aligned(const void *p, size_t a) { return ((uintptr_t) p % a) == 0; }
 
+// ---- row split: the other GPUs' copies of a product ------------------------------------------------
+// A mul_mat kernel stores every result value into its own dst and, when the weight is one row slice of a split, into
+// the same place of the other GPUs' output buffers (peer memory mapped through CUDA IPC): p[i] is the address in peer
+// i's buffer that corresponds to `dst`, the row stride is the same everywhere.
+struct PeerDst {
+    float *p[7];
+    int n;
+};
+#ifdef __CUDACC__
+__device__ __forceinline__ void store_f32(float *dst, const PeerDst &peers, int64_t byte_off, float v) {
+    *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + byte_off) = v;
+    for (int i = 0; i < peers.n; ++i) *reinterpret_cast<float *>(reinterpret_cast<char *>(peers.p[i]) + byte_off) = v;
+}
+#endif
+
 // ---- T16: tiled quantised weights ---------------------------------------------------------------
 // A [K, M] tensor (M rows of K/32 blocks) is padded to Mp = ceil16(M) rows and nbp = ceil4(K/32) blocks and cut
 // into tiles of 16 rows x 4 blocks.  Tile (rt, bg) is stored in the register order of an m16n8k32

@@ -130,7 +130,7 @@ struct MmqCfg {
 template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB>
 __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims, const uint8_t *__restrict__ w, ActDims act,
                                                           const uint8_t *__restrict__ aq, float *__restrict__ dst,
-                                                          int64_t dst_nb_row, float *__restrict__ partial, int ksplit, int canon, int cluster) {
+                                                          int64_t dst_nb_row, float *__restrict__ partial, int ksplit, int canon, int cluster, PeerDst peers) {
     pdl_prologue();
     using S = MmqCfg<WTYPE, NTW, WN, MT, WM, STAGES>;
     constexpr int MMQ_STAGES = STAGES;
@@ -348,14 +348,17 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
             const int c = (q4 * 4) / ROWS, r = (q4 * 4) % ROWS;
             const int64_t col = cta_nt0 * 8 + c, row = cta_rt0 * 16 + r;
             if (col < act.N) {
-                float *o = reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + col * dst_nb_row + row * 4);
-                if (row + 3 < dims.M && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
-                    *reinterpret_cast<float4 *>(o) = acc;
-                } else {
-                    if (row < dims.M) o[0] = acc.x;
-                    if (row + 1 < dims.M) o[1] = acc.y;
-                    if (row + 2 < dims.M) o[2] = acc.z;
-                    if (row + 3 < dims.M) o[3] = acc.w;
+                const int64_t off = col * dst_nb_row + row * 4;
+                for (int pi = -1; pi < peers.n; ++pi) {   // own buffer, then the other GPUs' of a row split
+                    float *o = reinterpret_cast<float *>(reinterpret_cast<char *>(pi < 0 ? dst : peers.p[pi]) + off);
+                    if (row + 3 < dims.M && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+                        *reinterpret_cast<float4 *>(o) = acc;
+                    } else {
+                        if (row < dims.M) o[0] = acc.x;
+                        if (row + 1 < dims.M) o[1] = acc.y;
+                        if (row + 2 < dims.M) o[2] = acc.z;
+                        if (row + 3 < dims.M) o[3] = acc.w;
+                    }
                 }
             }
         }
@@ -378,8 +381,8 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
                 v1 *= WS;
                 if (row < dims.M) {
                     if (ksplit == 1) {
-                        if (col < act.N) *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + col * dst_nb_row + row * 4) = v0;
-                        if (col + 1 < act.N) *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + (col + 1) * dst_nb_row + row * 4) = v1;
+                        if (col < act.N) store_f32(dst, peers, col * dst_nb_row + row * 4, v0);
+                        if (col + 1 < act.N) store_f32(dst, peers, (col + 1) * dst_nb_row + row * 4, v1);
                     } else {
                         if (col < act.N) partial[((int64_t) ks * act.N + col) * dims.M + row] = v0;
                         if (col + 1 < act.N) partial[((int64_t) ks * act.N + col + 1) * dims.M + row] = v1;
@@ -392,14 +395,14 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
 
 // dst[n][m] = sum over splits of partial[s][n][m], in split order
 __global__ void __launch_bounds__(256) mmq_reduce_kernel(const float *__restrict__ partial, int ksplit, int64_t M, int64_t N,
-                                                        float *__restrict__ dst, int64_t dst_nb_row) {
+                                                        float *__restrict__ dst, int64_t dst_nb_row, PeerDst peers) {
     pdl_prologue();
     const int64_t gid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
     if (gid >= M * N) return;
     const int64_t n = gid / M, m = gid - n * M;
     float s = 0.0f;
     for (int k = 0; k < ksplit; ++k) s += partial[((int64_t) k * N + n) * M + m];
-    *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + n * dst_nb_row + m * 4) = s;
+    store_f32(dst, peers, n * dst_nb_row + m * 4, s);
 }
 
 static int sm_count() {
@@ -419,17 +422,17 @@ struct MmqVariant {
     int cta_tiles;   // 16-row tiles per CTA
     int cta_nt;      // 8-column tiles per CTA
     int ctas_per_sm; // resident CTAs per SM (filled on first use)
-    int (*launch)(const TiledDims &, const uint8_t *, const ActDims &, const uint8_t *, float *, int64_t, float *, int, int, int, cudaStream_t);
+    int (*launch)(const TiledDims &, const uint8_t *, const ActDims &, const uint8_t *, float *, int64_t, float *, int, int, int, const PeerDst &, cudaStream_t);
     int (*max_clusters)(int);   // resident clusters of `ksplit` CTAs on this device (0 = cannot be launched that way)
 };
 
 template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB>
 static int launch_variant(const TiledDims &d, const uint8_t *w, const ActDims &a, const uint8_t *aq, float *dst, int64_t dst_nb_row,
-                          float *partial, int ksplit, int canon, int cluster, cudaStream_t st) {
+                          float *partial, int ksplit, int canon, int cluster, const PeerDst &peers, cudaStream_t st) {
     using S = MmqCfg<WTYPE, NTW, WN, MT, WM, STAGES>;
     dim3 grid((unsigned) ((d.n_rt + S::CTA_TILES - 1) / S::CTA_TILES), (unsigned) ((a.n_nt + S::NT - 1) / S::NT), (unsigned) ksplit);
     if (!cluster) {
-        launch_pdl(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB>, grid, dim3(S::THREADS), S::TOTAL, st, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 0);
+        launch_pdl(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB>, grid, dim3(S::THREADS), S::TOTAL, st, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 0, peers);
         return check_launch("mmq");
     }
     cudaLaunchConfig_t cfg = {};
@@ -446,7 +449,7 @@ static int launch_variant(const TiledDims &d, const uint8_t *w, const ActDims &a
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB>, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 1);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB>, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 1, peers);
     if (e != cudaSuccess) return set_error(B200_E_CUDA, "mmq cluster launch: %s", cudaGetErrorString(e));
     count_launch();
     return B200_OK;
@@ -602,11 +605,11 @@ size_t mmq_workspace_bytes(int wtype, int64_t K, int64_t M, int64_t N) {
 
 void launch_mmq_reduce(const float *partial, int ks, int64_t M, int64_t N, float *dst, int64_t dst_nb_row, cudaStream_t st) {
     const int64_t total = M * N;
-    launch_pdl(mmq_reduce_kernel, dim3((unsigned) ((total + 255) / 256)), dim3(256), 0, st, partial, ks, M, N, dst, dst_nb_row);
+    launch_pdl(mmq_reduce_kernel, dim3((unsigned) ((total + 255) / 256)), dim3(256), 0, st, partial, ks, M, N, dst, dst_nb_row, PeerDst{});
 }
 
 int launch_mmq(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
-               void *workspace, size_t workspace_bytes, cudaStream_t st, bool canon) {
+               void *workspace, size_t workspace_bytes, cudaStream_t st, bool canon, const PeerDst &peers) {
     const MmqVariant &v = variant_for(wtype, a.N);
     bool cluster = false;
     int ks = choose_ksplit(v, d, a.n_nt, &cluster);
@@ -614,10 +617,10 @@ int launch_mmq(int wtype, const TiledDims &d, const void *w, const ActDims &a, c
     if (ks > 1 && !cluster && (!workspace || workspace_bytes < per_split * ks)) {
         ks = workspace ? (int) std::max<size_t>(1, workspace_bytes / per_split) : 1;  // fewer splits fit: still correct, only slower
     }
-    if (int e = v.launch(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, (float *) workspace, ks, canon ? 1 : 0, cluster ? 1 : 0, st)) return e;
+    if (int e = v.launch(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, (float *) workspace, ks, canon ? 1 : 0, cluster ? 1 : 0, peers, st)) return e;
     if (ks > 1 && !cluster) {
         const int64_t total = d.M * a.N;
-        launch_pdl(mmq_reduce_kernel, dim3((unsigned) ((total + 255) / 256)), dim3(256), 0, st, (const float *) workspace, ks, d.M, a.N, dst, dst_nb_row);
+        launch_pdl(mmq_reduce_kernel, dim3((unsigned) ((total + 255) / 256)), dim3(256), 0, st, (const float *) workspace, ks, d.M, a.N, dst, dst_nb_row, peers);
         return check_launch("mmq_reduce");
     }
     return B200_OK;

@@ -39,7 +39,7 @@ namespace b200 {
 
 void launch_mmq_reduce(const float *partial, int ks, int64_t M, int64_t N, float *dst, int64_t dst_nb_row, cudaStream_t st);
 int launch_mmq(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
-               void *workspace, size_t workspace_bytes, cudaStream_t st, bool canon);
+               void *workspace, size_t workspace_bytes, cudaStream_t st, bool canon, const PeerDst &peers);
 
 __device__ int g_tc_error = 0;   // non-zero after a bounded wait gave up
 #ifdef B200_TC_PROFILE
@@ -464,10 +464,10 @@ static bool tc_act_maps(const ActDims &a, const void *aq, TcPair *out) {
 int launch_mmq_tc(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
                   void *workspace, size_t workspace_bytes, cudaStream_t st) {
     // Q8_0 weights stay on the mma.sync kernel, reading the canonical activation order
-    if (wtype != B200_TYPE_Q4_0) return launch_mmq(wtype, d, w, a, aq, dst, dst_nb_row, workspace, workspace_bytes, st, true);
+    if (wtype != B200_TYPE_Q4_0) return launch_mmq(wtype, d, w, a, aq, dst, dst_nb_row, workspace, workspace_bytes, st, true, PeerDst{});
     TcPair wm, am;
     if (!is_aligned(w, 16) || !is_aligned(aq, 16) || !tc_weight_maps(d, w, &wm) || !tc_act_maps(a, aq, &am)) {
-        return launch_mmq(wtype, d, w, a, aq, dst, dst_nb_row, workspace, workspace_bytes, st, true);
+        return launch_mmq(wtype, d, w, a, aq, dst, dst_nb_row, workspace, workspace_bytes, st, true, PeerDst{});
     }
     static bool configured[64] = {false};
     int dev = 0;

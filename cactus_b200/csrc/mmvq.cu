@@ -19,7 +19,7 @@ namespace b200 {
 template <int WTYPE, int NC, int MMVQ_WARPS>
 __global__ void __launch_bounds__(MMVQ_WARPS * 32) mmvq_kernel(TiledDims dims, const uint8_t *__restrict__ w, ActDims act,
                                                               const uint8_t *__restrict__ aq, float *__restrict__ dst,
-                                                              int64_t dst_nb_row) {
+                                                              int64_t dst_nb_row, PeerDst peers) {
     pdl_prologue();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -127,23 +127,24 @@ __global__ void __launch_bounds__(MMVQ_WARPS * 32) mmvq_kernel(TiledDims dims, c
             float s = 0.0f;
 #pragma unroll
             for (int wv = 0; wv < MMVQ_WARPS; ++wv) s += red[wv][r][n];
-            *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + n * dst_nb_row + row * 4) = s;
+            store_f32(dst, peers, n * dst_nb_row + row * 4, s);
         }
     }
 }
 
 template <int WTYPE, int WARPS>
-static int launch_mmvq_w(const TiledDims &d, const uint8_t *w, const ActDims &a, const uint8_t *aq, float *dst, int64_t dst_nb_row, cudaStream_t st) {
+static int launch_mmvq_w(const TiledDims &d, const uint8_t *w, const ActDims &a, const uint8_t *aq, float *dst, int64_t dst_nb_row, const PeerDst &peers,
+                         cudaStream_t st) {
     const dim3 grid((unsigned) d.n_rt), block(WARPS * 32);
     switch (a.N) {
-        case 1: launch_pdl(mmvq_kernel<WTYPE, 1, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row); break;
-        case 2: launch_pdl(mmvq_kernel<WTYPE, 2, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row); break;
-        case 3: launch_pdl(mmvq_kernel<WTYPE, 3, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row); break;
-        case 4: launch_pdl(mmvq_kernel<WTYPE, 4, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row); break;
-        case 5: launch_pdl(mmvq_kernel<WTYPE, 5, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row); break;
-        case 6: launch_pdl(mmvq_kernel<WTYPE, 6, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row); break;
-        case 7: launch_pdl(mmvq_kernel<WTYPE, 7, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row); break;
-        case 8: launch_pdl(mmvq_kernel<WTYPE, 8, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row); break;
+        case 1: launch_pdl(mmvq_kernel<WTYPE, 1, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
+        case 2: launch_pdl(mmvq_kernel<WTYPE, 2, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
+        case 3: launch_pdl(mmvq_kernel<WTYPE, 3, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
+        case 4: launch_pdl(mmvq_kernel<WTYPE, 4, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
+        case 5: launch_pdl(mmvq_kernel<WTYPE, 5, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
+        case 6: launch_pdl(mmvq_kernel<WTYPE, 6, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
+        case 7: launch_pdl(mmvq_kernel<WTYPE, 7, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
+        case 8: launch_pdl(mmvq_kernel<WTYPE, 8, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
         default: return set_error(B200_E_INVALID, "mmvq handles 1..8 columns, got %lld", (long long) a.N);
     }
     return check_launch("mmvq");
@@ -151,17 +152,17 @@ static int launch_mmvq_w(const TiledDims &d, const uint8_t *w, const ActDims &a,
 
 template <int WTYPE>
 static int launch_mmvq_t(const TiledDims &d, const uint8_t *w, const ActDims &a, const uint8_t *aq, float *dst,
-                         int64_t dst_nb_row, cudaStream_t st) {
+                         int64_t dst_nb_row, const PeerDst &peers, cudaStream_t st) {
     // measured on B200 at one column: 4096 x 4096 3.9 us with 16 warps against 4.8 with 8, 14336 x 4096 (K x M) 8.5 against 12.6;
     // 4096 x 14336 10.6 against 9.9, 4096 x 128256 73 against 54
-    if (d.n_rt <= 512 && d.n_bg >= 16) return launch_mmvq_w<WTYPE, 16>(d, w, a, aq, dst, dst_nb_row, st);
-    return launch_mmvq_w<WTYPE, 8>(d, w, a, aq, dst, dst_nb_row, st);
+    if (d.n_rt <= 512 && d.n_bg >= 16) return launch_mmvq_w<WTYPE, 16>(d, w, a, aq, dst, dst_nb_row, peers, st);
+    return launch_mmvq_w<WTYPE, 8>(d, w, a, aq, dst, dst_nb_row, peers, st);
 }
 
 int launch_mmvq(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
-                cudaStream_t st) {
-    if (wtype == B200_TYPE_Q4_0) return launch_mmvq_t<B200_TYPE_Q4_0>(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, st);
-    return launch_mmvq_t<B200_TYPE_Q8_0>(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, st);
+                const PeerDst &peers, cudaStream_t st) {
+    if (wtype == B200_TYPE_Q4_0) return launch_mmvq_t<B200_TYPE_Q4_0>(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, peers, st);
+    return launch_mmvq_t<B200_TYPE_Q8_0>(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, peers, st);
 }
 
 }  // namespace b200

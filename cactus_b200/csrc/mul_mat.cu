@@ -10,9 +10,11 @@ bool act_layout_canonical(int64_t N);
 int launch_mmq_tc(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
                   void *workspace, size_t workspace_bytes, cudaStream_t st);
 int mmvq_max_n();
-int launch_mmvq(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row, cudaStream_t st);
+int launch_mmvq(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row, const PeerDst &peers,
+                cudaStream_t st);
 int launch_mmq(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
-               void *workspace, size_t workspace_bytes, cudaStream_t st, bool canon);
+               void *workspace, size_t workspace_bytes, cudaStream_t st, bool canon, const PeerDst &peers);
+int launch_peer_signal_wait(void *const *flags_of_rank, int rank, int g, cudaStream_t st);
 size_t mmq_workspace_bytes(int wtype, int64_t K, int64_t M, int64_t N);
 }  // namespace b200
 
@@ -62,8 +64,32 @@ size_t b200_mul_mat_scratch_bytes(int wtype, int64_t K, int64_t M, int64_t N) {
     return b200_act_bytes(K, N) + mmq_workspace_bytes(wtype, K, M, N);
 }
 
+static int mul_mat_prequant(int wtype, const void *w, int64_t K, int64_t M, const void *act, int64_t N, float *dst, int64_t dst_row_stride_bytes,
+                            void *workspace, size_t workspace_bytes, const PeerDst &peers, b200_stream_t stream);
+
 int b200_mul_mat_q_prequant(int wtype, const void *w, int64_t K, int64_t M, const void *act, int64_t N, float *dst,
                             int64_t dst_row_stride_bytes, void *workspace, size_t workspace_bytes, b200_stream_t stream) {
+    return mul_mat_prequant(wtype, w, K, M, act, N, dst, dst_row_stride_bytes, workspace, workspace_bytes, PeerDst{}, stream);
+}
+
+int b200_mul_mat_q_rowsplit(int wtype, const void *w, int64_t K, int64_t M, const void *act, int64_t N, int rank, int g, void *const *dst_of_rank,
+                            int64_t dst_row_stride_bytes, int64_t first_column, void *workspace, size_t workspace_bytes,
+                            void *const *flags_of_rank, b200_stream_t stream) {
+    B200_REQUIRE(dst_of_rank && flags_of_rank && g >= 1 && g <= 8 && rank >= 0 && rank < g && first_column >= 0, "bad row-split arguments");
+    PeerDst peers = {};
+    float *own = nullptr;
+    for (int r = 0; r < g; ++r) {
+        B200_REQUIRE(dst_of_rank[r] && flags_of_rank[r], "null buffer of rank %d", r);
+        float *p = reinterpret_cast<float *>(dst_of_rank[r]) + first_column;
+        if (r == rank) own = p;
+        else peers.p[peers.n++] = p;
+    }
+    if (int e = mul_mat_prequant(wtype, w, K, M, act, N, own, dst_row_stride_bytes, workspace, workspace_bytes, peers, stream)) return e;
+    return launch_peer_signal_wait(flags_of_rank, rank, g, (cudaStream_t) stream);
+}
+
+static int mul_mat_prequant(int wtype, const void *w, int64_t K, int64_t M, const void *act, int64_t N, float *dst, int64_t dst_row_stride_bytes,
+                            void *workspace, size_t workspace_bytes, const PeerDst &peers, b200_stream_t stream) {
     B200_REQUIRE(shape_ok(wtype, K, M, N), "bad mul_mat shape/type: type %d K %lld M %lld N %lld", wtype, (long long) K, (long long) M, (long long) N);
     B200_REQUIRE(w && act && dst, "null pointer");
     B200_REQUIRE(is_aligned(w, 16) && is_aligned(act, 256) && is_aligned(dst, 4), "misaligned pointer");
@@ -71,9 +97,11 @@ int b200_mul_mat_q_prequant(int wtype, const void *w, int64_t K, int64_t M, cons
     B200_REQUIRE(!workspace || is_aligned(workspace, 256), "workspace must be 256-byte aligned");
     const TiledDims d = tiled_dims(wtype, K, M);
     const ActDims a = act_dims(K, N);
-    if (N <= mmvq_max_n()) return launch_mmvq(wtype, d, w, a, act, dst, dst_row_stride_bytes, (cudaStream_t) stream);
-    if (act_layout_canonical(N)) return launch_mmq_tc(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream);
-    return launch_mmq(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream, false);
+    if (N <= mmvq_max_n()) return launch_mmvq(wtype, d, w, a, act, dst, dst_row_stride_bytes, peers, (cudaStream_t) stream);
+    const bool canon = act_layout_canonical(N);
+    // the tcgen05 kernel writes one destination only: a row-split product takes the mma.sync kernel on either activation order
+    if (canon && peers.n == 0) return launch_mmq_tc(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream);
+    return launch_mmq(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream, canon, peers);
 }
 
 int b200_mul_mat_q(int wtype, const void *w, int64_t K, int64_t M, const float *x, int64_t x_row_stride_bytes, int64_t N,

@@ -4,7 +4,9 @@
 // LLAMA_SPLIT_MODE_ROW, cactus/ggml-backend.h:188, cactus/llama-model.cpp:339-351), each GPU computes
 // dst[:, r*M/g : (r+1)*M/g] and every GPU needs the whole dst for the next (replicated) op.  One process drives one
 // GPU; the dst buffers live in memory shared through CUDA IPC, and the join is done by our own kernels over NVLink:
-//   push     each GPU stores its slice into every GPU's dst buffer (plain 16-byte stores to peer memory);
+//   push     each GPU stores its slice into every GPU's dst buffer (plain stores to peer memory) -- from the write-back
+//            of the mul_mat kernel itself (b200_mul_mat_q_rowsplit: no local copy of the slice, no separate pass), or
+//            from a slice that already exists (b200_allgather_rows);
 //   signal   after the push has completed in stream order, one thread per peer writes this collective's number into
 //            that peer's flag word for us (st.release.sys);
 //   wait     the same kernel then polls our own flag words until every peer's number has arrived.  The poll is
@@ -60,6 +62,13 @@ __global__ void allgather_signal_wait_kernel(PeerPtrs flags, int rank, int g) {
     }
     __syncthreads();
     if (threadIdx.x == 0) mine[8] = e;
+}
+
+int launch_peer_signal_wait(void *const *flags_of_rank, int rank, int g, cudaStream_t st) {
+    PeerPtrs f;
+    for (int r = 0; r < 8; ++r) f.p[r] = r < g ? flags_of_rank[r] : nullptr;
+    allgather_signal_wait_kernel<<<1, 32, 0, st>>>(f, rank, g);
+    return check_launch("allgather_signal_wait");
 }
 
 }  // namespace b200
@@ -123,8 +132,7 @@ int b200_allgather_rows(const float *src, int64_t src_nb_row, int64_t T, int64_t
     const unsigned grid = (unsigned) std::min<int64_t>((total + 255) / 256, 592);
     allgather_push_kernel<<<grid, 256, 0, st>>>(src, src_nb_row, T, Mg, d, dst_nb_row, (int64_t) rank * Mg, g);
     if (int e = check_launch("allgather_push")) return e;
-    allgather_signal_wait_kernel<<<1, 32, 0, st>>>(f, rank, g);
-    return check_launch("allgather_signal_wait");
+    return launch_peer_signal_wait(flags_of_rank, rank, g, st);
 }
 
 int b200_peer_status(const void *flags) {

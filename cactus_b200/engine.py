@@ -100,12 +100,18 @@ class LlamaWeights:
             from .rowsplit import row_bounds
             gen = torch.Generator(device="cuda").manual_seed(seed * 1000 + 17 + rank)
         rows = (lambda M: M) if world == 1 else (lambda M: row_bounds(M, world)[rank + 1] - row_bounds(M, world)[rank])
-        w.tensors["output.weight"] = QWeight.from_blocks(cfg.head_type, d, rows(cfg.vocab), random_blocks(cfg.head_type, rows(cfg.vocab), d, gen))
+        row0 = (lambda M: 0) if world == 1 else (lambda M: row_bounds(M, world)[rank])
+
+        def make(wtype, K, M):
+            q = QWeight.from_blocks(wtype, K, rows(M), random_blocks(wtype, rows(M), K, gen))
+            q.row0 = row0(M)
+            return q
+        w.tensors["output.weight"] = make(cfg.head_type, d, cfg.vocab)
         w.tensors["output_norm.weight"] = torch.ones(d, device="cuda")
         names = {"wq": "attn_q", "wk": "attn_k", "wv": "attn_v", "wo": "attn_output", "gate": "ffn_gate", "up": "ffn_up", "down": "ffn_down"}
         for il in range(cfg.n_layer):
             for short, K, M in cfg.mul_mat_shapes():
-                w.tensors[f"blk.{il}.{names[short]}.weight"] = QWeight.from_blocks(cfg.layer_type, K, rows(M), random_blocks(cfg.layer_type, rows(M), K, gen))
+                w.tensors[f"blk.{il}.{names[short]}.weight"] = make(cfg.layer_type, K, M)
             w.tensors[f"blk.{il}.attn_norm.weight"] = torch.ones(d, device="cuda")
             w.tensors[f"blk.{il}.ffn_norm.weight"] = torch.ones(d, device="cuda")
         return w
@@ -196,7 +202,6 @@ class LlamaEngine:
             self.gate, self.up = out(T, cfg.d_ff), out(T, cfg.d_ff)
         self.tmp, self.tmp2 = out(T, cfg.d_model), out(T, cfg.d_model)   # attention branch / feed-forward branch of the residual
         self.logits = out(T, cfg.vocab)
-        self.local = f32(T * (max(cfg.d_ff, cfg.vocab) // g + 16)) if split is not None else None
         self.next_ids = torch.zeros(T, dtype=torch.int32, device=dev)
         self.logits_host = torch.empty((T, cfg.vocab), dtype=torch.float32).pin_memory()
         self.ids_host = torch.zeros(T, dtype=torch.int32).pin_memory()
@@ -217,10 +222,7 @@ class LlamaEngine:
             check(lib().b200_mul_mat_q_prequant(w.wtype, w.data.data_ptr(), w.K, w.M, act.data_ptr(), T, out.data_ptr(), out.stride(0) * 4,
                                                 self.ws.data_ptr(), self.ws.numel(), self._st))
             return
-        loc = self.local[:T * w.M].view(T, w.M)   # this rank's rows of the product, then the join
-        check(lib().b200_mul_mat_q_prequant(w.wtype, w.data.data_ptr(), w.K, w.M, act.data_ptr(), T, loc.data_ptr(), w.M * 4,
-                                            self.ws.data_ptr(), self.ws.numel(), self._st))
-        self.split.allgather(loc, T, w.M, out, self._st)
+        self.split.mul_mat(w, act, T, out, self.ws, self._st)   # this rank's rows, written into every rank's `out`, then the flag exchange
 
     def _quant(self, x: torch.Tensor, K: int, T: int, act: torch.Tensor):
         check(lib().b200_quantize_activations(x.data_ptr(), x.stride(0) * 4, K, T, act.data_ptr(), act.numel(), self.variant, self._st))

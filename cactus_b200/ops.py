@@ -30,8 +30,9 @@ def _need_cuda(*ts):
 class QWeight:
     """A quantised weight tensor [K, M] (ggml ne = [K, M]) resident on the device in the tiled layout."""
 
-    def __init__(self, wtype: int, K: int, M: int, data: torch.Tensor):
+    def __init__(self, wtype: int, K: int, M: int, data: torch.Tensor, row0: int = 0):
         self.wtype, self.K, self.M, self.data = wtype, K, M, data
+        self.row0 = row0   # first row of this weight within the tensor it was cut from (row split)
 
     @staticmethod
     def from_blocks(wtype: int, K: int, M: int, blocks, device="cuda") -> "QWeight":
@@ -58,7 +59,7 @@ class QWeight:
         t0, t1 = r0 // 16, (r1 + 15) // 16
         q = self.data[t0 * n_bg * tile:t1 * n_bg * tile]
         d = self.data[n_rt * n_bg * tile + t0 * n_bg * 128:n_rt * n_bg * tile + t1 * n_bg * 128]
-        return QWeight(self.wtype, self.K, r1 - r0, torch.cat([q, d]))
+        return QWeight(self.wtype, self.K, r1 - r0, torch.cat([q, d]), row0=self.row0 + r0)
 
     @staticmethod
     def cat(parts: list) -> "QWeight":

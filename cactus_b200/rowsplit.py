@@ -94,6 +94,13 @@ class RowSplit:
         check(lib().b200_allgather_rows(src.data_ptr(), src.stride(0) * 4, T, Mg, self.rank, self.world, arr, dst.stride(0) * 4,
                                         self._flag_arr, stream))
 
+    def mul_mat(self, w, act: torch.Tensor, T: int, dst: torch.Tensor, workspace: torch.Tensor, stream: int) -> None:
+        """dst[:T, w.row0 : w.row0 + w.M] = this rank's rows of the product, stored by the mul_mat kernel's own write-back
+        into every rank's dst; returns (in stream order) when all ranks' slices are in."""
+        arr = self._dst_arrays[dst.data_ptr()]
+        check(lib().b200_mul_mat_q_rowsplit(w.wtype, w.data.data_ptr(), w.K, w.M, act.data_ptr(), T, self.rank, self.world, arr, dst.stride(0) * 4,
+                                            w.row0, workspace.data_ptr(), workspace.numel(), self._flag_arr, stream))
+
     def status(self) -> int:
         """0, or 1 + the first rank whose slice did not arrive within the wait limit."""
         return int(lib().b200_peer_status(self.flags[self.rank]))

@@ -284,6 +284,12 @@ B200_API int b200_peer_free(void *ptr);
 B200_API int b200_allgather_rows(const float *src, int64_t src_nb_row, int64_t T, int64_t Mg, int rank, int g, void *const *dst_of_rank,
                                  int64_t dst_nb_row, void *const *flags_of_rank, b200_stream_t stream);
 B200_API int b200_peer_status(const void *flags);
+/* mul_mat and join in one step: b200_mul_mat_q_prequant on this rank's row slice (M rows, the columns first_column ..
+ * first_column + M - 1 of the full product), with the kernel's own write-back storing every value into dst_of_rank[r]
+ * of all g ranks, followed by the flag exchange of b200_allgather_rows.  dst_of_rank[r] is rank r's full [N, *] buffer. */
+B200_API int b200_mul_mat_q_rowsplit(int wtype, const void *w, int64_t K, int64_t M, const void *act, int64_t N, int rank, int g,
+                                     void *const *dst_of_rank, int64_t dst_row_stride_bytes, int64_t first_column, void *workspace,
+                                     size_t workspace_bytes, void *const *flags_of_rank, b200_stream_t stream);
 
 #ifdef __cplusplus
 }
