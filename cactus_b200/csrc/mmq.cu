@@ -127,7 +127,9 @@ struct MmqCfg {
     static constexpr int TOTAL = STAGE * STAGES;
 };
 
-template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB>
+// PEER: the write-back also stores into the other GPUs' buffers of a row split; a separate instantiation so that the
+// one-GPU kernel is the same machine code as without the feature (it measured 7 % slower on the widest shape otherwise)
+template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB, bool PEER = false>
 __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims, const uint8_t *__restrict__ w, ActDims act,
                                                           const uint8_t *__restrict__ aq, float *__restrict__ dst,
                                                           int64_t dst_nb_row, float *__restrict__ partial, int ksplit, int canon, int cluster, PeerDst peers) {
@@ -349,7 +351,8 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
             const int64_t col = cta_nt0 * 8 + c, row = cta_rt0 * 16 + r;
             if (col < act.N) {
                 const int64_t off = col * dst_nb_row + row * 4;
-                for (int pi = -1; pi < peers.n; ++pi) {   // own buffer, then the other GPUs' of a row split
+                const int n_peers = PEER ? peers.n : 0;
+                for (int pi = -1; pi < n_peers; ++pi) {   // own buffer, then the other GPUs' of a row split
                     float *o = reinterpret_cast<float *>(reinterpret_cast<char *>(pi < 0 ? dst : peers.p[pi]) + off);
                     if (row + 3 < dims.M && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
                         *reinterpret_cast<float4 *>(o) = acc;
@@ -381,8 +384,13 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
                 v1 *= WS;
                 if (row < dims.M) {
                     if (ksplit == 1) {
-                        if (col < act.N) store_f32(dst, peers, col * dst_nb_row + row * 4, v0);
-                        if (col + 1 < act.N) store_f32(dst, peers, (col + 1) * dst_nb_row + row * 4, v1);
+                        if (PEER) {
+                            if (col < act.N) store_f32(dst, peers, col * dst_nb_row + row * 4, v0);
+                            if (col + 1 < act.N) store_f32(dst, peers, (col + 1) * dst_nb_row + row * 4, v1);
+                        } else {
+                            if (col < act.N) *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + col * dst_nb_row + row * 4) = v0;
+                            if (col + 1 < act.N) *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + (col + 1) * dst_nb_row + row * 4) = v1;
+                        }
                     } else {
                         if (col < act.N) partial[((int64_t) ks * act.N + col) * dims.M + row] = v0;
                         if (col + 1 < act.N) partial[((int64_t) ks * act.N + col + 1) * dims.M + row] = v1;
@@ -431,8 +439,10 @@ static int launch_variant(const TiledDims &d, const uint8_t *w, const ActDims &a
                           float *partial, int ksplit, int canon, int cluster, const PeerDst &peers, cudaStream_t st) {
     using S = MmqCfg<WTYPE, NTW, WN, MT, WM, STAGES>;
     dim3 grid((unsigned) ((d.n_rt + S::CTA_TILES - 1) / S::CTA_TILES), (unsigned) ((a.n_nt + S::NT - 1) / S::NT), (unsigned) ksplit);
+    const bool peer = peers.n > 0;
     if (!cluster) {
-        launch_pdl(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB>, grid, dim3(S::THREADS), S::TOTAL, st, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 0, peers);
+        if (peer) launch_pdl(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, true>, grid, dim3(S::THREADS), S::TOTAL, st, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 0, peers);
+        else launch_pdl(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, false>, grid, dim3(S::THREADS), S::TOTAL, st, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 0, peers);
         return check_launch("mmq");
     }
     cudaLaunchConfig_t cfg = {};
@@ -449,7 +459,8 @@ static int launch_variant(const TiledDims &d, const uint8_t *w, const ActDims &a
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB>, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 1, peers);
+    cudaError_t e = peer ? cudaLaunchKernelEx(&cfg, mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, true>, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 1, peers)
+                         : cudaLaunchKernelEx(&cfg, mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, false>, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 1, peers);
     if (e != cudaSuccess) return set_error(B200_E_CUDA, "mmq cluster launch: %s", cudaGetErrorString(e));
     count_launch();
     return B200_OK;
@@ -492,7 +503,8 @@ static MmqVariant make_variant() {
     v.cta_nt = S::NT;
     v.launch = launch_variant<WTYPE, NTW, WN, MT, WM, STAGES, MINB>;
     v.max_clusters = max_clusters_variant<WTYPE, NTW, WN, MT, WM, STAGES, MINB>;
-    cudaFuncSetAttribute(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    cudaFuncSetAttribute(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    cudaFuncSetAttribute(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     int n = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB>, S::THREADS, S::TOTAL) != cudaSuccess || n <= 0) {
         cudaGetLastError();
