@@ -96,8 +96,11 @@ template <int WTYPE>
 __device__ __forceinline__ void load_wfrag(WFrag<WTYPE> &f, const uint8_t *__restrict__ wq, const uint8_t *__restrict__ wd, int lane) {
     const int g = lane >> 2;
     if (WTYPE == B200_TYPE_Q4_0) {
-        const uint4 *p = reinterpret_cast<const uint4 *>(wq) + lane * 2;
-        const uint4 u0 = p[0], u1 = p[1];
+        // lane i owns the 16-byte chunks 2i and 2i + 1 of the tile; in the ring chunk c sits at c ^ ((c >> 3) & 1) (see the
+        // copy plan), which spreads the eight lanes of a quarter warp over all eight 16-byte bank groups
+        const int sw = (lane >> 2) & 1;
+        const uint4 *p = reinterpret_cast<const uint4 *>(wq);
+        const uint4 u0 = p[(lane * 2) ^ sw], u1 = p[(lane * 2 + 1) ^ sw];
         f.a[0] = u0.x; f.a[1] = u0.y; f.a[2] = u0.z; f.a[3] = u0.w;
         f.b[0] = u1.x; f.b[1] = u1.y; f.b[2] = u1.z; f.b[3] = u1.w;
     } else {
@@ -127,9 +130,16 @@ struct MmqCfg {
     static constexpr int TOTAL = STAGE * STAGES;
 };
 
-// PEER: the write-back also stores into the other GPUs' buffers of a row split; a separate instantiation so that the
-// one-GPU kernel is the same machine code as without the feature (it measured 7 % slower on the widest shape otherwise)
-template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB, bool PEER = false>
+// MODE 1 (peer): the write-back also stores into the other GPUs' buffers of a row split; a separate instantiation so
+// that the one-GPU kernel is the same machine code as without the feature (it measured 7 % slower on the widest shape
+// otherwise).
+// MODE 2 (stream-K): the grid is one CTA per resident slot of the device, and the (row group, block group) iterations
+// of the whole product are dealt out evenly and contiguously, so every SM is busy for the same time whatever the row
+// count.  A CTA whose range ends inside a row group parks its partial tile in the workspace; the CTA that arrives last
+// at a row group (a counter per row group) adds the parts in K order and writes the result, so the sum does not
+// depend on the arrival order and nobody waits for anybody.
+constexpr int MMQ_PLAIN = 0, MMQ_PEER = 1, MMQ_STREAMK = 2;
+template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB, int MODE = MMQ_PLAIN>
 __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims, const uint8_t *__restrict__ w, ActDims act,
                                                           const uint8_t *__restrict__ aq, float *__restrict__ dst,
                                                           int64_t dst_nb_row, float *__restrict__ partial, int ksplit, int canon, int cluster, PeerDst peers) {
@@ -150,15 +160,46 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
     const int64_t per = (dims.n_bg + ksplit - 1) / ksplit;
     const int64_t bg_begin = ks * per;
     const int64_t bg_end = min(dims.n_bg, bg_begin + per);
-    const int64_t n_iter = max((int64_t) 0, bg_end - bg_begin);
+    constexpr bool SK = MODE == MMQ_STREAMK;
+    // Stream-K.  Iteration i of the product is block group i % n_bg of row group i / n_bg.  Two ways to deal them out:
+    //   even deal (ksplit <= 1): CTA j owns the contiguous iterations [j * total / G, (j + 1) * total / G) -- for
+    //     products with more row groups than CTAs; a CTA first does the piece its range ends with, then the rest, so it
+    //     finishes with whole row groups;
+    //   head/tail deal (ksplit = h > 1): fewer row groups than CTAs.  CTA b < groups does block groups [0, h) of row
+    //     group b; the other Gs CTAs share the tails [h, n_bg) of all row groups, contiguously, and are done first (h is
+    //     chosen that way), so every head finds its tail parked and finishes with one read and the store.
+    const uint32_t sk_nbg = (uint32_t) dims.n_bg;
+    const uint32_t sk_groups = SK ? (uint32_t) (dims.n_rt / S::CTA_TILES) : 0u;
+    const uint32_t sk_total = sk_groups * sk_nbg;
+    const uint32_t sk_h = SK && ksplit > 1 ? (uint32_t) ksplit : 0u;       // 0: even deal
+    const uint32_t sk_sl = sk_nbg - sk_h;                                    // tail length of a row group (head/tail deal)
+    const uint32_t sk_gs = SK ? gridDim.x - sk_groups : 1u;                  // CTAs that share the tails
+    const bool sk_tails = sk_h != 0 && blockIdx.x >= sk_groups;
+    // this CTA's range [sk_it0, sk_it0 + n_iter): in iteration space, or for a tail CTA in the space of all tails laid end to end
+    uint32_t sk_it0 = 0, sk_n = 0;
+    if (SK) {
+        if (sk_h == 0) {
+            sk_it0 = (uint32_t) ((uint64_t) blockIdx.x * sk_total / gridDim.x);
+            sk_n = (uint32_t) ((uint64_t) (blockIdx.x + 1) * sk_total / gridDim.x) - sk_it0;
+        } else if (!sk_tails) {
+            sk_it0 = blockIdx.x * sk_nbg;
+            sk_n = sk_h;
+        } else {
+            const uint64_t c = blockIdx.x - sk_groups, all = (uint64_t) sk_groups * sk_sl;
+            sk_it0 = (uint32_t) (c * all / sk_gs);
+            sk_n = (uint32_t) ((c + 1) * all / sk_gs) - sk_it0;
+        }
+    }
+    const int64_t n_iter = SK ? (int64_t) sk_n : max((int64_t) 0, bg_end - bg_begin);
 
     // Copy plan of this thread, fixed for the whole K loop: 16-byte chunk c of a stage comes from
     // base + (src16[k] + bg * step16) * 16.  Offsets are in 16-byte units and fit 32 bits.
-    const int64_t cta_rt0 = (int64_t) blockIdx.x * S::CTA_TILES;
+    const int64_t cta_rt0 = SK ? 0 : (int64_t) blockIdx.x * S::CTA_TILES;   // stream-K adds the row group per iteration
     constexpr int A_CH = S::A_BYTES / 16, AS_CH = S::AS_BYTES / 16, B_CH = S::B_BYTES / 16, S_CH = S::S_BYTES / 16;
     constexpr int A_N = (A_CH + MMQ_THREADS - 1) / MMQ_THREADS, AS_N = (AS_CH + MMQ_THREADS - 1) / MMQ_THREADS;
     constexpr int B_N = (B_CH + MMQ_THREADS - 1) / MMQ_THREADS, S_N = (S_CH + MMQ_THREADS - 1) / MMQ_THREADS;
     uint32_t a_src[A_N], as_src[AS_N], b_src[B_N], s_src[S_N];
+    uint32_t a_dst[A_N];   // Q4_0: chunk c of a tile lands at chunk position c ^ ((c >> 3) & 1): conflict-free for the fragment loads
     const uint8_t *w_sc = w + dims.qs_bytes, *a_sc = aq + act.d_offset;
 #pragma unroll
     for (int k = 0; k < A_N; ++k) {
@@ -166,6 +207,7 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
         const int tile = c / (S::TILE / 16), off = c % (S::TILE / 16);
         const int64_t rt = min(cta_rt0 + tile, dims.n_rt - 1);  // rows beyond the matrix are never written back
         a_src[k] = (uint32_t) (rt * dims.n_bg * (S::TILE / 16) + off);
+        a_dst[k] = (WTYPE == B200_TYPE_Q4_0) ? (uint32_t) (tile * S::TILE + (off ^ ((off >> 3) & 1)) * 16) : (uint32_t) (c * 16);
     }
 #pragma unroll
     for (int k = 0; k < AS_N; ++k) {
@@ -185,18 +227,46 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
         const int64_t nt = min(cta_nt0 + (c >> 4), act.n_nt - 1);
         s_src[k] = (uint32_t) (nt * act.n_bg * 16 + (c & 15));
     }
+    // Stream-K order inside a CTA: a range that ends inside a row group (or tail) starts with that last piece and then
+    // walks the rest from its beginning.  The pieces shared with a neighbour are then parked early, long before the CTA
+    // that completes the row group looks for them.
+    const uint32_t sk_unit = sk_tails ? sk_sl : sk_nbg;   // length of what the range is cut at
+    uint32_t sk_head = 0, sk_head_at = 0;
+    if (SK) {
+        const uint32_t it1 = sk_it0 + sk_n;
+        sk_head_at = it1 / sk_unit * sk_unit;
+        if (sk_head_at > sk_it0 && it1 > sk_head_at) sk_head = it1 - sk_head_at;
+    }
+    // local iteration -> (row group, block group)
+    auto sk_where = [&](int64_t it, uint32_t &ct, uint32_t &bg) {
+        const uint32_t u = it < (int64_t) sk_head ? sk_head_at + (uint32_t) it : sk_it0 + (uint32_t) it - sk_head;
+        ct = u / sk_unit;
+        bg = u - ct * sk_unit + (sk_tails ? sk_h : 0u);
+    };
+    uint32_t iss_ct = 0, iss_bg = 0;   // stream-K: where the next copy reads
+    if (SK) sk_where(0, iss_ct, iss_bg);
     auto issue = [&](int64_t it) {
         uint8_t *st = smem + (it % MMQ_STAGES) * S::STAGE;
-        const uint32_t bg = (uint32_t) (bg_begin + it);
+        uint32_t bg = (uint32_t) (bg_begin + it);
+        uint32_t wbg = bg;   // block-group index into the weight stream, row group included
+        if (SK) {
+            if (sk_head != 0 && it == (int64_t) sk_head) sk_where(it, iss_ct, iss_bg);   // the last piece is copied: on to the start of the range
+            bg = iss_bg;
+            wbg = iss_ct * (uint32_t) S::CTA_TILES * sk_nbg + iss_bg;
+            if (++iss_bg == sk_nbg) {
+                iss_bg = sk_tails ? sk_h : 0u;
+                ++iss_ct;
+            }
+        }
 #pragma unroll
         for (int k = 0; k < A_N; ++k) {
             const int c = tid + k * MMQ_THREADS;
-            if (A_CH % MMQ_THREADS == 0 || c < A_CH) cp_async16(st + c * 16, w + (size_t) (a_src[k] + bg * (S::TILE / 16)) * 16);
+            if (A_CH % MMQ_THREADS == 0 || c < A_CH) cp_async16(st + a_dst[k], w + (size_t) (a_src[k] + wbg * (S::TILE / 16)) * 16);
         }
 #pragma unroll
         for (int k = 0; k < AS_N; ++k) {
             const int c = tid + k * MMQ_THREADS;
-            if (AS_CH % MMQ_THREADS == 0 || c < AS_CH) cp_async16(st + S::A_BYTES + c * 16, w_sc + (size_t) (as_src[k] + bg * 8) * 16);
+            if (AS_CH % MMQ_THREADS == 0 || c < AS_CH) cp_async16(st + S::A_BYTES + c * 16, w_sc + (size_t) (as_src[k] + wbg * 8) * 16);
         }
         uint8_t *sb = st + S::A_BYTES + S::AS_BYTES;
 #pragma unroll
@@ -221,7 +291,7 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
         cp_async_commit();
     }
 
-    for (int64_t it = 0; it < n_iter; ++it) {
+    auto body = [&](int64_t it) {
         cp_async_wait<MMQ_STAGES - 2>();
         __syncthreads();
         if (it + MMQ_STAGES - 1 < n_iter) issue(it + MMQ_STAGES - 1);
@@ -304,12 +374,137 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
             if (step + 1 < NSTEP) start(step + 1, (step + 1) & 1);
             finish(step, step & 1);
         }
+    };
+    // write back; Q4_0 quants were used as 16 * value
+    constexpr float WS = (WTYPE == B200_TYPE_Q4_0) ? 0.0625f : 1.0f;
+    if constexpr (SK) {
+        // workspace: one arrival counter per row group (zeroed before the launch), then the slots partial tiles are parked
+        // in, each holding the accumulator registers of every thread in thread order -- all CTAs have the same shape, so
+        // the CTA that sums reads the values of its own (row, column) positions
+        constexpr int NACC = MMQ_MT * NT * 2;
+        constexpr int64_t SLOT = (int64_t) NACC * MMQ_THREADS;   // 8-byte pairs
+        const int64_t n_groups = dims.n_rt / S::CTA_TILES;
+        unsigned *arrived = reinterpret_cast<unsigned *>(partial);
+        uint64_t *slots = reinterpret_cast<uint64_t *>(reinterpret_cast<char *>(partial) + ((n_groups * 4 + 255) / 256) * 256);
+        __shared__ int sk_flag;
+        auto store_group = [&](uint32_t ct) {
+#pragma unroll
+            for (int mt = 0; mt < MMQ_MT; ++mt) {
+                const int64_t row_base = ((int64_t) ct * S::CTA_TILES + wm * MT + mt) * 16 + g;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const int64_t col = (nt0 + nt) * 8 + 2 * t;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int64_t row = row_base + h * 8;
+                        float v0, v1;
+                        unpack2(y[mt][nt][h], v0, v1);
+                        if (row < dims.M) {
+                            if (col < act.N) *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + col * dst_nb_row + row * 4) = v0 * WS;
+                            if (col + 1 < act.N) *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + (col + 1) * dst_nb_row + row * 4) = v1 * WS;
+                        }
+                    }
+                }
+            }
+        };
+        auto add_part = [&](int64_t slot) {   // y += the part parked in that slot
+            const uint64_t *src = slots + slot * SLOT + tid;
+            unsigned long long v[NACC];
+#pragma unroll
+            for (int i = 0; i < NACC; ++i) v[i] = __ldcg(reinterpret_cast<const unsigned long long *>(src + i * MMQ_THREADS));
+#pragma unroll
+            for (int i = 0; i < NACC; ++i) {
+                uint64_t &acc = y[i / (NT * 2)][(i / 2) % NT][i & 1];
+                float a0, a1;
+                unpack2(acc, a0, a1);
+                a0 += __uint_as_float((uint32_t) v[i]);
+                a1 += __uint_as_float((uint32_t) (v[i] >> 32));
+                acc = pack2(__float_as_uint(a0), __float_as_uint(a1));
+            }
+        };
+        const uint64_t G = gridDim.x;
+        int64_t it = 0;
+        while (it < n_iter) {
+            uint32_t ct, bg0;
+            sk_where(it, ct, bg0);
+            const int64_t seg_end = it < (int64_t) sk_head ? (int64_t) sk_head : min(n_iter, it + (int64_t) (sk_nbg - bg0));
+            const int64_t seg_len = seg_end - it;
+#pragma unroll
+            for (int mt = 0; mt < MMQ_MT; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) y[mt][nt][0] = y[mt][nt][1] = 0ull;
+            for (; it < seg_end; ++it) body(it);
+            if (it == n_iter) pdl_trigger();
+            if (seg_len == (int64_t) sk_nbg) {   // the whole K range of this row group: no parts
+                store_group(ct);
+                continue;
+            }
+            // The parts of row group ct in K order, their slots, and which of them this one is.
+            //   even deal: the CTA of iteration i is the largest j with j * total / G <= i; CTA j parks a piece that starts
+            //     where its range starts in slot 2j, the piece its range ends with in slot 2j + 1;
+            //   head/tail deal: slot 3 ct is the head, 3 ct + 1 the tail from block group h, 3 ct + 2 the rest of a tail
+            //     that two CTAs share.
+            uint32_t parts, own;
+            uint32_t first = 0;
+            if (sk_h == 0) {
+                first = (uint32_t) ((((uint64_t) ct * sk_nbg + 1) * G - 1) / sk_total);
+                parts = (uint32_t) ((((uint64_t) (ct + 1) * sk_nbg) * G - 1) / sk_total) - first + 1;
+                own = blockIdx.x - first;
+            } else {
+                const uint64_t all = (uint64_t) sk_groups * sk_sl;
+                const uint32_t ca = (uint32_t) ((((uint64_t) ct * sk_sl + 1) * sk_gs - 1) / all);
+                const uint32_t cb = (uint32_t) ((((uint64_t) (ct + 1) * sk_sl) * sk_gs - 1) / all);
+                parts = 2 + (cb - ca);
+                own = bg0 == 0 ? 0u : (bg0 == sk_h ? 1u : 2u);
+            }
+            auto slot_of = [&](uint32_t p) -> int64_t {
+                if (sk_h != 0) return (int64_t) ct * 3 + p;
+                const uint32_t j = first + p;
+                const uint32_t j_it0 = (uint32_t) ((uint64_t) j * sk_total / G);
+                return (int64_t) j * 2 + (j_it0 >= ct * sk_nbg ? 0 : 1);
+            };
+            // If every other part is already parked, add them to the registers and write the rows out: nothing of this
+            // part goes through memory.  Only for the first or second part in K order, where (own + p0) + p2 ... are the
+            // same bits as the sum from zero in K order (a + b = b + a), so the result does not depend on who finishes.
+            if (tid == 0) {
+                unsigned seen;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(arrived + ct) : "memory");
+                sk_flag = own <= 1 && seen == parts - 1;
+            }
+            __syncthreads();
+            if (sk_flag) {
+                for (uint32_t p = 0; p < parts; ++p)
+                    if (p != own) add_part(slot_of(p));
+                store_group(ct);
+                __syncthreads();   // sk_flag is rewritten by the next part
+                continue;
+            }
+            uint64_t *mine = slots + slot_of(own) * SLOT + tid;
+#pragma unroll
+            for (int i = 0; i < NACC; ++i) __stcg(reinterpret_cast<unsigned long long *>(mine + i * MMQ_THREADS), (unsigned long long) y[i / (NT * 2)][(i / 2) % NT][i & 1]);
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) sk_flag = atomicAdd(arrived + ct, 1u) == parts - 1;
+            __syncthreads();
+            if (sk_flag) {   // arrived last: add all parts in K order, this CTA's own from memory too
+                __threadfence();
+#pragma unroll
+                for (int mt = 0; mt < MMQ_MT; ++mt)
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) y[mt][nt][0] = y[mt][nt][1] = 0ull;
+                for (uint32_t p = 0; p < parts; ++p) add_part(slot_of(p));
+                store_group(ct);
+            }
+            __syncthreads();
+        }
+        cp_async_wait<0>();
+        return;
+    } else {
+        for (int64_t it = 0; it < n_iter; ++it) body(it);
     }
     cp_async_wait<0>();
     pdl_trigger();
 
-    // write back; Q4_0 quants were used as 16 * value
-    constexpr float WS = (WTYPE == B200_TYPE_Q4_0) ? 0.0625f : 1.0f;
     if (cluster) {
         // The K splits of one output tile form a thread-block cluster (cluster dimension z = ksplit).  Every CTA parks its
         // partial tile in its own shared memory; after a cluster barrier CTA r sums slice r of the tile over all CTAs,
@@ -351,7 +546,7 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
             const int64_t col = cta_nt0 * 8 + c, row = cta_rt0 * 16 + r;
             if (col < act.N) {
                 const int64_t off = col * dst_nb_row + row * 4;
-                const int n_peers = PEER ? peers.n : 0;
+                const int n_peers = MODE == MMQ_PEER ? peers.n : 0;
                 for (int pi = -1; pi < n_peers; ++pi) {   // own buffer, then the other GPUs' of a row split
                     float *o = reinterpret_cast<float *>(reinterpret_cast<char *>(pi < 0 ? dst : peers.p[pi]) + off);
                     if (row + 3 < dims.M && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
@@ -384,7 +579,7 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
                 v1 *= WS;
                 if (row < dims.M) {
                     if (ksplit == 1) {
-                        if (PEER) {
+                        if (MODE == MMQ_PEER) {
                             if (col < act.N) store_f32(dst, peers, col * dst_nb_row + row * 4, v0);
                             if (col + 1 < act.N) store_f32(dst, peers, (col + 1) * dst_nb_row + row * 4, v1);
                         } else {
@@ -432,7 +627,31 @@ struct MmqVariant {
     int ctas_per_sm; // resident CTAs per SM (filled on first use)
     int (*launch)(const TiledDims &, const uint8_t *, const ActDims &, const uint8_t *, float *, int64_t, float *, int, int, int, const PeerDst &, cudaStream_t);
     int (*max_clusters)(int);   // resident clusters of `ksplit` CTAs on this device (0 = cannot be launched that way)
+    int (*launch_streamk)(const TiledDims &, const uint8_t *, const ActDims &, const uint8_t *, float *, int64_t, void *, int, int, int, cudaStream_t);
+    size_t streamk_slot_bytes;  // one partial tile of a CTA in the stream-K workspace
 };
+
+__global__ void zero_u32_kernel(unsigned *p, int n) {
+    pdl_prologue();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = 0u;
+}
+
+static size_t streamk_counter_bytes(int64_t n_groups) { return (size_t) ((n_groups * 4 + 255) / 256) * 256; }
+
+// stream-K launch: `ctas` CTAs (one per resident slot), arrival counters zeroed first; head = 0 for the even deal, else
+// the block groups of a head in the head/tail deal
+template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB>
+static int launch_variant_streamk(const TiledDims &d, const uint8_t *w, const ActDims &a, const uint8_t *aq, float *dst, int64_t dst_nb_row,
+                                  void *workspace, int ctas, int head, int canon, cudaStream_t st) {
+    using S = MmqCfg<WTYPE, NTW, WN, MT, WM, STAGES>;
+    const int n_groups = (int) (d.n_rt / S::CTA_TILES);
+    launch_pdl(zero_u32_kernel, dim3((unsigned) ((n_groups + 255) / 256)), dim3(256), 0, st, (unsigned *) workspace, n_groups);
+    if (int e = check_launch("mmq stream-K counters")) return e;
+    launch_pdl(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, MMQ_STREAMK>, dim3((unsigned) ctas), dim3(S::THREADS), S::TOTAL, st, d, w, a, aq, dst,
+               dst_nb_row, (float *) workspace, head, canon, 0, PeerDst{});
+    return check_launch("mmq stream-K");
+}
 
 template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB>
 static int launch_variant(const TiledDims &d, const uint8_t *w, const ActDims &a, const uint8_t *aq, float *dst, int64_t dst_nb_row,
@@ -441,8 +660,8 @@ static int launch_variant(const TiledDims &d, const uint8_t *w, const ActDims &a
     dim3 grid((unsigned) ((d.n_rt + S::CTA_TILES - 1) / S::CTA_TILES), (unsigned) ((a.n_nt + S::NT - 1) / S::NT), (unsigned) ksplit);
     const bool peer = peers.n > 0;
     if (!cluster) {
-        if (peer) launch_pdl(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, true>, grid, dim3(S::THREADS), S::TOTAL, st, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 0, peers);
-        else launch_pdl(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, false>, grid, dim3(S::THREADS), S::TOTAL, st, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 0, peers);
+        if (peer) launch_pdl(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, MMQ_PEER>, grid, dim3(S::THREADS), S::TOTAL, st, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 0, peers);
+        else launch_pdl(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, MMQ_PLAIN>, grid, dim3(S::THREADS), S::TOTAL, st, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 0, peers);
         return check_launch("mmq");
     }
     cudaLaunchConfig_t cfg = {};
@@ -459,8 +678,8 @@ static int launch_variant(const TiledDims &d, const uint8_t *w, const ActDims &a
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    cudaError_t e = peer ? cudaLaunchKernelEx(&cfg, mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, true>, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 1, peers)
-                         : cudaLaunchKernelEx(&cfg, mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, false>, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 1, peers);
+    cudaError_t e = peer ? cudaLaunchKernelEx(&cfg, mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, MMQ_PEER>, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 1, peers)
+                         : cudaLaunchKernelEx(&cfg, mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, MMQ_PLAIN>, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 1, peers);
     if (e != cudaSuccess) return set_error(B200_E_CUDA, "mmq cluster launch: %s", cudaGetErrorString(e));
     count_launch();
     return B200_OK;
@@ -503,8 +722,11 @@ static MmqVariant make_variant() {
     v.cta_nt = S::NT;
     v.launch = launch_variant<WTYPE, NTW, WN, MT, WM, STAGES, MINB>;
     v.max_clusters = max_clusters_variant<WTYPE, NTW, WN, MT, WM, STAGES, MINB>;
-    cudaFuncSetAttribute(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-    cudaFuncSetAttribute(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    v.launch_streamk = launch_variant_streamk<WTYPE, NTW, WN, MT, WM, STAGES, MINB>;
+    v.streamk_slot_bytes = (size_t) S::CTA_TILES * 16 * S::NT * 8 * sizeof(float);
+    cudaFuncSetAttribute(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, MMQ_STREAMK>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    cudaFuncSetAttribute(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, MMQ_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    cudaFuncSetAttribute(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, MMQ_PEER>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     int n = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB>, S::THREADS, S::TOTAL) != cudaSuccess || n <= 0) {
         cudaGetLastError();
@@ -612,7 +834,47 @@ size_t mmq_workspace_bytes(int wtype, int64_t K, int64_t M, int64_t N) {
     const int64_t ctas = ((d.n_rt + 7) / 8) * ((N + 63) / 64);
     int64_t ks = std::min<int64_t>(16, std::max<int64_t>(1, d.n_bg / 2));
     ks = std::min<int64_t>(ks, std::max<int64_t>(1, (2368 + ctas - 1) / ctas));
-    return ks > 1 ? align_up((size_t) ks * N * M * sizeof(float), 256) : 0;
+    const size_t splitk = ks > 1 ? align_up((size_t) ks * N * M * sizeof(float), 256) : 0;
+    // stream-K (one column chunk only): counters + three partial tiles of 128 rows x 64 columns for each of at most 3 CTAs per SM
+    const size_t streamk = N <= 64 ? streamk_counter_bytes(d.n_rt) + (size_t) sm_count() * 3 * 3 * (128 * 64 * sizeof(float)) : 0;
+    return std::max(splitk, streamk);
+}
+
+// Stream-K is taken when the product has a single column chunk, whole row groups, and dealing the iterations out beats
+// the best wave-quantised split.  With at least as many row groups as resident CTAs
+// the deal is even; with between half as many and as many, heads and tails (*head = block groups of a head, chosen so
+// that the CTAs sharing the tails are done two block groups before the heads).  Fewer row groups are left to the
+// cluster split.  B200_MMQ_STREAMK=0 turns it off, =2 takes it whenever it is legal.
+static int streamk_ctas(const MmqVariant &v, const TiledDims &d, const ActDims &a, int ks, bool cluster, size_t workspace_bytes, int *head) {
+    static int mode = -1;
+    if (mode < 0) {
+        const char *e = getenv("B200_MMQ_STREAMK");
+        mode = e ? atoi(e) : 1;
+    }
+    *head = 0;
+    if (mode == 0 || a.n_nt > v.cta_nt || d.n_rt % v.cta_tiles != 0) return 0;
+    const int64_t groups = d.n_rt / v.cta_tiles, total = groups * d.n_bg;
+    const int64_t slots = (int64_t) sm_count() * v.ctas_per_sm;
+    if (total >= (1ll << 31) || groups == slots) return 0;
+    if (workspace_bytes < streamk_counter_bytes(groups) + (size_t) slots * 3 * v.streamk_slot_bytes) return 0;
+    if (groups < slots) {
+        if (2 * groups < slots) return 0;
+        const int64_t gs = slots - groups;
+        const int64_t h = (total + 2 * gs + slots - 1) / slots;
+        if (h < 2 || h >= d.n_bg || groups * (d.n_bg - h) < gs) return 0;
+        *head = (int) h;
+    }
+    if (mode >= 2) return (int) slots;
+    // An SM works through its CTAs' block groups at about the same rate whether one or two CTAs are resident (measured:
+    // 1.07 us per block group alone, 1.85 us for one of each of two), so what counts is the block groups per SM: the
+    // fullest SM of the wave-quantised launch against the even share plus about eight block groups for the counter
+    // reset, the parked parts and the last read.
+    const int64_t sms = sm_count();
+    const int64_t per = (d.n_bg + ks - 1) / ks;
+    const int64_t now = (groups * ks + sms - 1) / sms * (per + 3);
+    const int64_t sk = (total + sms - 1) / sms + 8;
+    (void) cluster;
+    return sk < now ? (int) slots : 0;
 }
 
 void launch_mmq_reduce(const float *partial, int ks, int64_t M, int64_t N, float *dst, int64_t dst_nb_row, cudaStream_t st) {
@@ -628,6 +890,11 @@ int launch_mmq(int wtype, const TiledDims &d, const void *w, const ActDims &a, c
     const size_t per_split = (size_t) a.N * d.M * sizeof(float);
     if (ks > 1 && !cluster && (!workspace || workspace_bytes < per_split * ks)) {
         ks = workspace ? (int) std::max<size_t>(1, workspace_bytes / per_split) : 1;  // fewer splits fit: still correct, only slower
+    }
+    if (peers.n == 0 && workspace) {
+        int head = 0;
+        if (const int ctas = streamk_ctas(v, d, a, ks, cluster, workspace_bytes, &head))
+            return v.launch_streamk(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, workspace, ctas, head, canon ? 1 : 0, st);
     }
     if (int e = v.launch(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, (float *) workspace, ks, canon ? 1 : 0, cluster ? 1 : 0, peers, st)) return e;
     if (ks > 1 && !cluster) {
