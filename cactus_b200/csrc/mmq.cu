@@ -139,6 +139,9 @@ struct MmqCfg {
 // at a row group (a counter per row group) adds the parts in K order and writes the result, so the sum does not
 // depend on the arrival order and nobody waits for anybody.
 constexpr int MMQ_PLAIN = 0, MMQ_PEER = 1, MMQ_STREAMK = 2;
+#ifndef MMQ_DEPTH
+#define MMQ_DEPTH 2
+#endif
 template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB, int MODE = MMQ_PLAIN>
 __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims, const uint8_t *__restrict__ w, ActDims act,
                                                           const uint8_t *__restrict__ aq, float *__restrict__ dst,
@@ -312,9 +315,11 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
         constexpr int NP = NT / 2;
         constexpr int NSTEP = 4 * NP;
         uint32_t a0[MMQ_MT], a1[MMQ_MT], a2[MMQ_MT], a3[MMQ_MT];
+        // DEPTH steps are in flight: the MMAs of steps s+1 .. s+DEPTH-1 are issued before the epilogue of step s
+        constexpr int DEPTH = MMQ_DEPTH;
         uint64_t dwa[2][MMQ_MT], dwb[2][MMQ_MT];   // weight scales of the block of the step in flight / the step being finished
-        uint64_t p01[2][2][MMQ_MT], p23[2][2][MMQ_MT];
-        uint2 sc[2][2];                              // {d0, d1} of the two column tiles of a step (-d * 12582912 is recomputed: half the shared-memory traffic)
+        uint64_t p01[DEPTH][2][MMQ_MT], p23[DEPTH][2][MMQ_MT];
+        uint2 sc[DEPTH][2];                          // {d0, d1} of the two column tiles of a step (-d * 12582912 is recomputed: half the shared-memory traffic)
         auto start = [&](int step, int buf) {
             const int j = step / NP, np = step % NP;
             if (np == 0) {
@@ -368,11 +373,12 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
                 }
             }
         };
-        start(0, 0);
+#pragma unroll
+        for (int step = 0; step < DEPTH - 1; ++step) start(step, step % DEPTH);
 #pragma unroll
         for (int step = 0; step < NSTEP; ++step) {
-            if (step + 1 < NSTEP) start(step + 1, (step + 1) & 1);
-            finish(step, step & 1);
+            if (step + DEPTH - 1 < NSTEP) start(step + DEPTH - 1, (step + DEPTH - 1) % DEPTH);
+            finish(step, step % DEPTH);
         }
     };
     // write back; Q4_0 quants were used as 16 * value
