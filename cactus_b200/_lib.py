@@ -36,6 +36,8 @@ SIGNATURES = {
     "b200_mask_index_build": (_i32, [_vp, _i64, _i64, _i64, _vp, _sz, _vp]),
     "b200_flash_attn_ext_indexed": (_i32, [_i64, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp,
                                            _i64, _vp, _f32, _f32, _f32, _vp, _vp, _sz, _vp]),
+    "b200_flash_attn_ext_quant": (_i32, [_i64, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp,
+                                         _i64, _vp, _f32, _f32, _f32, _vp, _vp, _sz, _i32, _vp, _sz, _vp]),
     "b200_flash_attn_ext_parity": (_i32, [_i64, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp,
                                           _i64, _vp, _f32, _f32, _f32, _vp, _vp]),
     "b200_rms_norm": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _i64, _f32, _vp]),

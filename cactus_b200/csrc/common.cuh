@@ -218,4 +218,23 @@ __device__ __forceinline__ void q8_quantize_store(const float (&v)[4], uint8_t *
     q8_store<LAYOUT>(out, d_offset, nb, nbp, n, b, j, packed, d, real);
 }
 
+// the same for one value per lane: the 32 lanes of a (fully active) warp hold one block in element order
+template <int LAYOUT>
+__device__ __forceinline__ void q8_quantize_store_warp(float v, uint8_t *__restrict__ out, size_t d_offset, int64_t nb, int64_t nbp, int64_t n,
+                                                       int64_t b, bool real, int variant) {
+    float amax = fabsf(v);
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    __half d;
+    float id;
+    q8_scales(amax, variant, &d, &id);
+    const uint32_t q = (uint32_t) (q8_round(v, id, variant) & 0xff);
+    uint32_t packed = q;
+    packed |= __shfl_down_sync(0xffffffffu, q, 1) << 8;
+    packed |= __shfl_down_sync(0xffffffffu, q, 2) << 16;
+    packed |= __shfl_down_sync(0xffffffffu, q, 3) << 24;
+    const int lane = threadIdx.x & 31;
+    if ((lane & 3) == 0) q8_store<LAYOUT>(out, d_offset, nb, nbp, n, b, lane >> 2, packed, d, real);
+}
+
 }  // namespace b200

@@ -19,6 +19,9 @@
 
 namespace b200 {
 
+bool act_layout_canonical(int64_t N);   // quantize.cu: which B8 layout the mul_mat kernels expect for N columns
+
+
 constexpr int FA_THREADS = 128;
 #ifndef FA_MIN_CTAS
 #define FA_MIN_CTAS 3
@@ -100,7 +103,11 @@ struct FattnParams {
     const int32_t *wlist, *wcount;    // per token: indices of the non-empty words and their number (with words)
     float scale, max_bias, softcap, m0, m1;
     uint32_t n_head_log2;
-    float *dst;
+    float *dst;      // may be null when qout is given
+    uint8_t *qout;   // optional: the output rows quantised to Q8_0 in the B8 activation layout of the mul_mat that follows
+    size_t q_d_offset;
+    int64_t q_nb, q_nbp;
+    int q_canon, q_variant;
     float *partial;  // [Nq][H][nsplit][D + 2]
     int nsplit, hgroups;
     int w0;          // > 0: a token gets ceil(words / w0) KV splits (at most nsplit), so long sequences are cut, short ones are not;
@@ -139,7 +146,35 @@ __device__ __forceinline__ int fattn_target_words(const FattnParams &p, int ctas
     return (int) max(4ll, min(w, 0x7fffffffll));
 }
 
-template <int D>
+// Called by the 32 lanes of a warp with 32 consecutive elements of one output row: quantises them as one Q8_0 block of
+// column n.  A real call (not inlined): the attention kernel sits at its register limit and its main loop must not pay
+// for this code.
+__device__ __noinline__ void fattn_quant_block(uint8_t *qout, size_t d_offset, int64_t nb, int64_t nbp, int canon, int variant, int64_t n, int64_t b,
+                                               float val, bool real) {
+    if (canon) q8_quantize_store_warp<2>(val, qout, d_offset, nb, nbp, n, b, real, variant);
+    else q8_quantize_store_warp<1>(val, qout, d_offset, nb, nbp, n, b, real, variant);
+}
+
+// One output element; a warp calls this for 32 consecutive d of one (token, head).  With QUANT the row is also (or only)
+// stored as Q8_0 blocks -- quantize_row_q8_0 applied to the f32 value, bit for bit what the separate quantiser makes of
+// dst -- and the last token's warps zero the padding columns of its 8-column tile.
+template <int D, bool QUANT>
+__device__ __forceinline__ void fattn_store_out(const FattnParams &p, int64_t j, int64_t head, int d, float val) {
+    if (!QUANT) {
+        p.dst[(j * p.H + head) * D + d] = val;
+        return;
+    }
+    if (p.dst) p.dst[(j * p.H + head) * D + d] = val;
+    const int64_t b = (head * D + d) >> 5;
+    fattn_quant_block(p.qout, p.q_d_offset, p.q_nb, p.q_nbp, p.q_canon, p.q_variant, j, b, val, true);
+    if (j == p.Nq - 1) {
+        for (int64_t n = p.Nq; n < ((p.Nq + 7) & ~(int64_t) 7); ++n) fattn_quant_block(p.qout, p.q_d_offset, p.q_nb, p.q_nbp, p.q_canon, p.q_variant, n, b, 0.0f, false);
+    }
+}
+
+// QUANT: the instantiation behind b200_flash_attn_ext_quant; kept apart because this kernel sits at its register limit
+// and the plain one must not change with it
+template <int D, bool QUANT>
 __global__ void __launch_bounds__(FA_THREADS, FA_MIN_CTAS) fattn_mma_kernel(FattnParams p) {
     pdl_prologue();
     constexpr int KS = D / 16;   // k-steps of the S MMA
@@ -363,7 +398,7 @@ __global__ void __launch_bounds__(FA_THREADS, FA_MIN_CTAS) fattn_mma_kernel(Fatt
         }
         const int64_t head = h0 + h;
         if (ns_j == 1) {
-            p.dst[(j * p.H + head) * D + d] = a * (1.0f / ls);
+            fattn_store_out<D, QUANT>(p, j, head, d, a * (1.0f / ls));
         } else {
             float *pp = p.partial + ((j * p.H + head) * p.nsplit + split) * (D + 2);
             pp[d] = a;
@@ -454,11 +489,10 @@ __global__ void __launch_bounds__(128) fattn_parity_kernel(FattnParams p) {
     for (int i = 0; i < E; ++i) p.dst[row * D + lane + 32 * i] = __fmul_rn(__half2float(acc[i]), S_inv);
 }
 
-template <int D>
+template <int D, bool QUANT>
 __global__ void __launch_bounds__(D) fattn_combine_kernel(FattnParams p, int ctas_per_token) {
     pdl_prologue();
     const float *__restrict__ partial = p.partial;
-    float *__restrict__ dst = p.dst;
     int nsplit = p.nsplit;
     const int64_t row = blockIdx.x;  // token * H + head
     const int d = threadIdx.x;
@@ -478,7 +512,7 @@ __global__ void __launch_bounds__(D) fattn_combine_kernel(FattnParams p, int cta
         a += pp[s * (D + 2) + d] * sc;
         ls += pp[s * (D + 2) + D + 1] * sc;
     }
-    dst[row * D + d] = a * (1.0f / ls);
+    fattn_store_out<D, QUANT>(p, row / p.H, row % p.H, d, a * (1.0f / ls));
 }
 
 
@@ -575,10 +609,16 @@ static int flash_attn_impl(bool parity, int64_t D, int64_t H, int64_t Hkv, int64
                            int64_t q_nb_head, const void *k, int64_t k_nb_cell, int64_t k_nb_head, const void *v,
                            int64_t v_nb_cell, int64_t v_nb_head, const void *mask, int64_t mask_nb_row, const void *index,
                            float scale, float max_bias, float logit_softcap, float *dst, void *scratch, size_t scratch_bytes,
-                           b200_stream_t stream) {
+                           b200_stream_t stream, void *act = nullptr, size_t act_bytes = 0, int variant = B200_Q8_AVX2) {
     B200_REQUIRE(D == 64 || D == 128, "head size %lld not supported (64 or 128)", (long long) D);
     B200_REQUIRE(H > 0 && Hkv > 0 && H % Hkv == 0 && Nq > 0 && n_kv > 0, "bad attention shape");
-    B200_REQUIRE(q && k && v && dst, "null pointer");
+    B200_REQUIRE(q && k && v && (dst || act), "null pointer");
+    if (act) {
+        B200_REQUIRE(!parity && (H * D) % 128 == 0, "quantised output needs H * D to be a multiple of 128");
+        B200_REQUIRE(variant == B200_Q8_AVX2 || variant == B200_Q8_SCALAR, "unknown quantiser variant %d", variant);
+        B200_REQUIRE(is_aligned(act, 256), "activation scratch must be 256-byte aligned");
+        if (act_bytes < act_dims(H * D, Nq).total_bytes) return set_error(B200_E_SCRATCH, "activation scratch too small: %zu < %zu", act_bytes, act_dims(H * D, Nq).total_bytes);
+    }
     B200_REQUIRE((mask == nullptr) == (index == nullptr), "mask and mask index must be given together");
     B200_REQUIRE(is_aligned(q, 4) && q_nb_tok % 4 == 0 && q_nb_head % 4 == 0, "misaligned q");
     B200_REQUIRE(is_aligned(k, 16) && k_nb_cell % 16 == 0 && k_nb_head % 16 == 0, "k rows must be 16-byte aligned");
@@ -611,6 +651,9 @@ static int flash_attn_impl(bool parity, int64_t D, int64_t H, int64_t Hkv, int64
     p.m0 = powf(2.0f, -(max_bias) / p.n_head_log2);
     p.m1 = powf(2.0f, -(max_bias / 2.0f) / p.n_head_log2);
     p.dst = dst; p.partial = (float *) scratch; p.nsplit = ns; p.hgroups = hgroups; p.w0 = w0;
+    const ActDims ad = act_dims(H * D, Nq);
+    p.qout = (uint8_t *) act; p.q_d_offset = ad.d_offset; p.q_nb = ad.nb; p.q_nbp = ad.nbp;
+    p.q_canon = act_layout_canonical(Nq) ? 1 : 0; p.q_variant = variant;
     p.order = index ? (const int32_t *) ((const char *) index + index_order_offset(Nq, p.nw)) : nullptr;
     p.plan = index ? (const int32_t *) ((const char *) index + index_plan_offset(Nq, p.nw)) : nullptr;
     p.slots = FA_MIN_CTAS * fa_sm_count();
@@ -624,12 +667,25 @@ static int flash_attn_impl(bool parity, int64_t D, int64_t H, int64_t Hkv, int64
         return check_launch("fattn_parity");
     }
     dim3 grid((unsigned) (Hkv * hgroups), (unsigned) Nq, (unsigned) ns);
-    if (D == 128) launch_pdl(fattn_mma_kernel<128>, grid, dim3(FA_THREADS), 0, st, p);
-    else launch_pdl(fattn_mma_kernel<64>, grid, dim3(FA_THREADS), 0, st, p);
+    const bool qo = act != nullptr;
+    if (D == 128) {
+        if (qo) launch_pdl(fattn_mma_kernel<128, true>, grid, dim3(FA_THREADS), 0, st, p);
+        else launch_pdl(fattn_mma_kernel<128, false>, grid, dim3(FA_THREADS), 0, st, p);
+    } else {
+        if (qo) launch_pdl(fattn_mma_kernel<64, true>, grid, dim3(FA_THREADS), 0, st, p);
+        else launch_pdl(fattn_mma_kernel<64, false>, grid, dim3(FA_THREADS), 0, st, p);
+    }
     if (int e = check_launch("fattn_mma")) return e;
     if (ns > 1) {
-        if (D == 128) launch_pdl(fattn_combine_kernel<128>, dim3((unsigned) (Nq * H)), dim3(128), 0, st, p, (int) (Hkv * hgroups));
-        else launch_pdl(fattn_combine_kernel<64>, dim3((unsigned) (Nq * H)), dim3(64), 0, st, p, (int) (Hkv * hgroups));
+        const dim3 cgrid((unsigned) (Nq * H));
+        const int cpt = (int) (Hkv * hgroups);
+        if (D == 128) {
+            if (qo) launch_pdl(fattn_combine_kernel<128, true>, cgrid, dim3(128), 0, st, p, cpt);
+            else launch_pdl(fattn_combine_kernel<128, false>, cgrid, dim3(128), 0, st, p, cpt);
+        } else {
+            if (qo) launch_pdl(fattn_combine_kernel<64, true>, cgrid, dim3(64), 0, st, p, cpt);
+            else launch_pdl(fattn_combine_kernel<64, false>, cgrid, dim3(64), 0, st, p, cpt);
+        }
         return check_launch("fattn_combine");
     }
     return B200_OK;
@@ -642,6 +698,16 @@ int b200_flash_attn_ext_indexed(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, i
                                 b200_stream_t stream) {
     return flash_attn_impl(false, D, H, Hkv, Nq, n_kv, q, q_nb_tok, q_nb_head, k, k_nb_cell, k_nb_head, v, v_nb_cell, v_nb_head, mask, mask_nb_row,
                            index, scale, max_bias, logit_softcap, dst, scratch, scratch_bytes, stream);
+}
+
+int b200_flash_attn_ext_quant(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, int64_t n_kv, const float *q, int64_t q_nb_tok,
+                              int64_t q_nb_head, const void *k, int64_t k_nb_cell, int64_t k_nb_head, const void *v,
+                              int64_t v_nb_cell, int64_t v_nb_head, const void *mask, int64_t mask_nb_row, const void *index,
+                              float scale, float max_bias, float logit_softcap, float *dst, void *act, size_t act_bytes, int variant,
+                              void *scratch, size_t scratch_bytes, b200_stream_t stream) {
+    B200_REQUIRE(act, "null activation scratch");
+    return flash_attn_impl(false, D, H, Hkv, Nq, n_kv, q, q_nb_tok, q_nb_head, k, k_nb_cell, k_nb_head, v, v_nb_cell, v_nb_head, mask, mask_nb_row,
+                           index, scale, max_bias, logit_softcap, dst, scratch, scratch_bytes, stream, act, act_bytes, variant);
 }
 
 int b200_flash_attn_ext_parity(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, int64_t n_kv, const float *q, int64_t q_nb_tok,

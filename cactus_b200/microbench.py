@@ -95,10 +95,16 @@ def bench_fattn(a):
     check(L.b200_mask_index_build(mask.data_ptr(), n_cells * 2, a.seqs, n_cells, index.data_ptr(), index.numel(), st))
     scratch = torch.empty(max(256, L.b200_flash_attn_scratch_bytes(D, H, Hkv, a.seqs, n_cells)), dtype=torch.uint8, device="cuda")
     out = torch.empty((a.seqs, H * D), device="cuda")
+    act = torch.empty(L.b200_act_bytes(H * D, a.seqs), dtype=torch.uint8, device="cuda")
 
     def run():
         st = torch.cuda.current_stream().cuda_stream
         for k, v in zip(ks, vs):
+            if a.quant:   # the output left as the quantised activations of the next mul_mat only
+                check(L.b200_flash_attn_ext_quant(D, H, Hkv, a.seqs, n_cells, q.data_ptr(), H * D * 4, D * 4, k.data_ptr(), Hkv * D * 2, D * 2,
+                                                  v.data_ptr(), Hkv * D * 2, D * 2, mask.data_ptr(), n_cells * 2, index.data_ptr(),
+                                                  D ** -0.5, 0.0, 0.0, None, act.data_ptr(), act.numel(), 0, scratch.data_ptr(), scratch.numel(), st))
+                continue
             check(L.b200_flash_attn_ext_indexed(D, H, Hkv, a.seqs, n_cells, q.data_ptr(), H * D * 4, D * 4, k.data_ptr(), Hkv * D * 2, D * 2,
                                                 v.data_ptr(), Hkv * D * 2, D * 2, mask.data_ptr(), n_cells * 2, index.data_ptr(),
                                                 D ** -0.5, 0.0, 0.0, out.data_ptr(), scratch.data_ptr(), scratch.numel(), st))
@@ -133,6 +139,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["mul_mat", "fattn", "quantize"])
     ap.add_argument("--ragged", action="store_true", help="fattn: the benchmark's ragged sequence lengths instead of --seqs x --ctx")
+    ap.add_argument("--quant", action="store_true", help="fattn: b200_flash_attn_ext_quant (quantised output only)")
     ap.add_argument("--K", type=int, default=4096)
     ap.add_argument("--M", type=int, default=14336)
     ap.add_argument("--N", type=int, default=64)

@@ -169,6 +169,20 @@ B200_API int b200_flash_attn_ext_indexed(int64_t D, int64_t H, int64_t Hkv, int6
                                          const void *mask, int64_t mask_nb_row, const void *index,
                                          float scale, float max_bias, float logit_softcap,
                                          float *dst, void *scratch, size_t scratch_bytes, b200_stream_t stream);
+/* b200_flash_attn_ext_indexed whose result is (also) left as the Q8_0-quantised activations of the mul_mat that
+ * consumes it (attention output -> wo in llm_build_llama, cactus/llama-model.cpp:4517-4671): what
+ * b200_quantize_activations(dst, ..., K = H * D, N = Nq, act, ...) would write, bit for bit, without the extra
+ * launch.  dst may be NULL when only the quantised form is wanted.  H * D must be a multiple of 128.  Measured on B200
+ * at 64 tokens x 32 heads x 128 over 57k cells it is slower than the two launches (70.5 us against 57.5 + 2.5: the
+ * attention kernel sits at its register limit), so it pays only where launches, not kernel time, are the cost. */
+B200_API int b200_flash_attn_ext_quant(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, int64_t n_kv,
+                                       const float *q, int64_t q_nb_tok, int64_t q_nb_head,
+                                       const void *k, int64_t k_nb_cell, int64_t k_nb_head,
+                                       const void *v, int64_t v_nb_cell, int64_t v_nb_head,
+                                       const void *mask, int64_t mask_nb_row, const void *index,
+                                       float scale, float max_bias, float logit_softcap,
+                                       float *dst, void *act, size_t act_bytes, int variant,
+                                       void *scratch, size_t scratch_bytes, b200_stream_t stream);
 /* Validation variant: one warp per (token, head) walks the unmasked cells in ascending order with the
  * reference's exact sequence of roundings (fp16 Q, the AVX2 lane order of the K.Q dot, the fp16 output
  * accumulator of cactus/ggml-cpu/ops.cpp:7103-7117).  Slow; it exists to show that the distance between the

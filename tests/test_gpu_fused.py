@@ -99,3 +99,39 @@ def test_rope_store(T):
     assert torch.equal(qa.view(torch.int32), qb.view(torch.int32))
     assert torch.equal(kca.view(torch.int16), kcb.view(torch.int16))
     assert torch.equal(vca.view(torch.int16), vcb.view(torch.int16))
+
+
+@pytest.mark.parametrize("Nq,n_kv,H,Hkv,D", [(13, 1024, 8, 2, 128),     # ragged tokens, padding columns, one KV split
+                                            (64, 2048, 32, 8, 128),    # the decode batch shape
+                                            (2, 16384, 8, 2, 128),     # few tokens over a long cache: several KV splits + combine kernel
+                                            (9, 512, 4, 4, 64)])       # head size 64, no grouping
+def test_flash_attn_quantised_output(Nq, n_kv, H, Hkv, D):
+    """b200_flash_attn_ext_quant leaves exactly what the attention followed by the activation quantiser leaves."""
+    from cactus_b200._lib import check, lib
+    L = lib()
+    g = torch.Generator(device="cuda").manual_seed(Nq * 7 + n_kv)
+    q = torch.randn((Nq, H, D), device="cuda", generator=g)
+    k = torch.randn((n_kv, Hkv, D), device="cuda", generator=g).half()
+    v = torch.randn((n_kv, Hkv, D), device="cuda", generator=g).half()
+    # every token sees its own random prefix of the cache
+    lens = torch.randint(1, n_kv + 1, (Nq,), device="cuda", generator=g)
+    mask = torch.full((Nq, n_kv), float("-inf"), dtype=torch.float16, device="cuda")
+    mask[torch.arange(n_kv, device="cuda")[None, :] < lens[:, None]] = 0
+    index = torch.empty(L.b200_mask_index_bytes(Nq, n_kv), dtype=torch.uint8, device="cuda")
+    check(L.b200_mask_index_build(mask.data_ptr(), n_kv * 2, Nq, n_kv, index.data_ptr(), index.numel(), _st()))
+    scratch = torch.empty(max(256, L.b200_flash_attn_scratch_bytes(D, H, Hkv, Nq, n_kv)), dtype=torch.uint8, device="cuda")
+    args = (D, H, Hkv, Nq, n_kv, q.data_ptr(), H * D * 4, D * 4, k.data_ptr(), Hkv * D * 2, D * 2, v.data_ptr(), Hkv * D * 2, D * 2,
+            mask.data_ptr(), n_kv * 2, index.data_ptr(), D ** -0.5, 0.0, 0.0)
+    out = torch.empty((Nq, H * D), device="cuda")
+    check(L.b200_flash_attn_ext_indexed(*args, out.data_ptr(), scratch.data_ptr(), scratch.numel(), _st()))
+    sa, sb = _scratch(L, H * D, Nq)
+    check(L.b200_quantize_activations(out.data_ptr(), H * D * 4, H * D, Nq, sa.data_ptr(), sa.numel(), 0, _st()))
+    out2 = torch.empty_like(out)
+    check(L.b200_flash_attn_ext_quant(*args, out2.data_ptr(), sb.data_ptr(), sb.numel(), 0, scratch.data_ptr(), scratch.numel(), _st()))
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int32), out2.view(torch.int32))
+    assert torch.equal(sa, sb)
+    sb.fill_(0xAB)
+    check(L.b200_flash_attn_ext_quant(*args, None, sb.data_ptr(), sb.numel(), 0, scratch.data_ptr(), scratch.numel(), _st()))
+    torch.cuda.synchronize()
+    assert torch.equal(sa, sb)
