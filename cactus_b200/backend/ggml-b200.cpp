@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -289,6 +290,164 @@ bool buft_is_b200(lm_ggml_backend_buffer_type_t buft) { return buft && buft->ifa
 bool buft_is_b200_host(lm_ggml_backend_buffer_type_t buft) { return buft && buft->iface.get_name == host_buft_get_name; }
 
 // ---------------------------------------------------------------------------------------------
+// split buffer type: the rows of a quantised weight matrix spread over the devices
+// (lm_ggml_backend_split_buffer_type_t, cactus/ggml-backend.h:188; the loader asks for it by name for
+// LLAMA_SPLIT_MODE_ROW, cactus/llama-model.cpp:333-356).  Device i holds rows [row0[i], row0[i+1]) as a T16 weight of
+// its own; MUL_MAT on the main device's backend lets every device multiply its rows and store them straight into the
+// main device's dst over NVLink (compute_mul_mat_split).  Nothing else can read such a tensor: supports_op says so
+// and the loader then takes the next buffer type of its list (cactus/llama-model.cpp:262-275).
+// ---------------------------------------------------------------------------------------------
+struct b200_split_buft_ctx {
+    int main_device;
+    int n_dev;
+    float cum[LM_GGML_B200_MAX_DEVICES + 1];   // cumulative share of the rows: device i owns [cum[i], cum[i+1])
+    std::string name;
+};
+
+struct b200_split_tensor {   // tensor->extra of a tensor in a split buffer
+    int n_dev = 0;
+    int64_t row0[LM_GGML_B200_MAX_DEVICES + 1] = {0};
+    void * data[LM_GGML_B200_MAX_DEVICES] = {nullptr};
+};
+
+struct b200_split_buffer_ctx {
+    std::vector<b200_split_tensor *> tensors;
+    ~b200_split_buffer_ctx() {
+        for (b200_split_tensor * t : tensors) {
+            for (int i = 0; i < t->n_dev; ++i) {
+                if (!t->data[i]) continue;
+                device_guard g(i);
+                cudaFree(t->data[i]);
+            }
+            delete t;
+        }
+    }
+};
+
+// rows of device i: cut on multiples of 128 rows (the row group of the tensor-core kernel), the last device takes the rest
+void split_rows(const b200_split_buft_ctx * bc, int64_t M, int64_t * row0) {
+    row0[0] = 0;
+    for (int i = 1; i < bc->n_dev; ++i) {
+        int64_t r = (int64_t) ((double) M * bc->cum[i]) / 128 * 128;
+        row0[i] = std::min(M, std::max(r, row0[i - 1]));
+    }
+    row0[bc->n_dev] = M;
+}
+
+const char * split_buft_get_name(lm_ggml_backend_buffer_type_t buft) { return ((b200_split_buft_ctx *) buft->context)->name.c_str(); }
+bool buft_is_b200_split(lm_ggml_backend_buffer_type_t buft) { return buft && buft->iface.get_name == split_buft_get_name; }
+
+void split_buffer_free(lm_ggml_backend_buffer_t buffer) { delete (b200_split_buffer_ctx *) buffer->context; }
+void * split_buffer_get_base(lm_ggml_backend_buffer_t) { return (void *) 0x1000; }   // never dereferenced: the data hangs off tensor->extra
+
+lm_ggml_status split_buffer_init_tensor(lm_ggml_backend_buffer_t buffer, lm_ggml_tensor * tensor) {
+    LM_GGML_ASSERT(tensor->view_src == nullptr && "views of split tensors are not supported");
+    LM_GGML_ASSERT(is_tiled_type(tensor->type) && tensor->ne[0] % 32 == 0 && tensor->ne[2] == 1 && tensor->ne[3] == 1);
+    b200_split_buffer_ctx * ctx = (b200_split_buffer_ctx *) buffer->context;
+    const b200_split_buft_ctx * bc = (const b200_split_buft_ctx *) buffer->buft->context;
+    b200_split_tensor * st = new b200_split_tensor;
+    st->n_dev = bc->n_dev;
+    split_rows(bc, tensor->ne[1], st->row0);
+    ctx->tensors.push_back(st);
+    for (int i = 0; i < bc->n_dev; ++i) {
+        const int64_t rows = st->row0[i + 1] - st->row0[i];
+        if (rows <= 0) continue;
+        device_guard g(i);
+        const size_t bytes = b200_weight_bytes(tensor->type, tensor->ne[0], rows);
+        if (!cuda_ok(cudaMalloc(&st->data[i], bytes), "cudaMalloc(split weight)")) return LM_GGML_STATUS_ALLOC_FAILED;
+    }
+    tensor->extra = st;
+    return LM_GGML_STATUS_SUCCESS;
+}
+
+// host block stream <-> the per-device T16 weights, staged through a bounce buffer on each device
+bool split_transfer(const lm_ggml_tensor * tensor, void * host, bool to_device) {
+    const b200_split_tensor * st = (const b200_split_tensor *) tensor->extra;
+    const int64_t K = tensor->ne[0];
+    const size_t rb = (size_t) (K / 32) * block_bytes(tensor->type);
+    const int64_t max_rows = std::max<int64_t>(16, (int64_t) (B200_STAGE_BYTES / rb) / 16 * 16);
+    for (int i = 0; i < st->n_dev; ++i) {
+        const int64_t Mi = st->row0[i + 1] - st->row0[i];
+        if (Mi <= 0) continue;
+        device_guard g(i);
+        void * stage = nullptr;
+        if (!cuda_ok(cudaMalloc(&stage, (size_t) std::min(Mi, max_rows) * rb), "cudaMalloc(stage)")) return false;
+        bool ok = true;
+        for (int64_t r = 0; r < Mi && ok; r += max_rows) {
+            const int64_t rows = std::min(max_rows, Mi - r);
+            uint8_t * hp = (uint8_t *) host + (size_t) (st->row0[i] + r) * rb;
+            if (to_device) {
+                ok = cuda_ok(cudaMemcpy(stage, hp, (size_t) rows * rb, cudaMemcpyHostToDevice), "cudaMemcpy H2D") &&
+                     b200_weight_upload(tensor->type, K, Mi, stage, st->data[i], r, rows, nullptr) == B200_OK &&
+                     cuda_ok(cudaStreamSynchronize(nullptr), "sync after upload");
+            } else {
+                ok = b200_weight_download(tensor->type, K, Mi, st->data[i], stage, r, rows, nullptr) == B200_OK &&
+                     cuda_ok(cudaMemcpy(hp, stage, (size_t) rows * rb, cudaMemcpyDeviceToHost), "cudaMemcpy D2H");
+            }
+        }
+        cudaFree(stage);
+        if (!ok) {
+            B200_LOG_ERROR("ggml-b200: split tensor %s transfer on device %d failed: %s\n", tensor->name, i, b200_last_error());
+            return false;
+        }
+    }
+    return true;
+}
+
+void split_buffer_set_tensor(lm_ggml_backend_buffer_t, lm_ggml_tensor * tensor, const void * data, size_t offset, size_t size) {
+    // whole tensors only, as the loader writes them (cactus/llama-model-loader.cpp:1034)
+    LM_GGML_ASSERT(offset == 0 && size == lm_ggml_nbytes(tensor));
+    LM_GGML_ASSERT(split_transfer(tensor, const_cast<void *>(data), true));
+}
+
+void split_buffer_get_tensor(lm_ggml_backend_buffer_t, const lm_ggml_tensor * tensor, void * data, size_t offset, size_t size) {
+    LM_GGML_ASSERT(offset == 0 && size == lm_ggml_nbytes(tensor));
+    LM_GGML_ASSERT(split_transfer(tensor, data, false));
+}
+
+void split_buffer_clear(lm_ggml_backend_buffer_t, uint8_t) {}
+
+const lm_ggml_backend_buffer_i b200_split_buffer_iface = {
+    /* .free_buffer   = */ split_buffer_free,
+    /* .get_base      = */ split_buffer_get_base,
+    /* .init_tensor   = */ split_buffer_init_tensor,
+    /* .memset_tensor = */ nullptr,
+    /* .set_tensor    = */ split_buffer_set_tensor,
+    /* .get_tensor    = */ split_buffer_get_tensor,
+    /* .cpy_tensor    = */ nullptr,
+    /* .clear         = */ split_buffer_clear,
+    /* .reset         = */ nullptr,
+};
+
+lm_ggml_backend_buffer_t split_buft_alloc_buffer(lm_ggml_backend_buffer_type_t buft, size_t size) {
+    // the device memory is allocated tensor by tensor in init_tensor, where the row ranges are known
+    return lm_ggml_backend_buffer_init(buft, b200_split_buffer_iface, new b200_split_buffer_ctx, size);
+}
+
+size_t split_buft_get_alloc_size(lm_ggml_backend_buffer_type_t buft, const lm_ggml_tensor * tensor) {
+    size_t total = lm_ggml_nbytes(tensor);
+    if (is_tiled_type(tensor->type) && tensor->ne[0] % 32 == 0) {
+        const b200_split_buft_ctx * bc = (const b200_split_buft_ctx *) buft->context;
+        int64_t row0[LM_GGML_B200_MAX_DEVICES + 1];
+        split_rows(bc, tensor->ne[1], row0);
+        size_t sum = 0;
+        for (int i = 0; i < bc->n_dev; ++i)
+            if (row0[i + 1] > row0[i]) sum += b200_weight_bytes(tensor->type, tensor->ne[0], row0[i + 1] - row0[i]);
+        total = std::max(total, sum);
+    }
+    return total;
+}
+
+const lm_ggml_backend_buffer_type_i b200_split_buft_iface = {
+    /* .get_name       = */ split_buft_get_name,
+    /* .alloc_buffer   = */ split_buft_alloc_buffer,
+    /* .get_alignment  = */ buft_get_alignment,
+    /* .get_max_size   = */ nullptr,
+    /* .get_alloc_size = */ split_buft_get_alloc_size,
+    /* .is_host        = */ buft_is_host,
+};
+
+// ---------------------------------------------------------------------------------------------
 // backend (one CUDA stream) and its scratch memory
 // ---------------------------------------------------------------------------------------------
 struct scratch_buf {
@@ -318,11 +477,23 @@ struct scratch_buf {
     }
 };
 
+// what a backend keeps on another device for MUL_MAT on split weights: a stream there, the copy of the quantised
+// activations, the kernel workspace, and the event the main stream waits for
+struct split_peer {
+    bool ready = false;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t done = nullptr;
+    scratch_buf act, workspace;
+    const lm_ggml_tensor * act_src = nullptr;
+};
+
 struct b200_backend_ctx {
     int device;
     std::string name;
     cudaStream_t stream = nullptr;
     scratch_buf act, workspace, fa_scratch, mask_index;
+    split_peer peers[LM_GGML_B200_MAX_DEVICES];
+    cudaEvent_t ev_act = nullptr;   // recorded on `stream` when the quantised activations are ready
     // what the scratch currently holds, valid inside one graph_compute
     const lm_ggml_tensor * act_src = nullptr;
     const lm_ggml_tensor * index_mask = nullptr;
@@ -353,7 +524,18 @@ void backend_free(lm_ggml_backend_t backend) {
         ctx->mask_index.release();
         if (ctx->ev0) cudaEventDestroy(ctx->ev0);
         if (ctx->ev1) cudaEventDestroy(ctx->ev1);
+        if (ctx->ev_act) cudaEventDestroy(ctx->ev_act);
         cudaStreamDestroy(ctx->stream);
+    }
+    for (int i = 0; i < LM_GGML_B200_MAX_DEVICES; ++i) {
+        split_peer & p = ctx->peers[i];
+        if (!p.ready) continue;
+        device_guard g(i);
+        cudaStreamSynchronize(p.stream);
+        p.act.release();
+        p.workspace.release();
+        cudaEventDestroy(p.done);
+        cudaStreamDestroy(p.stream);
     }
     delete ctx;
     delete backend;
@@ -432,9 +614,16 @@ bool weight_ok(const lm_ggml_tensor * w) {
            w->buffer && buft_is_b200(w->buffer->buft);
 }
 
+// a weight in a split buffer: usable by MUL_MAT only (the probe of the loader hangs a dummy buffer of the split type on
+// the tensor, cactus/llama-model.cpp:246-251, so only the buffer type may be looked at here)
+bool split_weight_ok(const lm_ggml_tensor * w) {
+    return w && is_tiled_type(w->type) && w->view_src == nullptr && w->ne[2] == 1 && w->ne[3] == 1 && w->ne[0] % 32 == 0 &&
+           w->buffer && buft_is_b200_split(w->buffer->buft);
+}
+
 bool supports_mul_mat(const lm_ggml_tensor * op) {
     const lm_ggml_tensor * a = op->src[0], * b = op->src[1];
-    if (!weight_ok(a) || !b) return false;
+    if ((!weight_ok(a) && !split_weight_ok(a)) || !b) return false;
     if (!f32_rows(b) || b->ne[0] != a->ne[0] || !rows_collapsible(b)) return false;
     return op->type == LM_GGML_TYPE_F32 && lm_ggml_is_contiguous(op);
 }
@@ -569,11 +758,94 @@ lm_ggml_status compute_cpy(b200_backend_ctx * ctx, const lm_ggml_tensor * node, 
     return LM_GGML_STATUS_SUCCESS;
 }
 
+// MUL_MAT with the weight rows spread over the devices (split buffer).  The activations are quantised once on this
+// backend's device; every other device gets a copy over NVLink, multiplies its rows and stores them straight into
+// this device's dst (plain peer stores from the kernel's write-back: dst columns [row0[i], row0[i+1]) of every
+// activation row), all in stream order: the peers wait for the event behind the quantiser, this stream waits for
+// theirs.  Only this device needs the result -- the next node runs here (cactus/llama-model.cpp:342-351 makes the
+// layer's device the main device of its split buffer).
+std::atomic<uint64_t> g_split_mul_mats{0};
+
+bool split_peer_init(b200_backend_ctx * ctx, int dev) {
+    split_peer & p = ctx->peers[dev];
+    if (p.ready) return true;
+    int can = 0;
+    cudaDeviceCanAccessPeer(&can, dev, ctx->device);
+    if (!can) {
+        B200_LOG_ERROR("ggml-b200: device %d cannot store into device %d: no peer access\n", dev, ctx->device);
+        return false;
+    }
+    device_guard g(dev);
+    cudaError_t e = cudaDeviceEnablePeerAccess(ctx->device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        cudaGetLastError();
+        e = cudaSuccess;
+    }
+    if (!cuda_ok(e, "cudaDeviceEnablePeerAccess")) return false;
+    if (!cuda_ok(cudaStreamCreateWithFlags(&p.stream, cudaStreamNonBlocking), "cudaStreamCreate(peer)")) return false;
+    if (!cuda_ok(cudaEventCreateWithFlags(&p.done, cudaEventDisableTiming), "cudaEventCreate(peer)")) return false;
+    p.ready = true;
+    return true;
+}
+
+lm_ggml_status compute_mul_mat_split(b200_backend_ctx * ctx, lm_ggml_tensor * node) {
+    const lm_ggml_tensor * s0 = node->src[0], * s1 = node->src[1];
+    const b200_split_tensor * sw = (const b200_split_tensor *) s0->extra;
+    LM_GGML_ASSERT(sw != nullptr);
+    cudaStream_t st = ctx->stream;
+    const int64_t K = s0->ne[0], N = s1->ne[1] * s1->ne[2] * s1->ne[3];
+    const size_t ab = b200_act_bytes(K, N);
+    if (ctx->act_src != s1) {
+        void * act = ctx->act.get(ab, st);
+        if (!act) return LM_GGML_STATUS_ALLOC_FAILED;
+        B200_CHECK(b200_quantize_activations((const float *) s1->data, s1->nb[1], K, N, act, ctx->act.bytes, ctx->q8_variant, st));
+        ctx->act_src = s1;
+        ctx->stats.act_quantized++;
+        for (split_peer & p : ctx->peers) p.act_src = nullptr;
+    }
+    if (!ctx->ev_act && !cuda_ok(cudaEventCreateWithFlags(&ctx->ev_act, cudaEventDisableTiming), "cudaEventCreate")) return LM_GGML_STATUS_FAILED;
+    if (!cuda_ok(cudaEventRecord(ctx->ev_act, st), "cudaEventRecord")) return LM_GGML_STATUS_FAILED;
+    bool waited[LM_GGML_B200_MAX_DEVICES] = {false};
+    for (int i = 0; i < sw->n_dev; ++i) {
+        const int64_t Mi = sw->row0[i + 1] - sw->row0[i];
+        if (Mi <= 0) continue;
+        float * dst = (float *) node->data + sw->row0[i];
+        const size_t wb = b200_mul_mat_workspace_bytes(s0->type, K, Mi, N);
+        if (i == ctx->device) {
+            void * ws = wb ? ctx->workspace.get(wb, st) : nullptr;
+            if (wb && !ws) return LM_GGML_STATUS_ALLOC_FAILED;
+            B200_CHECK(b200_mul_mat_q_prequant(s0->type, sw->data[i], K, Mi, ctx->act.ptr, N, dst, node->nb[1], ws, ws ? ctx->workspace.bytes : 0, st));
+            continue;
+        }
+        if (!split_peer_init(ctx, i)) return LM_GGML_STATUS_FAILED;
+        split_peer & p = ctx->peers[i];
+        device_guard g(i);
+        if (!cuda_ok(cudaStreamWaitEvent(p.stream, ctx->ev_act, 0), "cudaStreamWaitEvent")) return LM_GGML_STATUS_FAILED;
+        if (p.act_src != s1) {
+            void * act = p.act.get(ab, p.stream);
+            if (!act) return LM_GGML_STATUS_ALLOC_FAILED;
+            if (!cuda_ok(cudaMemcpyPeerAsync(act, i, ctx->act.ptr, ctx->device, ab, p.stream), "cudaMemcpyPeerAsync")) return LM_GGML_STATUS_FAILED;
+            p.act_src = s1;
+        }
+        void * ws = wb ? p.workspace.get(wb, p.stream) : nullptr;
+        if (wb && !ws) return LM_GGML_STATUS_ALLOC_FAILED;
+        B200_CHECK(b200_mul_mat_q_prequant(s0->type, sw->data[i], K, Mi, p.act.ptr, N, dst, node->nb[1], ws, ws ? p.workspace.bytes : 0, p.stream));
+        if (!cuda_ok(cudaEventRecord(p.done, p.stream), "cudaEventRecord")) return LM_GGML_STATUS_FAILED;
+        waited[i] = true;
+    }
+    for (int i = 0; i < sw->n_dev; ++i)
+        if (waited[i] && !cuda_ok(cudaStreamWaitEvent(st, ctx->peers[i].done, 0), "cudaStreamWaitEvent")) return LM_GGML_STATUS_FAILED;
+    ctx->stats.mul_mat++;
+    g_split_mul_mats.fetch_add(1, std::memory_order_relaxed);
+    return LM_GGML_STATUS_SUCCESS;
+}
+
 lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph * cgraph) {
     b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
     device_guard g(ctx->device);
     cudaStream_t st = ctx->stream;
     ctx->act_src = nullptr;
+    for (split_peer & p : ctx->peers) p.act_src = nullptr;
     ctx->index_mask = nullptr;
     ctx->stats.graphs++;
     if (ctx->timing) cudaEventRecord(ctx->ev0, st);
@@ -595,6 +867,11 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
         const lm_ggml_tensor * s0 = node->src[0], * s1 = node->src[1];
         switch (node->op) {
             case LM_GGML_OP_MUL_MAT: {
+                if (s0->buffer && buft_is_b200_split(s0->buffer->buft)) {
+                    const lm_ggml_status rc = compute_mul_mat_split(ctx, node);
+                    if (rc != LM_GGML_STATUS_SUCCESS) return rc;
+                    break;
+                }
                 const int64_t K = s0->ne[0], M = s0->ne[1], N = s1->ne[1] * s1->ne[2] * s1->ne[3];
                 const size_t ab = b200_act_bytes(K, N);
                 if (ctx->act_src != s1) {  // consecutive mul_mats on the same activations (wq/wk/wv, gate/up) quantise once
@@ -834,12 +1111,20 @@ bool dev_supports_op(lm_ggml_backend_dev_t dev, const lm_ggml_tensor * op) {
     for (int i = 0; i < LM_GGML_MAX_SRC; ++i) {
         const lm_ggml_tensor * s = op->src[i];
         if (s && s->buffer && buft_is_b200(s->buffer->buft) && ((b200_buft_ctx *) s->buffer->buft->context)->device != ctx->device) return false;
+        if (s && s->buffer && buft_is_b200_split(s->buffer->buft)) {
+            // a split tensor is the weight of a MUL_MAT on its main device and nothing else (norm weights, biases and the
+            // embedding table that the loader probes with MUL / ADD / GET_ROWS go to the next buffer type of its list)
+            if (op->op != LM_GGML_OP_MUL_MAT || i != 0) return false;
+            if (((b200_split_buft_ctx *) s->buffer->buft->context)->main_device != ctx->device) return false;
+        }
     }
     return b200_supports_op(op);
 }
 
 bool dev_supports_buft(lm_ggml_backend_dev_t dev, lm_ggml_backend_buffer_type_t buft) {
-    return buft_is_b200(buft) && ((b200_buft_ctx *) buft->context)->device == ((b200_device_ctx *) dev->context)->device;
+    const int device = ((b200_device_ctx *) dev->context)->device;
+    if (buft_is_b200_split(buft)) return ((b200_split_buft_ctx *) buft->context)->main_device == device;
+    return buft_is_b200(buft) && ((b200_buft_ctx *) buft->context)->device == device;
 }
 
 bool dev_offload_op(lm_ggml_backend_dev_t, const lm_ggml_tensor *) { return false; }
@@ -904,7 +1189,41 @@ lm_ggml_backend_feature * get_features(lm_ggml_backend_reg_t) {
     return features;
 }
 
+// lm_ggml_backend_split_buffer_type_t (cactus/ggml-backend.h:188): tensor_split holds one share per device, all zero
+// (or null) meaning equal shares.  One buffer type per distinct (main device, shares), never freed.
+lm_ggml_backend_buffer_type_t split_buffer_type(int main_device, const float * tensor_split) {
+    static std::mutex mu;
+    static std::vector<lm_ggml_backend_buffer_type *> made;
+    b200_registry * r = registry();
+    const int n = (int) r->devices.size();
+    if (main_device < 0 || main_device >= n) return nullptr;
+    float share[LM_GGML_B200_MAX_DEVICES], sum = 0.0f;
+    for (int i = 0; i < n; ++i) {
+        share[i] = tensor_split ? std::max(0.0f, tensor_split[i]) : 0.0f;
+        sum += share[i];
+    }
+    if (sum <= 0.0f) {
+        for (int i = 0; i < n; ++i) share[i] = 1.0f;
+        sum = (float) n;
+    }
+    float cum[LM_GGML_B200_MAX_DEVICES + 1] = {0.0f};
+    for (int i = 0; i < n; ++i) cum[i + 1] = cum[i] + share[i] / sum;
+    std::lock_guard<std::mutex> lock(mu);
+    for (lm_ggml_backend_buffer_type * t : made) {
+        const b200_split_buft_ctx * bc = (const b200_split_buft_ctx *) t->context;
+        if (bc->main_device == main_device && bc->n_dev == n && memcmp(bc->cum, cum, sizeof(float) * (n + 1)) == 0) return t;
+    }
+    b200_split_buft_ctx * bc = new b200_split_buft_ctx;
+    bc->main_device = main_device;
+    bc->n_dev = n;
+    memcpy(bc->cum, cum, sizeof(cum));
+    bc->name = std::string(LM_GGML_B200_NAME) + "_Split";
+    made.push_back(new lm_ggml_backend_buffer_type{b200_split_buft_iface, &r->devices[main_device], bc});
+    return made.back();
+}
+
 void * reg_get_proc_address(lm_ggml_backend_reg_t, const char * name) {
+    if (strcmp(name, "lm_ggml_backend_split_buffer_type") == 0) return (void *) split_buffer_type;
     if (strcmp(name, "lm_ggml_backend_set_abort_callback") == 0) return (void *) set_abort_callback;
     if (strcmp(name, "lm_ggml_backend_get_features") == 0) return (void *) get_features;
     if (strcmp(name, "lm_ggml_backend_b200_get_stats") == 0) return (void *) lm_ggml_backend_b200_get_stats;
@@ -987,6 +1306,8 @@ lm_ggml_backend_t lm_ggml_backend_b200_init(int device) {
     cudaEventCreate(&ctx->ev1);
     return new lm_ggml_backend{b200_guid(), b200_backend_iface, &r->devices[device], ctx};
 }
+
+uint64_t lm_ggml_backend_b200_split_mul_mat_count(void) { return g_split_mul_mats.load(); }
 
 void lm_ggml_backend_b200_get_stats(lm_ggml_backend_t backend, struct lm_ggml_b200_stats * out) {
     if (!lm_ggml_backend_is_b200(backend)) {

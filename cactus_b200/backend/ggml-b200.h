@@ -37,6 +37,8 @@ struct lm_ggml_b200_stats {
     double   device_ms;       // CUDA-event time of all graph_compute calls when timing is on (B200_TIMING=1)
 };
 LM_GGML_BACKEND_API void lm_ggml_backend_b200_get_stats(lm_ggml_backend_t backend, struct lm_ggml_b200_stats * out);
+// MUL_MAT nodes computed on weights of the split buffer type since the process started (all backends)
+LM_GGML_BACKEND_API uint64_t lm_ggml_backend_b200_split_mul_mat_count(void);
 
 #ifdef __cplusplus
 }

@@ -343,17 +343,29 @@ struct runner {
     int vocab = 0;
 };
 
+// split_row_gpus > 0: LLAMA_SPLIT_MODE_ROW over that many B200 devices (the loader then asks the plug-in for its split
+// buffer type by name, cactus/llama-model.cpp:333-356, and spreads the layers over the same devices)
+static int split_row_gpus = 0;
+
 static bool open_runner(runner & r, const std::string & path, bool gpu, const model_cfg & c, int n_seq, int n_threads) {
     llama_model_params mp = llama_model_default_params();
     static lm_ggml_backend_dev_t none[1] = { nullptr };
-    static lm_ggml_backend_dev_t devs[2] = { nullptr, nullptr };
+    static lm_ggml_backend_dev_t devs[LM_GGML_B200_MAX_DEVICES + 1] = { nullptr };
     static llama_model_tensor_buft_override ov[2];
     if (gpu) {
         devs[0] = lm_ggml_backend_reg_dev_get(lm_ggml_backend_b200_reg(), 0);
+        devs[1] = nullptr;
         mp.devices = devs;
         mp.n_gpu_layers = 999;
         mp.split_mode = LLAMA_SPLIT_MODE_NONE;
         mp.main_gpu = 0;
+        if (split_row_gpus > 0) {
+            const int have = (int) lm_ggml_backend_reg_dev_count(lm_ggml_backend_b200_reg());
+            const int n = std::min(split_row_gpus, have);
+            for (int i = 0; i < n; ++i) devs[i] = lm_ggml_backend_reg_dev_get(lm_ggml_backend_b200_reg(), i);
+            devs[n] = nullptr;
+            mp.split_mode = LLAMA_SPLIT_MODE_ROW;
+        }
         // the input layer is pinned to the CPU by the loader (cactus/llama-model.cpp:1517-1519); move the embedding table too
         ov[0] = { "token_embd\\.weight", lm_ggml_backend_b200_buffer_type(0) };
         ov[1] = { nullptr, nullptr };
@@ -432,6 +444,7 @@ static int run_model(int argc, char ** argv) {
         else if (a == "--skip-cpu") skip_cpu = true;
         else if (a == "--cpu-only") cpu_only = true;   // checks the GGUF writer and the driver without a GPU
         else if (a == "--path") path = argv[++i];
+        else if (a == "--split-row") split_row_gpus = val();
     }
     llama_log_set([](lm_ggml_log_level level, const char * text, void *) { if (level >= LM_GGML_LOG_LEVEL_ERROR) fputs(text, stderr); }, nullptr);
     if (!cpu_only) lm_ggml_backend_register(lm_ggml_backend_b200_reg());
@@ -507,8 +520,9 @@ static int run_model(int argc, char ** argv) {
         step_ms = (now_s() - t0) * 1e3 / bench_steps;
     }
     printf("{\"case\": \"model\", \"layers\": %d, \"d\": %d, \"seqs\": %d, \"decode_steps\": %d, \"rows\": %d, \"worst_rel\": %.3g, "
-           "\"rows_within_1e-3\": %.3f, \"greedy_agree\": %.3f, \"b200_step_ms\": %.3f}\n",
-           c.n_layer, c.d, n_seq, n_decode, total, worst, good_rows / sum_rows, (double) agree / total, step_ms);
+           "\"rows_within_1e-3\": %.3f, \"greedy_agree\": %.3f, \"b200_step_ms\": %.3f, \"split_mul_mats\": %llu}\n",
+           c.n_layer, c.d, n_seq, n_decode, total, worst, good_rows / sum_rows, (double) agree / total, step_ms,
+           (unsigned long long) (cpu_only ? 0 : lm_ggml_backend_b200_split_mul_mat_count()));
     if (cpu.ctx) llama_free(cpu.ctx);
     if (cpu.model) llama_model_free(cpu.model);
     if (gpu.ctx) llama_free(gpu.ctx);

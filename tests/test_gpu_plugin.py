@@ -71,3 +71,24 @@ def test_layer_ops_with_reference_order_attention():
         if r["tokens"] == 1:
             assert r["MUL_MAT"] < 1e-5 and r["FLASH_ATTN_EXT"] < 1e-5 and r["ADD"] < 1e-5, r
         assert r["FLASH_ATTN_EXT"] < 6e-4, r
+
+
+def _n_gpus():
+    import torch
+    return torch.cuda.device_count()
+
+
+@pytest.mark.parametrize("gpus", [1, 2])
+def test_row_split_buffer_type_through_llama_decode(gpus):
+    """LLAMA_SPLIT_MODE_ROW: the loader fetches "lm_ggml_backend_split_buffer_type" from the plug-in and puts the
+    mul_mat weights into it; their rows are spread over the devices and every MUL_MAT on them is computed by all
+    devices into the main device's result.  One device exercises the buffer type alone, two the peer stores."""
+    if _n_gpus() < gpus:
+        pytest.skip(f"needs {gpus} GPUs")
+    rc, lines, err = run("model", "--split-row", str(gpus), "--layers", "4", "--seqs", "5", "--max-prompt", "70", "--decode", "5")
+    assert lines, err
+    r = lines[-1]
+    assert "error" not in r, (r, err)
+    assert r["split_mul_mats"] > 0, r
+    assert r["greedy_agree"] >= 0.9 and r["worst_rel"] < 3e-2, r
+    assert rc == 0
