@@ -56,6 +56,9 @@ CASES = [(2, 28672, 4096, 64),    # the stacked gate/up weight of the 8B model: 
          (8, 19200, 2048, 33),    # Q8_0 weights
          (2, 4096, 4096, 64)]     # too few row groups: the cluster split, whatever the switch says
 
+# narrower column classes (16- and 32-column CTAs hold more CTAs per SM, so the deals differ) and the output head
+NARROW = [(2, 128256, 1024, 8), (2, 64000, 1024, 12), (2, 40064, 1024, 24), (2, 128256, 512, 3), (8, 51200, 512, 30)]
+
 
 def test_streamk_forced_vs_oracle():
     res = run_child(CASES, 2)
@@ -71,3 +74,12 @@ def test_streamk_default_choice():
     res = run_child([CASES[0], CASES[5]], 1)
     assert [r["launches"] for r in res] == [3, 2], res
     assert all(r["err"] < 1e-3 and r["same"] for r in res), res
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_streamk_narrow_column_classes(mode):
+    res = run_child(NARROW, mode)
+    for c, r in zip(NARROW, res):
+        assert r["err"] < 1e-3 and r["same"], (c, r, mode)
+    if mode == 2:
+        assert any(r["launches"] == 3 for r in res), res
