@@ -761,7 +761,7 @@ static const MmqVariant &pick_variant(int64_t N) {
         t[1][1] = make_variant<WTYPE, 4, 1, 1, 4>();
         t[1][2] = t[1][0]; t[1][3] = t[1][0];
         t[2][0] = make_variant<WTYPE, 8, 1, 2, 4, 4, 2>();   // 128 rows x 64 cols, a warp owns all 64 columns, 2 CTAs/SM
-        t[2][1] = make_variant<WTYPE, 4, 2, 4, 2, 4, 2>();   // 128 rows x 64 cols, 4 warps as 2 x 2, warp tile 64 x 32
+        t[2][1] = make_variant<WTYPE, 8, 1, 2, 4, 3, 3>();   // as [0] with 3 stages and 168 registers: 3 CTAs/SM
         t[2][2] = make_variant<WTYPE, 4, 2, 4, 1, 4, 3>();   //  64 rows x 64 cols, 2 warps, warp tile 64 x 32
         t[2][3] = make_variant<WTYPE, 4, 2, 2, 4, 3, 2>();   // 128 rows x 64 cols, 8 warps as 4 x 2, 3 stages
         ready[dev] = true;
