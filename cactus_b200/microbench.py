@@ -77,6 +77,8 @@ def bench_fattn(a):
     layers = a.copies
     ks = [torch.randn((n_cells, Hkv * D), device="cuda", generator=gen).half() for _ in range(layers)]
     vs = [torch.randn((n_cells, Hkv * D), device="cuda", generator=gen).half() for _ in range(layers)]
+    # --head-major: the same bytes addressed as [Hkv][cells][D] (a layout experiment: the reference's cache is cell-major)
+    nb_cell, nb_head = (D * 2, n_cells * D * 2) if a.head_major else (Hkv * D * 2, D * 2)
     q = torch.randn((a.seqs, H * D), device="cuda", generator=gen)
     ends = torch.cumsum(lens, 0)
     cells = torch.arange(n_cells, device="cuda")
@@ -101,12 +103,12 @@ def bench_fattn(a):
         st = torch.cuda.current_stream().cuda_stream
         for k, v in zip(ks, vs):
             if a.quant:   # the output left as the quantised activations of the next mul_mat only
-                check(L.b200_flash_attn_ext_quant(D, H, Hkv, a.seqs, n_cells, q.data_ptr(), H * D * 4, D * 4, k.data_ptr(), Hkv * D * 2, D * 2,
-                                                  v.data_ptr(), Hkv * D * 2, D * 2, mask.data_ptr(), n_cells * 2, index.data_ptr(),
+                check(L.b200_flash_attn_ext_quant(D, H, Hkv, a.seqs, n_cells, q.data_ptr(), H * D * 4, D * 4, k.data_ptr(), nb_cell, nb_head,
+                                                  v.data_ptr(), nb_cell, nb_head, mask.data_ptr(), n_cells * 2, index.data_ptr(),
                                                   D ** -0.5, 0.0, 0.0, None, act.data_ptr(), act.numel(), 0, scratch.data_ptr(), scratch.numel(), st))
                 continue
-            check(L.b200_flash_attn_ext_indexed(D, H, Hkv, a.seqs, n_cells, q.data_ptr(), H * D * 4, D * 4, k.data_ptr(), Hkv * D * 2, D * 2,
-                                                v.data_ptr(), Hkv * D * 2, D * 2, mask.data_ptr(), n_cells * 2, index.data_ptr(),
+            check(L.b200_flash_attn_ext_indexed(D, H, Hkv, a.seqs, n_cells, q.data_ptr(), H * D * 4, D * 4, k.data_ptr(), nb_cell, nb_head,
+                                                v.data_ptr(), nb_cell, nb_head, mask.data_ptr(), n_cells * 2, index.data_ptr(),
                                                 D ** -0.5, 0.0, 0.0, out.data_ptr(), scratch.data_ptr(), scratch.numel(), st))
         return layers
 
@@ -139,6 +141,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["mul_mat", "fattn", "quantize"])
     ap.add_argument("--ragged", action="store_true", help="fattn: the benchmark's ragged sequence lengths instead of --seqs x --ctx")
+    ap.add_argument("--head-major", action="store_true", help="fattn: address the cache as [Hkv][cells][D] instead of the reference's [cells][Hkv][D]")
     ap.add_argument("--quant", action="store_true", help="fattn: b200_flash_attn_ext_quant (quantised output only)")
     ap.add_argument("--K", type=int, default=4096)
     ap.add_argument("--M", type=int, default=14336)
