@@ -140,3 +140,24 @@ def test_permutation_property_full_size():
     ones = torch.ones_like(v)
     o = ops.flash_attn_ext(q, k, ones, mask, D ** -0.5)
     assert float((o - 1).abs().max()) < 1e-5
+
+
+@pytest.mark.parametrize("which", ["all", "one"])
+def test_mask_values_that_add_to_the_score(oracle, which):
+    """Finite non-zero mask values (what ALiBi-style or soft masks put there) are added to the scaled score exactly as
+    the reference does; the attention kernel skips reading a token's mask row only when every participating value of
+    that token is zero.  "one": a single token of the batch carries non-zero values, the others take the short cut."""
+    c = inputs.ragged_case(777, 128, 8, 2, 1024, [(300, 2), (150, 1), (64, 3)])
+    rng = np.random.default_rng(5)
+    mask = c["mask"].copy()
+    part = mask != 0xFC00
+    vals = rng.choice(np.array([0.0, -0.25, -1.0, -3.0], np.float16), size=mask.shape).view(np.uint16)
+    rows = slice(None) if which == "all" else slice(2, 3)
+    m2 = mask[rows]
+    m2[part[rows]] = vals[rows][part[rows]]
+    mask[rows] = m2
+    c = dict(c, mask=mask, max_bias=4.0)
+    truth = oracle.flash_attn_ext(c["q"], c["kc"], c["vc"], c["mask"], c["scale"], n_kv=c["n_kv"], max_bias=4.0, acc_mode=1)
+    got = run_case(c)
+    v = c["valid_rows"]
+    assert np.isfinite(got[v]).all() and rel_max_err(got[v], truth[v]) < 2e-5
