@@ -144,9 +144,9 @@ def test_permutation_property_full_size():
 
 @pytest.mark.parametrize("which", ["all", "one"])
 def test_mask_values_that_add_to_the_score(oracle, which):
-    """Finite non-zero mask values (what ALiBi-style or soft masks put there) are added to the scaled score exactly as
-    the reference does; the attention kernel skips reading a token's mask row only when every participating value of
-    that token is zero.  "one": a single token of the batch carries non-zero values, the others take the short cut."""
+    """Finite non-zero mask values (what ALiBi-style or soft masks put there) are added to the scaled score, times the
+    head's slope, exactly as the reference does (cactus/ggml-cpu/ops.cpp:7072-7090).  "one": a single token of the batch
+    carries non-zero values, the others the usual 0 / -inf."""
     c = inputs.ragged_case(777, 128, 8, 2, 1024, [(300, 2), (150, 1), (64, 3)])
     rng = np.random.default_rng(5)
     mask = c["mask"].copy()
