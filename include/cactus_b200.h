@@ -98,8 +98,9 @@ B200_API int b200_quantize_q8_0(const float *x, int64_t x_row_stride_bytes, int6
  *   dst      f32, N rows of M, row stride in bytes
  *   scratch  b200_mul_mat_scratch_bytes(wtype, K, M, N) bytes of device memory, 256-byte aligned,
  *            private to the call until it completes: the quantised activations (b200_act_bytes) followed
- *            by the split-K workspace (b200_mul_mat_workspace_bytes)
- * N <= 8 uses the HBM-bound dp4a kernel, larger N the int8 tensor-core kernel.
+ *            by the kernel workspace (b200_mul_mat_workspace_bytes: split-K partial sums or the parked tiles and
+ *            arrival counters of the stream-K work split)
+ * N <= 2 uses the HBM-bound dp4a kernel, larger N the int8 tensor-core kernel (B200_MMVQ_MAX_N moves the border up to 8).
  * ---------------------------------------------------------------------------------------------- */
 B200_API size_t b200_act_bytes(int64_t K, int64_t N);
 B200_API size_t b200_mul_mat_workspace_bytes(int wtype, int64_t K, int64_t M, int64_t N);
