@@ -66,6 +66,8 @@ SIGNATURES = {
     "b200_allgather_rows": (_i32, [_vp, _i64, _i64, _i64, _i32, _i32, C.POINTER(_vp), _i64, C.POINTER(_vp), _vp]),
     "b200_peer_status": (_i32, [_vp]),
     "b200_mul_mat_q_rowsplit": (_i32, [_i32, _vp, _i64, _i64, _vp, _i64, _i32, _i32, C.POINTER(_vp), _i64, _i64, _vp, _sz, C.POINTER(_vp), _vp]),
+    "b200_mul_mat_q_rowsplit_stacked": (_i32, [_i32, _vp, _i64, _i64, _vp, _i64, _i32, _i32, C.POINTER(_vp), _i64, _i32, C.POINTER(_i64), C.POINTER(_i64),
+                                               _vp, _sz, C.POINTER(_vp), _vp]),
 }
 
 _lib = None

@@ -59,11 +59,21 @@ static inline bool is_aligned(const void *p, size_t a) { return ((uintptr_t) p %
 // A mul_mat kernel stores every result value into its own dst and, when the weight is one row slice of a split, into
 // the same place of the other GPUs' output buffers (peer memory mapped through CUDA IPC): p[i] is the address in peer
 // i's buffer that corresponds to `dst`, the row stride is the same everywhere.
+// A stacked weight (the q, k, v rows -- or gate and up rows -- of one rank, one after the other) produces up to three
+// row ranges that belong at different columns of dst: rows from seg_end[i-1] on land seg_shift[i] bytes further than a
+// plain row-to-column mapping would put them (n_seg <= 1: no such ranges).  Ranges start on multiples of 16 rows.
 struct PeerDst {
     float *p[7];
     int n;
+    int n_seg;
+    int seg_end[2];
+    int64_t seg_shift[3];
 };
 #ifdef __CUDACC__
+__device__ __forceinline__ int64_t peer_row_shift(const PeerDst &peers, int64_t row) {
+    if (peers.n_seg <= 1 || row < peers.seg_end[0]) return 0;
+    return (peers.n_seg > 2 && row >= peers.seg_end[1]) ? peers.seg_shift[2] : peers.seg_shift[1];
+}
 __device__ __forceinline__ void store_f32(float *dst, const PeerDst &peers, int64_t byte_off, float v) {
     *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + byte_off) = v;
     for (int i = 0; i < peers.n; ++i) *reinterpret_cast<float *>(reinterpret_cast<char *>(peers.p[i]) + byte_off) = v;

@@ -551,7 +551,7 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
             const int c = (q4 * 4) / ROWS, r = (q4 * 4) % ROWS;
             const int64_t col = cta_nt0 * 8 + c, row = cta_rt0 * 16 + r;
             if (col < act.N) {
-                const int64_t off = col * dst_nb_row + row * 4;
+                const int64_t off = col * dst_nb_row + row * 4 + (MODE == MMQ_PEER ? peer_row_shift(peers, row) : 0);
                 const int n_peers = MODE == MMQ_PEER ? peers.n : 0;
                 for (int pi = -1; pi < n_peers; ++pi) {   // own buffer, then the other GPUs' of a row split
                     float *o = reinterpret_cast<float *>(reinterpret_cast<char *>(pi < 0 ? dst : peers.p[pi]) + off);
@@ -586,8 +586,9 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
                 if (row < dims.M) {
                     if (ksplit == 1) {
                         if (MODE == MMQ_PEER) {
-                            if (col < act.N) store_f32(dst, peers, col * dst_nb_row + row * 4, v0);
-                            if (col + 1 < act.N) store_f32(dst, peers, (col + 1) * dst_nb_row + row * 4, v1);
+                            const int64_t sh = peer_row_shift(peers, row);
+                            if (col < act.N) store_f32(dst, peers, col * dst_nb_row + row * 4 + sh, v0);
+                            if (col + 1 < act.N) store_f32(dst, peers, (col + 1) * dst_nb_row + row * 4 + sh, v1);
                         } else {
                             if (col < act.N) *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + col * dst_nb_row + row * 4) = v0;
                             if (col + 1 < act.N) *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + (col + 1) * dst_nb_row + row * 4) = v1;
@@ -611,7 +612,7 @@ __global__ void __launch_bounds__(256) mmq_reduce_kernel(const float *__restrict
     const int64_t n = gid / M, m = gid - n * M;
     float s = 0.0f;
     for (int k = 0; k < ksplit; ++k) s += partial[((int64_t) k * N + n) * M + m];
-    store_f32(dst, peers, n * dst_nb_row + m * 4, s);
+    store_f32(dst, peers, n * dst_nb_row + m * 4 + peer_row_shift(peers, m), s);
 }
 
 static int sm_count() {
@@ -664,7 +665,7 @@ static int launch_variant(const TiledDims &d, const uint8_t *w, const ActDims &a
                           float *partial, int ksplit, int canon, int cluster, const PeerDst &peers, cudaStream_t st) {
     using S = MmqCfg<WTYPE, NTW, WN, MT, WM, STAGES>;
     dim3 grid((unsigned) ((d.n_rt + S::CTA_TILES - 1) / S::CTA_TILES), (unsigned) ((a.n_nt + S::NT - 1) / S::NT), (unsigned) ksplit);
-    const bool peer = peers.n > 0;
+    const bool peer = peers.n > 0 || peers.n_seg > 1;
     if (!cluster) {
         if (peer) launch_pdl(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, MMQ_PEER>, grid, dim3(S::THREADS), S::TOTAL, st, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 0, peers);
         else launch_pdl(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, MMQ_PLAIN>, grid, dim3(S::THREADS), S::TOTAL, st, d, w, a, aq, dst, dst_nb_row, partial, ksplit, canon, 0, peers);
@@ -897,7 +898,7 @@ int launch_mmq(int wtype, const TiledDims &d, const void *w, const ActDims &a, c
     if (ks > 1 && !cluster && (!workspace || workspace_bytes < per_split * ks)) {
         ks = workspace ? (int) std::max<size_t>(1, workspace_bytes / per_split) : 1;  // fewer splits fit: still correct, only slower
     }
-    if (peers.n == 0 && workspace) {
+    if (peers.n == 0 && peers.n_seg <= 1 && workspace) {
         int head = 0;
         if (const int ctas = streamk_ctas(v, d, a, ks, cluster, workspace_bytes, &head))
             return v.launch_streamk(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, workspace, ctas, head, canon ? 1 : 0, st);

@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(MMVQ_WARPS * 32) mmvq_kernel(TiledDims dims, c
             float s = 0.0f;
 #pragma unroll
             for (int wv = 0; wv < MMVQ_WARPS; ++wv) s += red[wv][r][n];
-            store_f32(dst, peers, n * dst_nb_row + row * 4, s);
+            store_f32(dst, peers, n * dst_nb_row + row * 4 + peer_row_shift(peers, row), s);
         }
     }
 }

@@ -72,11 +72,41 @@ int b200_mul_mat_q_prequant(int wtype, const void *w, int64_t K, int64_t M, cons
     return mul_mat_prequant(wtype, w, K, M, act, N, dst, dst_row_stride_bytes, workspace, workspace_bytes, PeerDst{}, stream);
 }
 
+static int rowsplit_impl(int wtype, const void *w, int64_t K, int64_t M, const void *act, int64_t N, int rank, int g, void *const *dst_of_rank,
+                         int64_t dst_row_stride_bytes, int64_t first_column, PeerDst peers, void *workspace, size_t workspace_bytes,
+                         void *const *flags_of_rank, b200_stream_t stream);
+
 int b200_mul_mat_q_rowsplit(int wtype, const void *w, int64_t K, int64_t M, const void *act, int64_t N, int rank, int g, void *const *dst_of_rank,
                             int64_t dst_row_stride_bytes, int64_t first_column, void *workspace, size_t workspace_bytes,
                             void *const *flags_of_rank, b200_stream_t stream) {
-    B200_REQUIRE(dst_of_rank && flags_of_rank && g >= 1 && g <= 8 && rank >= 0 && rank < g && first_column >= 0, "bad row-split arguments");
+    return rowsplit_impl(wtype, w, K, M, act, N, rank, g, dst_of_rank, dst_row_stride_bytes, first_column, PeerDst{}, workspace, workspace_bytes,
+                         flags_of_rank, stream);
+}
+
+int b200_mul_mat_q_rowsplit_stacked(int wtype, const void *w, int64_t K, int64_t M, const void *act, int64_t N, int rank, int g,
+                                    void *const *dst_of_rank, int64_t dst_row_stride_bytes, int n_parts, const int64_t *part_rows,
+                                    const int64_t *part_first_column, void *workspace, size_t workspace_bytes, void *const *flags_of_rank,
+                                    b200_stream_t stream) {
+    B200_REQUIRE(n_parts >= 1 && n_parts <= 3 && part_rows && part_first_column, "a stacked weight has 1 to 3 parts");
     PeerDst peers = {};
+    peers.n_seg = n_parts;
+    int64_t row = 0;
+    for (int i = 0; i < n_parts; ++i) {
+        B200_REQUIRE(part_rows[i] > 0 && part_first_column[i] >= 0 && (i == n_parts - 1 || part_rows[i] % 16 == 0), "parts but the last hold a multiple of 16 rows");
+        // a plain mapping puts local row r at column part_first_column[0] + r
+        peers.seg_shift[i] = (part_first_column[i] - (part_first_column[0] + row)) * 4;
+        row += part_rows[i];
+        if (i < 2) peers.seg_end[i] = (int) row;
+    }
+    B200_REQUIRE(row == M, "the parts hold %lld rows, the weight %lld", (long long) row, (long long) M);
+    return rowsplit_impl(wtype, w, K, M, act, N, rank, g, dst_of_rank, dst_row_stride_bytes, part_first_column[0], peers, workspace, workspace_bytes,
+                         flags_of_rank, stream);
+}
+
+static int rowsplit_impl(int wtype, const void *w, int64_t K, int64_t M, const void *act, int64_t N, int rank, int g, void *const *dst_of_rank,
+                         int64_t dst_row_stride_bytes, int64_t first_column, PeerDst peers, void *workspace, size_t workspace_bytes,
+                         void *const *flags_of_rank, b200_stream_t stream) {
+    B200_REQUIRE(dst_of_rank && flags_of_rank && g >= 1 && g <= 8 && rank >= 0 && rank < g && first_column >= 0, "bad row-split arguments");
     float *own = nullptr;
     for (int r = 0; r < g; ++r) {
         B200_REQUIRE(dst_of_rank[r] && flags_of_rank[r], "null buffer of rank %d", r);
@@ -100,7 +130,7 @@ static int mul_mat_prequant(int wtype, const void *w, int64_t K, int64_t M, cons
     if (N <= mmvq_max_n()) return launch_mmvq(wtype, d, w, a, act, dst, dst_row_stride_bytes, peers, (cudaStream_t) stream);
     const bool canon = act_layout_canonical(N);
     // the tcgen05 kernel writes one destination only: a row-split product takes the mma.sync kernel on either activation order
-    if (canon && peers.n == 0) return launch_mmq_tc(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream);
+    if (canon && peers.n == 0 && peers.n_seg <= 1) return launch_mmq_tc(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream);
     return launch_mmq(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream, canon, peers);
 }
 

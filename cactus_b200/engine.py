@@ -169,14 +169,24 @@ class LlamaEngine:
         cfg, L = self.cfg, lib()
         # wq/wk/wv and gate/up read the same activations: stacked into one weight each, they are one mul_mat each (the
         # engine takes the stacked copies and drops the separate tensors).  Not with a row split, whose slices are per tensor.
-        self.fused = bool(fuse_weights) and split is None
+        # With a row split the rank's slices are stacked the same way; each piece then carries the column of the joined
+        # output where its rows belong (QWeight.parts), and one product stores all of them.
+        self.fused = bool(fuse_weights)
         if self.fused:
             t = self.w.tensors
+            kvd_ = cfg.n_kv_head * cfg.head_dim
+
+            def stack(ws, bases):
+                out = QWeight.cat(ws)
+                if split is not None:
+                    out.parts = [(w_.M, base + w_.row0) for w_, base in zip(ws, bases)]
+                return out
             for il in range(cfg.n_layer):
                 p = f"blk.{il}."
                 if p + "attn_qkv.weight" not in t:
-                    t[p + "attn_qkv.weight"] = QWeight.cat([t.pop(p + "attn_q.weight"), t.pop(p + "attn_k.weight"), t.pop(p + "attn_v.weight")])
-                    t[p + "ffn_gate_up.weight"] = QWeight.cat([t.pop(p + "ffn_gate.weight"), t.pop(p + "ffn_up.weight")])
+                    t[p + "attn_qkv.weight"] = stack([t.pop(p + "attn_q.weight"), t.pop(p + "attn_k.weight"), t.pop(p + "attn_v.weight")],
+                                                     [0, cfg.d_model, cfg.d_model + kvd_])
+                    t[p + "ffn_gate_up.weight"] = stack([t.pop(p + "ffn_gate.weight"), t.pop(p + "ffn_up.weight")], [0, cfg.d_ff])
         dev = "cuda"
         kvd = cfg.n_kv_head * cfg.head_dim
         T = max_tokens
@@ -194,7 +204,7 @@ class LlamaEngine:
         self.x, self.h, self.attn = f32(T, cfg.d_model), f32(T, cfg.d_model), f32(T, cfg.d_model)
         out = split.carve if split is not None else f32   # mul_mat outputs: where the peers' slices land
         if self.fused:   # the stacked products, and the reference's q/k/v and gate/up as column ranges of them
-            self.qkv, self.gu = f32(T, cfg.d_model + 2 * kvd), f32(T, 2 * cfg.d_ff)
+            self.qkv, self.gu = out(T, cfg.d_model + 2 * kvd), out(T, 2 * cfg.d_ff)
             self.q, self.k, self.v = self.qkv[:, :cfg.d_model], self.qkv[:, cfg.d_model:cfg.d_model + kvd], self.qkv[:, cfg.d_model + kvd:]
             self.gate, self.up = self.gu[:, :cfg.d_ff], self.gu[:, cfg.d_ff:]
         else:
@@ -207,7 +217,7 @@ class LlamaEngine:
         self.ids_host = torch.zeros(T, dtype=torch.int32).pin_memory()
         self.act_d = u8(L.b200_act_bytes(cfg.d_model, T))
         self.act_ff = u8(L.b200_act_bytes(cfg.d_ff, T))
-        shapes = [(K, M // g) for _, K, M in cfg.mul_mat_shapes()] + [(cfg.d_model, cfg.d_model + 2 * kvd), (cfg.d_model, 2 * cfg.d_ff)]
+        shapes = [(K, M // g) for _, K, M in cfg.mul_mat_shapes()] + [(cfg.d_model, (cfg.d_model + 2 * kvd) // g), (cfg.d_model, 2 * cfg.d_ff // g)]
         ws = [L.b200_mul_mat_workspace_bytes(cfg.layer_type, K, M, t) for K, M in shapes for t in range(1, T + 1)]
         ws += [L.b200_mul_mat_workspace_bytes(cfg.head_type, cfg.d_model, cfg.vocab // g, t) for t in range(1, T + 1)]
         self.ws = u8(max(ws))

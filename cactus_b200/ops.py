@@ -33,6 +33,7 @@ class QWeight:
     def __init__(self, wtype: int, K: int, M: int, data: torch.Tensor, row0: int = 0):
         self.wtype, self.K, self.M, self.data = wtype, K, M, data
         self.row0 = row0   # first row of this weight within the tensor it was cut from (row split)
+        self.parts = None  # row split of a stacked weight: [(rows, first column in the joined output), ...] of this rank's pieces
 
     @staticmethod
     def from_blocks(wtype: int, K: int, M: int, blocks, device="cuda") -> "QWeight":

@@ -98,6 +98,13 @@ class RowSplit:
         """dst[:T, w.row0 : w.row0 + w.M] = this rank's rows of the product, stored by the mul_mat kernel's own write-back
         into every rank's dst; returns (in stream order) when all ranks' slices are in."""
         arr = self._dst_arrays[dst.data_ptr()]
+        if w.parts is not None:   # this rank's rows of several tensors stacked: each piece has its own place in dst
+            n = len(w.parts)
+            rows = (C.c_int64 * n)(*[r for r, _ in w.parts])
+            cols = (C.c_int64 * n)(*[c for _, c in w.parts])
+            check(lib().b200_mul_mat_q_rowsplit_stacked(w.wtype, w.data.data_ptr(), w.K, w.M, act.data_ptr(), T, self.rank, self.world, arr,
+                                                        dst.stride(0) * 4, n, rows, cols, workspace.data_ptr(), workspace.numel(), self._flag_arr, stream))
+            return
         check(lib().b200_mul_mat_q_rowsplit(w.wtype, w.data.data_ptr(), w.K, w.M, act.data_ptr(), T, self.rank, self.world, arr, dst.stride(0) * 4,
                                             w.row0, workspace.data_ptr(), workspace.numel(), self._flag_arr, stream))
 

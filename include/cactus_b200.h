@@ -305,6 +305,13 @@ B200_API int b200_peer_status(const void *flags);
 B200_API int b200_mul_mat_q_rowsplit(int wtype, const void *w, int64_t K, int64_t M, const void *act, int64_t N, int rank, int g,
                                      void *const *dst_of_rank, int64_t dst_row_stride_bytes, int64_t first_column, void *workspace,
                                      size_t workspace_bytes, void *const *flags_of_rank, b200_stream_t stream);
+/* The same for a stacked weight of this rank (its rows of wq, wk, wv one after the other, or of gate and up): part i
+ * holds part_rows[i] rows (a multiple of 16 but for the last) that belong at columns part_first_column[i] ... of the
+ * joined output; one product and one flag exchange instead of one per tensor. */
+B200_API int b200_mul_mat_q_rowsplit_stacked(int wtype, const void *w, int64_t K, int64_t M, const void *act, int64_t N, int rank, int g,
+                                             void *const *dst_of_rank, int64_t dst_row_stride_bytes, int n_parts, const int64_t *part_rows,
+                                             const int64_t *part_first_column, void *workspace, size_t workspace_bytes,
+                                             void *const *flags_of_rank, b200_stream_t stream);
 
 #ifdef __cplusplus
 }
