@@ -168,7 +168,7 @@ class LlamaEngine:
         g = split.world if split is not None else 1
         cfg, L = self.cfg, lib()
         # wq/wk/wv and gate/up read the same activations: stacked into one weight each, they are one mul_mat each (the
-        # engine takes the stacked copies and drops the separate tensors).  Not with a row split, whose slices are per tensor.
+        # engine takes the stacked copies and drops the separate tensors).
         # With a row split the rank's slices are stacked the same way; each piece then carries the column of the joined
         # output where its rows belong (QWeight.parts), and one product stores all of them.
         self.fused = bool(fuse_weights)
