@@ -41,8 +41,33 @@ def main():
         dist.barrier()   # the next repetition overwrites dst: a one-buffer test needs what the model's buffer rotation gives
     out["join_exact"] = ok
     out["join_status"] = rs.status()
-    # ---- part 2: the model ----
+    # ---- part 1b: a stacked product -- this rank's rows of two weights in one mul_mat, each piece at its own columns ----
     oracle = Oracle()
+    from cactus_b200 import ops
+    from cactus_b200.ops import QWeight
+    from cactus_b200._lib import lib
+    rngw = np.random.default_rng(7)
+    K, Ma, Mb = 256, 64 * world, 32 * world
+    wa = QWeight.from_blocks(Q4_0, K, Ma, oracle.quantize_weights(Q4_0, (rngw.standard_normal((Ma, K)) * 0.05).astype(np.float32)))
+    wb = QWeight.from_blocks(Q4_0, K, Mb, oracle.quantize_weights(Q4_0, (rngw.standard_normal((Mb, K)) * 0.05).astype(np.float32)))
+    sa, sb = wa.row_slice(rank * Ma // world, (rank + 1) * Ma // world), wb.row_slice(rank * Mb // world, (rank + 1) * Mb // world)
+    stacked = QWeight.cat([sa, sb])
+    stacked.parts = [(sa.M, sa.row0), (sb.M, Ma + sb.row0)]
+    joined = rs.carve(8, Ma + Mb)
+    ws = torch.empty(max(256, lib().b200_mul_mat_workspace_bytes(Q4_0, K, stacked.M, 8)), dtype=torch.uint8, device="cuda")
+    stacked_err = 0.0
+    for N in (1, 5):
+        x = torch.from_numpy(rngw.standard_normal((N, K)).astype(np.float32)).cuda()
+        act = torch.empty(lib().b200_act_bytes(K, N), dtype=torch.uint8, device="cuda")
+        from cactus_b200._lib import check
+        check(lib().b200_quantize_activations(x.data_ptr(), K * 4, K, N, act.data_ptr(), act.numel(), 0, st))
+        rs.mul_mat(stacked, act, N, joined, ws, st)
+        torch.cuda.synchronize()
+        want = torch.cat([ops.mul_mat(wa, x), ops.mul_mat(wb, x)], dim=1)
+        stacked_err = max(stacked_err, float((joined[:N] - want).abs().max() / want.abs().max()))
+        dist.barrier()
+    out["stacked_err"] = stacked_err
+    # ---- part 2: the model ----
     cfg = LlamaConfig(n_layer=2, d_model=256, n_head=4, n_kv_head=2, d_ff=512, vocab=320, head_type=Q4_0)
     arrays = tiny_model(oracle, cfg)
     full = LlamaWeights.from_numpy(cfg, arrays)

@@ -43,5 +43,6 @@ def test_two_gpu_row_split():
         results.append(json.loads(line[7:]))
     for r in results:
         assert r["join_exact"] and r["join_status"] == 0 and r["model_status"] == 0 and r["ranks_agree"], r
+        assert r["stacked_err"] < 1e-5, r
     r0 = [r for r in results if r["rank"] == 0][0]
     assert r0["same_argmax"] and r0["max_err_vs_single_gpu"] < 3e-2, r0
