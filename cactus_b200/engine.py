@@ -158,7 +158,7 @@ class LlamaEngine:
     """
 
     def __init__(self, weights: LlamaWeights, n_cells: int, max_tokens: int = 512, variant: int = Q8_AVX2, use_graphs: bool = True, split=None,
-                 fuse_weights: bool = True):
+                 fuse_weights: bool = True, head_parallel: bool = True):
         assert n_cells % 256 == 0, "the cache is padded to 256 cells for flash attention (cactus/llama-kv-cache.cpp:20-23)"
         self.w, self.cfg, self.n_cells, self.max_tokens, self.variant = weights, weights.cfg, n_cells, max_tokens, variant
         self.use_graphs = use_graphs
@@ -172,6 +172,11 @@ class LlamaEngine:
         # With a row split the rank's slices are stacked the same way; each piece then carries the column of the joined
         # output where its rows belong (QWeight.parts), and one product stores all of them.
         self.fused = bool(fuse_weights)
+        # Row split with the heads of a rank kept at home: wq/wk/wv cut by rows are cut by heads, so a rank rotates, caches
+        # and attends its own H/g query and Hkv/g KV heads only (its share of the cache, too) and the ranks exchange the
+        # attention output instead of q, k and v: attention time and cache memory divide by g.
+        self.hp = bool(head_parallel) and split is not None and self.fused and cfg.n_head % g == 0 and cfg.n_kv_head % g == 0 and \
+            (cfg.n_kv_head // g * cfg.head_dim) % 16 == 0
         if self.fused:
             t = self.w.tensors
             kvd_ = cfg.n_kv_head * cfg.head_dim
@@ -186,9 +191,14 @@ class LlamaEngine:
                 if p + "attn_qkv.weight" not in t:
                     t[p + "attn_qkv.weight"] = stack([t.pop(p + "attn_q.weight"), t.pop(p + "attn_k.weight"), t.pop(p + "attn_v.weight")],
                                                      [0, cfg.d_model, cfg.d_model + kvd_])
+                    if self.hp:
+                        t[p + "attn_qkv.weight"].parts = None   # the product stays on this rank
                     t[p + "ffn_gate_up.weight"] = stack([t.pop(p + "ffn_gate.weight"), t.pop(p + "ffn_up.weight")], [0, cfg.d_ff])
         dev = "cuda"
-        kvd = cfg.n_kv_head * cfg.head_dim
+        self.n_head_local = cfg.n_head // g if self.hp else cfg.n_head
+        self.n_kv_head_local = cfg.n_kv_head // g if self.hp else cfg.n_kv_head
+        kvd = self.n_kv_head_local * cfg.head_dim      # K/V row of one cell as this rank caches it
+        qd = self.n_head_local * cfg.head_dim          # q row of one token as this rank holds it
         T = max_tokens
         f32 = lambda *s: torch.empty(s, dtype=torch.float32, device=dev)  # noqa: E731
         u8 = lambda n: torch.empty(max(int(n), 256), dtype=torch.uint8, device=dev)  # noqa: E731
@@ -204,8 +214,10 @@ class LlamaEngine:
         self.x, self.h, self.attn = f32(T, cfg.d_model), f32(T, cfg.d_model), f32(T, cfg.d_model)
         out = split.carve if split is not None else f32   # mul_mat outputs: where the peers' slices land
         if self.fused:   # the stacked products, and the reference's q/k/v and gate/up as column ranges of them
-            self.qkv, self.gu = out(T, cfg.d_model + 2 * kvd), out(T, 2 * cfg.d_ff)
-            self.q, self.k, self.v = self.qkv[:, :cfg.d_model], self.qkv[:, cfg.d_model:cfg.d_model + kvd], self.qkv[:, cfg.d_model + kvd:]
+            self.qkv, self.gu = (f32 if self.hp else out)(T, qd + 2 * kvd), out(T, 2 * cfg.d_ff)
+            self.q, self.k, self.v = self.qkv[:, :qd], self.qkv[:, qd:qd + kvd], self.qkv[:, qd + kvd:]
+            if self.hp:   # this rank's heads of the attention output, and the joined output every rank continues with
+                self.attn_part, self.attn = f32(T, qd), out(T, cfg.d_model)
             self.gate, self.up = self.gu[:, :cfg.d_ff], self.gu[:, cfg.d_ff:]
         else:
             self.q, self.k, self.v = out(T, cfg.d_model), out(T, kvd), out(T, kvd)
@@ -217,11 +229,12 @@ class LlamaEngine:
         self.ids_host = torch.zeros(T, dtype=torch.int32).pin_memory()
         self.act_d = u8(L.b200_act_bytes(cfg.d_model, T))
         self.act_ff = u8(L.b200_act_bytes(cfg.d_ff, T))
-        shapes = [(K, M // g) for _, K, M in cfg.mul_mat_shapes()] + [(cfg.d_model, (cfg.d_model + 2 * kvd) // g), (cfg.d_model, 2 * cfg.d_ff // g)]
+        kvd_all = cfg.n_kv_head * cfg.head_dim
+        shapes = [(K, M // g) for _, K, M in cfg.mul_mat_shapes()] + [(cfg.d_model, (cfg.d_model + 2 * kvd_all) // g), (cfg.d_model, 2 * cfg.d_ff // g)]
         ws = [L.b200_mul_mat_workspace_bytes(cfg.layer_type, K, M, t) for K, M in shapes for t in range(1, T + 1)]
         ws += [L.b200_mul_mat_workspace_bytes(cfg.head_type, cfg.d_model, cfg.vocab // g, t) for t in range(1, T + 1)]
         self.ws = u8(max(ws))
-        self.fa_scratch = u8(max(L.b200_flash_attn_scratch_bytes(cfg.head_dim, cfg.n_head, cfg.n_kv_head, t, n_cells) for t in range(1, T + 1)))
+        self.fa_scratch = u8(max(L.b200_flash_attn_scratch_bytes(cfg.head_dim, self.n_head_local, self.n_kv_head_local, t, n_cells) for t in range(1, T + 1)))
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
         self.launches_per_step: dict[int, int] = {}
 
@@ -229,6 +242,10 @@ class LlamaEngine:
     def _mm(self, name: str, act: torch.Tensor, T: int, out: torch.Tensor):
         w: QWeight = self.w.tensors[name]
         if self.split is None:
+            check(lib().b200_mul_mat_q_prequant(w.wtype, w.data.data_ptr(), w.K, w.M, act.data_ptr(), T, out.data_ptr(), out.stride(0) * 4,
+                                                self.ws.data_ptr(), self.ws.numel(), self._st))
+            return
+        if self.hp and name.endswith("attn_qkv.weight"):   # q, k, v of this rank's heads: nobody else needs them
             check(lib().b200_mul_mat_q_prequant(w.wtype, w.data.data_ptr(), w.K, w.M, act.data_ptr(), T, out.data_ptr(), out.stride(0) * 4,
                                                 self.ws.data_ptr(), self.ws.numel(), self._st))
             return
@@ -240,7 +257,7 @@ class LlamaEngine:
     def enqueue(self, T: int) -> None:
         cfg, L = self.cfg, lib()
         st = self._st = torch.cuda.current_stream().cuda_stream
-        D, H, Hkv, d, nkv = cfg.head_dim, cfg.n_head, cfg.n_kv_head, cfg.d_model, self.n_cells
+        D, H, Hkv, d, nkv = cfg.head_dim, self.n_head_local, self.n_kv_head_local, cfg.d_model, self.n_cells
         kvd = Hkv * D
         tokens, pos, seq, slots = (self.inp[i].data_ptr() for i in range(4))
         # cell bookkeeping, mask and its index (shared by all layers)
@@ -276,8 +293,10 @@ class LlamaEngine:
             # 57.5 + 2.5 for the two launches at this shape: the attention kernel sits at its register limit)
             check(L.b200_flash_attn_ext_indexed(D, H, Hkv, T, nkv, self.q.data_ptr(), qs, D * 4, kc.data_ptr(), kvd * 2, D * 2,
                                                 vc.data_ptr(), kvd * 2, D * 2, self.mask.data_ptr(), nkv * 2, self.index.data_ptr(),
-                                                D ** -0.5, 0.0, 0.0, self.attn.data_ptr(), self.fa_scratch.data_ptr(),
+                                                D ** -0.5, 0.0, 0.0, (self.attn_part if self.hp else self.attn).data_ptr(), self.fa_scratch.data_ptr(),
                                                 self.fa_scratch.numel(), st))
+            if self.hp:   # every rank's heads side by side, on every rank
+                self.split.allgather(self.attn_part, T, H * D, self.attn, st)
             self._quant(self.attn, d, T, self.act_d)
             self._mm(p + "attn_output.weight", self.act_d, T, self.tmp)
             norm_quant(p + "ffn_norm.weight", self.tmp)
