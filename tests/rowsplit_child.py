@@ -82,6 +82,11 @@ def main():
     for step in range(2):
         steps.append((rng.integers(0, cfg.vocab, 3), np.array(lens) + step, np.arange(3), sum(lens) + 3 * step + np.arange(3)))
     got = [eng.decode(*s)[0].copy() for s in steps for _ in range(1)]
+    # the same with attention replicated on every rank (what the engine does when the head counts do not divide)
+    eng2 = LlamaEngine(full.shard(rank, world), 256, max_tokens=32, use_graphs=False, split=rs, head_parallel=False)
+    got2 = [eng2.decode(*s)[0].copy() for s in steps]
+    out["head_parallel"] = bool(eng.hp) and not eng2.hp
+    out["replicated_attention_err"] = max(float(np.abs(a - b).max() / np.abs(b).max()) for a, b in zip(got2, got))
     out["model_status"] = rs.status()
     sums = torch.tensor([float(np.abs(g).sum()) for g in got], dtype=torch.float64)
     gathered = [torch.zeros_like(sums) for _ in range(world)]

@@ -44,5 +44,6 @@ def test_two_gpu_row_split():
     for r in results:
         assert r["join_exact"] and r["join_status"] == 0 and r["model_status"] == 0 and r["ranks_agree"], r
         assert r["stacked_err"] < 1e-5, r
+        assert r["head_parallel"] and r["replicated_attention_err"] < 3e-2, r
     r0 = [r for r in results if r["rank"] == 0][0]
     assert r0["same_argmax"] and r0["max_err_vs_single_gpu"] < 3e-2, r0
