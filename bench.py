@@ -303,7 +303,8 @@ def gpu_arm(args):
                        "prompt_lengths": f"U[16,2048] seed 0 scaled by {scale:.3f} to leave 128 decode cells per sequence; "
                                          f"{int(lens.sum())} prompt cells hold synthetic N(0,1) K/V",
                        "parallelism": (f"row split over {world} GPUs: every mul_mat weight cut by rows, the products' own write-back stores into every GPU's "
-                                       f"buffers over NVLink (b200_mul_mat_q_rowsplit / _stacked), everything else replicated; peer_status {peer_status}") if rows
+                                       f"buffers over NVLink (b200_mul_mat_q_rowsplit / _stacked); attention, rope and the KV cache follow the heads of a rank "
+                                       f"(attention output joined with b200_allgather_rows), norms replicated; peer_status {peer_status}") if rows
                                       else ("one replica per GPU, no collective" if world > 1 else "single GPU"),
                        "model": args.model if not args.small else "small",
                        "l2": "inputs larger than L2: 4.2 GB of weights and ~7 GB of KV are streamed every step"},
