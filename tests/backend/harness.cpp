@@ -531,7 +531,42 @@ static int run_model(int argc, char ** argv) {
     return (worst < 3e-2 && agree >= 0.9 * total) ? 0 : 1;
 }
 
+// A quantised tensor placed in the plug-in's split buffer type (rows spread over all B200 devices, ragged row count):
+// what set_tensor scatters must come back from get_tensor byte for byte.
+static int run_split_roundtrip() {
+    lm_ggml_backend_reg_t reg = lm_ggml_backend_b200_reg();
+    auto fn = (lm_ggml_backend_split_buffer_type_t) lm_ggml_backend_reg_get_proc_address(reg, "lm_ggml_backend_split_buffer_type");
+    if (!fn) { printf("{\"case\": \"split roundtrip\", \"error\": \"no split buffer type\"}\n"); return 2; }
+    lm_ggml_backend_buffer_type_t buft = fn(0, nullptr);
+    if (!buft) { printf("{\"case\": \"split roundtrip\", \"error\": \"null buffer type\"}\n"); return 2; }
+    std::mt19937 rng(5);
+    bool equal = true;
+    for (lm_ggml_type type : {LM_GGML_TYPE_Q4_0, LM_GGML_TYPE_Q8_0}) {
+        for (int64_t M : {300, 128, 2064}) {
+            const int64_t K = 256;
+            lm_ggml_init_params ip = { lm_ggml_tensor_overhead() * 4, nullptr, true };
+            lm_ggml_context * ctx = lm_ggml_init(ip);
+            lm_ggml_tensor * t = lm_ggml_new_tensor_2d(ctx, type, K, M);
+            lm_ggml_backend_buffer_t buf = lm_ggml_backend_alloc_ctx_tensors_from_buft(ctx, buft);
+            if (!buf) { printf("{\"case\": \"split roundtrip\", \"error\": \"allocation failed\"}\n"); return 2; }
+            std::vector<float> w((size_t) M * K);
+            fill_normal(w, rng, 0.05f);
+            std::vector<uint8_t> q(lm_ggml_nbytes(t)), back(lm_ggml_nbytes(t), 0xAB);
+            lm_ggml_quantize_chunk(type, w.data(), q.data(), 0, M, K, nullptr);
+            lm_ggml_backend_tensor_set(t, q.data(), 0, q.size());
+            lm_ggml_backend_tensor_get(t, back.data(), 0, back.size());
+            equal = equal && memcmp(q.data(), back.data(), q.size()) == 0;
+            lm_ggml_backend_buffer_free(buf);
+            lm_ggml_free(ctx);
+        }
+    }
+    printf("{\"case\": \"split roundtrip\", \"equal\": %s, \"devices\": %d, \"buffer_type\": \"%s\"}\n", equal ? "true" : "false",
+           (int) lm_ggml_backend_reg_dev_count(reg), lm_ggml_backend_buft_name(buft));
+    return equal ? 0 : 1;
+}
+
 int main(int argc, char ** argv) {
+    if (argc >= 2 && strcmp(argv[1], "split") == 0) return run_split_roundtrip();
     if (argc >= 2 && strcmp(argv[1], "ops") == 0) {
         int rc = 0;
         for (lm_ggml_type t : {LM_GGML_TYPE_Q4_0, LM_GGML_TYPE_Q8_0})

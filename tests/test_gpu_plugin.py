@@ -92,3 +92,11 @@ def test_row_split_buffer_type_through_llama_decode(gpus):
     assert r["split_mul_mats"] > 0, r
     assert r["greedy_agree"] >= 0.9 and r["worst_rel"] < 3e-2, r
     assert rc == 0
+
+
+def test_split_buffer_set_get_round_trip():
+    """set_tensor scatters the rows of a quantised tensor over the devices (ragged row counts, both block types);
+    get_tensor brings the same bytes back."""
+    rc, lines, err = run("split")
+    assert lines and "error" not in lines[-1], (lines, err)
+    assert lines[-1]["equal"] and rc == 0, lines
