@@ -50,6 +50,16 @@ def test_size_queries_and_argument_checks_without_a_gpu():
     assert rc == -1 and b"bad mul_mat" in L.b200_last_error()
     rc = L.b200_flash_attn_ext(96, 8, 8, 1, 256, None, 0, 0, None, 0, 0, None, 0, 0, None, 0, 1.0, 0.0, 0.0, None, None, 0, None)
     assert rc == -1 and b"head size" in L.b200_last_error()
+    # a stacked row-split product: the parts must add up to the weight's rows and all but the last hold whole 16-row tiles
+    import ctypes as C
+    rows, cols = (C.c_int64 * 2)(24, 40), (C.c_int64 * 2)(0, 128)
+    rc = L.b200_mul_mat_q_rowsplit_stacked(2, None, 64, 64, None, 4, 0, 1, None, 1024, 2, rows, cols, None, 0, None, None)
+    assert rc == -1 and b"multiple of 16" in L.b200_last_error()
+    rows = (C.c_int64 * 2)(32, 16)
+    rc = L.b200_mul_mat_q_rowsplit_stacked(2, None, 64, 64, None, 4, 0, 1, None, 1024, 2, rows, cols, None, 0, None, None)
+    assert rc == -1 and b"the parts hold 48 rows" in L.b200_last_error()
+    rc = L.b200_mul_mat_q_rowsplit_stacked(2, None, 64, 64, None, 4, 0, 1, None, 1024, 4, rows, cols, None, 0, None, None)
+    assert rc == -1 and b"1 to 3 parts" in L.b200_last_error()
 
 
 def test_missing_library_fails_loudly(monkeypatch):
