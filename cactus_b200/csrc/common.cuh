@@ -126,9 +126,17 @@ __host__ __device__ static inline TiledDims tiled_dims(int wtype, int64_t K, int
 // Rows beyond N and blocks beyond K/32 are zero.
 constexpr float ACT_MAGIC = 12582912.0f;   // 1.5 * 2^23 = as_float(0x4B400000)
 __host__ __device__ static inline int act_scale_index(int j, int col) { return ((j * 4 + (col >> 1)) * 4) + (col & 1); }
+// Products of ACT_F8_MIN_N and more columns also carry what the tcgen05 kernel (mmq_tc.cu) reads: after the scale plane
+// two more quant planes in K-major core-matrix order (per n-tile and block two 8-column x 16-byte matrices, elements
+// 0..15 then 16..31), holding each quant a = 16 h + l (h = a >> 4, l = a & 15) as two e4m3 bytes -- `hi` the byte whose
+// value is h * 2^-5, `lo` the byte l, whose value is l * 2^-9 (the subnormals and first binade of e4m3 are the
+// integers 0..15 times 2^-9) -- and a second scale plane with {D[2cp], D[2cp+1], C[2cp], C[2cp+1]} at the same float
+// indices, D = d * 2^18 and C = -8 * d * sum(a) (the kernel multiplies unsigned weight nibbles u = q + 8).
+constexpr int ACT_F8_MIN_N = 16;
 struct ActDims {
     int64_t N, K, nb, nbp, n_bg, n_nt;
     size_t d_offset;     // byte offset of the scale plane
+    size_t hi_offset, lo_offset, s2_offset;   // the e4m3 planes and their scale plane (0 when absent)
     size_t total_bytes;
 };
 
@@ -142,6 +150,13 @@ __host__ __device__ static inline ActDims act_dims(int64_t K, int64_t N) {
     a.n_nt = (N + 7) / 8;
     a.d_offset = (size_t) a.n_nt * a.nbp * 256;
     a.total_bytes = a.d_offset + (size_t) a.n_nt * a.n_bg * 256;
+    a.hi_offset = a.lo_offset = a.s2_offset = 0;
+    if (N >= ACT_F8_MIN_N) {   // every offset below follows from d_offset alone: the scale planes are a quarter of a quant plane
+        a.hi_offset = a.total_bytes;
+        a.lo_offset = a.hi_offset + a.d_offset;
+        a.s2_offset = a.lo_offset + a.d_offset;
+        a.total_bytes = a.s2_offset + a.d_offset / 4;
+    }
     return a;
 }
 
@@ -178,12 +193,18 @@ __device__ __forceinline__ double rms_block_sum(double sum) {
     return tot;
 }
 
+// e4m3 byte of h * 2^-5 for the signed nibble h (index = h & 15)
+__device__ __forceinline__ uint32_t e4m3_hi_byte(uint32_t nib) {
+    const uint64_t tab = (nib & 8) ? 0x90989CA0A2A4A6A8ull : 0x262422201C181000ull;   // h = -8..-1 | h = 0..7, lowest byte first
+    return (uint32_t) (tab >> (8 * (nib & 7))) & 0xffu;
+}
 // Stores one lane's share (4 quants, element group j of 8) of a quantised block (row n, block b).  LAYOUT 0: the
-// reference's block_q8_0 stream; 1: B8 tiles in mma.sync B-fragment order; 2: B8 tiles as K-major core matrices.
-// Lane j == 0 also stores the block scale (layouts 1/2: the f32 pair {d, -d * 12582912}; zero for padding).
+// reference's block_q8_0 stream; 1: B8 tiles in mma.sync B-fragment order; 2: B8 tiles as K-major core matrices;
+// 3: layout 1 plus the e4m3 planes of ACT_F8_MIN_N (qsum = the sum of the block's 32 quants).
+// Lane j == 0 also stores the block scale (layouts 1/2/3: the f32 pair {d, -d * 12582912}; zero for padding).
 template <int LAYOUT>
 __device__ __forceinline__ void q8_store(uint8_t *__restrict__ out, size_t d_offset, int64_t nb, int64_t nbp, int64_t n, int64_t b, int j,
-                                         uint32_t packed, __half d, bool real) {
+                                         uint32_t packed, __half d, bool real, int qsum = 0) {
     if (LAYOUT == 0) {
         uint8_t *blkp = out + (n * nb + b) * 34;
         if (j == 0) *reinterpret_cast<__half *>(blkp) = d;
@@ -195,8 +216,17 @@ __device__ __forceinline__ void q8_store(uint8_t *__restrict__ out, size_t d_off
         const int g = (int) (n & 7);
         const int t = j & 3;
         uint8_t *tile = out + (nt * nbp + b) * 256;
-        if (LAYOUT == 1) {
+        if (LAYOUT == 1 || LAYOUT == 3) {
             *reinterpret_cast<uint32_t *>(tile + (g * 4 + t) * 8 + (j >= 4 ? 4 : 0)) = packed;
+            if (LAYOUT == 3) {
+                const size_t hi_off = d_offset + d_offset / 4, lo_off = hi_off + d_offset;
+                const size_t at = (size_t) (nt * nbp + b) * 256 + (j >> 2) * 128 + g * 16 + t * 4;
+                const uint32_t nib = (packed >> 4) & 0x0F0F0F0Fu;
+                const uint32_t hi = e4m3_hi_byte(nib & 0xff) | (e4m3_hi_byte((nib >> 8) & 0xff) << 8) | (e4m3_hi_byte((nib >> 16) & 0xff) << 16) |
+                                    (e4m3_hi_byte(nib >> 24) << 24);
+                *reinterpret_cast<uint32_t *>(out + hi_off + at) = hi;
+                *reinterpret_cast<uint32_t *>(out + lo_off + at) = packed & 0x0F0F0F0Fu;
+            }
         } else {
             // two 8-column x 16-byte core matrices: elements 0..15 of each column, then elements 16..31
             *reinterpret_cast<uint32_t *>(tile + (j >> 2) * 128 + g * 16 + t * 4) = packed;
@@ -206,6 +236,11 @@ __device__ __forceinline__ void q8_store(uint8_t *__restrict__ out, size_t d_off
             const float df = real ? __half2float(d) : 0.0f;
             dp[0] = df;
             dp[2] = -df * ACT_MAGIC;
+            if (LAYOUT == 3) {
+                float *dp2 = reinterpret_cast<float *>(out + d_offset + d_offset / 4 + 2 * d_offset) + (dp - reinterpret_cast<float *>(out + d_offset));
+                dp2[0] = df * 262144.0f;
+                dp2[2] = __fmul_rn((float) (-8 * qsum), df);
+            }
         }
     }
 }
@@ -223,9 +258,19 @@ __device__ __forceinline__ void q8_quantize_store(const float (&v)[4], uint8_t *
     float id;
     q8_scales(amax, variant, &d, &id);
     uint32_t packed = 0;
+    int qsum = 0;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) packed |= ((uint32_t) (q8_round(v[i], id, variant) & 0xff)) << (8 * i);
-    q8_store<LAYOUT>(out, d_offset, nb, nbp, n, b, j, packed, d, real);
+    for (int i = 0; i < 4; ++i) {
+        const int q = q8_round(v[i], id, variant);
+        qsum += q;
+        packed |= ((uint32_t) (q & 0xff)) << (8 * i);
+    }
+    if (LAYOUT == 3) {
+        qsum += __shfl_xor_sync(grp, qsum, 1);
+        qsum += __shfl_xor_sync(grp, qsum, 2);
+        qsum += __shfl_xor_sync(grp, qsum, 4);
+    }
+    q8_store<LAYOUT>(out, d_offset, nb, nbp, n, b, j, packed, d, real, qsum);
 }
 
 // the same for one value per lane: the 32 lanes of a (fully active) warp hold one block in element order
@@ -238,13 +283,19 @@ __device__ __forceinline__ void q8_quantize_store_warp(float v, uint8_t *__restr
     __half d;
     float id;
     q8_scales(amax, variant, &d, &id);
-    const uint32_t q = (uint32_t) (q8_round(v, id, variant) & 0xff);
+    const int qi = q8_round(v, id, variant);
+    int qsum = qi;
+    if (LAYOUT == 3) {
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) qsum += __shfl_xor_sync(0xffffffffu, qsum, o);
+    }
+    const uint32_t q = (uint32_t) (qi & 0xff);
     uint32_t packed = q;
     packed |= __shfl_down_sync(0xffffffffu, q, 1) << 8;
     packed |= __shfl_down_sync(0xffffffffu, q, 2) << 16;
     packed |= __shfl_down_sync(0xffffffffu, q, 3) << 24;
     const int lane = threadIdx.x & 31;
-    if ((lane & 3) == 0) q8_store<LAYOUT>(out, d_offset, nb, nbp, n, b, lane >> 2, packed, d, real);
+    if ((lane & 3) == 0) q8_store<LAYOUT>(out, d_offset, nb, nbp, n, b, lane >> 2, packed, d, real, qsum);
 }
 
 }  // namespace b200

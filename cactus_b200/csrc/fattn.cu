@@ -19,7 +19,7 @@
 
 namespace b200 {
 
-bool act_layout_canonical(int64_t N);   // quantize.cu: which B8 layout the mul_mat kernels expect for N columns
+int act_layout(int64_t N);   // quantize.cu: which B8 layout the mul_mat kernels expect for N columns
 
 
 constexpr int FA_THREADS = 128;
@@ -154,7 +154,7 @@ __device__ __forceinline__ int fattn_target_words(const FattnParams &p, int ctas
 // for this code.
 __device__ __noinline__ void fattn_quant_block(uint8_t *qout, size_t d_offset, int64_t nb, int64_t nbp, int canon, int variant, int64_t n, int64_t b,
                                                float val, bool real) {
-    if (canon) q8_quantize_store_warp<2>(val, qout, d_offset, nb, nbp, n, b, real, variant);
+    if (canon) q8_quantize_store_warp<3>(val, qout, d_offset, nb, nbp, n, b, real, variant);
     else q8_quantize_store_warp<1>(val, qout, d_offset, nb, nbp, n, b, real, variant);
 }
 
@@ -661,7 +661,7 @@ static int flash_attn_impl(bool parity, int64_t D, int64_t H, int64_t Hkv, int64
     p.dst = dst; p.partial = (float *) scratch; p.nsplit = ns; p.hgroups = hgroups; p.w0 = w0;
     const ActDims ad = act_dims(H * D, Nq);
     p.qout = (uint8_t *) act; p.q_d_offset = ad.d_offset; p.q_nb = ad.nb; p.q_nbp = ad.nbp;
-    p.q_canon = act_layout_canonical(Nq) ? 1 : 0; p.q_variant = variant;
+    p.q_canon = act_layout(Nq) == 3 ? 1 : 0; p.q_variant = variant;
     p.order = index ? (const int32_t *) ((const char *) index + index_order_offset(Nq, p.nw)) : nullptr;
     p.plan = index ? (const int32_t *) ((const char *) index + index_plan_offset(Nq, p.nw)) : nullptr;
     p.slots = FA_MIN_CTAS * fa_sm_count();

@@ -9,7 +9,7 @@
 
 namespace b200 {
 
-bool act_layout_canonical(int64_t N);
+int act_layout(int64_t N);
 
 // One CTA per (padded) token row, one pass: a thread keeps its groups of 4 elements in registers from the load to the
 // quantised store.  The sum of squares is accumulated in the order rms_norm_kernel uses (rms_block_sum), so the
@@ -174,8 +174,8 @@ int b200_add_rms_norm_quantize(float *x, int64_t x_nb_row, const float *residual
     const unsigned grid = (unsigned) (a.n_nt * 8);
     const unsigned threads = rms_threads(d);
     cudaStream_t st = (cudaStream_t) stream;
-    if (act_layout_canonical(rows)) {
-        launch_pdl(add_rms_norm_quantize_kernel<2>, dim3(grid), dim3(threads), 0, st, x, x_nb_row, residual, residual_nb_row, w, h, h_nb_row, d, rows, eps, a.nb, a.nbp,
+    if (act_layout(rows) == 3) {
+        launch_pdl(add_rms_norm_quantize_kernel<3>, dim3(grid), dim3(threads), 0, st, x, x_nb_row, residual, residual_nb_row, w, h, h_nb_row, d, rows, eps, a.nb, a.nbp,
                                                                   (uint8_t *) scratch, a.d_offset, variant);
     } else {
         launch_pdl(add_rms_norm_quantize_kernel<1>, dim3(grid), dim3(threads), 0, st, x, x_nb_row, residual, residual_nb_row, w, h, h_nb_row, d, rows, eps, a.nb, a.nbp,
@@ -197,8 +197,8 @@ int b200_silu_mul_quantize(const float *gate, const float *up, int64_t nb_row, f
     const int64_t threads = rows_padded * a.nbp * 8;
     const unsigned grid = (unsigned) ((threads + 255) / 256);
     cudaStream_t st = (cudaStream_t) stream;
-    if (act_layout_canonical(N)) {
-        launch_pdl(silu_mul_quantize_kernel<2>, dim3(grid), dim3(256), 0, st, gate, up, nb_row, dst, dst_nb_row, N, rows_padded, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
+    if (act_layout(N) == 3) {
+        launch_pdl(silu_mul_quantize_kernel<3>, dim3(grid), dim3(256), 0, st, gate, up, nb_row, dst, dst_nb_row, N, rows_padded, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
     } else {
         launch_pdl(silu_mul_quantize_kernel<1>, dim3(grid), dim3(256), 0, st, gate, up, nb_row, dst, dst_nb_row, N, rows_padded, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
     }

@@ -5,8 +5,7 @@
 #include "common.cuh"
 
 namespace b200 {
-int launch_quantize_b8(const float *x, int64_t x_nb_row, int64_t K, int64_t N, void *scratch, int variant, bool canonical, cudaStream_t st);
-bool act_layout_canonical(int64_t N);
+int act_layout(int64_t N);
 int launch_mmq_tc(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
                   void *workspace, size_t workspace_bytes, cudaStream_t st);
 int mmvq_max_n();
@@ -128,10 +127,12 @@ static int mul_mat_prequant(int wtype, const void *w, int64_t K, int64_t M, cons
     const TiledDims d = tiled_dims(wtype, K, M);
     const ActDims a = act_dims(K, N);
     if (N <= mmvq_max_n()) return launch_mmvq(wtype, d, w, a, act, dst, dst_row_stride_bytes, peers, (cudaStream_t) stream);
-    const bool canon = act_layout_canonical(N);
-    // the tcgen05 kernel writes one destination only: a row-split product takes the mma.sync kernel on either activation order
-    if (canon && peers.n == 0 && peers.n_seg <= 1) return launch_mmq_tc(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream);
-    return launch_mmq(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream, canon, peers);
+    // the tcgen05 kernel reads the e4m3 planes, multiplies Q4_0 weights and writes one destination; everything else (Q8_0
+    // weights, a row-split product) takes the mma.sync kernel on the fragment-order plane that is always there
+    if (act_layout(N) == 3 && wtype == B200_TYPE_Q4_0 && peers.n == 0 && peers.n_seg <= 1) {
+        return launch_mmq_tc(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream);
+    }
+    return launch_mmq(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream, false, peers);
 }
 
 int b200_mul_mat_q(int wtype, const void *w, int64_t K, int64_t M, const float *x, int64_t x_row_stride_bytes, int64_t N,

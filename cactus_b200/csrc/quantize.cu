@@ -9,8 +9,8 @@ namespace b200 {
 // ---------------------------------------------------------------------------------------------
 // quantize_row_q8_0 (cactus/ggml-cpu/ggml-cpu-quants.c:732-1045).  8 threads per 32-element block,
 // 4 elements each; the block maximum is reduced with three shuffles.  LAYOUT 0 writes the reference's
-// block_q8_0 stream, LAYOUT 1 the B8 scratch layout (mma.sync fragment order), LAYOUT 2 the same tiles in the
-// canonical K-major core-matrix order the tcgen05 kernel's shared-memory descriptors expect.
+// block_q8_0 stream, LAYOUT 1 the B8 scratch layout (mma.sync fragment order), LAYOUT 3 that plus the e4m3 planes in
+// the K-major core-matrix order the tcgen05 kernel's shared-memory descriptors expect (common.cuh, ACT_F8_MIN_N).
 // ---------------------------------------------------------------------------------------------
 template <int LAYOUT>
 __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float *__restrict__ x, int64_t x_nb_row, int64_t K,
@@ -206,26 +206,28 @@ static int check_wtype(int wtype) {
     return B200_OK;
 }
 
-int launch_quantize_b8(const float *x, int64_t x_nb_row, int64_t K, int64_t N, void *scratch, int variant, bool canonical, cudaStream_t st) {
+int launch_quantize_b8(const float *x, int64_t x_nb_row, int64_t K, int64_t N, void *scratch, int variant, int layout, cudaStream_t st) {
     const ActDims a = act_dims(K, N);
     const int64_t threads = a.n_nt * 8 * a.nbp * 8;
     const int64_t grid = (threads + 255) / 256;
-    if (canonical) launch_pdl(quantize_q8_0_kernel<2>, dim3((unsigned) grid), dim3(256), 0, st, x, x_nb_row, K, N, a.n_nt * 8, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
+    if (layout == 3) launch_pdl(quantize_q8_0_kernel<3>, dim3((unsigned) grid), dim3(256), 0, st, x, x_nb_row, K, N, a.n_nt * 8, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
     else launch_pdl(quantize_q8_0_kernel<1>, dim3((unsigned) grid), dim3(256), 0, st, x, x_nb_row, K, N, a.n_nt * 8, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
     return check_launch("quantize_q8_0 (activations)");
 }
 
-// Which order the quantised activations of an N-column product are kept in: the tcgen05 kernel (N > 8, only with
-// B200_MMQ_TC=1: it is correct but, at decode widths, still slower than the mma.sync kernel) reads canonical core
-// matrices, the dp4a kernel and the mma.sync kernel read fragment order.
-bool act_layout_canonical(int64_t N) {
+// What the quantised activations of an N-column product hold: 1 = the B8 tiles in fragment order, which the dp4a and
+// mma.sync kernels read; 3 = those plus the e4m3 planes of the tcgen05 kernel (ACT_F8_MIN_N columns and more; the
+// scratch of such a product always has room for them).  The tcgen05 kernel is taken with B200_MMQ_TC=1: it passes every
+// parity case, but at the decode width of 64 columns it does not beat the mma.sync kernel yet (see mmq_tc.cu).
+bool mmq_tc_enabled() {
     static int mode = -1;
     if (mode < 0) {
         const char *e = getenv("B200_MMQ_TC");
         mode = (e && atoi(e) == 1) ? 1 : 0;
     }
-    return mode == 1 && N > 8;
+    return mode == 1;
 }
+int act_layout(int64_t N) { return (N >= ACT_F8_MIN_N && mmq_tc_enabled()) ? 3 : 1; }
 
 }  // namespace b200
 
@@ -298,7 +300,7 @@ int b200_quantize_activations(const float *x, int64_t x_row_stride_bytes, int64_
     B200_REQUIRE(is_aligned(x, 4) && x_row_stride_bytes % 4 == 0, "misaligned activations");
     B200_REQUIRE(is_aligned(scratch, 256), "scratch must be 256-byte aligned");
     if (scratch_bytes < act_dims(K, N).total_bytes) return set_error(B200_E_SCRATCH, "scratch too small: %zu < %zu", scratch_bytes, act_dims(K, N).total_bytes);
-    return launch_quantize_b8(x, x_row_stride_bytes, K, N, scratch, variant, act_layout_canonical(N), (cudaStream_t) stream);
+    return launch_quantize_b8(x, x_row_stride_bytes, K, N, scratch, variant, act_layout(N), (cudaStream_t) stream);
 }
 
 int b200_block_dots(int wtype, const void *w, int64_t K, int64_t M, const float *x, int64_t x_row_stride_bytes, int64_t N,
@@ -306,7 +308,7 @@ int b200_block_dots(int wtype, const void *w, int64_t K, int64_t M, const float 
     if (int e = check_wtype(wtype)) return e;
     B200_REQUIRE(w && out && is_aligned(w, 16), "null or misaligned pointer");
     B200_REQUIRE(x && scratch && is_aligned(scratch, 256) && scratch_bytes >= act_dims(K, N).total_bytes, "bad activation scratch");
-    if (int e = launch_quantize_b8(x, x_row_stride_bytes, K, N, scratch, variant, false, (cudaStream_t) stream)) return e;
+    if (int e = launch_quantize_b8(x, x_row_stride_bytes, K, N, scratch, variant, 1, (cudaStream_t) stream)) return e;
     const TiledDims d = tiled_dims(wtype, K, M);
     const ActDims a = act_dims(K, N);
     const int64_t total = N * M * d.nb;
