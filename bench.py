@@ -1,5 +1,5 @@
 """Benchmark: Q4_0 decode tok/s, Llama-3-8B architecture, 64 ragged sequences in a unified f16 KV cache of
-65536 cells (BASELINE.json configs[3]); mul_mat HBM GB/s against the measured peak.
+65536 cells; mul_mat HBM GB/s against the measured peak.
 
     python bench.py --gpus 1 --steps K --warmup W            # this repository's CUDA path
     python bench.py --impl reference --steps K --warmup W    # the reference's ggml-cpu on the host cores
@@ -7,7 +7,10 @@
 One "step" is one decode ubatch: every one of the 64 sequences advances by one token (32 layers of
 quantised mul_mat + ragged flash attention + the small row ops, then the output head), i.e. 64 tokens.
 With N > 1 (torchrun) every rank runs its own replica with its own 64 sequences (the 8B model fits one
-GPU; there is no data-path collective), so the job is weak-scaled and `value` sums the ranks.
+GPU; there is no data-path collective), so the job is weak-scaled and `value` sums the ranks.  The same
+line then carries a `rowsplit` record: ONE job of the 8B and of the 70B architecture whose mul_mat weights
+are cut by rows over the N GPUs (strong scaling; at N = 1 the record holds the one-GPU time of the 70B
+model the speed-ups refer to).
 
 Prints ONE JSON line on rank 0.
 """
@@ -131,12 +134,15 @@ def cpu_layer_sample(reps: int, warmup: int):
 # -------------------------------------------------------------------------------------------------
 # GPU arm
 # -------------------------------------------------------------------------------------------------
-# DRAM bytes (read + write) per launch of the tensor-core mul_mat at 64 columns, from `ncu --metrics
-# dram__bytes_read.sum,dram__bytes_write.sum` captures of `python -m cactus_b200.microbench mul_mat` on each of the
-# step's shapes (profiles/mul_mat_q4_0_n64.md).  Keyed by (K, M).
-NCU_DRAM_BYTES_PER_LAUNCH: dict = {(4096, 4096): 9.82e6, (4096, 1024): 2.73e6, (4096, 14336): 33.40e6, (14336, 4096): 34.23e6,
-                                   (4096, 6144): 14.53e6, (4096, 28672): 66.9e6,   # the stacked wq/wk/wv and gate/up products
-                                   (4096, 128256): 296.6e6}   # output head: weight bytes + 1 MB of activations, not captured (1002 CTAs, no K split)
+def ncu_dram_bytes_per_launch() -> dict:
+    """DRAM bytes (read + write) per launch of the mul_mat at 64 columns, keyed by (K, M): ncu captures of
+    `python -m cactus_b200.microbench mul_mat` on each of the step's shapes, kept with their commands in
+    profiles/mul_mat_dram_bytes.json."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "mul_mat_dram_bytes.json")) as f:
+            return {(int(e["K"]), int(e["M"])): float(e["dram_bytes"]) for e in json.load(f)["launches"]}
+    except (OSError, ValueError, KeyError):
+        return {}
 
 
 def mul_mat_roofline(eng, cfg, reps: int = 3):
@@ -191,14 +197,127 @@ def mul_mat_roofline(eng, cfg, reps: int = 3):
     peak, which = peaks()
     achieved = total_bytes / total_ms / 1e6
     traffic = None
-    if all((K, M) in NCU_DRAM_BYTES_PER_LAUNCH for _, K, M, _, _ in shapes):
-        traffic = int(sum(NCU_DRAM_BYTES_PER_LAUNCH[(K, M)] * len(t) for _, K, M, t, _ in shapes))
+    table = ncu_dram_bytes_per_launch()
+    if all((K, M) in table for _, K, M, _, _ in shapes):
+        traffic = int(sum(table[(K, M)] * len(t) for _, K, M, t, _ in shapes))
     return {"bound": "hbm", "kernel": "mmq_kernel<Q4_0,64> (all mul_mat launches of one decode step)", "achieved": round(achieved, 1),
             "peak": peak, "peak_source": which, "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": traffic,
             "algorithmic_bytes_per_step": int(total_bytes), "ms_per_step_in_mul_mat": round(total_ms, 4), "per_shape": per_shape}
 
 
+def fill_prompt_cells(eng, head: int, seed: int):
+    """The prefilled prompts: synthetic K/V ~ N(0, 1) in the cells the prompts own."""
+    import torch
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    for il in range(eng.cfg.n_layer):
+        eng.k_cache[il][:head].copy_(torch.randn((head, eng.k_cache[il].shape[1]), device="cuda", generator=gen).half())
+        eng.v_cache[il][:head].copy_(torch.randn((head, eng.v_cache[il].shape[1]), device="cuda", generator=gen).half())
+
+
+def time_decode_steps(eng, steps_dev, cp0, cs0, K: int, W: int, local: int):
+    """Device time (ms, maximum over the ranks) of K decode ubatches after W untimed ones, inputs resident in HBM;
+    clocks sampled during the timed region."""
+    import torch
+    from cactus_b200 import dist as bdist
+
+    def barrier():
+        torch.cuda.synchronize()
+        bdist.barrier()
+        torch.cuda.synchronize()
+
+    eng.cell_pos.copy_(cp0)
+    eng.cell_seq.copy_(cs0)
+    for s in range(W):
+        eng.inp.copy_(steps_dev[s])
+        eng.run_device(N_SEQ)
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for s in range(W, W + K):
+        if s % N_DECODE == 0:
+            eng.cell_pos.copy_(cp0)
+            eng.cell_seq.copy_(cs0)
+        eng.inp.copy_(steps_dev[s])
+        eng.run_device(N_SEQ)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    return bdist.max_over_ranks(ms, "cuda"), clocks
+
+
+def rowsplit_record(model: str, rank: int, world: int, local: int, lens, head, cp0, cs0, steps_dev, K: int, W: int):
+    """ONE job of `model` on `world` GPUs: every mul_mat weight cut by rows, joined after every product (with one GPU:
+    the plain engine -- the time the speed-ups of the sharded runs refer to)."""
+    import gc
+
+    import torch
+    from cactus_b200.engine import LLAMA_3_8B, LLAMA_3_70B, LlamaEngine, LlamaWeights
+    from cactus_b200.rowsplit import RowSplit
+    cfg = LLAMA_3_70B if model == "70b" else LLAMA_3_8B
+    split = RowSplit(rank, world, 128 << 20) if world > 1 else None
+    weights = LlamaWeights.random(cfg, seed=0, rank=rank, world=world)
+    eng = LlamaEngine(weights, N_CELLS, max_tokens=N_SEQ, split=split)
+    fill_prompt_cells(eng, head, 100)
+    ms, clocks = time_decode_steps(eng, steps_dev, cp0, cs0, K, W, local)
+    status = split.status() if split is not None else 0
+    per_gpu_weight_bytes = cfg.weight_bytes_per_step() / world
+    peak, _ = peaks()
+    rec = {"n_gpus": world, "ms_per_step": round(ms / K, 4), "tok_s": round(N_SEQ * K / (ms / 1e3), 1), "peer_status": status, "steps": K,
+           "launches_per_step": int(eng.launches_per_step[N_SEQ]), "head_parallel_attention": bool(eng.hp),
+           "weight_stream_frac_of_hbm_peak": round(per_gpu_weight_bytes / (ms / K / 1e3) / 1e9 / peak, 4), "sm_mhz": clocks.get("sm_mhz")}
+    del eng, weights
+    if split is not None:
+        split.close()
+    gc.collect()
+    torch.cuda.empty_cache()
+    return rec
+
+
+def other_configs(L, local: int):
+    """The smaller workloads of the hot path, each timed on the device: the single 4096 x 4096 Q4_0 mul_mat at 1, 8 and
+    512 columns (distinct weight copies larger than L2 in turn), and one-sequence decode of the 1B architecture."""
+    from types import SimpleNamespace
+
+    import torch
+    from cactus_b200 import microbench
+    from cactus_b200.engine import LLAMA_32_1B, LlamaEngine, LlamaWeights
+    peak, _ = peaks()
+    out = {"mul_mat_4096x4096_q4_0": {}}
+    for N in (1, 8, 512):
+        r = microbench.bench_mul_mat(SimpleNamespace(K=4096, M=4096, N=N, wtype=2, copies=24, reps=5))
+        out["mul_mat_4096x4096_q4_0"][f"N={N}"] = {"us": round(r["ms_per_launch"] * 1e3, 2), "GBps": round(r["GBps"], 1), "frac_of_hbm_peak": round(r["GBps"] / peak, 3),
+                                                    "TOPS": round(r["TOPS"], 1)}
+    cfg = LLAMA_32_1B
+    eng = LlamaEngine(LlamaWeights.random(cfg, seed=3), 1024, max_tokens=8)
+    n_prompt = 512
+    eng.cell_pos[:n_prompt] = torch.arange(n_prompt, dtype=torch.int32, device="cuda")
+    eng.cell_seq[:n_prompt] = 0
+    fill_prompt_cells(eng, n_prompt, 5)
+    steps = 64
+    for s in range(steps + 5):
+        if s == 5:
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        eng.inp[:, 0] = torch.tensor([s % cfg.vocab, n_prompt + s, 0, n_prompt + s], dtype=torch.int32, device="cuda")
+        eng.run_device(1)
+    e1.record()
+    e1.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    out["llama_1b_one_sequence_decode"] = {"ms_per_token": round(ms, 4), "tok_s": round(1e3 / ms, 1), "context": n_prompt,
+                                           "weight_stream_frac_of_hbm_peak": round(cfg.weight_bytes_per_step() / (ms / 1e3) / 1e9 / peak, 3),
+                                           "launches_per_token": int(eng.launches_per_step[1])}
+    del eng
+    torch.cuda.empty_cache()
+    return out
+
+
 def gpu_arm(args):
+    import gc
+
     import torch
 
     from cactus_b200 import dist as bdist
@@ -226,10 +345,7 @@ def gpu_arm(args):
         weights = LlamaWeights.random(cfg, seed=rank)
         eng = LlamaEngine(weights, N_CELLS, max_tokens=N_SEQ)
     jobs = 1 if rows else world
-    gen = torch.Generator(device="cuda").manual_seed(100 + (0 if rows else rank))
-    for il in range(cfg.n_layer):      # the prefilled prompts: synthetic K/V ~ N(0, 1) in the cells the prompts own
-        eng.k_cache[il][:head].copy_(torch.randn((head, eng.k_cache[il].shape[1]), device="cuda", generator=gen).half())
-        eng.v_cache[il][:head].copy_(torch.randn((head, eng.v_cache[il].shape[1]), device="cuda", generator=gen).half())
+    fill_prompt_cells(eng, head, 100 + (0 if rows else rank))
     cp0, cs0 = torch.from_numpy(cell_pos).cuda(), torch.from_numpy(cell_seq).cuda()
 
     def reset_state():
@@ -247,41 +363,27 @@ def gpu_arm(args):
     steps_dev = torch.from_numpy(np.stack([np.stack(decode_step_inputs(lens, head, s % N_DECODE)) for s in range(total)])).cuda()  # [total,4,64]
 
     # ---- value: inputs resident in HBM, device-timed ---------------------------------------------
-    reset_state()
-    for s in range(W):
-        eng.inp.copy_(steps_dev[s])
-        eng.run_device(N_SEQ)
-    barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
+    ms_max, clocks = time_decode_steps(eng, steps_dev, cp0, cs0, K, W, local)
     launches0 = eng.launches_per_step[N_SEQ]
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for s in range(W, total):
-        if s % N_DECODE == 0:
-            reset_state()
-        eng.inp.copy_(steps_dev[s])
-        eng.run_device(N_SEQ)
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    clocks = sampler.stop()
-    ms_max = bdist.max_over_ranks(ms, "cuda")
     value = jobs * N_SEQ * K / (ms_max / 1e3)
 
     # ---- e2e: the public call with host buffers, H2D of the inputs and D2H of the logits inside ---
-    reset_state()
-    tok = None
-    e2e_steps = min(K, N_DECODE - W)
-    for s in range(W):
-        _, tok = eng.decode(*decode_step_inputs(lens, head, s, tokens=tok))
-    barrier()
-    t0 = time.perf_counter()
-    for s in range(W, W + e2e_steps):
-        logits, tok = eng.decode(*decode_step_inputs(lens, head, s, tokens=tok))
-    torch.cuda.synchronize()
-    dt = time.perf_counter() - t0
-    e2e = bdist.job_throughput(N_SEQ * e2e_steps, dt, "cuda") * jobs / world
+    def e2e_leg(want_logits: bool):
+        reset_state()
+        tok = None
+        n = min(K, N_DECODE - W)
+        for s in range(W):
+            _, tok = eng.decode(*decode_step_inputs(lens, head, s, tokens=tok), want_logits=want_logits)
+        barrier()
+        t0 = time.perf_counter()
+        for s in range(W, W + n):
+            _, tok = eng.decode(*decode_step_inputs(lens, head, s, tokens=tok), want_logits=want_logits)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        return bdist.job_throughput(N_SEQ * n, dt, "cuda") * jobs / world, n
+
+    e2e, e2e_steps = e2e_leg(True)
+    e2e_ids, _ = e2e_leg(False)     # the greedy ids only (b200_argmax_rows on the device): what the 32.8 MB logits read-back costs
     h2d = 4 * N_SEQ * 4
     d2h = N_SEQ * cfg.vocab * 4 + N_SEQ * 4
 
@@ -291,31 +393,48 @@ def gpu_arm(args):
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_layer_sample(reps=2, warmup=1)
 
+    # ---- the sharded job (row split) on the same GPUs, and the smaller workloads --------------------------------
+    del eng, weights
+    if rows:
+        split.close()
+    gc.collect()
+    torch.cuda.empty_cache()
+    rowsplit = None
+    if not args.small and not args.no_extras:
+        Kr = min(K, 10)
+        rowsplit = {"what": "ONE job per model on all GPUs of the run: mul_mat weights cut by rows, every product joined over NVLink "
+                            "(strong scaling); n_gpus 1 = the plain engine"}
+        for model in (("8b", "70b") if world > 1 else ("70b",)):
+            rowsplit[model] = rowsplit_record(model, rank, world, local, lens, head, cp0, cs0, steps_dev, Kr, W)
+        if world == 1:
+            rowsplit["8b"] = {"n_gpus": 1, "ms_per_step": round(ms_max / K, 4), "tok_s": round(value, 1), "peer_status": 0, "steps": K}
+    extras = other_configs(L, local) if (rank == 0 and world == 1 and not args.small and not args.no_extras) else None
+
     if rank == 0:
         kv_bytes = int(lens.sum() + N_SEQ * (W + K / 2)) * cfg.n_layer * 2 * cfg.n_kv_head * cfg.head_dim * 2
         line = {
             "metric": METRIC, "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": round(ms_max / K, 4), "higher_is_better": True, "scaling": "strong" if rows else "weak", "vs_baseline": None,
             "dtype": "int8 x int4/int8 block dots, f32 accumulate; f16 KV", "data": "synthetic",
-            "config": {"workload": ("BASELINE configs[4] architecture (Llama-3-70B) on the configs[3] workload" if args.model == "70b" and not args.small
-                                    else "BASELINE configs[3]: Llama-3-8B architecture") + ", random N(0,0.02) weights in Q4_0, 64 sequences, "
-                                   "unified f16 KV cache of 65536 cells, one decode ubatch of 64 tokens per step",
+            "config": {"workload": ("Llama-3-70B architecture" if args.model == "70b" and not args.small else "Llama-3-8B architecture") +
+                                   ", random N(0,0.02) weights in Q4_0, continuous batching of 64 sequences in a unified f16 KV cache of 65536 cells, "
+                                   "one decode ubatch of 64 tokens per step",
                        "prompt_lengths": f"U[16,2048] seed 0 scaled by {scale:.3f} to leave 128 decode cells per sequence; "
                                          f"{int(lens.sum())} prompt cells hold synthetic N(0,1) K/V",
                        "parallelism": (f"row split over {world} GPUs: every mul_mat weight cut by rows, the products' own write-back stores into every GPU's "
                                        f"buffers over NVLink (b200_mul_mat_q_rowsplit / _stacked); attention, rope and the KV cache follow the heads of a rank "
                                        f"(attention output joined with b200_allgather_rows), norms replicated; peer_status {peer_status}") if rows
-                                      else ("one replica per GPU, no collective" if world > 1 else "single GPU"),
+                                      else ("one replica per GPU, no collective (the row split of the same GPUs is in `rowsplit`)" if world > 1 else "single GPU"),
                        "model": args.model if not args.small else "small",
                        "l2": "inputs larger than L2: 4.2 GB of weights and ~7 GB of KV are streamed every step"},
-            "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "ids_only": {"value": round(e2e_ids, 1), "unit": "tok/s", "d2h_bytes_per_step": N_SEQ * 4}},
             "gpu_launches": int(launches0 * K), "launches_per_step": int(launches0),
             "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
             "step_bytes": {"weights": cfg.weight_bytes_per_step(), "kv_read_about": kv_bytes},
+            "rowsplit": rowsplit, "other_configs": extras,
         }
         print(json.dumps(line))
-    if rows:
-        split.close()
     bdist.shutdown()
 
 
@@ -331,7 +450,7 @@ def reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": round(r["value"], 3), "unit": "tok/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")),
         "steps": K, "warmup": W, "ms_per_step": round(r["step_seconds"] * 1e3, 2), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8 x int4 block dots (AVX2), f32 accumulate", "data": "synthetic",
-        "config": {"workload": "BASELINE configs[3] decode ubatch of 64 tokens, reference ggml-cpu on the host cores, timed on a bounded sample",
+        "config": {"workload": "Llama-3-8B architecture, Q4_0, decode ubatch of 64 tokens over the 64-sequence cache: reference ggml-cpu on the host cores, timed on a bounded sample",
                    "sample": r["sample"], "timed_reps_per_op": reps, "wall_seconds": None},
         "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": round(r["value"], 3), "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -350,8 +469,9 @@ def main():
     ap.add_argument("--split", default="none", choices=["none", "rows"],
                     help="rows: ONE job whose mul_mat weights are row-split over the GPUs and joined after every product (strong scaling); "
                          "none: one replica per GPU (weak scaling, the default)")
-    ap.add_argument("--model", default="8b", choices=["8b", "70b"], help="70b: BASELINE configs[4] architecture on the same 64-sequence workload")
+    ap.add_argument("--model", default="8b", choices=["8b", "70b"], help="70b: the Llama-3-70B architecture on the same 64-sequence workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extras", action="store_true", help="skip the row-split record and the smaller workloads")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)

@@ -354,6 +354,12 @@ class LlamaEngine:
             self.logits_host[:T].copy_(self.logits[:T], non_blocking=True)
         self.ids_host[:T].copy_(self.next_ids[:T], non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        if self.split is not None:
+            # a join whose bounded wait ran out leaves a peer's rows stale in the joined buffers: the logits are not to be trusted
+            st = self.split.status()
+            if st != 0:
+                from ._lib import B200Error
+                raise B200Error(f"row split: the rows of rank {st - 1} did not arrive within the wait limit")
         return (self.logits_host[:T].numpy() if want_logits else None), self.ids_host[:T].numpy()
 
     def clear(self):
