@@ -315,6 +315,29 @@ def other_configs(L, local: int):
     return out
 
 
+def plugin_record():
+    """The same decode step through the drop-in itself: the ggml backend plug-in driven by the reference's unchanged
+    llama_decode (tests/_bin/harness, built where a checkout of the reference is present; it travels as a binary with the
+    reference's runtime compiled into oracle/_ref).  Synthetic 8B GGUF written to /tmp, 64 sequences with random prompts
+    in a 65536-cell cache, then timed 64-token decode batches; the KQ mask is synthesised on the device (the driver's
+    replacement of set_input_kq_mask hands the cell metadata to the backend's extension proc)."""
+    harness = os.path.join(ROOT, "tests", "_bin", "harness")
+    if not os.path.exists(harness):
+        return {"unavailable": "tests/_bin/harness was not built (needs a checkout of the reference at build time)"}
+    cmd = [harness, "model", "--layers", "32", "--d", "4096", "--heads", "32", "--kv", "8", "--ff", "14336", "--vocab", "128256", "--ctx", "65536",
+           "--seqs", "64", "--max-prompt", "1790", "--skip-cpu", "--head-q4", "--bench-steps", "10", "--decode", "2", "--device-mask", "--path", "/tmp/b200_bench_8b.gguf"]
+    try:
+        p = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=dict(os.environ, B200_TIMING="1"))
+        r = [json.loads(line) for line in p.stdout.splitlines() if line.startswith("{")][-1]
+    except (subprocess.SubprocessError, IndexError, ValueError, OSError) as e:
+        return {"unavailable": f"harness run failed: {e!r}"[:200]}
+    if "error" in r:
+        return {"unavailable": str(r)[:200]}
+    return {"path": "llama_decode (reference runtime, unchanged) -> scheduler -> libggml-b200.so graph_compute -> C ABI", "ms_per_step_wall": r["b200_step_ms"],
+            "tok_s": round(N_SEQ / (r["b200_step_ms"] / 1e3), 1), "device_ms_per_step": r["device_ms_per_graph"], "device_side_masks": r["device_masks"],
+            "logits": "full 64 x 128256 f32 read back into the context's pinned buffer every step", "steps": 10}
+
+
 def gpu_arm(args):
     import gc
 
@@ -409,6 +432,7 @@ def gpu_arm(args):
         if world == 1:
             rowsplit["8b"] = {"n_gpus": 1, "ms_per_step": round(ms_max / K, 4), "tok_s": round(value, 1), "peer_status": 0, "steps": K}
     extras = other_configs(L, local) if (rank == 0 and world == 1 and not args.small and not args.no_extras) else None
+    plugin = plugin_record() if (rank == 0 and world == 1 and not args.small and not args.no_extras) else None
 
     if rank == 0:
         kv_bytes = int(lens.sum() + N_SEQ * (W + K / 2)) * cfg.n_layer * 2 * cfg.n_kv_head * cfg.head_dim * 2
@@ -432,7 +456,7 @@ def gpu_arm(args):
             "gpu_launches": int(launches0 * K), "launches_per_step": int(launches0),
             "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
             "step_bytes": {"weights": cfg.weight_bytes_per_step(), "kv_read_about": kv_bytes},
-            "rowsplit": rowsplit, "other_configs": extras,
+            "rowsplit": rowsplit, "other_configs": extras, "plugin": plugin,
         }
         print(json.dumps(line))
     bdist.shutdown()

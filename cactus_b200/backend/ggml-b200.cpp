@@ -149,9 +149,63 @@ void buffer_memset_tensor(lm_ggml_backend_buffer_t buffer, lm_ggml_tensor * tens
     cudaStreamSynchronize(nullptr);
 }
 
+// ---------------------------------------------------------------------------------------------
+// KQ mask synthesised on the device (extension proc "lm_ggml_backend_b200_kq_mask_from_cells").
+// llama_kv_cache_unified::set_input_kq_mask (cactus/llama-kv-cache.cpp:696-761) fills an f32 mask of n_kv x pad64(n_tokens)
+// on the host, one std::set lookup per (token, cell), the scheduler uploads it and a CPY node casts it to f16.  A driver
+// that knows the cells hands over what the loop reads instead -- position and sequence of every cell of the attended
+// window, position and sequence of every token -- together with the host address of the mask tensor it did NOT fill.
+// When the scheduler then uploads from that address, the upload is skipped (the small arrays go up instead), and the CPY
+// node that reads the uploaded tensor writes the f16 mask with b200_kq_mask_build.  One sequence per cell; the driver
+// keeps the host loop for anything else (ALiBi, sliding windows, cells shared by sequences).
+// ---------------------------------------------------------------------------------------------
+struct kq_mask_hint_t {
+    std::mutex mu;
+    const void * host_mask = nullptr;
+    size_t host_bytes = 0;
+    std::vector<int32_t> cell_pos, cell_seq, tok_pos, tok_seq;
+    uint64_t serial = 0;
+    struct dev_state {
+        int32_t * buf = nullptr;      // [cell_pos | cell_seq | tok_pos | tok_seq]
+        size_t cap = 0;               // in int32
+        const void * dev_mask = nullptr;   // the uploaded f32 tensor that stands for the mask
+        int64_t n_kv = 0, n_tokens = 0;
+        uint64_t serial = 0;
+    } dev[LM_GGML_B200_MAX_DEVICES];
+    std::atomic<uint64_t> masks_built{0};
+};
+kq_mask_hint_t g_kq_hint;
+
+// true: `data` is the mask the driver left unfilled; its description is now on device `device`, `dst` stands for it
+bool kq_hint_take_upload(int device, const void * data, size_t size, const void * dst) {
+    kq_mask_hint_t & h = g_kq_hint;
+    std::lock_guard<std::mutex> lock(h.mu);
+    if (!h.host_mask || data != h.host_mask || size != h.host_bytes || device < 0 || device >= LM_GGML_B200_MAX_DEVICES) return false;
+    kq_mask_hint_t::dev_state & d = h.dev[device];
+    const size_t n_kv = h.cell_pos.size(), n_tok = h.tok_pos.size(), need = 2 * n_kv + 2 * n_tok;
+    if (need > d.cap) {
+        if (d.buf) cudaFree(d.buf);
+        d.buf = nullptr;
+        d.cap = 0;
+        if (!cuda_ok(cudaMalloc((void **) &d.buf, need * 2 * sizeof(int32_t)), "cudaMalloc(kq mask cells)")) return false;
+        d.cap = need * 2;
+    }
+    bool ok = cuda_ok(cudaMemcpy(d.buf, h.cell_pos.data(), n_kv * 4, cudaMemcpyHostToDevice), "cudaMemcpy(cells)");
+    ok = ok && cuda_ok(cudaMemcpy(d.buf + n_kv, h.cell_seq.data(), n_kv * 4, cudaMemcpyHostToDevice), "cudaMemcpy(cells)");
+    ok = ok && cuda_ok(cudaMemcpy(d.buf + 2 * n_kv, h.tok_pos.data(), n_tok * 4, cudaMemcpyHostToDevice), "cudaMemcpy(tokens)");
+    ok = ok && cuda_ok(cudaMemcpy(d.buf + 2 * n_kv + n_tok, h.tok_seq.data(), n_tok * 4, cudaMemcpyHostToDevice), "cudaMemcpy(tokens)");
+    if (!ok) return false;
+    d.dev_mask = dst;
+    d.n_kv = (int64_t) n_kv;
+    d.n_tokens = (int64_t) n_tok;
+    d.serial = h.serial;
+    return true;
+}
+
 void buffer_set_tensor(lm_ggml_backend_buffer_t buffer, lm_ggml_tensor * tensor, const void * data, size_t offset, size_t size) {
     b200_buffer_ctx * ctx = (b200_buffer_ctx *) buffer->context;
     device_guard g(ctx->device);
+    if (offset == 0 && tensor->type == LM_GGML_TYPE_F32 && kq_hint_take_upload(ctx->device, data, size, tensor->data)) return;
     if (tensor_is_tiled(tensor)) {
         LM_GGML_ASSERT(tiled_transfer(ctx, tensor, const_cast<void *>(data), offset, size, true));
         return;
@@ -487,6 +541,11 @@ struct split_peer {
     const lm_ggml_tensor * act_src = nullptr;
 };
 
+struct rope_store_state {
+    bool active = false;
+    const lm_ggml_tensor * rope_q = nullptr, * rope_k = nullptr, * cpy_k = nullptr, * cpy_v = nullptr, * v_src = nullptr;
+};
+
 struct b200_backend_ctx {
     int device;
     std::string name;
@@ -501,6 +560,8 @@ struct b200_backend_ctx {
     void * abort_cb_data = nullptr;
     int q8_variant = B200_Q8_AVX2;
     bool fa_parity = false;  // B200_FA_PARITY=1: the reference-order attention kernel (validation)
+    bool fuse = true;        // B200_FUSE=0: one kernel per node (except the norm and silu pairs)
+    rope_store_state rs;     // the ROPE / cache-store group of a layer that one kernel will do
     bool timing = false;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     lm_ggml_b200_stats stats = {};
@@ -765,6 +826,11 @@ lm_ggml_status compute_cpy(b200_backend_ctx * ctx, const lm_ggml_tensor * node, 
 // theirs.  Only this device needs the result -- the next node runs here (cactus/llama-model.cpp:342-351 makes the
 // layer's device the main device of its split buffer).
 std::atomic<uint64_t> g_split_mul_mats{0};
+// CUDA-event time of every graph_compute of every backend of the process (B200_TIMING=1), for drivers that cannot reach
+// the backends a llama_context owns
+std::mutex g_totals_mu;
+double g_total_device_ms = 0.0;
+uint64_t g_total_timed_graphs = 0;
 
 bool split_peer_init(b200_backend_ctx * ctx, int dev) {
     split_peer & p = ctx->peers[dev];
@@ -840,6 +906,83 @@ lm_ggml_status compute_mul_mat_split(b200_backend_ctx * ctx, lm_ggml_tensor * no
     return LM_GGML_STATUS_SUCCESS;
 }
 
+// ROPE(q), ROPE(k), CPY(k -> cache) and CPY(v -> cache) of one layer as one kernel (b200_rope_store).  llm_build_llama
+// emits them as: ROPE q ... ROPE k ... [V product] ... CPY k, CPY v, with the K and V products in between
+// (cactus/llama-model.cpp:4576-4596, cactus/llama-kv-cache.cpp:617-656), so the group is recognised when its first ROPE
+// comes up, its four nodes are skipped, and the kernel runs in the place of the V store -- after everything it reads has
+// been computed and before the attention that reads the cache (node order is the only ordering the graph has there).
+// Needs: q rotated in place (the allocator reuses the product's buffer), same positions and parameters for both
+// ROPEs, K and V stored as f16 into whole consecutive cache rows.
+const lm_ggml_tensor * through_views(const lm_ggml_tensor * t) {
+    while (t && (t->op == LM_GGML_OP_RESHAPE || t->op == LM_GGML_OP_VIEW) && t->src[0]) t = t->src[0];
+    return t;
+}
+
+bool rope_store_group(b200_backend_ctx * ctx, const lm_ggml_cgraph * g, int i) {
+    rope_store_state & rs = ctx->rs;
+    const lm_ggml_tensor * node = g->nodes[i];
+    if (rs.active) return node == rs.rope_q || node == rs.rope_k;   // a member of the group in flight: skip it
+    if (node->src[0]->type != LM_GGML_TYPE_F32 || node->data != node->src[0]->data || !lm_ggml_is_contiguous(node)) return false;
+    const lm_ggml_tensor * rq = node, * rk = nullptr, * ck = nullptr, * cv = nullptr;
+    for (int j = i + 1; j < g->n_nodes && j < i + 24; ++j) {
+        const lm_ggml_tensor * n = g->nodes[j];
+        if (n->op == LM_GGML_OP_ROPE) {
+            if (rk) return false;
+            rk = n;
+        } else if (n->op == LM_GGML_OP_CPY) {
+            if (!ck) ck = n;
+            else { cv = n; break; }
+        } else if (n->op == LM_GGML_OP_FLASH_ATTN_EXT) {
+            return false;
+        }
+    }
+    if (!rk || !ck || !cv) return false;
+    if (rk->src[0]->type != LM_GGML_TYPE_F32 || rk->src[1] != rq->src[1] || rk->src[2] != rq->src[2] || !lm_ggml_is_contiguous(rk) ||
+        memcmp(rk->op_params, rq->op_params, sizeof(int32_t) * 11) != 0) return false;
+    const int64_t D = rq->ne[0], T = rq->ne[2], Hkv = rk->ne[1];
+    if (rk->ne[0] != D || rk->ne[2] != T || rq->ne[3] != 1 || rk->ne[3] != 1) return false;
+    // the K store reads the rotated k, the V store the V product; both write f16 rows of Hkv * D values, T of them in a row
+    const lm_ggml_tensor * ksrc = through_views(ck->src[0]), * vsrc = through_views(cv->src[0]);
+    const lm_ggml_tensor * kdst = ck->src[1], * vdst = cv->src[1];
+    if (ksrc != rk || !vsrc || vsrc->op != LM_GGML_OP_MUL_MAT || !kdst || !vdst) return false;
+    if (kdst->type != LM_GGML_TYPE_F16 || vdst->type != LM_GGML_TYPE_F16 || !lm_ggml_is_contiguous(kdst) || !lm_ggml_is_contiguous(vdst)) return false;
+    if (lm_ggml_nelements(kdst) != Hkv * D * T || lm_ggml_nelements(vdst) != Hkv * D * T || lm_ggml_nelements(vsrc) != Hkv * D * T) return false;
+    if (!lm_ggml_is_contiguous(vsrc) || !lm_ggml_is_contiguous(rk->src[0])) return false;
+    if (!only_user_is(g, rk, ck)) {
+        // the rotated k may only feed the store (through its views): nobody else reads the f32 result that is not produced
+        for (int j = i + 1; j < g->n_nodes; ++j) {
+            const lm_ggml_tensor * n = g->nodes[j];
+            if (n == ck) continue;
+            for (int s = 0; s < LM_GGML_MAX_SRC; ++s)
+                if (n->src[s] && through_views(n->src[s]) == rk && !(n->op == LM_GGML_OP_RESHAPE || n->op == LM_GGML_OP_VIEW)) return false;
+        }
+    }
+    if (((uintptr_t) rq->data % 8) || ((uintptr_t) rk->src[0]->data % 8) || ((uintptr_t) vsrc->data % 8) || ((uintptr_t) kdst->data % 4) || ((uintptr_t) vdst->data % 4)) return false;
+    rs.active = true;
+    rs.rope_q = rq; rs.rope_k = rk; rs.cpy_k = ck; rs.cpy_v = cv; rs.v_src = vsrc;
+    return true;
+}
+
+lm_ggml_status rope_store_run(b200_backend_ctx * ctx) {
+    rope_store_state & rs = ctx->rs;
+    const lm_ggml_tensor * node = rs.rope_q;   // for B200_CHECK's message
+    const lm_ggml_tensor * rq = rs.rope_q, * rk = rs.rope_k;
+    const int32_t * p = (const int32_t *) rq->op_params;
+    float freq_base, freq_scale, attn_factor;
+    memcpy(&freq_base, p + 5, sizeof(float));
+    memcpy(&freq_scale, p + 6, sizeof(float));
+    memcpy(&attn_factor, p + 8, sizeof(float));
+    const int64_t D = rq->ne[0], H = rq->ne[1], T = rq->ne[2], Hkv = rk->ne[1];
+    rs.active = false;
+    B200_CHECK(b200_rope_store((float *) rq->data, rq->nb[1], rq->nb[2], (const float *) rk->src[0]->data, rk->src[0]->nb[1], rk->src[0]->nb[2],
+                               (const float *) rs.v_src->data, Hkv * D * 4, D, H, Hkv, T, p[1], (const int32_t *) rq->src[1]->data,
+                               rq->src[2] ? (const float *) rq->src[2]->data : nullptr, freq_base, freq_scale, attn_factor, nullptr,
+                               rs.cpy_k->src[1]->data, Hkv * D * 2, rs.cpy_v->src[1]->data, Hkv * D * 2, ctx->stream));
+    ctx->stats.nodes += 3;
+    ctx->stats.rope_stores++;
+    return LM_GGML_STATUS_SUCCESS;
+}
+
 lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph * cgraph) {
     b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
     device_guard g(ctx->device);
@@ -847,6 +990,7 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
     ctx->act_src = nullptr;
     for (split_peer & p : ctx->peers) p.act_src = nullptr;
     ctx->index_mask = nullptr;
+    ctx->rs.active = false;
     ctx->stats.graphs++;
     if (ctx->timing) cudaEventRecord(ctx->ev0, st);
 
@@ -952,6 +1096,35 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
             } break;
             case LM_GGML_OP_ADD:
             case LM_GGML_OP_MUL: {
+                if (node->op == LM_GGML_OP_ADD && ctx->fuse) {
+                    // residual ADD written over one of its operands, then RMS_NORM, MUL by the norm weight and a MUL_MAT on the
+                    // result (ffn_inp -> ffn_norm -> gate/up, l_out -> next layer's attn_norm -> q/k/v): one kernel
+                    lm_ggml_tensor * rn = i + 1 < cgraph->n_nodes ? cgraph->nodes[i + 1] : nullptr;
+                    lm_ggml_tensor * mu = i + 2 < cgraph->n_nodes ? cgraph->nodes[i + 2] : nullptr;
+                    lm_ggml_tensor * mm = i + 3 < cgraph->n_nodes ? cgraph->nodes[i + 3] : nullptr;
+                    const int64_t d = s0->ne[0], rows = lm_ggml_nrows(s0);
+                    const bool in_place = node->data == s0->data || node->data == s1->data;
+                    if (in_place && lm_ggml_are_same_shape(s0, s1) && rn && mu && mm && rn->op == LM_GGML_OP_RMS_NORM && rn->src[0] == node &&
+                        mu->op == LM_GGML_OP_MUL && mu->src[0] == rn && mu->src[1] && mu->src[1]->type == LM_GGML_TYPE_F32 && mu->src[1]->ne[0] == d &&
+                        lm_ggml_nelements(mu->src[1]) == d && lm_ggml_is_contiguous(mu->src[1]) && lm_ggml_is_contiguous(mu) && only_user_is(cgraph, rn, mu) &&
+                        mm->op == LM_GGML_OP_MUL_MAT && mm->src[1] == mu && d % 32 == 0 && d <= 16384 && ((uintptr_t) s0->data % 16) == 0 &&
+                        ((uintptr_t) s1->data % 16) == 0 && ((uintptr_t) mu->data % 16) == 0 && mu->data != node->data) {
+                        void * act = ctx->act.get(b200_act_bytes(d, rows), st);
+                        if (act) {
+                            float eps;
+                            memcpy(&eps, rn->op_params, sizeof(float));
+                            float * x = (float *) node->data;
+                            const float * res = node->data == s0->data ? (const float *) s1->data : (const float *) s0->data;
+                            B200_CHECK(b200_add_rms_norm_quantize(x, d * 4, res, d * 4, (const float *) mu->src[1]->data, (float *) mu->data, d * 4, d, rows, eps,
+                                                                  act, ctx->act.bytes, ctx->q8_variant, st));
+                            ctx->act_src = mu;
+                            ctx->stats.act_quantized++;
+                            ctx->stats.nodes += 2;
+                            i += 2;
+                            break;
+                        }
+                    }
+                }
                 const int64_t d = s0->ne[0], rows = lm_ggml_nrows(s0);
                 const int64_t brows = lm_ggml_are_same_shape(s0, s1) ? rows : 1;
                 if (node->op == LM_GGML_OP_ADD) B200_CHECK(b200_add((const float *) s0->data, (const float *) s1->data, (float *) node->data, d, rows, brows, st));
@@ -984,6 +1157,7 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
                 }
             } break;
             case LM_GGML_OP_ROPE: {
+                if (ctx->fuse && rope_store_group(ctx, cgraph, i)) break;   // this ROPE, or the group it starts, is done by one kernel at the V store
                 const int32_t * p = (const int32_t *) node->op_params;
                 float freq_base, freq_scale, attn_factor;
                 memcpy(&freq_base, p + 5, sizeof(float));
@@ -1000,6 +1174,25 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
                                           freq_base, freq_scale, attn_factor, st));
             } break;
             case LM_GGML_OP_CPY: {
+                if (ctx->rs.active && (node == ctx->rs.cpy_k || node == ctx->rs.cpy_v)) {
+                    if (node == ctx->rs.cpy_v) {
+                        const lm_ggml_status rc = rope_store_run(ctx);
+                        if (rc != LM_GGML_STATUS_SUCCESS) return rc;
+                    }
+                    break;
+                }
+                {   // the f32 -> f16 cast of a mask the driver described instead of filling: synthesise the f16 mask
+                    kq_mask_hint_t::dev_state & d = g_kq_hint.dev[ctx->device];
+                    const lm_ggml_tensor * dstt = s1 ? s1 : node;
+                    if (d.dev_mask && s0->data == d.dev_mask && d.serial == g_kq_hint.serial && s0->type == LM_GGML_TYPE_F32 &&
+                        dstt->type == LM_GGML_TYPE_F16 && lm_ggml_is_contiguous(dstt) && s0->ne[0] == d.n_kv && s0->ne[1] == (d.n_tokens + 63) / 64 * 64 &&
+                        lm_ggml_nelements(s0) == lm_ggml_nelements(dstt)) {
+                        B200_CHECK(b200_kq_mask_build(d.buf, d.buf + d.n_kv, d.n_kv, d.buf + 2 * d.n_kv, d.buf + 2 * d.n_kv + d.n_tokens, d.n_tokens,
+                                                      dstt->data, d.n_kv * 2, st));
+                        g_kq_hint.masks_built.fetch_add(1, std::memory_order_relaxed);
+                        break;
+                    }
+                }
                 lm_ggml_status rc = compute_cpy(ctx, node, s0, s1 ? s1 : node);
                 if (rc != LM_GGML_STATUS_SUCCESS) return rc;
             } break;
@@ -1027,6 +1220,9 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
         float ms = 0;
         cudaEventElapsedTime(&ms, ctx->ev0, ctx->ev1);
         ctx->stats.device_ms += ms;
+        std::lock_guard<std::mutex> lock(g_totals_mu);
+        g_total_device_ms += ms;
+        g_total_timed_graphs++;
     }
     return LM_GGML_STATUS_SUCCESS;
 }
@@ -1222,7 +1418,34 @@ lm_ggml_backend_buffer_type_t split_buffer_type(int main_device, const float * t
     return made.back();
 }
 
+// Extension proc: the next upload from `mask_host_data` (mask_bytes = n_kv * pad64(n_tokens) * 4) is a mask that was not
+// filled; what it would hold follows from the cells and tokens given here.  Null mask_host_data withdraws the hint.
+void kq_mask_from_cells(const void * mask_host_data, size_t mask_bytes, const int32_t * cell_pos, const int32_t * cell_seq, int64_t n_kv,
+                        const int32_t * tok_pos, const int32_t * tok_seq, int64_t n_tokens) {
+    kq_mask_hint_t & h = g_kq_hint;
+    std::lock_guard<std::mutex> lock(h.mu);
+    h.serial++;
+    h.host_mask = nullptr;
+    if (!mask_host_data || !cell_pos || !cell_seq || !tok_pos || !tok_seq || n_kv <= 0 || n_tokens <= 0) return;
+    if (mask_bytes != (size_t) n_kv * (size_t) ((n_tokens + 63) / 64 * 64) * sizeof(float)) return;
+    h.cell_pos.assign(cell_pos, cell_pos + n_kv);
+    h.cell_seq.assign(cell_seq, cell_seq + n_kv);
+    h.tok_pos.assign(tok_pos, tok_pos + n_tokens);
+    h.tok_seq.assign(tok_seq, tok_seq + n_tokens);
+    h.host_mask = mask_host_data;
+    h.host_bytes = mask_bytes;
+}
+uint64_t kq_masks_built() { return g_kq_hint.masks_built.load(); }
+void timing_totals(double * device_ms, uint64_t * graphs) {
+    std::lock_guard<std::mutex> lock(g_totals_mu);
+    if (device_ms) *device_ms = g_total_device_ms;
+    if (graphs) *graphs = g_total_timed_graphs;
+}
+
 void * reg_get_proc_address(lm_ggml_backend_reg_t, const char * name) {
+    if (strcmp(name, "lm_ggml_backend_b200_kq_mask_from_cells") == 0) return (void *) kq_mask_from_cells;
+    if (strcmp(name, "lm_ggml_backend_b200_kq_masks_built") == 0) return (void *) kq_masks_built;
+    if (strcmp(name, "lm_ggml_backend_b200_timing_totals") == 0) return (void *) timing_totals;
     if (strcmp(name, "lm_ggml_backend_split_buffer_type") == 0) return (void *) split_buffer_type;
     if (strcmp(name, "lm_ggml_backend_set_abort_callback") == 0) return (void *) set_abort_callback;
     if (strcmp(name, "lm_ggml_backend_get_features") == 0) return (void *) get_features;
@@ -1298,6 +1521,8 @@ lm_ggml_backend_t lm_ggml_backend_b200_init(int device) {
     }
     const char * v = getenv("B200_Q8_VARIANT");
     if (v && strcmp(v, "scalar") == 0) ctx->q8_variant = B200_Q8_SCALAR;
+    const char * fu = getenv("B200_FUSE");
+    ctx->fuse = !(fu && atoi(fu) == 0);
     const char * fp = getenv("B200_FA_PARITY");
     ctx->fa_parity = fp && atoi(fp) != 0;
     const char * t = getenv("B200_TIMING");

@@ -34,9 +34,24 @@ struct lm_ggml_b200_stats {
     uint64_t flash_attn;      // FLASH_ATTN_EXT nodes
     uint64_t act_quantized;   // activation tensors quantised (shared by consecutive mul_mats)
     uint64_t mask_indexed;    // mask scans (shared by all layers of a graph)
+    uint64_t rope_stores;     // ROPE(q), ROPE(k), CPY(k), CPY(v) groups done by one kernel
     double   device_ms;       // CUDA-event time of all graph_compute calls when timing is on (B200_TIMING=1)
 };
 LM_GGML_BACKEND_API void lm_ggml_backend_b200_get_stats(lm_ggml_backend_t backend, struct lm_ggml_b200_stats * out);
+// Extension procs behind lm_ggml_backend_reg_get_proc_address (private to this backend):
+//   "lm_ggml_backend_b200_kq_mask_from_cells": the driver did not fill the f32 KQ mask whose host data is
+//   `mask_host_data` (n_kv * pad64(n_tokens) floats); the next upload from that address is skipped and the CPY node
+//   that casts the uploaded tensor to f16 writes, on the device, what llama_kv_cache_unified::set_input_kq_mask
+//   (cactus/llama-kv-cache.cpp:696-761) would have written: 0 where cell i holds sequence tok_seq[j] and
+//   cell_pos[i] <= tok_pos[j], -inf elsewhere and in the padding rows.  cell_seq[i] = -1 for an empty cell; one sequence
+//   per cell.  The arrays are copied before the call returns.  A null mask_host_data withdraws the hint.
+//   "lm_ggml_backend_b200_kq_masks_built": how many masks were synthesised that way since the process started.
+typedef void (*lm_ggml_b200_kq_mask_from_cells_t)(const void * mask_host_data, size_t mask_bytes, const int32_t * cell_pos, const int32_t * cell_seq,
+                                                  int64_t n_kv, const int32_t * tok_pos, const int32_t * tok_seq, int64_t n_tokens);
+typedef uint64_t (*lm_ggml_b200_kq_masks_built_t)(void);
+//   "lm_ggml_backend_b200_timing_totals": CUDA-event time and count of all graph_compute calls of all backends of the
+//   process while B200_TIMING=1 (for drivers that cannot reach the backends a llama_context owns).
+typedef void (*lm_ggml_b200_timing_totals_t)(double * device_ms, uint64_t * graphs);
 // MUL_MAT nodes computed on weights of the split buffer type since the process started (all backends)
 LM_GGML_BACKEND_API uint64_t lm_ggml_backend_b200_split_mul_mat_count(void);
 

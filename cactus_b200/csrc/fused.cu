@@ -15,8 +15,9 @@ int act_layout(int64_t N);
 // quantised store.  The sum of squares is accumulated in the order rms_norm_kernel uses (rms_block_sum), so the
 // scale -- and with it every quantised value -- is bit-identical to the unfused chain.
 template <int LAYOUT>
-__global__ void __launch_bounds__(1024) add_rms_norm_quantize_kernel(float *__restrict__ x, int64_t x_nb_row, const float *__restrict__ res,
-                                                                    int64_t res_nb_row, const float *__restrict__ w, float *__restrict__ h,
+// (x, res and h carry no __restrict__: a graph allocator may hand the same memory to the residual and to the normalised output)
+__global__ void __launch_bounds__(1024) add_rms_norm_quantize_kernel(float *x, int64_t x_nb_row, const float *res,
+                                                                    int64_t res_nb_row, const float *__restrict__ w, float *h,
                                                                     int64_t h_nb_row, int64_t d, int64_t N, float eps, int64_t nb, int64_t nbp,
                                                                     uint8_t *__restrict__ out, size_t d_offset, int variant) {
     pdl_prologue();
@@ -68,8 +69,8 @@ __global__ void __launch_bounds__(1024) add_rms_norm_quantize_kernel(float *__re
 
 // silu(gate) * up, quantised; the same index space as quantize_q8_0_kernel
 template <int LAYOUT>
-__global__ void __launch_bounds__(256) silu_mul_quantize_kernel(const float *__restrict__ gate, const float *__restrict__ up, int64_t nb_row,
-                                                               float *__restrict__ dst, int64_t dst_nb_row,
+__global__ void __launch_bounds__(256) silu_mul_quantize_kernel(const float *gate, const float *up, int64_t nb_row,
+                                                               float *dst, int64_t dst_nb_row,
                                                                int64_t N, int64_t n_rows_padded, int64_t nb, int64_t nbp,
                                                                uint8_t *__restrict__ out, size_t d_offset, int variant) {
     pdl_prologue();
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(512) rope_store_kernel(float *__restrict__ q, 
     }
     __syncthreads();
     const int64_t pairs = D / 2;
-    const int64_t slot = slots[t];
+    const int64_t slot = slots ? (int64_t) slots[t] : t;   // no slot list: token t goes to row t of the cache pointers given
     __half *krow = reinterpret_cast<__half *>(reinterpret_cast<char *>(kc) + slot * kc_nb_row);
     __half *vrow = reinterpret_cast<__half *>(reinterpret_cast<char *>(vc) + slot * vc_nb_row);
     for (int64_t i = threadIdx.x; i < (H + 2 * Hkv) * pairs; i += blockDim.x) {
@@ -209,7 +210,7 @@ int b200_rope_store(float *q, int64_t q_nb_head, int64_t q_nb_tok, const float *
                     int64_t v_nb_tok, int64_t D, int64_t H, int64_t Hkv, int64_t T, int n_dims, const int32_t *pos, const float *freq_factors,
                     float freq_base, float freq_scale, float attn_factor, const int32_t *slots, void *k_cache, int64_t k_cache_nb_row,
                     void *v_cache, int64_t v_cache_nb_row, b200_stream_t stream) {
-    B200_REQUIRE(q && k && v && pos && slots && k_cache && v_cache, "null pointer");
+    B200_REQUIRE(q && k && v && pos && k_cache && v_cache, "null pointer");
     B200_REQUIRE(D > 0 && D % 2 == 0 && H > 0 && Hkv > 0 && T >= 0 && n_dims > 0 && n_dims <= D && n_dims % 2 == 0, "bad rope arguments");
     B200_REQUIRE(q_nb_head % 8 == 0 && q_nb_tok % 8 == 0 && k_nb_head % 8 == 0 && k_nb_tok % 8 == 0 && v_nb_tok % 8 == 0 && is_aligned(q, 8) &&
                      is_aligned(k, 8) && is_aligned(v, 8) && k_cache_nb_row % 4 == 0 && v_cache_nb_row % 4 == 0 && is_aligned(k_cache, 4) && is_aligned(v_cache, 4),

@@ -6,8 +6,8 @@ namespace b200 {
 
 // RMS_NORM: ops.cpp:3268-3316.  The reference sums squares in double and scales by 1/sqrtf(mean + eps);
 // a following MUL by the weight row (binary-ops.cpp:152-154) is fused when w != NULL.
-__global__ void __launch_bounds__(1024) rms_norm_kernel(const float *__restrict__ x, int64_t x_nb_row, const float *__restrict__ w,
-                                                       float *__restrict__ dst, int64_t dst_nb_row, int64_t d, float eps) {
+__global__ void __launch_bounds__(1024) rms_norm_kernel(const float *x, int64_t x_nb_row, const float *__restrict__ w,
+                                                       float *dst, int64_t dst_nb_row, int64_t d, float eps) {
     const int64_t r = blockIdx.x;
     const float *xr = reinterpret_cast<const float *>(reinterpret_cast<const char *>(x) + r * x_nb_row);
     float *o = reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + r * dst_nb_row);
@@ -32,7 +32,7 @@ __global__ void __launch_bounds__(1024) rms_norm_kernel(const float *__restrict_
 }
 
 template <int OP>  // 0 add, 1 mul
-__global__ void __launch_bounds__(256) binary_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ dst,
+__global__ void __launch_bounds__(256) binary_kernel(const float *a, const float *b, float *dst,
                                                     int64_t d, int64_t total, int64_t b_rows) {
     const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
@@ -41,7 +41,7 @@ __global__ void __launch_bounds__(256) binary_kernel(const float *__restrict__ a
 }
 
 // SILU: ops.cpp:2902-2981 (x / (1 + exp(-x))), optionally times b
-__global__ void __launch_bounds__(256) silu_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ dst, int64_t n) {
+__global__ void __launch_bounds__(256) silu_kernel(const float *a, const float *b, float *dst, int64_t n) {
     const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const float x = a[i];
@@ -53,8 +53,8 @@ __global__ void __launch_bounds__(256) silu_kernel(const float *__restrict__ a, 
 // multiplication in the reference; one thread of the token's CTA walks that recurrence (cheap), the cos/sin
 // of the D/2 angles are then taken in parallel and applied to every head of the token, so the angles are
 // bit-identical to the reference's.
-__global__ void __launch_bounds__(128) rope_norm_kernel(const float *__restrict__ x, int64_t x_nb_head, int64_t x_nb_tok,
-                                                       float *__restrict__ dst, int64_t dst_nb_head, int64_t dst_nb_tok, int64_t D,
+__global__ void __launch_bounds__(128) rope_norm_kernel(const float *x, int64_t x_nb_head, int64_t x_nb_tok,
+                                                       float *dst, int64_t dst_nb_head, int64_t dst_nb_tok, int64_t D,
                                                        int64_t H, int64_t T, int n_dims, const int32_t *__restrict__ pos,
                                                        const float *__restrict__ ff, float theta_scale, float freq_scale,
                                                        float attn_factor) {
@@ -99,8 +99,8 @@ __global__ void __launch_bounds__(128) rope_norm_kernel(const float *__restrict_
 // The same rotation on f16 rows, as the K-shift graph applies it in place to the cached keys
 // (lm_ggml_compute_forward_rope_f16, ops.cpp:5364-5520): values widened to f32, rotated, rounded back to f16.
 // pos[t] is the shift of cell t; a zero shift returns the row unchanged bit for bit (cos 1, sin 0).
-__global__ void __launch_bounds__(128) rope_norm_f16_kernel(const __half *__restrict__ x, int64_t x_nb_head, int64_t x_nb_tok,
-                                                           __half *__restrict__ dst, int64_t dst_nb_head, int64_t dst_nb_tok, int64_t D,
+__global__ void __launch_bounds__(128) rope_norm_f16_kernel(const __half *x, int64_t x_nb_head, int64_t x_nb_tok,
+                                                           __half *dst, int64_t dst_nb_head, int64_t dst_nb_tok, int64_t D,
                                                            int64_t H, int n_dims, const int32_t *__restrict__ pos,
                                                            const float *__restrict__ ff, float theta_scale, float freq_scale, float attn_factor) {
     extern __shared__ float cs[];   // [n_dims/2] cos, [n_dims/2] sin, [n_dims/2] theta

@@ -262,7 +262,8 @@ B200_API int b200_argmax_rows(const float *x, int64_t x_nb_row, int64_t d, int64
  * b200_silu_mul_quantize: silu(gate) * up (ops.cpp:2902-2981 + MUL) quantised into `scratch`; the f32 product is stored
  *   only when `dst` is not NULL.
  * b200_rope_store: ROPE (mode 0, as b200_rope_norm) of q in place and of k, with k and v stored as f16 into the cache
- *   rows slots[t] (cpy_k / cpy_v, cactus/llama-kv-cache.cpp:617-656); the f32 k is left as it was.
+ *   rows slots[t] (cpy_k / cpy_v, cactus/llama-kv-cache.cpp:617-656); the f32 k is left as it was.  With slots NULL
+ *   token t goes to row t of the k_cache / v_cache pointers given (a ubatch occupies consecutive cells from `head` on).
  * ------------------------------------------------------------------------------------------------ */
 B200_API int b200_add_rms_norm_quantize(float *x, int64_t x_nb_row, const float *residual, int64_t residual_nb_row, const float *w, float *h,
                                         int64_t h_nb_row, int64_t d, int64_t rows, float eps, void *scratch, size_t scratch_bytes,

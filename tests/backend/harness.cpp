@@ -392,7 +392,7 @@ static bool open_runner(runner & r, const std::string & path, bool gpu, const mo
 // One logical batch, submitted in pieces of at most n_batch tokens (llama_decode asserts n_tokens <= n_batch,
 // cactus/llama-context.cpp:895), the way a serving loop feeds long prompts; the logits of the wanted tokens are collected in order.
 static int decode_batch(runner & r, const std::vector<int32_t> & tok, const std::vector<int32_t> & pos, const std::vector<int32_t> & seq,
-                        const std::vector<int8_t> & want, std::vector<float> & logits_out) {
+                        const std::vector<int8_t> & want, std::vector<float> & logits_out, bool collect = true) {
     const int n_all = (int) tok.size(), n_batch = 2048;
     logits_out.clear();
     for (int i0 = 0; i0 < n_all; i0 += n_batch) {
@@ -407,7 +407,9 @@ static int decode_batch(runner & r, const std::vector<int32_t> & tok, const std:
             b.logits[i] = want[i0 + i];
         }
         const int rc = llama_decode(r.ctx, b);
-        if (rc == 0) {
+        if (rc == 0 && !collect) {
+            (void) llama_get_logits_ith(r.ctx, 0);   // waits for the step (the logits are in the context's pinned buffer)
+        } else if (rc == 0) {
             for (int i = 0; i < n; ++i)
                 if (want[i0 + i]) {
                     const float * l = llama_get_logits_ith(r.ctx, i);
@@ -419,6 +421,9 @@ static int decode_batch(runner & r, const std::vector<int32_t> & tok, const std:
     }
     return 0;
 }
+
+extern bool g_b200_device_mask;
+extern unsigned long long g_b200_device_mask_calls;
 
 static int run_model(int argc, char ** argv) {
     model_cfg c;
@@ -445,6 +450,7 @@ static int run_model(int argc, char ** argv) {
         else if (a == "--cpu-only") cpu_only = true;   // checks the GGUF writer and the driver without a GPU
         else if (a == "--path") path = argv[++i];
         else if (a == "--split-row") split_row_gpus = val();
+        else if (a == "--device-mask") g_b200_device_mask = true;   // device_mask.cpp: the KQ mask is synthesised on the device
     }
     llama_log_set([](lm_ggml_log_level level, const char * text, void *) { if (level >= LM_GGML_LOG_LEVEL_ERROR) fputs(text, stderr); }, nullptr);
     if (!cpu_only) lm_ggml_backend_register(lm_ggml_backend_b200_reg());
@@ -509,20 +515,27 @@ static int run_model(int argc, char ** argv) {
         compare(n_seq);
     }
     // optional timing of further decode steps on the B200 context
-    double step_ms = 0;
+    double step_ms = 0, bench_device_ms = 0;
     if (bench_steps > 0) {
+        auto totals = (lm_ggml_b200_timing_totals_t) lm_ggml_backend_reg_get_proc_address(lm_ggml_backend_b200_reg(), "lm_ggml_backend_b200_timing_totals");
+        double ms0 = 0, ms1 = 0;
+        uint64_t g0 = 0, g1 = 0;
+        if (totals) totals(&ms0, &g0);
         for (int s = 0; s < n_seq; ++s) seq[s] = s;
         const double t0 = now_s();
         for (int step = 0; step < bench_steps; ++step) {
             for (int s = 0; s < n_seq; ++s) pos[s] = len[s] + n_decode + step;
-            decode_batch(gpu, tok, pos, seq, want, lg);
+            decode_batch(gpu, tok, pos, seq, want, lg, false);
         }
         step_ms = (now_s() - t0) * 1e3 / bench_steps;
+        if (totals) totals(&ms1, &g1);
+        if (g1 > g0) bench_device_ms = (ms1 - ms0) / (double) (g1 - g0);   // only with B200_TIMING=1
     }
     printf("{\"case\": \"model\", \"layers\": %d, \"d\": %d, \"seqs\": %d, \"decode_steps\": %d, \"rows\": %d, \"worst_rel\": %.3g, "
-           "\"rows_within_1e-3\": %.3f, \"greedy_agree\": %.3f, \"b200_step_ms\": %.3f, \"split_mul_mats\": %llu}\n",
+           "\"rows_within_1e-3\": %.3f, \"greedy_agree\": %.3f, \"b200_step_ms\": %.3f, \"split_mul_mats\": %llu, \"device_masks\": %llu, "
+           "\"device_ms_per_graph\": %.3f}\n",
            c.n_layer, c.d, n_seq, n_decode, total, worst, good_rows / sum_rows, (double) agree / total, step_ms,
-           (unsigned long long) (cpu_only ? 0 : lm_ggml_backend_b200_split_mul_mat_count()));
+           (unsigned long long) (cpu_only ? 0 : lm_ggml_backend_b200_split_mul_mat_count()), g_b200_device_mask_calls, bench_device_ms);
     if (cpu.ctx) llama_free(cpu.ctx);
     if (cpu.model) llama_model_free(cpu.model);
     if (gpu.ctx) llama_free(gpu.ctx);

@@ -56,6 +56,34 @@ def test_synthetic_llama_through_llama_decode(extra):
     assert rc == 0
 
 
+def test_device_side_kq_mask_through_llama_decode():
+    """The driver leaves the host mask loop out and describes the cells to the backend's extension proc
+    (tests/backend/device_mask.cpp); the backend writes the f16 mask on the device.  Same results as with the
+    reference's host-built mask, and every B200 ubatch was served that way."""
+    args = ["model", "--head-q4", "--seqs", "7", "--max-prompt", "90", "--decode", "6"]
+    rc0, host, err0 = run(*args)
+    rc1, dev, err1 = run(*args, "--device-mask")
+    assert host and dev, (err0, err1)
+    h, d = host[-1], dev[-1]
+    assert "error" not in d, (d, err1)
+    assert d["device_masks"] == 7 and h["device_masks"] == 0, (h, d)   # one prompt ubatch + 6 decode ubatches
+    assert d["worst_rel"] == h["worst_rel"] and d["greedy_agree"] == h["greedy_agree"], (h, d)
+    assert rc1 == 0
+
+
+def test_fused_groups_do_not_change_results():
+    """ADD + RMS_NORM + MUL + quantiser and ROPE(q, k) + K/V store run as one kernel each where the graph allows it;
+    with B200_FUSE=0 every node runs by itself.  The two must agree exactly (the fused kernels are bit-identical)."""
+    if not os.path.exists(HARNESS):
+        pytest.skip("tests/_bin/harness was not built")
+    out = []
+    for fuse in ("1", "0"):
+        p = subprocess.run([HARNESS, "model", "--layers", "3", "--seqs", "5", "--max-prompt", "50", "--decode", "4"], capture_output=True, text=True,
+                           timeout=600, env=dict(os.environ, B200_FUSE=fuse))
+        out.append([json.loads(line) for line in p.stdout.splitlines() if line.startswith("{")][-1])
+    assert out[0]["worst_rel"] == out[1]["worst_rel"] and out[0]["greedy_agree"] == out[1]["greedy_agree"], out
+
+
 def test_layer_ops_with_reference_order_attention():
     """With the validation attention kernel (fp16 accumulator, the reference's order) single-token graphs agree
     with the reference CPU backend node by node to float rounding: the attention accumulator is the whole gap."""
