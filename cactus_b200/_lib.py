@@ -59,6 +59,8 @@ SIGNATURES = {
     "b200_silu_mul_quantize": (_i32, [_vp, _vp, _i64, _vp, _i64, _i64, _i64, _vp, _sz, _i32, _vp]),
     "b200_rope_store": (_i32, [_vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _f32, _f32, _f32, _vp,
                                _vp, _i64, _vp, _i64, _vp]),
+    "b200_rope_store_to": (_i32, [_vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _f32, _f32, _f32, _vp,
+                                  _vp, _i64, _vp, _i64, _vp]),
     "b200_peer_alloc": (_i32, [_sz, C.POINTER(_vp), C.c_char_p]),
     "b200_peer_open": (_i32, [C.c_char_p, C.POINTER(_vp)]),
     "b200_peer_close": (_i32, [_vp]),

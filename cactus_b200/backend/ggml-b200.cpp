@@ -542,8 +542,7 @@ struct split_peer {
 };
 
 struct rope_store_state {
-    bool active = false;
-    const lm_ggml_tensor * rope_q = nullptr, * rope_k = nullptr, * cpy_k = nullptr, * cpy_v = nullptr, * v_src = nullptr;
+    const lm_ggml_tensor * cpy_k = nullptr;   // the K store that the kernel of the preceding ROPE has already done
 };
 
 struct b200_backend_ctx {
@@ -561,7 +560,7 @@ struct b200_backend_ctx {
     int q8_variant = B200_Q8_AVX2;
     bool fa_parity = false;  // B200_FA_PARITY=1: the reference-order attention kernel (validation)
     bool fuse = true;        // B200_FUSE=0: one kernel per node (except the norm and silu pairs)
-    rope_store_state rs;     // the ROPE / cache-store group of a layer that one kernel will do
+    rope_store_state rs;
     bool timing = false;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     lm_ggml_b200_stats stats = {};
@@ -828,6 +827,7 @@ lm_ggml_status compute_cpy(b200_backend_ctx * ctx, const lm_ggml_tensor * node, 
 std::atomic<uint64_t> g_split_mul_mats{0};
 // CUDA-event time of every graph_compute of every backend of the process (B200_TIMING=1), for drivers that cannot reach
 // the backends a llama_context owns
+std::atomic<uint64_t> g_rope_store_groups{0}, g_add_norm_groups{0};   // fused groups of all backends of the process
 std::mutex g_totals_mu;
 double g_total_device_ms = 0.0;
 uint64_t g_total_timed_graphs = 0;
@@ -906,81 +906,49 @@ lm_ggml_status compute_mul_mat_split(b200_backend_ctx * ctx, lm_ggml_tensor * no
     return LM_GGML_STATUS_SUCCESS;
 }
 
-// ROPE(q), ROPE(k), CPY(k -> cache) and CPY(v -> cache) of one layer as one kernel (b200_rope_store).  llm_build_llama
-// emits them as: ROPE q ... ROPE k ... [V product] ... CPY k, CPY v, with the K and V products in between
-// (cactus/llama-model.cpp:4576-4596, cactus/llama-kv-cache.cpp:617-656), so the group is recognised when its first ROPE
-// comes up, its four nodes are skipped, and the kernel runs in the place of the V store -- after everything it reads has
-// been computed and before the attention that reads the cache (node order is the only ordering the graph has there).
-// Needs: q rotated in place (the allocator reuses the product's buffer), same positions and parameters for both
-// ROPEs, K and V stored as f16 into whole consecutive cache rows.
+// ROPE(k) and the CPY that stores the rotated k as f16 into the cache rows of the ubatch (cpy_k,
+// cactus/llama-kv-cache.cpp:617-628) as one kernel, run in the place of the ROPE.  The store is only moved EARLIER: the
+// rows it writes are read by nothing before the attention of the same layer.  (Moving a node LATER is not possible under
+// ggml-alloc: the ROPE's source is handed to the next product as soon as the ROPE's place in the node order has passed, so
+// ROPE(q) and the V store stay where they are.)  Needs: the rotated k feeds nothing but that store, which writes whole
+// consecutive f16 rows of Hkv * D values.
 const lm_ggml_tensor * through_views(const lm_ggml_tensor * t) {
     while (t && (t->op == LM_GGML_OP_RESHAPE || t->op == LM_GGML_OP_VIEW) && t->src[0]) t = t->src[0];
     return t;
 }
 
 bool rope_store_group(b200_backend_ctx * ctx, const lm_ggml_cgraph * g, int i) {
-    rope_store_state & rs = ctx->rs;
-    const lm_ggml_tensor * node = g->nodes[i];
-    if (rs.active) return node == rs.rope_q || node == rs.rope_k;   // a member of the group in flight: skip it
-    if (node->src[0]->type != LM_GGML_TYPE_F32 || node->data != node->src[0]->data || !lm_ggml_is_contiguous(node)) return false;
-    const lm_ggml_tensor * rq = node, * rk = nullptr, * ck = nullptr, * cv = nullptr;
-    for (int j = i + 1; j < g->n_nodes && j < i + 24; ++j) {
+    const lm_ggml_tensor * rk = g->nodes[i];
+    if (rk->src[0]->type != LM_GGML_TYPE_F32 || !lm_ggml_is_contiguous(rk) || !lm_ggml_is_contiguous(rk->src[0]) || rk->ne[3] != 1) return false;
+    const lm_ggml_tensor * ck = nullptr;
+    for (int j = i + 1; j < g->n_nodes && j < i + 24 && !ck; ++j) {
         const lm_ggml_tensor * n = g->nodes[j];
-        if (n->op == LM_GGML_OP_ROPE) {
-            if (rk) return false;
-            rk = n;
-        } else if (n->op == LM_GGML_OP_CPY) {
-            if (!ck) ck = n;
-            else { cv = n; break; }
-        } else if (n->op == LM_GGML_OP_FLASH_ATTN_EXT) {
-            return false;
-        }
+        if (n->op == LM_GGML_OP_FLASH_ATTN_EXT) return false;
+        if (n->op == LM_GGML_OP_CPY && n->src[0] == rk) ck = n;
     }
-    if (!rk || !ck || !cv) return false;
-    if (rk->src[0]->type != LM_GGML_TYPE_F32 || rk->src[1] != rq->src[1] || rk->src[2] != rq->src[2] || !lm_ggml_is_contiguous(rk) ||
-        memcmp(rk->op_params, rq->op_params, sizeof(int32_t) * 11) != 0) return false;
-    const int64_t D = rq->ne[0], T = rq->ne[2], Hkv = rk->ne[1];
-    if (rk->ne[0] != D || rk->ne[2] != T || rq->ne[3] != 1 || rk->ne[3] != 1) return false;
-    // the K store reads the rotated k, the V store the V product; both write f16 rows of Hkv * D values, T of them in a row
-    const lm_ggml_tensor * ksrc = through_views(ck->src[0]), * vsrc = through_views(cv->src[0]);
-    const lm_ggml_tensor * kdst = ck->src[1], * vdst = cv->src[1];
-    if (ksrc != rk || !vsrc || vsrc->op != LM_GGML_OP_MUL_MAT || !kdst || !vdst) return false;
-    if (kdst->type != LM_GGML_TYPE_F16 || vdst->type != LM_GGML_TYPE_F16 || !lm_ggml_is_contiguous(kdst) || !lm_ggml_is_contiguous(vdst)) return false;
-    if (lm_ggml_nelements(kdst) != Hkv * D * T || lm_ggml_nelements(vdst) != Hkv * D * T || lm_ggml_nelements(vsrc) != Hkv * D * T) return false;
-    if (!lm_ggml_is_contiguous(vsrc) || !lm_ggml_is_contiguous(rk->src[0])) return false;
-    if (!only_user_is(g, rk, ck)) {
-        // the rotated k may only feed the store (through its views): nobody else reads the f32 result that is not produced
-        for (int j = i + 1; j < g->n_nodes; ++j) {
-            const lm_ggml_tensor * n = g->nodes[j];
-            if (n == ck) continue;
-            for (int s = 0; s < LM_GGML_MAX_SRC; ++s)
-                if (n->src[s] && through_views(n->src[s]) == rk && !(n->op == LM_GGML_OP_RESHAPE || n->op == LM_GGML_OP_VIEW)) return false;
-        }
-    }
-    if (((uintptr_t) rq->data % 8) || ((uintptr_t) rk->src[0]->data % 8) || ((uintptr_t) vsrc->data % 8) || ((uintptr_t) kdst->data % 4) || ((uintptr_t) vdst->data % 4)) return false;
-    rs.active = true;
-    rs.rope_q = rq; rs.rope_k = rk; rs.cpy_k = ck; rs.cpy_v = cv; rs.v_src = vsrc;
-    return true;
-}
-
-lm_ggml_status rope_store_run(b200_backend_ctx * ctx) {
-    rope_store_state & rs = ctx->rs;
-    const lm_ggml_tensor * node = rs.rope_q;   // for B200_CHECK's message
-    const lm_ggml_tensor * rq = rs.rope_q, * rk = rs.rope_k;
-    const int32_t * p = (const int32_t *) rq->op_params;
+    if (!ck || !ck->src[1]) return false;
+    const lm_ggml_tensor * kdst = ck->src[1];
+    const int64_t D = rk->ne[0], Hkv = rk->ne[1], T = rk->ne[2];
+    if (kdst->type != LM_GGML_TYPE_F16 || !lm_ggml_is_contiguous(kdst) || lm_ggml_nelements(kdst) != Hkv * D * T) return false;
+    if (!only_user_is(g, rk, ck)) return false;
+    if (((uintptr_t) rk->src[0]->data % 8) || ((uintptr_t) kdst->data % 4)) return false;
+    const lm_ggml_tensor * node = rk;   // for B200_CHECK's message
+    const int32_t * p = (const int32_t *) rk->op_params;
     float freq_base, freq_scale, attn_factor;
     memcpy(&freq_base, p + 5, sizeof(float));
     memcpy(&freq_scale, p + 6, sizeof(float));
     memcpy(&attn_factor, p + 8, sizeof(float));
-    const int64_t D = rq->ne[0], H = rq->ne[1], T = rq->ne[2], Hkv = rk->ne[1];
-    rs.active = false;
-    B200_CHECK(b200_rope_store((float *) rq->data, rq->nb[1], rq->nb[2], (const float *) rk->src[0]->data, rk->src[0]->nb[1], rk->src[0]->nb[2],
-                               (const float *) rs.v_src->data, Hkv * D * 4, D, H, Hkv, T, p[1], (const int32_t *) rq->src[1]->data,
-                               rq->src[2] ? (const float *) rq->src[2]->data : nullptr, freq_base, freq_scale, attn_factor, nullptr,
-                               rs.cpy_k->src[1]->data, Hkv * D * 2, rs.cpy_v->src[1]->data, Hkv * D * 2, ctx->stream));
-    ctx->stats.nodes += 3;
+    if (b200_rope_store_to(nullptr, nullptr, 0, 0, (const float *) rk->src[0]->data, rk->src[0]->nb[1], rk->src[0]->nb[2], nullptr, 0, D, 0, Hkv, T, p[1],
+                           (const int32_t *) rk->src[1]->data, rk->src[2] ? (const float *) rk->src[2]->data : nullptr, freq_base, freq_scale, attn_factor,
+                           nullptr, kdst->data, Hkv * D * 2, nullptr, 0, ctx->stream) != B200_OK) {
+        B200_LOG_ERROR("ggml-b200: %s: %s\n", lm_ggml_op_name(node->op), b200_last_error());
+        return false;   // the separate kernels take over
+    }
+    ctx->rs.cpy_k = ck;
+    ctx->stats.nodes += 1;
     ctx->stats.rope_stores++;
-    return LM_GGML_STATUS_SUCCESS;
+    g_rope_store_groups.fetch_add(1, std::memory_order_relaxed);
+    return true;
 }
 
 lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph * cgraph) {
@@ -990,7 +958,7 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
     ctx->act_src = nullptr;
     for (split_peer & p : ctx->peers) p.act_src = nullptr;
     ctx->index_mask = nullptr;
-    ctx->rs.active = false;
+    ctx->rs.cpy_k = nullptr;
     ctx->stats.graphs++;
     if (ctx->timing) cudaEventRecord(ctx->ev0, st);
 
@@ -1120,6 +1088,7 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
                             ctx->act_src = mu;
                             ctx->stats.act_quantized++;
                             ctx->stats.nodes += 2;
+                            g_add_norm_groups.fetch_add(1, std::memory_order_relaxed);
                             i += 2;
                             break;
                         }
@@ -1157,7 +1126,7 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
                 }
             } break;
             case LM_GGML_OP_ROPE: {
-                if (ctx->fuse && rope_store_group(ctx, cgraph, i)) break;   // this ROPE, or the group it starts, is done by one kernel at the V store
+                if (ctx->fuse && s0->type == LM_GGML_TYPE_F32 && rope_store_group(ctx, cgraph, i)) break;   // rotated and stored into the cache by one kernel
                 const int32_t * p = (const int32_t *) node->op_params;
                 float freq_base, freq_scale, attn_factor;
                 memcpy(&freq_base, p + 5, sizeof(float));
@@ -1174,11 +1143,8 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
                                           freq_base, freq_scale, attn_factor, st));
             } break;
             case LM_GGML_OP_CPY: {
-                if (ctx->rs.active && (node == ctx->rs.cpy_k || node == ctx->rs.cpy_v)) {
-                    if (node == ctx->rs.cpy_v) {
-                        const lm_ggml_status rc = rope_store_run(ctx);
-                        if (rc != LM_GGML_STATUS_SUCCESS) return rc;
-                    }
+                if (node == ctx->rs.cpy_k) {   // already stored by the kernel that rotated k
+                    ctx->rs.cpy_k = nullptr;
                     break;
                 }
                 {   // the f32 -> f16 cast of a mask the driver described instead of filling: synthesise the f16 mask
@@ -1436,6 +1402,10 @@ void kq_mask_from_cells(const void * mask_host_data, size_t mask_bytes, const in
     h.host_bytes = mask_bytes;
 }
 uint64_t kq_masks_built() { return g_kq_hint.masks_built.load(); }
+void fused_group_counts(uint64_t * rope_stores, uint64_t * add_norms) {
+    if (rope_stores) *rope_stores = g_rope_store_groups.load();
+    if (add_norms) *add_norms = g_add_norm_groups.load();
+}
 void timing_totals(double * device_ms, uint64_t * graphs) {
     std::lock_guard<std::mutex> lock(g_totals_mu);
     if (device_ms) *device_ms = g_total_device_ms;
@@ -1446,6 +1416,7 @@ void * reg_get_proc_address(lm_ggml_backend_reg_t, const char * name) {
     if (strcmp(name, "lm_ggml_backend_b200_kq_mask_from_cells") == 0) return (void *) kq_mask_from_cells;
     if (strcmp(name, "lm_ggml_backend_b200_kq_masks_built") == 0) return (void *) kq_masks_built;
     if (strcmp(name, "lm_ggml_backend_b200_timing_totals") == 0) return (void *) timing_totals;
+    if (strcmp(name, "lm_ggml_backend_b200_fused_group_counts") == 0) return (void *) fused_group_counts;
     if (strcmp(name, "lm_ggml_backend_split_buffer_type") == 0) return (void *) split_buffer_type;
     if (strcmp(name, "lm_ggml_backend_set_abort_callback") == 0) return (void *) set_abort_callback;
     if (strcmp(name, "lm_ggml_backend_get_features") == 0) return (void *) get_features;

@@ -52,6 +52,9 @@ typedef uint64_t (*lm_ggml_b200_kq_masks_built_t)(void);
 //   "lm_ggml_backend_b200_timing_totals": CUDA-event time and count of all graph_compute calls of all backends of the
 //   process while B200_TIMING=1 (for drivers that cannot reach the backends a llama_context owns).
 typedef void (*lm_ggml_b200_timing_totals_t)(double * device_ms, uint64_t * graphs);
+//   "lm_ggml_backend_b200_fused_group_counts": groups of nodes that ran as one kernel since the process started --
+//   ROPE(q), ROPE(k), CPY(k), CPY(v) of a layer; residual ADD + RMS_NORM + MUL + activation quantiser.
+typedef void (*lm_ggml_b200_fused_group_counts_t)(uint64_t * rope_stores, uint64_t * add_norms);
 // MUL_MAT nodes computed on weights of the split buffer type since the process started (all backends)
 LM_GGML_BACKEND_API uint64_t lm_ggml_backend_b200_split_mul_mat_count(void);
 

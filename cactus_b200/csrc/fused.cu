@@ -96,9 +96,9 @@ __global__ void __launch_bounds__(256) silu_mul_quantize_kernel(const float *gat
     q8_quantize_store<LAYOUT>(v, out, d_offset, nb, nbp, n, b, j, real, variant);
 }
 
-// One CTA per token: the angles as rope_norm_kernel builds them, q rotated in place, k rotated and stored as f16 into
-// its cache row, v stored as f16 into its cache row.
-__global__ void __launch_bounds__(512) rope_store_kernel(float *__restrict__ q, int64_t q_nb_head, int64_t q_nb_tok, const float *__restrict__ k,
+// One CTA per token: the angles as rope_norm_kernel builds them, q rotated into qo (which may be q itself, with the same
+// strides), k rotated and stored as f16 into its cache row, v stored as f16 into its cache row.
+__global__ void __launch_bounds__(512) rope_store_kernel(const float *q, float *qo, int64_t q_nb_head, int64_t q_nb_tok, const float *__restrict__ k,
                                                         int64_t k_nb_head, int64_t k_nb_tok, const float *__restrict__ v, int64_t v_nb_tok,
                                                         int64_t D, int64_t H, int64_t Hkv, int n_dims, const int32_t *__restrict__ pos,
                                                         const float *__restrict__ ff, float theta_scale, float freq_scale, float attn_factor,
@@ -131,11 +131,14 @@ __global__ void __launch_bounds__(512) rope_store_kernel(float *__restrict__ q, 
     for (int64_t i = threadIdx.x; i < (H + 2 * Hkv) * pairs; i += blockDim.x) {
         const int64_t hh = i / pairs, p = i - hh * pairs;
         if (hh < H) {
-            float *s = reinterpret_cast<float *>(reinterpret_cast<char *>(q) + t * q_nb_tok + hh * q_nb_head) + 2 * p;
-            const float2 x = *reinterpret_cast<const float2 *>(s);
+            const int64_t off = t * q_nb_tok + hh * q_nb_head;
+            const float2 x = *(reinterpret_cast<const float2 *>(reinterpret_cast<const char *>(q) + off) + p);
+            float2 *d = reinterpret_cast<float2 *>(reinterpret_cast<char *>(qo) + off) + p;
             if (p < half_dims) {
                 const float c = cs[p], sn = cs[half_dims + p];
-                *reinterpret_cast<float2 *>(s) = make_float2(x.x * c - x.y * sn, x.x * sn + x.y * c);
+                *d = make_float2(x.x * c - x.y * sn, x.x * sn + x.y * c);
+            } else if (qo != q) {
+                *d = x;
             }
         } else if (hh < H + Hkv) {
             const int64_t hk = hh - H;
@@ -146,7 +149,7 @@ __global__ void __launch_bounds__(512) rope_store_kernel(float *__restrict__ q, 
                 r = make_float2(x.x * c - x.y * sn, x.x * sn + x.y * c);
             }
             *reinterpret_cast<__half2 *>(krow + hk * D + 2 * p) = __halves2half2(__float2half_rn(r.x), __float2half_rn(r.y));
-        } else {
+        } else if (v) {
             const int64_t hv = hh - H - Hkv;
             const float2 x = *reinterpret_cast<const float2 *>(reinterpret_cast<const float *>(reinterpret_cast<const char *>(v) + t * v_nb_tok) + hv * D + 2 * p);
             *reinterpret_cast<__half2 *>(vrow + hv * D + 2 * p) = __halves2half2(__float2half_rn(x.x), __float2half_rn(x.y));
@@ -210,15 +213,24 @@ int b200_rope_store(float *q, int64_t q_nb_head, int64_t q_nb_tok, const float *
                     int64_t v_nb_tok, int64_t D, int64_t H, int64_t Hkv, int64_t T, int n_dims, const int32_t *pos, const float *freq_factors,
                     float freq_base, float freq_scale, float attn_factor, const int32_t *slots, void *k_cache, int64_t k_cache_nb_row,
                     void *v_cache, int64_t v_cache_nb_row, b200_stream_t stream) {
-    B200_REQUIRE(q && k && v && pos && k_cache && v_cache, "null pointer");
-    B200_REQUIRE(D > 0 && D % 2 == 0 && H > 0 && Hkv > 0 && T >= 0 && n_dims > 0 && n_dims <= D && n_dims % 2 == 0, "bad rope arguments");
+    return b200_rope_store_to(q, q, q_nb_head, q_nb_tok, k, k_nb_head, k_nb_tok, v, v_nb_tok, D, H, Hkv, T, n_dims, pos, freq_factors, freq_base, freq_scale,
+                              attn_factor, slots, k_cache, k_cache_nb_row, v_cache, v_cache_nb_row, stream);
+}
+
+int b200_rope_store_to(const float *q, float *q_dst, int64_t q_nb_head, int64_t q_nb_tok, const float *k, int64_t k_nb_head, int64_t k_nb_tok, const float *v,
+                       int64_t v_nb_tok, int64_t D, int64_t H, int64_t Hkv, int64_t T, int n_dims, const int32_t *pos, const float *freq_factors,
+                       float freq_base, float freq_scale, float attn_factor, const int32_t *slots, void *k_cache, int64_t k_cache_nb_row,
+                       void *v_cache, int64_t v_cache_nb_row, b200_stream_t stream) {
+    B200_REQUIRE(k && pos && k_cache && (H == 0 || (q && q_dst)) && (!v || v_cache), "null pointer");
+    B200_REQUIRE(is_aligned(q_dst, 8), "pairs must be 8-byte aligned");
+    B200_REQUIRE(D > 0 && D % 2 == 0 && H >= 0 && Hkv > 0 && T >= 0 && n_dims > 0 && n_dims <= D && n_dims % 2 == 0, "bad rope arguments");
     B200_REQUIRE(q_nb_head % 8 == 0 && q_nb_tok % 8 == 0 && k_nb_head % 8 == 0 && k_nb_tok % 8 == 0 && v_nb_tok % 8 == 0 && is_aligned(q, 8) &&
                      is_aligned(k, 8) && is_aligned(v, 8) && k_cache_nb_row % 4 == 0 && v_cache_nb_row % 4 == 0 && is_aligned(k_cache, 4) && is_aligned(v_cache, 4),
                  "pairs must be 8-byte aligned (f32) / 4-byte aligned (f16)");
     if (T == 0) return B200_OK;
     const float theta_scale = powf(freq_base, -2.0f / (float) n_dims);
     launch_pdl(rope_store_kernel, dim3((unsigned) T), dim3(512), (size_t) (n_dims + n_dims / 2) * sizeof(float), (cudaStream_t) stream,
-        q, q_nb_head, q_nb_tok, k, k_nb_head, k_nb_tok, v, v_nb_tok, D, H, Hkv, n_dims, pos, freq_factors, theta_scale, freq_scale, attn_factor,
+        q, q_dst, q_nb_head, q_nb_tok, k, k_nb_head, k_nb_tok, v, v_nb_tok, D, H, Hkv, n_dims, pos, freq_factors, theta_scale, freq_scale, attn_factor,
         slots, (__half *) k_cache, k_cache_nb_row, (__half *) v_cache, v_cache_nb_row);
     return check_launch("rope_store");
 }

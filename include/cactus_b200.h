@@ -274,6 +274,14 @@ B200_API int b200_rope_store(float *q, int64_t q_nb_head, int64_t q_nb_tok, cons
                              const float *v, int64_t v_nb_tok, int64_t D, int64_t H, int64_t Hkv, int64_t T, int n_dims, const int32_t *pos,
                              const float *freq_factors, float freq_base, float freq_scale, float attn_factor, const int32_t *slots,
                              void *k_cache, int64_t k_cache_nb_row, void *v_cache, int64_t v_cache_nb_row, b200_stream_t stream);
+/* the same with the rotated q written to q_dst (same strides as q; q_dst == q is the call above): the ROPE node of a
+ * graph whose allocator did not place the result over its source.  H = 0 (q, q_dst NULL) leaves q out, v NULL leaves
+ * the V store out: ROPE(k) + K store alone, what a graph_compute can run in the place of the ROPE(k) node. */
+B200_API int b200_rope_store_to(const float *q, float *q_dst, int64_t q_nb_head, int64_t q_nb_tok, const float *k, int64_t k_nb_head,
+                                int64_t k_nb_tok, const float *v, int64_t v_nb_tok, int64_t D, int64_t H, int64_t Hkv, int64_t T, int n_dims,
+                                const int32_t *pos, const float *freq_factors, float freq_base, float freq_scale, float attn_factor,
+                                const int32_t *slots, void *k_cache, int64_t k_cache_nb_row, void *v_cache, int64_t v_cache_nb_row,
+                                b200_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Row-split mul_mat over the GPUs of one node (one process per GPU).
