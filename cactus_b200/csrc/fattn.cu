@@ -37,7 +37,7 @@ constexpr int FA_ADAPTIVE_SPLITS = 2;   // most KV splits a long sequence is cut
 
 // ---- mask scan: one warp per 64 cells of one token row ------------------------------------------
 __global__ void __launch_bounds__(256) mask_index_kernel(const __half *__restrict__ mask, int64_t mask_nb_row, int64_t Nq,
-                                                        int64_t n_kv, int64_t nw, unsigned long long *__restrict__ words) {
+                                                        int64_t n_kv, int64_t nw, unsigned long long *__restrict__ words, int32_t *soft) {
     const int lane = threadIdx.x & 31;
     const int64_t wid = ((int64_t) blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (wid >= Nq * nw) return;
@@ -45,8 +45,10 @@ __global__ void __launch_bounds__(256) mask_index_kernel(const __half *__restric
     const __half *row = reinterpret_cast<const __half *>(reinterpret_cast<const char *>(mask) + j * mask_nb_row);
     const int64_t c0 = wi * 64 + lane, c1 = c0 + 32;
     const unsigned short ninf = 0xFC00u;
-    const bool v0 = c0 < n_kv && __half_as_ushort(row[c0]) != ninf;
-    const bool v1 = c1 < n_kv && __half_as_ushort(row[c1]) != ninf;
+    const unsigned short m0 = c0 < n_kv ? __half_as_ushort(row[c0]) : ninf, m1 = c1 < n_kv ? __half_as_ushort(row[c1]) : ninf;
+    const bool v0 = m0 != ninf, v1 = m1 != ninf;
+    // a participating cell whose mask value is not +-0 is added to the score: the mask is then more than its bits
+    if (((v0 && (m0 & 0x7fffu)) || (v1 && (m1 & 0x7fffu))) && soft) *soft = 1;
     const unsigned lo = __ballot_sync(0xffffffffu, v0), hi = __ballot_sync(0xffffffffu, v1);
     if (lane == 0) words[wid] = (unsigned long long) lo | ((unsigned long long) hi << 32);
 }
@@ -93,8 +95,29 @@ __global__ void __launch_bounds__(1024) fattn_plan_kernel(const int32_t *__restr
     }
     atomicAdd((unsigned long long *) &total_s, (unsigned long long) part);
     __syncthreads();
-    if (threadIdx.x == 0) plan[0] = (int32_t) min(total_s, (long long) 0x7fffffff);
+    if (threadIdx.x == 0) {
+        plan[0] = (int32_t) min(total_s, (long long) 0x7fffffff);
+        plan[1] = 0;   // filled by fattn_tile_vote_kernel
+    }
 }
+
+// Fourth pass: how much the tokens of a ubatch share their cells.  plan[1] = the sum, over groups of 16 consecutive
+// tokens, of the number of mask words any token of the group attends to.  Against plan[0] (the same sum token by token)
+// it tells whether walking the cells once per group (fattn_tile_kernel) beats walking them once per token: a prompt's
+// tokens share nearly all their words, the tokens of a decode batch share none.
+__global__ void __launch_bounds__(256) fattn_tile_vote_kernel(const unsigned long long *__restrict__ words, int64_t Nq, int64_t nw, int32_t *__restrict__ plan) {
+    const int64_t t0 = (int64_t) blockIdx.x * 16, t1 = min(Nq, t0 + 16);
+    int cnt = 0;
+    for (int64_t wi = threadIdx.x; wi < nw; wi += blockDim.x) {
+        unsigned long long bits = 0;
+        for (int64_t j = t0; j < t1; ++j) bits |= words[j * nw + wi];
+        cnt += bits != 0ull;
+    }
+    for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+    if ((threadIdx.x & 31) == 0 && cnt) atomicAdd(plan + 1, cnt);
+}
+// the choice both attention kernels derive from the plan: true = the query-tiled kernel does the work
+__device__ __forceinline__ bool fattn_tiled_chosen(const int32_t *plan) { return 2ll * plan[1] <= (long long) plan[0]; }
 
 struct FattnParams {
     int64_t H, Hkv, Nq, n_kv, nw;
@@ -117,6 +140,8 @@ struct FattnParams {
                      // < 0: w0 is derived on the device from the mask's total word count (fattn_target_words)
     const int32_t *order, *plan;   // tokens by decreasing word count; plan[0] = total words (NULL without a mask index)
     int slots;       // CTAs of this kernel the device holds at once
+    int vote;        // both attention kernels were launched and the plan decides which one works (the other returns at once):
+                     // 1 = these are the per-token kernel's launches, 2 = the query-tiled kernel's
 };
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -128,6 +153,10 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t *>(&h);
 }
+
+}  // namespace b200
+#include "fattn_tile.cuh"   // the query-tiled kernel for ubatches with many tokens
+namespace b200 {
 
 // Tensor-core kernel.  One CTA per (token, kv-head, head group of up to 8 query heads, KV split); its 4 warps take
 // 16-cell chunks of the token's cell list in turn.  Per chunk and warp:
@@ -180,6 +209,7 @@ __device__ __forceinline__ void fattn_store_out(const FattnParams &p, int64_t j,
 template <int D, bool QUANT>
 __global__ void __launch_bounds__(FA_THREADS, FA_MIN_CTAS) fattn_mma_kernel(FattnParams p) {
     pdl_prologue();
+    if (p.vote == 1 && fattn_tiled_chosen(p.plan)) return;   // the query-tiled kernel takes this ubatch
     constexpr int KS = D / 16;   // k-steps of the S MMA
     constexpr int NU = D / 32;   // 16-byte K pieces per lane and cell
     constexpr int NR = D / 64;   // 64-wide d ranges of V
@@ -500,6 +530,8 @@ __global__ void __launch_bounds__(128) fattn_parity_kernel(FattnParams p) {
 template <int D, bool QUANT>
 __global__ void __launch_bounds__(D) fattn_combine_kernel(FattnParams p, int ctas_per_token) {
     pdl_prologue();
+    if (p.vote == 1 && fattn_tiled_chosen(p.plan)) return;    // the query-tiled kernel wrote the result
+    if (p.vote == 2 && !fattn_tiled_chosen(p.plan)) return;   // this is the query-tiled kernel's combine pass and the per-token kernel worked
     const float *__restrict__ partial = p.partial;
     int nsplit = p.nsplit;
     const int64_t row = blockIdx.x;  // token * H + head
@@ -564,6 +596,33 @@ static int fattn_nsplit(int64_t Nq, int64_t Hkv, int hgroups, int64_t n_kv) {
     return (int) std::min<int64_t>(ns, 64);
 }
 
+static bool cuda_memset_ok(void *p, size_t n, cudaStream_t st) { return cudaMemsetAsync(p, 0, n, st) == cudaSuccess; }
+int fattn_tile_min_nq();
+
+// KV splits of the query-tiled kernel: enough CTAs for two per SM twice over, a split walks at least 256 cells
+static int fattn_tile_nsplit(int64_t Nq, int64_t Hkv, int gqa, int64_t n_kv) {
+    int gl = 0;
+    while ((1 << gl) < gqa) ++gl;
+    const int64_t tiles = (Nq + (64 >> gl) - 1) / (64 >> gl), ctas = tiles * Hkv, want = 4 * (int64_t) fa_sm_count();
+    int64_t ns = ctas >= want ? 1 : (want + ctas - 1) / ctas;
+    ns = std::min<int64_t>(ns, std::max<int64_t>(1, n_kv / 256));
+    return (int) std::min<int64_t>(ns, 8);
+}
+static bool fattn_tile_possible(int64_t Nq, int gqa) {
+    const int tile_min = fattn_tile_min_nq();
+    return tile_min > 0 && Nq >= tile_min && (gqa & (gqa - 1)) == 0 && gqa >= 2 && gqa <= 16;   // a tile holds 64 / gqa tokens: at most 32
+}
+
+// token count from which the query-tiled kernel is considered (B200_FA_TILE_MIN_NQ; 0 turns it off)
+int fattn_tile_min_nq() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("B200_FA_TILE_MIN_NQ");
+        v = e ? atoi(e) : 128;
+    }
+    return v;
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -571,7 +630,8 @@ using namespace b200;
 extern "C" {
 
 // index layout: words [Nq][nw] u64 | list of non-empty word indices [Nq][nw] i32 | their counts [Nq] i32 |
-// tokens by decreasing count [Nq] i32 | plan: total words i32
+// tokens by decreasing count [Nq] i32 | plan: total words i32, words summed over 16-token groups i32, 1 if the mask
+// holds values other than 0 and -inf in participating cells i32
 static size_t index_list_offset(int64_t Nq, int64_t nw) { return align_up((size_t) Nq * nw * 8, 256); }
 static size_t index_count_offset(int64_t Nq, int64_t nw) { return index_list_offset(Nq, nw) + align_up((size_t) Nq * nw * 4, 256); }
 
@@ -591,8 +651,10 @@ int b200_mask_index_build(const void *mask, int64_t mask_nb_row, int64_t Nq, int
     if (index_bytes < b200_mask_index_bytes(Nq, n_kv)) return set_error(B200_E_SCRATCH, "mask index buffer too small");
     const int64_t nw = (n_kv + 63) / 64;
     const int64_t threads = Nq * nw * 32;
+    int32_t *plan = (int32_t *) ((char *) index + index_plan_offset(Nq, nw));
+    if (!cuda_memset_ok(plan + 2, 4, (cudaStream_t) stream)) return set_error(B200_E_CUDA, "mask index: cudaMemsetAsync failed");
     mask_index_kernel<<<(unsigned) ((threads + 255) / 256), 256, 0, (cudaStream_t) stream>>>(
-        (const __half *) mask, mask_nb_row, Nq, n_kv, nw, (unsigned long long *) index);
+        (const __half *) mask, mask_nb_row, Nq, n_kv, nw, (unsigned long long *) index, plan + 2);
     if (int e = check_launch("mask_index")) return e;
     mask_words_compact_kernel<<<(unsigned) ((Nq * 32 + 255) / 256), 256, 0, (cudaStream_t) stream>>>(
         (const unsigned long long *) index, Nq, nw, (int32_t *) ((char *) index + index_list_offset(Nq, nw)),
@@ -601,7 +663,13 @@ int b200_mask_index_build(const void *mask, int64_t mask_nb_row, int64_t Nq, int
     fattn_plan_kernel<<<1, 1024, 0, (cudaStream_t) stream>>>((const int32_t *) ((char *) index + index_count_offset(Nq, nw)), Nq,
                                                              (int32_t *) ((char *) index + index_order_offset(Nq, nw)),
                                                              (int32_t *) ((char *) index + index_plan_offset(Nq, nw)));
-    return check_launch("fattn_plan");
+    if (int e = check_launch("fattn_plan")) return e;
+    if (Nq >= fattn_tile_min_nq() && fattn_tile_min_nq() > 0) {   // only ubatches the query-tiled kernel may take need the vote
+        fattn_tile_vote_kernel<<<(unsigned) ((Nq + 15) / 16), 256, 0, (cudaStream_t) stream>>>((const unsigned long long *) index, Nq, nw,
+                                                                                                 (int32_t *) ((char *) index + index_plan_offset(Nq, nw)));
+        return check_launch("fattn_tile_vote");
+    }
+    return B200_OK;
 }
 
 size_t b200_flash_attn_scratch_bytes(int64_t D, int64_t H, int64_t Hkv, int64_t Nq, int64_t n_kv) {
@@ -609,6 +677,7 @@ size_t b200_flash_attn_scratch_bytes(int64_t D, int64_t H, int64_t Hkv, int64_t 
     const int hgroups = fattn_hgroups((int) (H / Hkv));
     int ns = fattn_nsplit(Nq, Hkv, hgroups, n_kv);
     if (ns == 1 && fattn_adaptive(Nq, Hkv, hgroups, true)) ns = FA_ADAPTIVE_SPLITS;
+    if (fattn_tile_possible(Nq, (int) (H / Hkv))) ns = std::max(ns, fattn_tile_nsplit(Nq, Hkv, (int) (H / Hkv), n_kv));
     const size_t part = ns > 1 ? align_up((size_t) Nq * H * ns * (D + 2) * sizeof(float), 256) : 0;
     return b200_mask_index_bytes(Nq, n_kv) + part;
 }
@@ -673,6 +742,32 @@ static int flash_attn_impl(bool parity, int64_t D, int64_t H, int64_t Hkv, int64
         if (D == 128) fattn_parity_kernel<128><<<blocks, 128, 0, st>>>(p);
         else fattn_parity_kernel<64><<<blocks, 128, 0, st>>>(p);
         return check_launch("fattn_parity");
+    }
+    // Many query tokens: the query-tiled kernel shares every staged K/V chunk between the 64 / gqa tokens of a tile.  That
+    // pays when the tokens share their cells (a prompt), not when every token has its own sequence (a large decode batch);
+    // with a mask index both kernels are launched and the plan the index holds decides on the device which one works.
+    int gqa_log2 = 0;
+    while ((1 << gqa_log2) < gqa) ++gqa_log2;
+    p.vote = 0;
+    if (!act && dst && fattn_tile_possible(Nq, gqa) && p.nw <= 2048) {
+        FattnParams pt = p;
+        pt.vote = index ? 2 : 0;
+        pt.w0 = 0;
+        pt.nsplit = fattn_tile_nsplit(Nq, Hkv, gqa, n_kv);
+        const size_t tpart = pt.nsplit > 1 ? (size_t) Nq * H * pt.nsplit * (D + 2) * sizeof(float) : 0;
+        if (tpart && (!scratch || scratch_bytes < tpart || !is_aligned(scratch, 16))) pt.nsplit = 1;   // an older scratch size: no splits
+        const int tile_tokens = 64 >> gqa_log2;
+        dim3 tgrid((unsigned) Hkv, (unsigned) ((Nq + tile_tokens - 1) / tile_tokens), (unsigned) pt.nsplit);
+        if (D == 128) launch_pdl(fattn_tile_kernel<128>, tgrid, dim3(FT_THREADS), 0, st, pt, gqa_log2);
+        else launch_pdl(fattn_tile_kernel<64>, tgrid, dim3(FT_THREADS), 0, st, pt, gqa_log2);
+        if (int e = check_launch("fattn_tile")) return e;
+        if (pt.nsplit > 1) {
+            if (D == 128) launch_pdl(fattn_combine_kernel<128, false>, dim3((unsigned) (Nq * H)), dim3(128), 0, st, pt, 1);
+            else launch_pdl(fattn_combine_kernel<64, false>, dim3((unsigned) (Nq * H)), dim3(64), 0, st, pt, 1);
+            if (int e = check_launch("fattn_combine")) return e;
+        }
+        if (!index) return B200_OK;   // no mask: every token attends every cell, nothing to vote on
+        p.vote = 1;
     }
     dim3 grid((unsigned) (Hkv * hgroups), (unsigned) Nq, (unsigned) ns);
     const bool qo = act != nullptr;

@@ -2,6 +2,7 @@
 
     python -m cactus_b200.microbench mul_mat --K 4096 --M 14336 --N 64 --copies 8 --reps 3
     python -m cactus_b200.microbench fattn --seqs 64 --ctx 900 --reps 3
+    python -m cactus_b200.microbench fattn --cfg2 a --copies 8       # the 512-token prefill ubatch of 16 ragged sequences
     python -m cactus_b200.microbench quantize --K 4096 --N 64
 
 `--copies` distinct weight tensors are cycled so the weights streamed per pass exceed the 126 MB L2.
@@ -121,6 +122,71 @@ def bench_fattn(a):
     return {"kernel": "flash_attn_ext", "seqs": a.seqs, "ctx": "ragged" if a.ragged else a.ctx, "cells": total, "D": D, "H": H, "Hkv": Hkv, "ms_per_launch": ms, "GBps": alg / ms / 1e6}
 
 
+def bench_fattn_prefill(a):
+    """The single FLASH_ATTN_EXT op of a prefill ubatch: 32 query heads / 8 KV heads, head 128, 16 sequences with
+    contexts ~ U[64, 4096] and 1-256 query tokens each (seed 0), causal + per-slot sequence mask.
+    variant a: contexts rescaled to fit 8192 slots, query tokens clipped to a 512-token ubatch;
+    variant b: the cache enlarged to pad256(sum of contexts), lengths as drawn, still one ubatch of at most 512 tokens."""
+    L = lib()
+    D, H, Hkv = a.D, a.H, a.Hkv
+    rng = np.random.default_rng(0)
+    ctx = rng.integers(64, 4097, 16)
+    nq = rng.integers(1, 257, 16)
+    if a.cfg2 == "a":
+        ctx = np.maximum(64, (ctx * min(1.0, 8192 / ctx.sum() * 0.999)).astype(int))
+        while ctx.sum() > 8192:
+            ctx[np.argmax(ctx)] -= ctx.sum() - 8192
+    nq = np.minimum(nq, ctx)
+    nq = np.maximum(1, (nq * min(1.0, 512 / nq.sum())).astype(int))
+    total = int(ctx.sum())
+    n_cells = (total + 255) // 256 * 256
+    cell_pos = np.full(n_cells, -1, np.int32)
+    cell_seq = np.full(n_cells, -1, np.int32)
+    head = 0
+    for s_, n in enumerate(ctx):
+        cell_pos[head:head + n] = np.arange(n)
+        cell_seq[head:head + n] = s_
+        head += n
+    tok_pos = np.concatenate([np.arange(c - q_, c) for c, q_ in zip(ctx, nq)]).astype(np.int32)
+    tok_seq = np.concatenate([np.full(q_, s_) for s_, q_ in enumerate(nq)]).astype(np.int32)
+    Nq = len(tok_pos)
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    layers = a.copies
+    ks = [torch.randn((n_cells, Hkv * D), device="cuda", generator=gen).half() for _ in range(layers)]
+    vs = [torch.randn((n_cells, Hkv * D), device="cuda", generator=gen).half() for _ in range(layers)]
+    q = torch.randn((Nq, H * D), device="cuda", generator=gen)
+    mask = torch.empty(((Nq + 63) // 64 * 64, n_cells), dtype=torch.float16, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    dv = lambda x: torch.from_numpy(x).cuda()  # noqa: E731
+    cp, cs, tp, ts = dv(cell_pos), dv(cell_seq), dv(tok_pos), dv(tok_seq)
+    check(L.b200_kq_mask_build(cp.data_ptr(), cs.data_ptr(), n_cells, tp.data_ptr(), ts.data_ptr(), Nq, mask.data_ptr(), n_cells * 2, st))
+    index = torch.empty(L.b200_mask_index_bytes(Nq, n_cells), dtype=torch.uint8, device="cuda")
+    check(L.b200_mask_index_build(mask.data_ptr(), n_cells * 2, Nq, n_cells, index.data_ptr(), index.numel(), st))
+    scratch = torch.empty(max(256, L.b200_flash_attn_scratch_bytes(D, H, Hkv, Nq, n_cells)), dtype=torch.uint8, device="cuda")
+    out = torch.empty((Nq, H * D), device="cuda")
+
+    def run():
+        st = torch.cuda.current_stream().cuda_stream
+        for k, v in zip(ks, vs):
+            check(L.b200_flash_attn_ext_indexed(D, H, Hkv, Nq, n_cells, q.data_ptr(), H * D * 4, D * 4, k.data_ptr(), Hkv * D * 2, D * 2,
+                                                v.data_ptr(), Hkv * D * 2, D * 2, mask.data_ptr(), n_cells * 2, index.data_ptr(),
+                                                D ** -0.5, 0.0, 0.0, out.data_ptr(), scratch.data_ptr(), scratch.numel(), st))
+        return layers
+
+    run()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        run()
+    ms = time_launches(lambda: (g.replay(), layers)[1], a.reps)
+    # algorithmic bytes: every sequence's attended K/V once per kv-head, Q in, O out, the f16 mask once
+    alg = total * Hkv * D * 2 * 2 + 2 * Nq * H * D * 4 + n_cells * ((Nq + 63) // 64 * 64) * 2
+    # flops: 2 * H * (DK + DV) per (query token, attended cell) pair
+    pairs = int(sum(int(c) * int(q_) - int(q_) * (int(q_) - 1) // 2 for c, q_ in zip(ctx, nq)))
+    flops = 2 * H * 2 * D * pairs
+    return {"kernel": "flash_attn_ext prefill", "variant": a.cfg2, "tokens": Nq, "sequences": 16, "cells": total, "D": D, "H": H, "Hkv": Hkv,
+            "ms_per_launch": ms, "TFLOPs": flops / ms / 1e9, "GBps": alg / ms / 1e6, "attended_pairs": pairs}
+
+
 def bench_quantize(a):
     L = lib()
     x = torch.randn((a.N, a.K), device="cuda")
@@ -143,6 +209,7 @@ def main():
     ap.add_argument("--ragged", action="store_true", help="fattn: the benchmark's ragged sequence lengths instead of --seqs x --ctx")
     ap.add_argument("--head-major", action="store_true", help="fattn: address the cache as [Hkv][cells][D] instead of the reference's [cells][Hkv][D]")
     ap.add_argument("--quant", action="store_true", help="fattn: b200_flash_attn_ext_quant (quantised output only)")
+    ap.add_argument("--cfg2", choices=["a", "b"], default=None, help="fattn: the 16-sequence prefill ubatch (a: fits 8192 slots, b: cache enlarged)")
     ap.add_argument("--K", type=int, default=4096)
     ap.add_argument("--M", type=int, default=14336)
     ap.add_argument("--N", type=int, default=64)
@@ -155,7 +222,10 @@ def main():
     ap.add_argument("--H", type=int, default=32)
     ap.add_argument("--Hkv", type=int, default=8)
     a = ap.parse_args()
-    r = {"mul_mat": bench_mul_mat, "fattn": bench_fattn, "quantize": bench_quantize}[a.kernel](a)
+    fn = {"mul_mat": bench_mul_mat, "fattn": bench_fattn, "quantize": bench_quantize}[a.kernel]
+    if a.kernel == "fattn" and a.cfg2:
+        fn = bench_fattn_prefill
+    r = fn(a)
     print(json.dumps(r))
 
 
