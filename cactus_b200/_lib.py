@@ -17,6 +17,7 @@ SIGNATURES = {
     "b200_device_info": (_i32, [_i32, C.c_char_p, _sz, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_i32)]),
     "b200_launch_count": (C.c_uint64, []),
     "b200_kernel_status": (C.c_int, []),
+    "b200_kernel_set_wait_limit": (None, [C.c_uint]),
     "b200_weight_bytes": (_sz, [_i32, _i64, _i64]),
     "b200_weight_upload": (_i32, [_i32, _i64, _i64, _vp, _vp, _i64, _i64, _vp]),
     "b200_weight_download": (_i32, [_i32, _i64, _i64, _vp, _vp, _i64, _i64, _vp]),
@@ -67,6 +68,7 @@ SIGNATURES = {
     "b200_peer_free": (_i32, [_vp]),
     "b200_allgather_rows": (_i32, [_vp, _i64, _i64, _i64, _i32, _i32, C.POINTER(_vp), _i64, C.POINTER(_vp), _vp]),
     "b200_peer_status": (_i32, [_vp]),
+    "b200_peer_set_wait_limit": (_i32, [_vp, C.c_uint]),
     "b200_mul_mat_q_rowsplit": (_i32, [_i32, _vp, _i64, _i64, _vp, _i64, _i32, _i32, C.POINTER(_vp), _i64, _i64, _vp, _sz, C.POINTER(_vp), _vp]),
     "b200_mul_mat_q_rowsplit_stacked": (_i32, [_i32, _vp, _i64, _i64, _vp, _i64, _i32, _i32, C.POINTER(_vp), _i64, _i32, C.POINTER(_i64), C.POINTER(_i64),
                                                _vp, _sz, C.POINTER(_vp), _vp]),

@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "lib")
 LIB = os.path.join(OUT, "libcactus_b200.so")
-SOURCES = ["abi.cu", "quantize.cu", "mmvq.cu", "mmq.cu", "mmq_tc.cu", "mul_mat.cu", "fattn.cu", "rowops.cu", "kvops.cu", "fused.cu", "peer.cu"]
+SOURCES = ["abi.cu", "quantize.cu", "mmvq.cu", "mmq.cu", "mmq_tc.cu", "mmq_tcf.cu", "mul_mat.cu", "fattn.cu", "rowops.cu", "kvops.cu", "fused.cu", "peer.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "--fmad=true",

@@ -22,11 +22,10 @@ int set_error(int code, const char *fmt, ...) {
 }
 
 bool pdl_enabled() {
-    static int v = -1;
-    if (v < 0) {
+    static const int v = [] {
         const char *e = getenv("B200_PDL");
-        v = (e && atoi(e) == 0) ? 0 : 1;
-    }
+        return (e && atoi(e) == 0) ? 0 : 1;
+    }();
     return v == 1;
 }
 

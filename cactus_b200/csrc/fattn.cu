@@ -558,14 +558,13 @@ __global__ void __launch_bounds__(D) fattn_combine_kernel(FattnParams p, int cta
 
 static int fattn_hgroups(int gqa) { return (gqa + 7) / 8; }   // a CTA takes up to 8 query heads of one KV head
 
-static int fa_sm_count() {
-    static int n = 0;
-    if (!n) {
-        int dev = 0;
+static int fa_sm_count() {   // every device of a process is the same model
+    static const int n = [] {
+        int dev = 0, v = 0;
         cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        if (n <= 0) n = 148;
-    }
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+        return v > 0 ? v : 148;
+    }();
     return n;
 }
 
@@ -573,20 +572,18 @@ static int fa_sm_count() {
 // duration.  When the grid is small enough for spare CTAs to be cheap (at most two waves), a token whose mask has more
 // words than fattn_target_words is cut into up to FA_ADAPTIVE_SPLITS KV splits; the rest are written directly.
 static bool fattn_adaptive(int64_t Nq, int64_t Hkv, int hgroups, bool have_index) {
-    static int allow = -1;
-    if (allow < 0) {
+    static const int allow = [] {
         const char *e = getenv("B200_FA_ADAPTIVE");   // opt-in: on the 64-sequence decode batch the cuts cost more than they save
-        allow = (e && atoi(e) == 1) ? 1 : 0;
-    }
+        return (e && atoi(e) == 1) ? 1 : 0;
+    }();
     return allow && have_index && Nq * Hkv * hgroups <= 2 * (int64_t) FA_MIN_CTAS * fa_sm_count();
 }
 
 static int fattn_nsplit(int64_t Nq, int64_t Hkv, int hgroups, int64_t n_kv) {
-    static int forced = -1;
-    if (forced < 0) {
+    static const int forced = [] {
         const char *e = getenv("B200_FA_NSPLIT");
-        forced = e ? atoi(e) : 0;
-    }
+        return e ? atoi(e) : 0;
+    }();
     if (forced > 0) return (int) std::min<int64_t>(forced, 64);
     const int64_t ctas = Nq * Hkv * hgroups;
     const int64_t want = 2 * fa_sm_count();
@@ -615,11 +612,10 @@ static bool fattn_tile_possible(int64_t Nq, int gqa) {
 
 // token count from which the query-tiled kernel is considered (B200_FA_TILE_MIN_NQ; 0 turns it off)
 int fattn_tile_min_nq() {
-    static int v = -1;
-    if (v < 0) {
+    static const int v = [] {
         const char *e = getenv("B200_FA_TILE_MIN_NQ");
-        v = e ? atoi(e) : 128;
-    }
+        return e ? atoi(e) : 128;
+    }();
     return v;
 }
 

@@ -19,6 +19,8 @@
 // and a second kernel adds them in a fixed order.
 #include <cstdlib>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -615,11 +617,15 @@ __global__ void __launch_bounds__(256) mmq_reduce_kernel(const float *__restrict
     store_f32(dst, peers, n * dst_nb_row + m * 4 + peer_row_shift(peers, m), s);
 }
 
+// The per-device tables below are filled on first use; calls may come from several host threads (one backend per thread
+// is a supported way to drive the C ABI), so every table has its lock.
 static int sm_count() {
     static int n[64] = {0};
+    static std::mutex mu;
     int dev = 0;
     cudaGetDevice(&dev);
     dev &= 63;
+    std::lock_guard<std::mutex> lock(mu);
     if (!n[dev]) {
         cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
         if (n[dev] <= 0) n[dev] = 148;
@@ -696,10 +702,12 @@ template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB>
 static int max_clusters_variant(int ksplit) {
     using S = MmqCfg<WTYPE, NTW, WN, MT, WM, STAGES>;
     static int cache[64][9];   // per device and cluster size: 0 = not asked yet, -1 = none, else the count
+    static std::mutex mu;
     int dev = 0;
     cudaGetDevice(&dev);
     dev &= 63;
     if (ksplit < 2 || ksplit > 8) return 0;
+    std::lock_guard<std::mutex> lock(mu);
     if (cache[dev][ksplit] != 0) return cache[dev][ksplit] < 0 ? 0 : cache[dev][ksplit];
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1, 1, (unsigned) ksplit);
@@ -750,9 +758,15 @@ static const MmqVariant &pick_variant(int64_t N) {
     // per device: kernel attributes and occupancy are per-context properties
     static MmqVariant table[64][3][4];
     static bool ready[64] = {false};
+    static std::mutex mu;
+    static const int forced = [] {
+        const char *e = getenv("B200_MMQ_VARIANT");
+        return e ? atoi(e) : -1;
+    }();
     int dev = 0;
     cudaGetDevice(&dev);
     dev &= 63;
+    std::lock_guard<std::mutex> lock(mu);
     if (!ready[dev]) {
         MmqVariant(*t)[4] = table[dev];
         t[0][0] = make_variant<WTYPE, 2, 1, 2, 4>();   // 128 rows x 16 cols, 4 warps
@@ -767,11 +781,6 @@ static const MmqVariant &pick_variant(int64_t N) {
         t[2][3] = make_variant<WTYPE, 4, 2, 2, 4, 3, 2>();   // 128 rows x 64 cols, 8 warps as 4 x 2, 3 stages
         ready[dev] = true;
     }
-    static int forced = -2;
-    if (forced == -2) {
-        const char *e = getenv("B200_MMQ_VARIANT");
-        forced = e ? atoi(e) : -1;
-    }
     const int cls = N > 32 ? 2 : (N > 16 ? 1 : 0);
     return table[dev][cls][(forced >= 0 && forced < 4) ? forced : 0];
 }
@@ -781,11 +790,10 @@ static const MmqVariant &pick_variant(int64_t N) {
 // its partial tiles through distributed shared memory; more splits, or a device that cannot place such clusters,
 // write partial sums to the workspace for the reduction kernel (about two block groups' worth of time more).
 static int choose_ksplit(const MmqVariant &v, const TiledDims &d, int64_t n_nt, bool *cluster) {
-    static int allow = -1;
-    if (allow < 0) {
+    static const int allow = [] {
         const char *e = getenv("B200_MMQ_CLUSTER");
-        allow = (e && atoi(e) == 0) ? 0 : 1;
-    }
+        return (e && atoi(e) == 0) ? 0 : 1;
+    }();
     const int64_t ctas = ((d.n_rt + v.cta_tiles - 1) / v.cta_tiles) * ((n_nt + v.cta_nt - 1) / v.cta_nt);
     const int64_t slots = (int64_t) sm_count() * v.ctas_per_sm;
     int best = 1;
@@ -825,11 +833,10 @@ static const MmqVariant &variant_for(int wtype, int64_t N) {
 // 17.0 us for 1..4 columns of a 14336 x 4096 Q4_0 weight on B200), where the tensor-core kernel's 16-column tile costs
 // 13.4 us for any count up to 16.
 int mmvq_max_n() {
-    static int v = -1;
-    if (v < 0) {
+    static const int v = [] {
         const char *e = getenv("B200_MMVQ_MAX_N");
-        v = e ? std::max(2, std::min(8, atoi(e))) : 2;
-    }
+        return e ? std::max(2, std::min(8, atoi(e))) : 2;
+    }();
     return v;
 }
 
@@ -853,11 +860,10 @@ size_t mmq_workspace_bytes(int wtype, int64_t K, int64_t M, int64_t N) {
 // that the CTAs sharing the tails are done two block groups before the heads).  Fewer row groups are left to the
 // cluster split.  B200_MMQ_STREAMK=0 turns it off, =2 takes it whenever it is legal.
 static int streamk_ctas(const MmqVariant &v, const TiledDims &d, const ActDims &a, int ks, bool cluster, size_t workspace_bytes, int *head) {
-    static int mode = -1;
-    if (mode < 0) {
+    static const int mode = [] {
         const char *e = getenv("B200_MMQ_STREAMK");
-        mode = e ? atoi(e) : 1;
-    }
+        return e ? atoi(e) : 1;
+    }();
     *head = 0;
     if (mode == 0 || a.n_nt > v.cta_nt || d.n_rt % v.cta_tiles != 0) return 0;
     const int64_t groups = d.n_rt / v.cta_tiles, total = groups * d.n_bg;

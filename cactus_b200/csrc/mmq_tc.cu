@@ -60,6 +60,7 @@ int launch_mmq(int wtype, const TiledDims &d, const void *w, const ActDims &a, c
 
 __device__ int g_tc_error = 0;   // non-zero after a bounded wait gave up
 __device__ unsigned g_tc_spin_limit = 1u << 20;   // try_wait rounds before a wait gives up (each may suspend for a while)
+constexpr uint32_t TC_DRAIN_LIMIT = 1u << 22;     // what a CTA that gave up still waits for: its own copies and MMAs in flight
 #ifdef B200_TC_PROFILE
 __device__ long long g_tc_prof[4][64];   // [role][iteration]: clock of CTA 0 when the role starts work on an iteration
 #define TC_PROF(role, it) do { if (blockIdx.x == 0 && blockIdx.z == 0 && lane == 0 && (it) < 64) g_tc_prof[role][it] = clock64(); } while (0)
@@ -228,7 +229,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_q4_kernel(const __grid_c
         }
         if (lane == 0) {   // no MMA of this CTA may be in flight when its tensor memory is freed, whatever happened elsewhere
             tc_commit(BAR(BAR_DRAIN, warp));
-            for (uint32_t spin = 0; spin < spin_limit && !tc_try(BAR(BAR_DRAIN, warp), 0); ++spin) {}
+            for (uint32_t spin = 0; spin < TC_DRAIN_LIMIT && !tc_try(BAR(BAR_DRAIN, warp), 0); ++spin) {}
         }
         __syncwarp();
     } else if (warp < 8) {
@@ -256,7 +257,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_q4_kernel(const __grid_c
             // copies in flight must land before the CTA may exit, whatever happened elsewhere
             for (int it = max(0, issued - TC_STAGES); it < issued && lane == 0; ++it) {
                 const uint32_t bar = BAR(BAR_FULL, it % TC_STAGES), parity = (uint32_t) ((it / TC_STAGES) & 1);
-                for (uint32_t spin = 0; spin < spin_limit && !tc_try(bar, parity); ++spin) {}
+                for (uint32_t spin = 0; spin < TC_DRAIN_LIMIT && !tc_try(bar, parity); ++spin) {}
             }
             __syncwarp();
         }
@@ -420,14 +421,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) mmq_tc_q4_kernel(const __grid_c
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;\n" ::"r"(tmem) : "memory");
 }
 
-static int tc_sm_count() {
-    static int n = 0;
-    if (!n) {
-        int dev = 0;
+static int tc_sm_count() {   // every device of a process is the same model
+    static const int n = [] {
+        int dev = 0, v = 0;
         cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        if (n <= 0) n = 148;
-    }
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+        return v > 0 ? v : 148;
+    }();
     return n;
 }
 
@@ -527,11 +527,10 @@ int launch_mmq_tc(int wtype, const TiledDims &d, const void *w, const ActDims &a
         if (e != cudaSuccess) return set_error(B200_E_CUDA, "mmq_tc shared memory opt-in: %s", cudaGetErrorString(e));
         configured[dev & 63] = true;
     }
-    static int mode = -1;   // debugging switches, see the kernel
-    if (mode < 0) {
+    static const int mode = [] {   // debugging switches, see the kernel
         const char *e = getenv("B200_TC_DEBUG");
-        mode = e ? atoi(e) : 0;
-    }
+        return e ? atoi(e) : 0;
+    }();
     TcMaps maps;
     maps.wq = wm.q; maps.wd = wm.d; maps.bh = am.h; maps.bl = am.l; maps.bs = am.s;
     const int64_t row_groups = (d.n_rt + 7) / 8, col_chunks = (a.n_nt + 7) / 8;
@@ -563,10 +562,21 @@ int tc_error_flag() {
     cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int));
     return v;
 }
+void tc_set_wait_limit(unsigned rounds) {
+    const unsigned v = rounds ? rounds : 1u << 20;
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_tc_spin_limit, &v, sizeof(v));
+    cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(zero));
+}
 
 }  // namespace b200
 
-extern "C" B200_API int b200_kernel_status(void) { return b200::tc_error_flag(); }
+namespace b200 { int tcf_error_flag(); void tcf_set_wait_limit(unsigned rounds); }
+extern "C" B200_API int b200_kernel_status(void) { return b200::tc_error_flag() | (b200::tcf_error_flag() << 1); }
+extern "C" B200_API void b200_kernel_set_wait_limit(unsigned rounds) {
+    b200::tc_set_wait_limit(rounds);
+    b200::tcf_set_wait_limit(rounds);
+}
 #ifdef B200_TC_PROFILE
 extern "C" B200_API void b200_tc_profile(long long *out) { cudaMemcpyFromSymbol(out, b200::g_tc_prof, sizeof(long long) * 256); }
 #endif

@@ -8,6 +8,9 @@ namespace b200 {
 int act_layout(int64_t N);
 int launch_mmq_tc(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
                   void *workspace, size_t workspace_bytes, cudaStream_t st);
+int launch_mmq_tcf(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
+                   void *workspace, size_t workspace_bytes, cudaStream_t st, int terms);
+int mmq_tc_mode();
 int mmvq_max_n();
 int launch_mmvq(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row, const PeerDst &peers,
                 cudaStream_t st);
@@ -131,6 +134,9 @@ static int mul_mat_prequant(int wtype, const void *w, int64_t K, int64_t M, cons
     // weights, a row-split product) takes the mma.sync kernel on the fragment-order plane that is always there
     if (act_layout(N) == 3 && wtype == B200_TYPE_Q4_0 && peers.n == 0 && peers.n_seg <= 1) {
         return launch_mmq_tc(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream);
+    }
+    if (mmq_tc_mode() >= 2 && N >= 16 && wtype == B200_TYPE_Q4_0 && peers.n == 0 && peers.n_seg <= 1) {
+        return launch_mmq_tcf(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream, mmq_tc_mode() == 2 ? 3 : 2);
     }
     return launch_mmq(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream, false, peers);
 }

@@ -40,25 +40,26 @@ __global__ void __launch_bounds__(256) allgather_push_kernel(const float *__rest
     }
 }
 
-// flags layout in every rank's shared block: uint32 arrived[8] (written by peers), then (local use only) uint32 counter, uint32 error
+// flags layout in every rank's shared block: uint32 arrived[8] (written by peers), then (local use only) uint32 counter, uint32 error,
+// uint32 poll limit (0 = PEER_SPIN_LIMIT)
 __global__ void allgather_signal_wait_kernel(PeerPtrs flags, int rank, int g) {
     uint32_t *mine = reinterpret_cast<uint32_t *>(flags.p[rank]);
     __shared__ uint32_t epoch;
     if (threadIdx.x == 0) epoch = mine[8] + 1;
     __syncthreads();
-    const uint32_t e = epoch;
+    const uint32_t e = epoch, limit = mine[10] ? mine[10] : PEER_SPIN_LIMIT;
     const int r = threadIdx.x;
     if (r < g) {
         uint32_t *theirs = reinterpret_cast<uint32_t *>(flags.p[r]) + rank;
         asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(theirs), "r"(e) : "memory");
         const uint32_t *from_r = mine + r;
         uint32_t spin = 0, v = 0;
-        for (; spin < PEER_SPIN_LIMIT; ++spin) {
+        for (; spin < limit; ++spin) {
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(from_r) : "memory");
             if ((int32_t) (v - e) >= 0) break;
             __nanosleep(100);
         }
-        if (spin == PEER_SPIN_LIMIT) atomicExch(mine + 9, (uint32_t) (r + 1));   // gave up on peer r
+        if (spin == limit) atomicExch(mine + 9, (uint32_t) (r + 1));   // gave up on peer r
     }
     __syncthreads();
     if (threadIdx.x == 0) mine[8] = e;
@@ -133,6 +134,13 @@ int b200_allgather_rows(const float *src, int64_t src_nb_row, int64_t T, int64_t
     allgather_push_kernel<<<grid, 256, 0, st>>>(src, src_nb_row, T, Mg, d, dst_nb_row, (int64_t) rank * Mg, g);
     if (int e = check_launch("allgather_push")) return e;
     return launch_peer_signal_wait(flags_of_rank, rank, g, st);
+}
+
+int b200_peer_set_wait_limit(void *flags, unsigned polls) {
+    B200_REQUIRE(flags, "null pointer");
+    const uint32_t v[2] = {0u, (uint32_t) polls};   // the error word and the limit sit side by side
+    cudaError_t e = cudaMemcpy(reinterpret_cast<uint32_t *>(flags) + 9, v, sizeof(v), cudaMemcpyHostToDevice);
+    return e == cudaSuccess ? B200_OK : set_error(B200_E_CUDA, "peer_set_wait_limit: %s", cudaGetErrorString(e));
 }
 
 int b200_peer_status(const void *flags) {

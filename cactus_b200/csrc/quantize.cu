@@ -219,14 +219,18 @@ int launch_quantize_b8(const float *x, int64_t x_nb_row, int64_t K, int64_t N, v
 // mma.sync kernels read; 3 = those plus the e4m3 planes of the tcgen05 kernel (ACT_F8_MIN_N columns and more; the
 // scratch of such a product always has room for them).  The tcgen05 kernel is taken with B200_MMQ_TC=1: it passes every
 // parity case, but at the decode width of 64 columns it does not beat the mma.sync kernel yet (see mmq_tc.cu).
-bool mmq_tc_enabled() {
-    static int mode = -1;
-    if (mode < 0) {
+// B200_MMQ_TC: 0 mma.sync kernel, 1 the per-block tcgen05 kernel (mmq_tc.cu), 2 / 3 the folded-scale tcgen05 kernel
+// (mmq_tcf.cu) with 3 / 2 product terms.
+int mmq_tc_mode() {
+    static const int mode = [] {
         const char *e = getenv("B200_MMQ_TC");
-        mode = (e && atoi(e) == 1) ? 1 : 0;
-    }
-    return mode == 1;
+        int mode = e ? atoi(e) : 0;
+        if (mode < 0 || mode > 3) mode = 0;
+        return mode;
+    }();
+    return mode;
 }
+bool mmq_tc_enabled() { return mmq_tc_mode() == 1; }
 int act_layout(int64_t N) { return (N >= ACT_F8_MIN_N && mmq_tc_enabled()) ? 3 : 1; }
 
 }  // namespace b200

@@ -1,5 +1,5 @@
-"""Synthetic workloads of the benchmark (numpy only): the 64-sequence continuous-batching state of
-BASELINE.json configs[3] after its prompts have been prefilled."""
+"""Synthetic workloads of the benchmark (numpy only): the continuous-batching serving state -- 64 sequences with ragged
+prompts of up to 1024 tokens in a unified KV cache of 65536 cells -- after the prompts have been prefilled."""
 from __future__ import annotations
 
 import numpy as np

@@ -61,6 +61,10 @@ B200_API uint64_t b200_launch_count(void);
 /* 0, or non-zero once a kernel on the current device gave up a bounded wait on one of its own barriers (its result
  * is then invalid; the context stays usable).  No reference counterpart: the CPU kernels have no such waits. */
 B200_API int b200_kernel_status(void);
+/* How many polling rounds such a wait makes before it gives up (0 restores the default, which amounts to seconds), and
+ * clears b200_kernel_status.  A monitoring or test hook: a kernel that gave up has waited for its own copies and tensor
+ * core work in flight (that wait keeps its own, fixed limit) and returned normally. */
+B200_API void b200_kernel_set_wait_limit(unsigned rounds);
 
 /* ------------------------------------------------------------------------------------------------
  * Weight storage.
@@ -125,7 +129,9 @@ B200_API int b200_mul_mat_q_prequant(int wtype, const void *w, int64_t K, int64_
  * the call takes inputs and outputs only and performs no cudaMalloc / cudaFree of its own.
  *
  * Limits: N <= B200_NOALLOC_MAX_N columns (the decode kernel) and K <= B200_NOALLOC_MAX_K; larger sizes are
- * refused with B200_E_INVALID.  Results are those of b200_mul_mat_q.  The first call on a device looks up the
+ * refused with B200_E_INVALID.  Results are within the mul_mat tolerance of b200_mul_mat_q, and bit-identical to it
+ * whenever both calls split K the same way (for 3 to 8 columns b200_mul_mat_q may split K across CTAs through its
+ * workspace; this entry point has no workspace and never does).  The first call on a device looks up the
  * array's device address (a one-off set-up step): make that first call outside any stream capture.  All calls
  * share the one array, which keeps whatever the last call left in it: two calls that overlap on the GPU (different
  * streams, or different threads without ordering between them) race; calls ordered on one stream are fine. */
@@ -308,6 +314,10 @@ B200_API int b200_peer_free(void *ptr);
 B200_API int b200_allgather_rows(const float *src, int64_t src_nb_row, int64_t T, int64_t Mg, int rank, int g, void *const *dst_of_rank,
                                  int64_t dst_nb_row, void *const *flags_of_rank, b200_stream_t stream);
 B200_API int b200_peer_status(const void *flags);
+/* The number of polls (about 100 ns each) after which the wait for a peer gives up; 0 restores the default (seconds).
+ * Also clears the status of the flag block.  A rank that left between steps is noticed this way: the next collective of
+ * the others returns after the limit with b200_peer_status = 1 + that rank, and their contexts stay usable. */
+B200_API int b200_peer_set_wait_limit(void *flags, unsigned polls);
 /* mul_mat and join in one step: b200_mul_mat_q_prequant on this rank's row slice (M rows, the columns first_column ..
  * first_column + M - 1 of the full product), with the kernel's own write-back storing every value into dst_of_rank[r]
  * of all g ranks, followed by the flag exchange of b200_allgather_rows.  dst_of_rank[r] is rank r's full [N, *] buffer. */

@@ -35,8 +35,14 @@ def build_oracle() -> str:
     return path
 
 
-def build_ref(reference_root: str = "/root/reference/cactus") -> str | None:
+def default_reference_root() -> str:
+    """A checkout of the reference: $CACTUS_REFERENCE, else the directory "reference/cactus" beside this repository."""
+    return os.environ.get("CACTUS_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference", "cactus")
+
+
+def build_ref(reference_root: str | None = None) -> str | None:
     """Compile the reference from its own sources when a checkout is present; otherwise use what is there."""
+    reference_root = reference_root or default_reference_root()
     path = os.path.join(HERE, "_ref", "libref_ops.so")
     if os.path.isdir(reference_root):
         subprocess.check_call(["make", "-C", HERE, "-j8", "ref", f"REF={reference_root}"], stdout=subprocess.DEVNULL)

@@ -424,6 +424,8 @@ static int decode_batch(runner & r, const std::vector<int32_t> & tok, const std:
 
 extern bool g_b200_device_mask;
 extern unsigned long long g_b200_device_mask_calls;
+extern bool g_b200_mask_verify;
+extern unsigned long long g_b200_mask_values, g_b200_mask_mismatches;
 
 static int run_model(int argc, char ** argv) {
     model_cfg c;
@@ -451,6 +453,7 @@ static int run_model(int argc, char ** argv) {
         else if (a == "--path") path = argv[++i];
         else if (a == "--split-row") split_row_gpus = val();
         else if (a == "--device-mask") g_b200_device_mask = true;   // device_mask.cpp: the KQ mask is synthesised on the device
+        else if (a == "--verify-mask") g_b200_mask_verify = true;   // ... and compared bit for bit with the reference's host mask
     }
     llama_log_set([](lm_ggml_log_level level, const char * text, void *) { if (level >= LM_GGML_LOG_LEVEL_ERROR) fputs(text, stderr); }, nullptr);
     if (!cpu_only) lm_ggml_backend_register(lm_ggml_backend_b200_reg());
@@ -538,9 +541,10 @@ static int run_model(int argc, char ** argv) {
     }
     printf("{\"case\": \"model\", \"layers\": %d, \"d\": %d, \"seqs\": %d, \"decode_steps\": %d, \"rows\": %d, \"worst_rel\": %.3g, "
            "\"rows_within_1e-3\": %.3f, \"greedy_agree\": %.3f, \"b200_step_ms\": %.3f, \"split_mul_mats\": %llu, \"device_masks\": %llu, "
-           "\"device_ms_per_graph\": %.3f, \"rope_store_groups\": %llu, \"add_norm_groups\": %llu}\n",
+           "\"device_ms_per_graph\": %.3f, \"rope_store_groups\": %llu, \"add_norm_groups\": %llu, \"mask_values_checked\": %llu, \"mask_mismatches\": %llu}\n",
            c.n_layer, c.d, n_seq, n_decode, total, worst, good_rows / sum_rows, (double) agree / total, step_ms,
-           (unsigned long long) (cpu_only ? 0 : lm_ggml_backend_b200_split_mul_mat_count()), g_b200_device_mask_calls, bench_device_ms, (unsigned long long) n_rope_store, (unsigned long long) n_add_norm);
+           (unsigned long long) (cpu_only ? 0 : lm_ggml_backend_b200_split_mul_mat_count()), g_b200_device_mask_calls, bench_device_ms, (unsigned long long) n_rope_store, (unsigned long long) n_add_norm,
+           g_b200_mask_values, g_b200_mask_mismatches);
     if (cpu.ctx) llama_free(cpu.ctx);
     if (cpu.model) llama_model_free(cpu.model);
     if (gpu.ctx) llama_free(gpu.ctx);
@@ -583,7 +587,10 @@ static int run_split_roundtrip() {
     return equal ? 0 : 1;
 }
 
+int run_faults();   // faults.cpp
+
 int main(int argc, char ** argv) {
+    if (argc >= 2 && strcmp(argv[1], "faults") == 0) return run_faults();
     if (argc >= 2 && strcmp(argv[1], "split") == 0) return run_split_roundtrip();
     if (argc >= 2 && strcmp(argv[1], "ops") == 0) {
         int rc = 0;
@@ -593,6 +600,6 @@ int main(int argc, char ** argv) {
         return rc;
     }
     if (argc >= 2 && strcmp(argv[1], "model") == 0) return run_model(argc, argv);
-    fprintf(stderr, "usage: harness ops | harness model [--layers N --d N --heads N --kv N --ff N --vocab N --ctx N --seqs N --decode N]\n");
+    fprintf(stderr, "usage: harness ops | harness split | harness faults | harness model [--layers N --d N --heads N --kv N --ff N --vocab N --ctx N --seqs N --decode N]\n");
     return 64;
 }

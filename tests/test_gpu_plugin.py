@@ -71,6 +71,33 @@ def test_device_side_kq_mask_through_llama_decode():
     assert rc1 == 0
 
 
+def test_device_kq_mask_is_the_reference_mask_bit_for_bit():
+    """Every ubatch of a ragged 7-sequence run (a prompt ubatch of unequal lengths, then decode ubatches): the reference's
+    own set_input_kq_mask fills its f32 host mask, b200_kq_mask_build writes the f16 mask for the same cells and tokens,
+    and the driver compares the two value by value (0 against 0x0000, -inf against 0xFC00, padding rows included)."""
+    rc, out, err = run("model", "--head-q4", "--seqs", "7", "--max-prompt", "90", "--decode", "6", "--device-mask", "--verify-mask")
+    assert out, err
+    r = out[-1]
+    assert "error" not in r, (r, err)
+    assert r["device_masks"] == 7 and r["mask_values_checked"] > 7 * 64 * 7, r
+    assert r["mask_mismatches"] == 0, r
+    assert rc == 0
+
+
+def test_host_made_failures_abort_callback_and_failing_allocator():
+    """Failure paths without a GPU fault (tests/backend/faults.cpp): an abort callback that says stop gives
+    LM_GGML_STATUS_ABORTED (1), a cudaMalloc that fails gives no buffer and LM_GGML_STATUS_ALLOC_FAILED (-2); after each the
+    same backend computes the graph again with bit-identical results."""
+    rc, out, err = run("faults")
+    assert out, err
+    r = out[-1]
+    assert "error" not in r, (r, err)
+    assert r["first"] == 0 and r["aborted"] == 1 and r["after_abort"] == 0 and r["after_abort_same"], r
+    assert r["buffer_refused"] and r["alloc_failed"] == -2 and r["refused_mallocs"] >= 2, r
+    assert r["after_alloc"] == 0 and r["after_alloc_same"] and r["finite"], r
+    assert rc == 0
+
+
 def test_fused_groups_do_not_change_results():
     """ADD + RMS_NORM + MUL + quantiser and ROPE(q, k) + K/V store run as one kernel each where the graph allows it;
     with B200_FUSE=0 every node runs by itself.  The two must agree exactly (the fused kernels are bit-identical)."""

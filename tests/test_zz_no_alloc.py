@@ -40,6 +40,41 @@ def test_noalloc_matches_the_scratch_taking_entry_point_twice_in_a_row():
             assert np.array_equal(a, b)
 
 
+@pytest.mark.parametrize("wtype,bb", [(2, 18), (8, 34)])
+@pytest.mark.parametrize("K,N", [(32768, 8), (2048 + 3 * 32, 3), (2048 + 32, 8), (32768, 1)])
+def test_noalloc_at_its_limits_and_with_ragged_block_counts(wtype, bb, K, N):
+    """The largest size the built-in array admits (8 columns of 32768 values) and rows whose block count is not a
+    multiple of the 4-block groups of the tiled layout.  For 3 and more columns the ordinary entry point may split K
+    through its workspace and this one may not, so the comparison is the mul_mat tolerance, against the oracle too.
+    The device's free memory (cudaMemGetInfo) must not move across the call."""
+    from cactus_b200 import ops
+    from cactus_b200._lib import check, lib
+    from oracle.binding import Oracle
+    L = lib()
+    g = torch.Generator(device="cuda").manual_seed(K + N)
+    M = 80
+    blocks = torch.randint(0, 256, (M, K // 32 * bb), dtype=torch.uint8, device="cuda", generator=g)
+    blocks.view(M, K // 32, bb)[:, :, 1] = 0x1C
+    w = ops.QWeight.from_blocks(wtype, K, M, blocks)
+    x = torch.randn((N, K), device="cuda", generator=g)
+    want = ops.mul_mat(w, x)
+    got = torch.full((N, M), float("nan"), device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    check(L.b200_mul_mat_q_noalloc(wtype, w.data.data_ptr(), K, M, x.data_ptr(), K * 4, N, got.data_ptr(), M * 4, 0, st))   # first use on this device
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    got.fill_(float("nan"))
+    check(L.b200_mul_mat_q_noalloc(wtype, w.data.data_ptr(), K, M, x.data_ptr(), K * 4, N, got.data_ptr(), M * 4, 0, st))
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    a, b = got.cpu().numpy(), want.cpu().numpy()
+    assert np.isfinite(a).all()
+    assert np.abs(a - b).max() / np.abs(b).max() < 1e-3
+    ref, _ = Oracle().mul_mat(wtype, blocks.cpu().numpy(), x.cpu().numpy(), 0)
+    assert np.abs(a - ref).max() / np.abs(ref).max() < 1e-3
+
+
 def test_noalloc_refuses_sizes_beyond_the_built_in_array():
     from cactus_b200._lib import lib
     L = lib()
