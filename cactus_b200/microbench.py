@@ -4,6 +4,7 @@
     python -m cactus_b200.microbench fattn --seqs 64 --ctx 900 --reps 3
     python -m cactus_b200.microbench fattn --cfg2 a --copies 8       # the 512-token prefill ubatch of 16 ragged sequences
     python -m cactus_b200.microbench quantize --K 4096 --N 64
+    python -m cactus_b200.microbench umma-rate                      # tcgen05.mma issue rates per kind and shape (csrc/probes)
 
 `--copies` distinct weight tensors are cycled so the weights streamed per pass exceed the 126 MB L2.
 Prints one JSON line with the CUDA-event time per launch and the algorithmic GB/s.
@@ -203,7 +204,24 @@ def bench_quantize(a):
     return {"kernel": "quantize_q8_0", "K": a.K, "N": a.N, "ms_per_launch": ms, "GBps": (a.N * a.K * 4 + a.N * a.K * 34 / 32) / ms / 1e6}
 
 
+def run_umma_rate():
+    """Builds csrc/probes/umma_rate.cu (a stand-alone program) next to the library and runs it; returns its report."""
+    import os
+    import subprocess
+
+    from .build import CSRC, OUT, nvcc
+    src, exe = os.path.join(CSRC, "probes", "umma_rate.cu"), os.path.join(OUT, "umma_rate")
+    if not os.path.exists(exe) or os.path.getmtime(exe) < os.path.getmtime(src):
+        os.makedirs(OUT, exist_ok=True)
+        subprocess.check_call([nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-o", exe, src])
+    return subprocess.run([exe], capture_output=True, text=True, timeout=120, check=True).stdout
+
+
 def main():
+    import sys
+    if len(sys.argv) > 1 and sys.argv[1] == "umma-rate":
+        print(run_umma_rate())
+        return
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["mul_mat", "fattn", "quantize"])
     ap.add_argument("--ragged", action="store_true", help="fattn: the benchmark's ragged sequence lengths instead of --seqs x --ctx")
