@@ -92,7 +92,9 @@ static void set_f32(lm_ggml_tensor * t, std::mt19937 & rng, float std_, float me
 }
 
 // One llama layer worth of ops (the node list the plug-in receives, cactus/llama-model.cpp:4517-4671) on small shapes.
-static int run_ops(int n_tokens, lm_ggml_type wtype) {
+// `inplace`: the norm, its weight multiply, SILU, the gate x up product and the last residual add overwrite their first
+// operand (the _inplace forms of the graph builder), so the row kernels and the plug-in's peepholes see aliased pointers.
+static int run_ops(int n_tokens, lm_ggml_type wtype, bool inplace = false) {
     lm_ggml_backend_t cpu = lm_ggml_backend_cpu_init();
     lm_ggml_backend_t gpu = lm_ggml_backend_b200_init(0);
     if (!gpu) { printf("{\"error\": \"no B200 backend\"}\n"); return 2; }
@@ -115,7 +117,9 @@ static int run_ops(int n_tokens, lm_ggml_type wtype) {
 
     // graph
     lm_ggml_tensor * e = lm_ggml_get_rows(ctx, emb, ids);
-    lm_ggml_tensor * h = lm_ggml_mul(ctx, lm_ggml_rms_norm(ctx, lm_ggml_add(ctx, x, e), 1e-5f), wn);
+    auto norm = [&](lm_ggml_tensor * a, bool fresh) { return inplace && fresh ? lm_ggml_rms_norm_inplace(ctx, a, 1e-5f) : lm_ggml_rms_norm(ctx, a, 1e-5f); };
+    auto mul = [&](lm_ggml_tensor * a, lm_ggml_tensor * b) { return inplace ? lm_ggml_mul_inplace(ctx, a, b) : lm_ggml_mul(ctx, a, b); };
+    lm_ggml_tensor * h = mul(norm(lm_ggml_add(ctx, x, e), true), wn);
     lm_ggml_tensor * q = lm_ggml_rope_ext(ctx, lm_ggml_reshape_3d(ctx, lm_ggml_mul_mat(ctx, wq, h), D, H, T), pos, nullptr, D, 0, 0, 500000.0f, 1.0f, 0.0f, 1.0f, 0.0f, 0.0f);
     lm_ggml_tensor * k = lm_ggml_rope_ext(ctx, lm_ggml_reshape_3d(ctx, lm_ggml_mul_mat(ctx, wk, h), D, Hkv, T), pos, nullptr, D, 0, 0, 500000.0f, 1.0f, 0.0f, 1.0f, 0.0f, 0.0f);
     lm_ggml_tensor * v = lm_ggml_mul_mat(ctx, wv, h);
@@ -131,10 +135,10 @@ static int run_ops(int n_tokens, lm_ggml_type wtype) {
     lm_ggml_flash_attn_ext_set_prec(att, LM_GGML_PREC_F32);
     lm_ggml_tensor * ao = lm_ggml_mul_mat(ctx, wo, lm_ggml_reshape_2d(ctx, att, H * D, T));
     lm_ggml_tensor * r1 = lm_ggml_add(ctx, ao, x);
-    lm_ggml_tensor * h2 = lm_ggml_mul(ctx, lm_ggml_rms_norm(ctx, r1, 1e-5f), wn);
-    lm_ggml_tensor * gate = lm_ggml_silu(ctx, lm_ggml_mul_mat(ctx, wg, h2));
-    lm_ggml_tensor * par = lm_ggml_mul(ctx, gate, lm_ggml_mul_mat(ctx, wu, h2));
-    lm_ggml_tensor * out = lm_ggml_add(ctx, lm_ggml_mul_mat(ctx, wd, par), r1);
+    lm_ggml_tensor * h2 = mul(norm(r1, false), wn);   // r1 is read again by the last add: its norm gets a buffer of its own
+    lm_ggml_tensor * gate = inplace ? lm_ggml_silu_inplace(ctx, lm_ggml_mul_mat(ctx, wg, h2)) : lm_ggml_silu(ctx, lm_ggml_mul_mat(ctx, wg, h2));
+    lm_ggml_tensor * par = mul(gate, lm_ggml_mul_mat(ctx, wu, h2));
+    lm_ggml_tensor * out = inplace ? lm_ggml_add_inplace(ctx, lm_ggml_mul_mat(ctx, wd, par), r1) : lm_ggml_add(ctx, lm_ggml_mul_mat(ctx, wd, par), r1);
     lm_ggml_set_output(out);
 
     lm_ggml_cgraph * gf = lm_ggml_new_graph(ctx);
@@ -180,7 +184,7 @@ static int run_ops(int n_tokens, lm_ggml_type wtype) {
     const bool ok = lm_ggml_backend_compare_graph_backend(cpu, gpu, gf, cmp_cb, &st);
     lm_ggml_b200_stats bs;
     lm_ggml_backend_b200_get_stats(gpu, &bs);
-    printf("{\"case\": \"layer\", \"tokens\": %d, \"wtype\": \"%s\", \"compared\": %s, \"nan_mismatch\": %s", n_tokens, lm_ggml_type_name(wtype),
+    printf("{\"case\": \"%s\", \"tokens\": %d, \"wtype\": \"%s\", \"compared\": %s, \"nan_mismatch\": %s", inplace ? "layer in place" : "layer", n_tokens, lm_ggml_type_name(wtype),
            ok ? "true" : "false", st.nan_seen ? "true" : "false");
     for (int op = 0; op < LM_GGML_OP_COUNT; ++op)
         if (st.count[op]) printf(", \"%s\": %.3g", lm_ggml_op_name((lm_ggml_op) op), st.worst[op]);
@@ -550,7 +554,7 @@ static int run_model(int argc, char ** argv) {
     if (gpu.ctx) llama_free(gpu.ctx);
     if (gpu.model) llama_model_free(gpu.model);
     remove(path.c_str());
-    return (worst < 3e-2 && agree >= 0.9 * total) ? 0 : 1;
+    return (worst < 3e-2 && agree >= 0.95 * total) ? 0 : 1;
 }
 
 // A quantised tensor placed in the plug-in's split buffer type (rows spread over all B200 devices, ragged row count):
@@ -596,6 +600,7 @@ int main(int argc, char ** argv) {
         int rc = 0;
         for (lm_ggml_type t : {LM_GGML_TYPE_Q4_0, LM_GGML_TYPE_Q8_0})
             for (int n : {1, 5, 24, 70}) rc |= run_ops(n, t);
+        for (int n : {1, 24, 70}) rc |= run_ops(n, LM_GGML_TYPE_Q4_0, true);
         rc |= run_kv_ops();
         return rc;
     }

@@ -40,6 +40,8 @@ def test_layer_ops_node_by_node_against_reference_cpu():
         assert r["FLASH_ATTN_EXT"] < 6e-3, r
         assert r["GET_ROWS"] == 0, r
         assert r["b200_mul_mat"] == 7 and r["b200_flash_attn"] == 1, r
+    # the same layer with the norm, its weight multiply, SILU, gate x up and the residual add in place (aliased operands)
+    assert sum(r.get("case") == "layer in place" for r in lines) == 3, lines
     assert rc == 0, (lines, err)
 
 
@@ -49,7 +51,7 @@ def test_synthetic_llama_through_llama_decode(extra):
     assert lines, err
     r = lines[-1]
     assert "error" not in r, (r, err)
-    assert r["greedy_agree"] >= 0.9, r   # near-ties can flip with the int8 rounding flips described below
+    assert r["greedy_agree"] >= 0.95, r   # measured 1.0 and 0.98: a near-tie can flip with the int8 rounding flips described below
     # every mul_mat re-quantises its input to int8, so last-bit differences flip roundings and move a token's
     # logits by up to ~1e-2 on this small model (the reference moves as much when its own inputs get 2e-7 noise)
     assert r["worst_rel"] < 3e-2, r
