@@ -8,6 +8,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -504,12 +505,20 @@ const lm_ggml_backend_buffer_type_i b200_split_buft_iface = {
 // ---------------------------------------------------------------------------------------------
 // backend (one CUDA stream) and its scratch memory
 // ---------------------------------------------------------------------------------------------
+// While a node list is being recorded into a CUDA graph nothing may synchronise or allocate: a scratch block that would
+// have to grow fails the recording instead (the list then runs directly, which grows the block, and is recorded next time).
+thread_local bool t_recording = false, t_recording_failed = false;
+
 struct scratch_buf {
     void * ptr = nullptr;
     size_t bytes = 0;
     // grows when needed; growing synchronises the stream first because earlier kernels may still use the old block
     void * get(size_t need, cudaStream_t st) {
         if (need <= bytes) return ptr;
+        if (t_recording) {
+            t_recording_failed = true;
+            return nullptr;
+        }
         if (ptr) {
             cudaStreamSynchronize(st);
             cudaFree(ptr);
@@ -564,6 +573,25 @@ struct b200_backend_ctx {
     bool timing = false;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     lm_ggml_b200_stats stats = {};
+    // CUDA-graph replay of node lists (graph_cache below)
+    bool graphs = true;      // B200_GRAPHS=0: every node list is launched kernel by kernel
+    bool warmed = false;     // one node list has run directly (lazy per-device set-up of the kernel library is done)
+    struct graph_entry {
+        uint64_t h1 = 0, h2 = 0, stamp = 0;
+        int n_nodes = 0;
+        cudaGraphExec_t exec = nullptr;
+        lm_ggml_b200_stats delta = {};               // what one run adds to the counters
+        uint64_t rope_stores = 0, add_norms = 0, masks = 0;
+    } cache[4];
+    uint64_t stamp = 0, last_h1 = 0, last_h2 = 0;
+    int cold_records = 0;    // recordings since the last replay
+    std::vector<uint64_t> dbg_trail;
+    // rows of the KV cache that the ubatch's K / V stores write: the one thing that moves from step to step in a decode
+    // graph.  The stores take (cache tensor, list of rows); the lists sit in device memory and are refreshed before every run.
+    int32_t * slots_dev = nullptr;
+    size_t slots_cap = 0;
+    std::vector<int32_t> slots_host;
+    std::vector<std::pair<const lm_ggml_tensor *, int>> slot_of;   // CPY node -> offset of its row list
 };
 
 lm_ggml_guid_t b200_guid() {
@@ -585,6 +613,8 @@ void backend_free(lm_ggml_backend_t backend) {
         if (ctx->ev0) cudaEventDestroy(ctx->ev0);
         if (ctx->ev1) cudaEventDestroy(ctx->ev1);
         if (ctx->ev_act) cudaEventDestroy(ctx->ev_act);
+        for (auto & e : ctx->cache) if (e.exec) cudaGraphExecDestroy(e.exec);
+        if (ctx->slots_dev) cudaFree(ctx->slots_dev);
         cudaStreamDestroy(ctx->stream);
     }
     for (int i = 0; i < LM_GGML_B200_MAX_DEVICES; ++i) {
@@ -906,17 +936,73 @@ lm_ggml_status compute_mul_mat_split(b200_backend_ctx * ctx, lm_ggml_tensor * no
     return LM_GGML_STATUS_SUCCESS;
 }
 
+// A CPY that stores f32 rows as f16 into whole consecutive rows of a cache tensor (cpy_k / cpy_v,
+// cactus/llama-kv-cache.cpp:617-656: the destination is a view of the layer's cache at the rows the ubatch was given).
+// Such a store runs as "rows r[0..T) of the cache tensor", with the row numbers in device memory, so that its launch is the
+// same for every position of the ubatch in the cache.
+bool row_store(const lm_ggml_tensor * cpy, int64_t * rows, int64_t * row_elems, int64_t * first_row) {
+    const lm_ggml_tensor * src = cpy->src[0], * dst = cpy->src[1];
+    if (cpy->op != LM_GGML_OP_CPY || !src || !dst || !dst->view_src || src->type != LM_GGML_TYPE_F32 || dst->type != LM_GGML_TYPE_F16) return false;
+    const lm_ggml_tensor * cache = dst->view_src;
+    if (cache->type != LM_GGML_TYPE_F16 || !lm_ggml_is_contiguous(cache) || !lm_ggml_is_contiguous(dst) || !lm_ggml_is_contiguous(src)) return false;
+    if (!cache->buffer || !buft_is_b200(cache->buffer->buft) || tensor_is_tiled(cache)) return false;
+    const int64_t n = lm_ggml_nelements(dst), re = cache->ne[0];
+    if (re <= 0 || n <= 0 || n % re || lm_ggml_nelements(src) != n || cache->nb[1] != (size_t) re * 2 || dst->view_offs % cache->nb[1]) return false;
+    if (((uintptr_t) src->data % 4) || dst->data != (char *) cache->data + dst->view_offs) return false;
+    *rows = n / re;
+    *row_elems = re;
+    *first_row = (int64_t) (dst->view_offs / cache->nb[1]);
+    return true;
+}
+
+int slot_offset(const b200_backend_ctx * ctx, const lm_ggml_tensor * cpy) {
+    for (const auto & e : ctx->slot_of) if (e.first == cpy) return e.second;
+    return -1;
+}
+
+// finds the row stores of a node list, writes their row numbers to the device (in stream order, before the list runs)
+bool prepare_row_lists(b200_backend_ctx * ctx, const lm_ggml_cgraph * g) {
+    ctx->slot_of.clear();
+    ctx->slots_host.clear();
+    for (int i = 0; i < g->n_nodes; ++i) {
+        int64_t rows, re, first;
+        if (!row_store(g->nodes[i], &rows, &re, &first) || rows > (1 << 20)) continue;
+        ctx->slot_of.emplace_back(g->nodes[i], (int) ctx->slots_host.size());
+        for (int64_t r = 0; r < rows; ++r) ctx->slots_host.push_back((int32_t) (first + r));
+    }
+    if (ctx->slots_host.empty()) return true;
+    if (ctx->slots_host.size() > ctx->slots_cap) {
+        cudaStreamSynchronize(ctx->stream);
+        if (ctx->slots_dev) cudaFree(ctx->slots_dev);
+        ctx->slots_dev = nullptr;
+        ctx->slots_cap = 0;
+        const size_t want = std::max<size_t>(4096, ctx->slots_host.size() * 2);
+        if (!cuda_ok(cudaMalloc((void **) &ctx->slots_dev, want * sizeof(int32_t)), "cudaMalloc(row lists)")) {
+            ctx->slot_of.clear();   // the stores fall back to their absolute addresses
+            return false;
+        }
+        ctx->slots_cap = want;
+    }
+    // pageable source: the copy is staged before the call returns, so the vector may be reused
+    if (!cuda_ok(cudaMemcpyAsync(ctx->slots_dev, ctx->slots_host.data(), ctx->slots_host.size() * sizeof(int32_t), cudaMemcpyHostToDevice, ctx->stream),
+                 "cudaMemcpyAsync(row lists)")) {
+        ctx->slot_of.clear();
+        return false;
+    }
+    return true;
+}
+
+const lm_ggml_tensor * through_views(const lm_ggml_tensor * t) {
+    while (t && (t->op == LM_GGML_OP_RESHAPE || t->op == LM_GGML_OP_VIEW) && t->src[0]) t = t->src[0];
+    return t;
+}
+
 // ROPE(k) and the CPY that stores the rotated k as f16 into the cache rows of the ubatch (cpy_k,
 // cactus/llama-kv-cache.cpp:617-628) as one kernel, run in the place of the ROPE.  The store is only moved EARLIER: the
 // rows it writes are read by nothing before the attention of the same layer.  (Moving a node LATER is not possible under
 // ggml-alloc: the ROPE's source is handed to the next product as soon as the ROPE's place in the node order has passed, so
 // ROPE(q) and the V store stay where they are.)  Needs: the rotated k feeds nothing but that store, which writes whole
 // consecutive f16 rows of Hkv * D values.
-const lm_ggml_tensor * through_views(const lm_ggml_tensor * t) {
-    while (t && (t->op == LM_GGML_OP_RESHAPE || t->op == LM_GGML_OP_VIEW) && t->src[0]) t = t->src[0];
-    return t;
-}
-
 bool rope_store_group(b200_backend_ctx * ctx, const lm_ggml_cgraph * g, int i) {
     const lm_ggml_tensor * rk = g->nodes[i];
     if (rk->src[0]->type != LM_GGML_TYPE_F32 || !lm_ggml_is_contiguous(rk) || !lm_ggml_is_contiguous(rk->src[0]) || rk->ne[3] != 1) return false;
@@ -938,9 +1024,20 @@ bool rope_store_group(b200_backend_ctx * ctx, const lm_ggml_cgraph * g, int i) {
     memcpy(&freq_base, p + 5, sizeof(float));
     memcpy(&freq_scale, p + 6, sizeof(float));
     memcpy(&attn_factor, p + 8, sizeof(float));
+    // through the row list when the store is a cache-row store (see row_store): nothing in the launch then depends on where
+    // in the cache the ubatch lands
+    const int32_t * rows_list = nullptr;
+    void * k_base = kdst->data;
+    int64_t k_nb_row = Hkv * D * 2;
+    const int at = slot_offset(ctx, ck);
+    if (at >= 0) {
+        rows_list = ctx->slots_dev + at;
+        k_base = kdst->view_src->data;
+        k_nb_row = (int64_t) kdst->view_src->nb[1];
+    }
     if (b200_rope_store_to(nullptr, nullptr, 0, 0, (const float *) rk->src[0]->data, rk->src[0]->nb[1], rk->src[0]->nb[2], nullptr, 0, D, 0, Hkv, T, p[1],
                            (const int32_t *) rk->src[1]->data, rk->src[2] ? (const float *) rk->src[2]->data : nullptr, freq_base, freq_scale, attn_factor,
-                           nullptr, kdst->data, Hkv * D * 2, nullptr, 0, ctx->stream) != B200_OK) {
+                           rows_list, k_base, k_nb_row, nullptr, 0, ctx->stream) != B200_OK) {
         B200_LOG_ERROR("ggml-b200: %s: %s\n", lm_ggml_op_name(node->op), b200_last_error());
         return false;   // the separate kernels take over
     }
@@ -951,16 +1048,22 @@ bool rope_store_group(b200_backend_ctx * ctx, const lm_ggml_cgraph * g, int i) {
     return true;
 }
 
-lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph * cgraph) {
-    b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
-    device_guard g(ctx->device);
+// the mask-cast CPY of a mask that the driver described instead of filling (kq_mask_hint_t)
+bool mask_hint_serves(const b200_backend_ctx * ctx, const lm_ggml_tensor * node) {
+    if (node->op != LM_GGML_OP_CPY) return false;
+    const lm_ggml_tensor * s0 = node->src[0], * dstt = node->src[1] ? node->src[1] : node;
+    const kq_mask_hint_t::dev_state & d = g_kq_hint.dev[ctx->device];
+    return d.dev_mask && s0->data == d.dev_mask && d.serial == g_kq_hint.serial && s0->type == LM_GGML_TYPE_F32 && dstt->type == LM_GGML_TYPE_F16 &&
+           lm_ggml_is_contiguous(dstt) && s0->ne[0] == d.n_kv && s0->ne[1] == (d.n_tokens + 63) / 64 * 64 && lm_ggml_nelements(s0) == lm_ggml_nelements(dstt);
+}
+
+// launches the kernels of a node list on the backend's stream (directly, or into a stream capture)
+lm_ggml_status run_nodes(b200_backend_ctx * ctx, lm_ggml_cgraph * cgraph, bool check_abort) {
     cudaStream_t st = ctx->stream;
     ctx->act_src = nullptr;
     for (split_peer & p : ctx->peers) p.act_src = nullptr;
     ctx->index_mask = nullptr;
     ctx->rs.cpy_k = nullptr;
-    ctx->stats.graphs++;
-    if (ctx->timing) cudaEventRecord(ctx->ev0, st);
 
     for (int i = 0; i < cgraph->n_nodes; ++i) {
         lm_ggml_tensor * node = cgraph->nodes[i];
@@ -971,7 +1074,7 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
             default:
                 break;
         }
-        if (ctx->abort_cb && (i & 63) == 0 && ctx->abort_cb(ctx->abort_cb_data)) {
+        if (check_abort && ctx->abort_cb && (i & 63) == 0 && ctx->abort_cb(ctx->abort_cb_data)) {
             cudaStreamSynchronize(st);
             return LM_GGML_STATUS_ABORTED;
         }
@@ -1147,15 +1250,20 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
                     ctx->rs.cpy_k = nullptr;
                     break;
                 }
-                {   // the f32 -> f16 cast of a mask the driver described instead of filling: synthesise the f16 mask
+                if (mask_hint_serves(ctx, node)) {   // the f32 -> f16 cast of a mask the driver described instead of filling: synthesise the f16 mask
                     kq_mask_hint_t::dev_state & d = g_kq_hint.dev[ctx->device];
                     const lm_ggml_tensor * dstt = s1 ? s1 : node;
-                    if (d.dev_mask && s0->data == d.dev_mask && d.serial == g_kq_hint.serial && s0->type == LM_GGML_TYPE_F32 &&
-                        dstt->type == LM_GGML_TYPE_F16 && lm_ggml_is_contiguous(dstt) && s0->ne[0] == d.n_kv && s0->ne[1] == (d.n_tokens + 63) / 64 * 64 &&
-                        lm_ggml_nelements(s0) == lm_ggml_nelements(dstt)) {
-                        B200_CHECK(b200_kq_mask_build(d.buf, d.buf + d.n_kv, d.n_kv, d.buf + 2 * d.n_kv, d.buf + 2 * d.n_kv + d.n_tokens, d.n_tokens,
-                                                      dstt->data, d.n_kv * 2, st));
-                        g_kq_hint.masks_built.fetch_add(1, std::memory_order_relaxed);
+                    B200_CHECK(b200_kq_mask_build(d.buf, d.buf + d.n_kv, d.n_kv, d.buf + 2 * d.n_kv, d.buf + 2 * d.n_kv + d.n_tokens, d.n_tokens,
+                                                  dstt->data, d.n_kv * 2, st));
+                    g_kq_hint.masks_built.fetch_add(1, std::memory_order_relaxed);
+                    break;
+                }
+                {   // a store into cache rows goes through its row list (row_store)
+                    const int at = slot_offset(ctx, node);
+                    if (at >= 0) {
+                        const lm_ggml_tensor * cache = s1->view_src;
+                        B200_CHECK(b200_set_rows_f16((const float *) s0->data, cache->ne[0] * 4, ctx->slots_dev + at, cache->data, (int64_t) cache->nb[1],
+                                                     cache->ne[0], lm_ggml_nelements(s1) / cache->ne[0], st));
                         break;
                     }
                 }
@@ -1180,6 +1288,216 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
                 return LM_GGML_STATUS_FAILED;
         }
     }
+    return LM_GGML_STATUS_SUCCESS;
+}
+
+// ---------------------------------------------------------------------------------------------
+// CUDA-graph replay.  The reference rebuilds its graph for every ubatch (cactus/llama-context.cpp, graph_build) but a
+// decode step's node list comes out the same every time: same ops, shapes, addresses (ggml-alloc is deterministic) --
+// except where the ubatch lands in the cache, which the row lists above take out of the launches, and the attended
+// window n_kv, which grows by 256 cells now and then.  A node list is reduced to two 64-bit hashes over everything a
+// launch depends on; a list seen for the first time is recorded into a CUDA graph while it runs, a known one is replayed
+// with one cudaGraphLaunch.  Lists on split weights (several devices and streams) always run directly.
+// ---------------------------------------------------------------------------------------------
+std::atomic<uint64_t> g_graph_records{0}, g_graph_replays{0}, g_graph_updates{0};   // updates: recordings that re-used an instance
+
+struct hash2 {   // two independent 64-bit mixes over 8-byte words (a node list is a few hundred KB: byte-wise hashing would cost milliseconds)
+    uint64_t a = 0xcbf29ce484222325ull, b = 0x9e3779b97f4a7c15ull;
+    void word(uint64_t w) {
+        a = (a ^ w) * 0x9e3779b97f4a7c15ull;
+        a ^= a >> 29;
+        b = (b + w) * 0xd6e8feb86659fd93ull;
+        b ^= b >> 32;
+    }
+    void add(const void * p, size_t n) {
+        const uint8_t * c = (const uint8_t *) p;
+        for (; n >= 8; n -= 8, c += 8) {
+            uint64_t w;
+            memcpy(&w, c, 8);
+            word(w);
+        }
+        if (n) {
+            uint64_t w = 0;
+            memcpy(&w, c, n);
+            word(w ^ ((uint64_t) n << 56));
+        }
+    }
+    template <typename T> void val(const T & v) {
+        uint64_t w = 0;
+        static_assert(sizeof(T) <= 8, "scalar");
+        memcpy(&w, &v, sizeof(T));
+        word(w);
+    }
+};
+
+void hash_tensor(hash2 & h, const lm_ggml_tensor * t, bool with_address) {
+    if (!t) { h.val((int) -1); return; }
+    h.val((int) t->type);
+    h.val((int) t->op);
+    h.add(t->ne, sizeof(t->ne));
+    h.add(t->nb, sizeof(t->nb));
+    if (with_address) h.val((uintptr_t) t->data);
+    else h.val((uintptr_t) (t->view_src ? t->view_src->data : nullptr));
+}
+
+// false: the list cannot be replayed (weights on a split buffer)
+bool graph_signature(const b200_backend_ctx * ctx, const lm_ggml_cgraph * g, uint64_t * h1, uint64_t * h2, std::vector<uint64_t> * trail) {
+    hash2 h;
+    if (trail) trail->clear();
+    h.val(g->n_nodes);
+    h.val((uintptr_t) ctx->act.ptr); h.val((uintptr_t) ctx->workspace.ptr); h.val((uintptr_t) ctx->fa_scratch.ptr); h.val((uintptr_t) ctx->mask_index.ptr);
+    h.val((uintptr_t) ctx->slots_dev);
+    h.val(ctx->fuse); h.val(ctx->fa_parity); h.val(ctx->q8_variant);
+    for (int i = 0; i < g->n_nodes; ++i) {
+        const lm_ggml_tensor * n = g->nodes[i];
+        const int at = slot_offset(ctx, n);
+        h.val(at);   // -1, or where the node's row list starts: the launch reads its rows from there
+        // view nodes launch nothing (their readers hash what they read): the view into the cache that a row store writes
+        // through is such a node, and it moves
+        const bool is_view = n->op == LM_GGML_OP_NONE || n->op == LM_GGML_OP_RESHAPE || n->op == LM_GGML_OP_VIEW || n->op == LM_GGML_OP_PERMUTE ||
+                             n->op == LM_GGML_OP_TRANSPOSE;
+        hash_tensor(h, n, at < 0 && !is_view);
+        if (!is_view) h.add(n->op_params, sizeof(n->op_params));   // a view keeps its byte offset there
+        h.val(n->flags);
+        for (int k = 0; k < LM_GGML_MAX_SRC; ++k) {
+            const lm_ggml_tensor * sk = n->src[k];
+            if (!sk) { h.val((int) -1); continue; }
+            if (n->op == LM_GGML_OP_MUL_MAT && k == 0 && sk->buffer && buft_is_b200_split(sk->buffer->buft)) return false;
+            hash_tensor(h, sk, !(at >= 0 && k == 1));   // the destination view of a row store moves; its cache tensor does not
+        }
+        if (mask_hint_serves(ctx, n)) {
+            const kq_mask_hint_t::dev_state & d = g_kq_hint.dev[ctx->device];
+            h.val((uintptr_t) d.buf); h.val(d.n_kv); h.val(d.n_tokens);
+        } else {
+            h.val((int) 0);
+        }
+        if (trail) trail->push_back(h.a);
+    }
+    *h1 = h.a;
+    *h2 = h.b;
+    return true;
+}
+
+lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph * cgraph) {
+    b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
+    device_guard g(ctx->device);
+    cudaStream_t st = ctx->stream;
+    ctx->stats.graphs++;
+    if (ctx->timing) cudaEventRecord(ctx->ev0, st);
+    prepare_row_lists(ctx, cgraph);
+
+    lm_ggml_status rc = LM_GGML_STATUS_SUCCESS;
+    uint64_t h1 = 0, h2 = 0;
+    bool done = false;
+    // B200_GRAPH_DEBUG=1: when a list differs from the one before, say at which node
+    static const bool debug = [] { const char * e = getenv("B200_GRAPH_DEBUG"); return e && atoi(e) != 0; }();
+    std::vector<uint64_t> trail;
+    if (ctx->graphs && ctx->warmed && graph_signature(ctx, cgraph, &h1, &h2, debug ? &trail : nullptr)) {
+        if (debug) {
+            if (h1 != ctx->last_h1 && !ctx->dbg_trail.empty()) {
+                size_t k = 0;
+                while (k < trail.size() && k < ctx->dbg_trail.size() && trail[k] == ctx->dbg_trail[k]) ++k;
+                if (k < (size_t) cgraph->n_nodes) {
+                    const lm_ggml_tensor * n = cgraph->nodes[k];
+                    fprintf(stderr, "ggml-b200: node list differs from the previous one at node %zu of %d (%zu before): %s %s\n", k, cgraph->n_nodes, ctx->dbg_trail.size(),
+                            lm_ggml_op_name(n->op), n->name);
+                }
+            }
+            ctx->dbg_trail = trail;
+        }
+        if (ctx->abort_cb && ctx->abort_cb(ctx->abort_cb_data)) {
+            cudaStreamSynchronize(st);
+            return LM_GGML_STATUS_ABORTED;
+        }
+        b200_backend_ctx::graph_entry * hit = nullptr, * victim = nullptr;   // victim: a free entry, else the least recently used
+        for (auto & e : ctx->cache) {
+            if (e.exec && e.h1 == h1 && e.h2 == h2) hit = &e;
+            if (!victim || (victim->exec && (!e.exec || e.stamp < victim->stamp))) victim = &e;
+        }
+        // A recording costs more than a direct run.  Lists that keep changing (two recordings in a row that were never
+        // replayed) are therefore recorded only once they repeat.
+        const bool repeats = h1 == ctx->last_h1 && h2 == ctx->last_h2;
+        ctx->last_h1 = h1;
+        ctx->last_h2 = h2;
+        if (hit) {
+            if (cuda_ok(cudaGraphLaunch(hit->exec, st), "cudaGraphLaunch")) {
+                hit->stamp = ++ctx->stamp;
+                ctx->stats.nodes += hit->delta.nodes; ctx->stats.mul_mat += hit->delta.mul_mat; ctx->stats.flash_attn += hit->delta.flash_attn;
+                ctx->stats.act_quantized += hit->delta.act_quantized; ctx->stats.mask_indexed += hit->delta.mask_indexed; ctx->stats.rope_stores += hit->delta.rope_stores;
+                g_rope_store_groups.fetch_add(hit->rope_stores, std::memory_order_relaxed);
+                g_add_norm_groups.fetch_add(hit->add_norms, std::memory_order_relaxed);
+                g_kq_hint.masks_built.fetch_add(hit->masks, std::memory_order_relaxed);
+                g_graph_replays.fetch_add(1, std::memory_order_relaxed);
+                ctx->cold_records = 0;
+                done = true;
+            }
+        } else if (ctx->cold_records < 2 || repeats) {
+            // record while running: capture the launches, instantiate, launch the instance
+            const lm_ggml_b200_stats before = ctx->stats;
+            const uint64_t r0 = g_rope_store_groups.load(), a0 = g_add_norm_groups.load(), m0 = g_kq_hint.masks_built.load();
+            cudaGraph_t graph = nullptr;
+            cudaGraphExec_t exec = nullptr;
+            const auto t_rec0 = std::chrono::steady_clock::now();
+            if (cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed) == cudaSuccess) {
+                t_recording = true;
+                t_recording_failed = false;
+                const lm_ggml_status rrc = run_nodes(ctx, cgraph, false);
+                t_recording = false;
+                const cudaError_t ee = cudaStreamEndCapture(st, &graph);
+                // a list that differs from a recorded one only in sizes and addresses (the attended window grew) updates that
+                // instance in place, which is much cheaper than a new one
+                bool ready = false;
+                if (rrc == LM_GGML_STATUS_SUCCESS && ee == cudaSuccess && graph && !t_recording_failed) {
+                    b200_backend_ctx::graph_entry * like = nullptr;
+                    for (auto & e : ctx->cache)
+                        if (e.exec && e.n_nodes == cgraph->n_nodes && (!like || e.stamp > like->stamp)) like = &e;
+                    if (like) {
+                        cudaGraphExecUpdateResultInfo info;
+                        if (cudaGraphExecUpdate(like->exec, graph, &info) == cudaSuccess) {
+                            exec = like->exec;
+                            like->exec = nullptr;
+                            victim = like;
+                            g_graph_updates.fetch_add(1, std::memory_order_relaxed);
+                        } else {
+                            cudaGetLastError();
+                        }
+                    }
+                    if (!exec && cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) exec = nullptr;
+                    ready = exec && cudaGraphLaunch(exec, st) == cudaSuccess;
+                }
+                if (ready) {
+                    if (victim->exec) cudaGraphExecDestroy(victim->exec);
+                    victim->exec = exec;
+                    victim->h1 = h1; victim->h2 = h2;
+                    victim->n_nodes = cgraph->n_nodes;
+                    victim->stamp = ++ctx->stamp;
+                    victim->delta = {};
+                    victim->delta.nodes = ctx->stats.nodes - before.nodes; victim->delta.mul_mat = ctx->stats.mul_mat - before.mul_mat;
+                    victim->delta.flash_attn = ctx->stats.flash_attn - before.flash_attn; victim->delta.act_quantized = ctx->stats.act_quantized - before.act_quantized;
+                    victim->delta.mask_indexed = ctx->stats.mask_indexed - before.mask_indexed; victim->delta.rope_stores = ctx->stats.rope_stores - before.rope_stores;
+                    victim->rope_stores = g_rope_store_groups.load() - r0;
+                    victim->add_norms = g_add_norm_groups.load() - a0;
+                    victim->masks = g_kq_hint.masks_built.load() - m0;
+                    g_graph_records.fetch_add(1, std::memory_order_relaxed);
+                    ctx->cold_records++;
+                    done = true;
+                } else {
+                    if (exec) cudaGraphExecDestroy(exec);   // (an instance taken over for an update is gone with it: it may be half updated)
+                    cudaGetLastError();   // a failed recording leaves no sticky error; the list runs directly below
+                    ctx->stats = before;
+                    g_rope_store_groups.store(r0); g_add_norm_groups.store(a0); g_kq_hint.masks_built.store(m0);
+                }
+                if (graph) cudaGraphDestroy(graph);
+            }
+            if (debug) fprintf(stderr, "ggml-b200: recording %d nodes took %.2f ms on the host (%s)\n", cgraph->n_nodes,
+                               std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t_rec0).count(), done ? "ok" : "failed");
+        }
+    }
+    if (!done) {
+        rc = run_nodes(ctx, cgraph, true);
+        if (rc == LM_GGML_STATUS_SUCCESS) ctx->warmed = true;
+    }
+    if (rc != LM_GGML_STATUS_SUCCESS) return rc;
     if (ctx->timing) {
         cudaEventRecord(ctx->ev1, st);
         cudaEventSynchronize(ctx->ev1);
@@ -1402,6 +1720,11 @@ void kq_mask_from_cells(const void * mask_host_data, size_t mask_bytes, const in
     h.host_bytes = mask_bytes;
 }
 uint64_t kq_masks_built() { return g_kq_hint.masks_built.load(); }
+void graph_counts(uint64_t * recorded, uint64_t * replayed) {
+    if (recorded) *recorded = g_graph_records.load();
+    if (replayed) *replayed = g_graph_replays.load();
+}
+
 void fused_group_counts(uint64_t * rope_stores, uint64_t * add_norms) {
     if (rope_stores) *rope_stores = g_rope_store_groups.load();
     if (add_norms) *add_norms = g_add_norm_groups.load();
@@ -1417,6 +1740,7 @@ void * reg_get_proc_address(lm_ggml_backend_reg_t, const char * name) {
     if (strcmp(name, "lm_ggml_backend_b200_kq_masks_built") == 0) return (void *) kq_masks_built;
     if (strcmp(name, "lm_ggml_backend_b200_timing_totals") == 0) return (void *) timing_totals;
     if (strcmp(name, "lm_ggml_backend_b200_fused_group_counts") == 0) return (void *) fused_group_counts;
+    if (strcmp(name, "lm_ggml_backend_b200_graph_counts") == 0) return (void *) graph_counts;
     if (strcmp(name, "lm_ggml_backend_split_buffer_type") == 0) return (void *) split_buffer_type;
     if (strcmp(name, "lm_ggml_backend_set_abort_callback") == 0) return (void *) set_abort_callback;
     if (strcmp(name, "lm_ggml_backend_get_features") == 0) return (void *) get_features;
@@ -1494,6 +1818,8 @@ lm_ggml_backend_t lm_ggml_backend_b200_init(int device) {
     if (v && strcmp(v, "scalar") == 0) ctx->q8_variant = B200_Q8_SCALAR;
     const char * fu = getenv("B200_FUSE");
     ctx->fuse = !(fu && atoi(fu) == 0);
+    const char * gr = getenv("B200_GRAPHS");
+    ctx->graphs = !(gr && atoi(gr) == 0);
     const char * fp = getenv("B200_FA_PARITY");
     ctx->fa_parity = fp && atoi(fp) != 0;
     const char * t = getenv("B200_TIMING");

@@ -55,6 +55,9 @@ typedef void (*lm_ggml_b200_timing_totals_t)(double * device_ms, uint64_t * grap
 //   "lm_ggml_backend_b200_fused_group_counts": groups of nodes that ran as one kernel since the process started --
 //   ROPE(q), ROPE(k), CPY(k), CPY(v) of a layer; residual ADD + RMS_NORM + MUL + activation quantiser.
 typedef void (*lm_ggml_b200_fused_group_counts_t)(uint64_t * rope_stores, uint64_t * add_norms);
+//   "lm_ggml_backend_b200_graph_counts": node lists recorded into a CUDA graph and node lists replayed from one since the
+//   process started (B200_GRAPHS=0 switches the replay off: every list is then launched kernel by kernel).
+typedef void (*lm_ggml_b200_graph_counts_t)(uint64_t * recorded, uint64_t * replayed);
 // MUL_MAT nodes computed on weights of the split buffer type since the process started (all backends)
 LM_GGML_BACKEND_API uint64_t lm_ggml_backend_b200_split_mul_mat_count(void);
 

@@ -538,17 +538,19 @@ static int run_model(int argc, char ** argv) {
         if (totals) totals(&ms1, &g1);
         if (g1 > g0) bench_device_ms = (ms1 - ms0) / (double) (g1 - g0);   // only with B200_TIMING=1
     }
-    uint64_t n_rope_store = 0, n_add_norm = 0;
+    uint64_t n_rope_store = 0, n_add_norm = 0, n_recorded = 0, n_replayed = 0;
     if (!cpu_only) {
         auto counts = (lm_ggml_b200_fused_group_counts_t) lm_ggml_backend_reg_get_proc_address(lm_ggml_backend_b200_reg(), "lm_ggml_backend_b200_fused_group_counts");
         if (counts) counts(&n_rope_store, &n_add_norm);
+        auto gc = (lm_ggml_b200_graph_counts_t) lm_ggml_backend_reg_get_proc_address(lm_ggml_backend_b200_reg(), "lm_ggml_backend_b200_graph_counts");
+        if (gc) gc(&n_recorded, &n_replayed);
     }
     printf("{\"case\": \"model\", \"layers\": %d, \"d\": %d, \"seqs\": %d, \"decode_steps\": %d, \"rows\": %d, \"worst_rel\": %.3g, "
            "\"rows_within_1e-3\": %.3f, \"greedy_agree\": %.3f, \"b200_step_ms\": %.3f, \"split_mul_mats\": %llu, \"device_masks\": %llu, "
-           "\"device_ms_per_graph\": %.3f, \"rope_store_groups\": %llu, \"add_norm_groups\": %llu, \"mask_values_checked\": %llu, \"mask_mismatches\": %llu}\n",
+           "\"device_ms_per_graph\": %.3f, \"rope_store_groups\": %llu, \"add_norm_groups\": %llu, \"mask_values_checked\": %llu, \"mask_mismatches\": %llu, \"graphs_recorded\": %llu, \"graphs_replayed\": %llu}\n",
            c.n_layer, c.d, n_seq, n_decode, total, worst, good_rows / sum_rows, (double) agree / total, step_ms,
            (unsigned long long) (cpu_only ? 0 : lm_ggml_backend_b200_split_mul_mat_count()), g_b200_device_mask_calls, bench_device_ms, (unsigned long long) n_rope_store, (unsigned long long) n_add_norm,
-           g_b200_mask_values, g_b200_mask_mismatches);
+           g_b200_mask_values, g_b200_mask_mismatches, (unsigned long long) n_recorded, (unsigned long long) n_replayed);
     if (cpu.ctx) llama_free(cpu.ctx);
     if (cpu.model) llama_model_free(cpu.model);
     if (gpu.ctx) llama_free(gpu.ctx);

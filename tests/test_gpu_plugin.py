@@ -86,6 +86,27 @@ def test_device_kq_mask_is_the_reference_mask_bit_for_bit():
     assert rc == 0
 
 
+def test_decode_steps_replay_a_cuda_graph_with_the_same_results():
+    """The reference rebuilds its graph every ubatch, yet the decode steps of a run come out as the same node list (the
+    rows of the KV cache they write go through row lists in device memory): the plug-in records the list once and replays
+    it.  Same logits as with B200_GRAPHS=0 (every list launched kernel by kernel), and most decode steps were replays."""
+    if not os.path.exists(HARNESS):
+        pytest.skip("tests/_bin/harness was not built")
+    args = ["model", "--head-q4", "--seqs", "7", "--max-prompt", "90", "--decode", "12", "--device-mask"]
+    out = {}
+    for graphs in ("1", "0"):
+        env = dict(os.environ, B200_GRAPHS=graphs)
+        p = subprocess.run([HARNESS, *args], capture_output=True, text=True, timeout=600, env=env)
+        lines = [json.loads(line) for line in p.stdout.splitlines() if line.startswith("{")]
+        assert lines and p.returncode == 0, p.stderr[-2000:]
+        out[graphs] = lines[-1]
+    on, off = out["1"], out["0"]
+    assert off["graphs_recorded"] == 0 and off["graphs_replayed"] == 0, off
+    assert on["graphs_recorded"] >= 1 and on["graphs_replayed"] >= 6, on
+    assert on["worst_rel"] == off["worst_rel"] and on["greedy_agree"] == off["greedy_agree"], (on, off)
+    assert on["device_masks"] == off["device_masks"] and on["rope_store_groups"] == off["rope_store_groups"], (on, off)
+
+
 def test_host_made_failures_abort_callback_and_failing_allocator():
     """Failure paths without a GPU fault (tests/backend/faults.cpp): an abort callback that says stop gives
     LM_GGML_STATUS_ABORTED (1), a cudaMalloc that fails gives no buffer and LM_GGML_STATUS_ALLOC_FAILED (-2); after each the
