@@ -3,20 +3,24 @@
 // Replaces lm_ggml_vec_dot_q4_0_q8_0 / lm_ggml_vec_dot_q8_0_q8_0 under mul_mat
 // (cactus/ggml-cpu/ggml-cpu-quants.c:1906, :3591; cactus/ggml-cpu/ggml-cpu.c:1167-1255).
 //
-// One CTA per 16-row tile of the weight matrix, 8 or 16 warps splitting the K dimension by block group.
+// One CTA per 16-row tile of the weight matrix, 4, 8 or 16 warps splitting the K dimension by block group (launch_mmvq_n
+// picks the count with which all row tiles are resident at once).
 // A warp streams 1 KB (Q4_0) / 2 KB (Q8_0) tiles with two/four 128-bit loads per lane, lane (g, t)
 // holding word t of every block of rows g and g+8, multiplies them against the Q8_0 activation words
 // with dp4a and applies the two fp16 block scales per (row, column, block).  Partial sums are folded
 // over the four t lanes with shuffles and over the warps through shared memory in a fixed order, so
 // the result does not depend on scheduling.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace b200 {
 
 
-// MMVQ_WARPS warps split the block groups of a row tile: 8 for tall matrices, 16 when there are few row tiles (a
-// 4096-row weight has only 256 CTAs, and more warps per CTA are what keeps enough loads in flight)
-template <int WTYPE, int NC, int MMVQ_WARPS>
+// MMVQ_WARPS warps split the block groups of a row tile: many when there are few row tiles (a 4096-row weight has only 256
+// CTAs, and more warps per CTA are what keeps enough loads in flight), fewer for tall matrices
+// DEPTH: tiles a warp has requested beyond the one it works on (1 or 2)
+template <int WTYPE, int NC, int MMVQ_WARPS, int DEPTH = 1>
 __global__ void __launch_bounds__(MMVQ_WARPS * 32) mmvq_kernel(TiledDims dims, const uint8_t *__restrict__ w, ActDims act,
                                                               const uint8_t *__restrict__ aq, float *__restrict__ dst,
                                                               int64_t dst_nb_row, PeerDst peers) {
@@ -50,11 +54,17 @@ __global__ void __launch_bounds__(MMVQ_WARPS * 32) mmvq_kernel(TiledDims dims, c
         tl.sa = __ldg(wd + bg * 16 + g);
         tl.sb = __ldg(wd + bg * 16 + g + 8);
     };
-    Tile nxt;
+    Tile nxt, nxt2;
     if (warp < dims.n_bg) load_tile(warp, nxt);
+    if (DEPTH >= 2 && warp + MMVQ_WARPS < dims.n_bg) load_tile(warp + MMVQ_WARPS, nxt2);
     for (int64_t bg = warp; bg < dims.n_bg; bg += MMVQ_WARPS) {
         const Tile cur = nxt;
-        if (bg + MMVQ_WARPS < dims.n_bg) load_tile(bg + MMVQ_WARPS, nxt);
+        if (DEPTH >= 2) {
+            nxt = nxt2;
+            if (bg + 2 * MMVQ_WARPS < dims.n_bg) load_tile(bg + 2 * MMVQ_WARPS, nxt2);
+        } else if (bg + MMVQ_WARPS < dims.n_bg) {
+            load_tile(bg + MMVQ_WARPS, nxt);
+        }
         // weights of this tile
         uint32_t wa[8], wb[8];  // row g / row g+8: Q4_0 uses [0..3] (blocks), Q8_0 [2*j], [2*j+1] (word t, word 4+t)
         if (WTYPE == B200_TYPE_Q4_0) {
@@ -132,20 +142,58 @@ __global__ void __launch_bounds__(MMVQ_WARPS * 32) mmvq_kernel(TiledDims dims, c
     }
 }
 
-template <int WTYPE, int WARPS>
-static int launch_mmvq_w(const TiledDims &d, const uint8_t *w, const ActDims &a, const uint8_t *aq, float *dst, int64_t dst_nb_row, const PeerDst &peers,
+template <int WTYPE, int NC, int WARPS, int DEPTH>
+static int mmvq_ctas_per_sm() {   // resident CTAs of one variant (every device of a process is the same model)
+    static const int n = [] {
+        int v = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, mmvq_kernel<WTYPE, NC, WARPS, DEPTH>, WARPS * 32, 0) != cudaSuccess || v <= 0) {
+            cudaGetLastError();
+            v = 1;
+        }
+        return v;
+    }();
+    return n;
+}
+static int mmvq_sm_count() {
+    static const int n = [] {
+        int dev = 0, v = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+        return v > 0 ? v : 148;
+    }();
+    return n;
+}
+
+// A launch of this kernel lasts about as long as one CTA does, so a second, partly filled wave of CTAs costs as much as
+// the first: the row tiles should all be resident at once.  More warps per CTA keep more loads in flight per row tile
+// (what small matrices need), fewer warps let more CTAs reside.  Taken: the most warps (16, 8, 4) with which all row tiles
+// fit at once; with 16 warps a warp requests two tiles ahead.  Measured on B200 at one column (us per launch, 16 / 8 / 4
+// warps): 4096 x 4096 (K x M) 4.7 / 5.7 / 8.6, 14336 x 4096 10.1 / 13.9 / 25.6, 4096 x 6144 8.2 / 6.2 / 8.6 (384 row tiles:
+// 16 warps need 1.3 waves), 4096 x 14336 12.7 / 12.5 / 9.7 (896 row tiles: 8 warps need 1.2 waves), 4096 x 128256
+// 88.9 / 67.8 / 65.0.  B200_MMVQ_CFG=<warps><depth> (42, 81, 162, ...) forces a variant (tuning aid).
+template <int WTYPE, int NC>
+static int launch_mmvq_n(const TiledDims &d, const uint8_t *w, const ActDims &a, const uint8_t *aq, float *dst, int64_t dst_nb_row, const PeerDst &peers,
                          cudaStream_t st) {
-    const dim3 grid((unsigned) d.n_rt), block(WARPS * 32);
-    switch (a.N) {
-        case 1: launch_pdl(mmvq_kernel<WTYPE, 1, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
-        case 2: launch_pdl(mmvq_kernel<WTYPE, 2, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
-        case 3: launch_pdl(mmvq_kernel<WTYPE, 3, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
-        case 4: launch_pdl(mmvq_kernel<WTYPE, 4, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
-        case 5: launch_pdl(mmvq_kernel<WTYPE, 5, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
-        case 6: launch_pdl(mmvq_kernel<WTYPE, 6, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
-        case 7: launch_pdl(mmvq_kernel<WTYPE, 7, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
-        case 8: launch_pdl(mmvq_kernel<WTYPE, 8, WARPS>, grid, block, 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
-        default: return set_error(B200_E_INVALID, "mmvq handles 1..8 columns, got %lld", (long long) a.N);
+    static const int forced = [] {
+        const char *e = getenv("B200_MMVQ_CFG");
+        return e ? atoi(e) : 0;
+    }();
+    const dim3 grid((unsigned) d.n_rt);
+    const int64_t sms = mmvq_sm_count();
+    int cfg = forced;
+    if (cfg != 41 && cfg != 42 && cfg != 81 && cfg != 82 && cfg != 161 && cfg != 162) {
+        if (d.n_bg >= 16 && d.n_rt <= sms * mmvq_ctas_per_sm<WTYPE, NC, 16, 2>()) cfg = 162;
+        else if (d.n_rt <= sms * mmvq_ctas_per_sm<WTYPE, NC, 8, 1>()) cfg = 81;
+        else if (d.n_rt <= sms * mmvq_ctas_per_sm<WTYPE, NC, 4, 1>()) cfg = 41;
+        else cfg = 42;
+    }
+    switch (cfg) {
+        case 41: launch_pdl(mmvq_kernel<WTYPE, NC, 4, 1>, grid, dim3(128), 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
+        case 42: launch_pdl(mmvq_kernel<WTYPE, NC, 4, 2>, grid, dim3(128), 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
+        case 81: launch_pdl(mmvq_kernel<WTYPE, NC, 8, 1>, grid, dim3(256), 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
+        case 82: launch_pdl(mmvq_kernel<WTYPE, NC, 8, 2>, grid, dim3(256), 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
+        case 161: launch_pdl(mmvq_kernel<WTYPE, NC, 16, 1>, grid, dim3(512), 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
+        default: launch_pdl(mmvq_kernel<WTYPE, NC, 16, 2>, grid, dim3(512), 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
     }
     return check_launch("mmvq");
 }
@@ -153,10 +201,17 @@ static int launch_mmvq_w(const TiledDims &d, const uint8_t *w, const ActDims &a,
 template <int WTYPE>
 static int launch_mmvq_t(const TiledDims &d, const uint8_t *w, const ActDims &a, const uint8_t *aq, float *dst,
                          int64_t dst_nb_row, const PeerDst &peers, cudaStream_t st) {
-    // measured on B200 at one column: 4096 x 4096 3.9 us with 16 warps against 4.8 with 8, 14336 x 4096 (K x M) 8.5 against 12.6;
-    // 4096 x 14336 10.6 against 9.9, 4096 x 128256 73 against 54
-    if (d.n_rt <= 512 && d.n_bg >= 16) return launch_mmvq_w<WTYPE, 16>(d, w, a, aq, dst, dst_nb_row, peers, st);
-    return launch_mmvq_w<WTYPE, 8>(d, w, a, aq, dst, dst_nb_row, peers, st);
+    switch (a.N) {
+        case 1: return launch_mmvq_n<WTYPE, 1>(d, w, a, aq, dst, dst_nb_row, peers, st);
+        case 2: return launch_mmvq_n<WTYPE, 2>(d, w, a, aq, dst, dst_nb_row, peers, st);
+        case 3: return launch_mmvq_n<WTYPE, 3>(d, w, a, aq, dst, dst_nb_row, peers, st);
+        case 4: return launch_mmvq_n<WTYPE, 4>(d, w, a, aq, dst, dst_nb_row, peers, st);
+        case 5: return launch_mmvq_n<WTYPE, 5>(d, w, a, aq, dst, dst_nb_row, peers, st);
+        case 6: return launch_mmvq_n<WTYPE, 6>(d, w, a, aq, dst, dst_nb_row, peers, st);
+        case 7: return launch_mmvq_n<WTYPE, 7>(d, w, a, aq, dst, dst_nb_row, peers, st);
+        case 8: return launch_mmvq_n<WTYPE, 8>(d, w, a, aq, dst, dst_nb_row, peers, st);
+        default: return set_error(B200_E_INVALID, "mmvq handles 1..8 columns, got %lld", (long long) a.N);
+    }
 }
 
 int launch_mmvq(int wtype, const TiledDims &d, const void *w, const ActDims &a, const void *aq, float *dst, int64_t dst_nb_row,
