@@ -278,7 +278,8 @@ def rowsplit_record(model: str, rank: int, world: int, local: int, lens, head, c
 
 def other_configs(L, local: int):
     """The smaller workloads of the hot path, each timed on the device: the single 4096 x 4096 Q4_0 mul_mat at 1, 8 and
-    512 columns (distinct weight copies larger than L2 in turn), and one-sequence decode of the 1B architecture."""
+    512 columns (distinct weight copies larger than L2 in turn), the single FLASH_ATTN_EXT op on a ragged 16-sequence
+    ubatch over an 8192-slot cache, and the 1B architecture with one sequence: a 512-token prompt ubatch, then decode."""
     from types import SimpleNamespace
 
     import torch
@@ -290,7 +291,27 @@ def other_configs(L, local: int):
         r = microbench.bench_mul_mat(SimpleNamespace(K=4096, M=4096, N=N, wtype=2, copies=24, reps=5))
         out["mul_mat_4096x4096_q4_0"][f"N={N}"] = {"us": round(r["ms_per_launch"] * 1e3, 2), "GBps": round(r["GBps"], 1), "frac_of_hbm_peak": round(r["GBps"] / peak, 3),
                                                     "TOPS": round(r["TOPS"], 1)}
+    r = microbench.bench_fattn_prefill(SimpleNamespace(D=128, H=32, Hkv=8, cfg2="a", copies=8, reps=5))
+    out["flash_attn_16seq_ubatch_8192_slots"] = {"us": round(r["ms_per_launch"] * 1e3, 1), "query_tokens": r["tokens"], "attended_pairs": r["attended_pairs"],
+                                                  "TFLOPs": round(r["TFLOPs"], 1), "GBps": round(r["GBps"], 1), "frac_of_hbm_peak": round(r["GBps"] / peak, 3)}
     cfg = LLAMA_32_1B
+    # the prompt as one 512-token ubatch through the public call (host inputs, the step, greedy ids back)
+    import numpy as np
+    eng = LlamaEngine(LlamaWeights.random(cfg, seed=3), 1024, max_tokens=512, use_graphs=False)
+    rng = np.random.default_rng(0)
+    toks, pos, seq, slots = rng.integers(0, cfg.vocab, 512), np.arange(512), np.zeros(512, np.int64), np.arange(512)
+    eng.decode(toks, pos, seq, slots, want_logits=False)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        eng.decode(toks, pos, seq, slots, want_logits=False)
+    e1.record()
+    e1.synchronize()
+    ms_prompt = e0.elapsed_time(e1) / 3
+    out["llama_1b_prompt_512_tokens"] = {"ms": round(ms_prompt, 3), "tok_s": round(512 / (ms_prompt / 1e3), 1), "includes": "H2D of the inputs, all 512 rows of the output head, greedy ids D2H (no logits read-back)"}
+    del eng
+    torch.cuda.empty_cache()
     eng = LlamaEngine(LlamaWeights.random(cfg, seed=3), 1024, max_tokens=8)
     n_prompt = 512
     eng.cell_pos[:n_prompt] = torch.arange(n_prompt, dtype=torch.int32, device="cuda")

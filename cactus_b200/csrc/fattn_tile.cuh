@@ -35,7 +35,7 @@ __device__ __forceinline__ void ft_ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t 
 }
 
 template <int D>
-__global__ void __launch_bounds__(FT_THREADS, 2) fattn_tile_kernel(FattnParams p, int gqa_log2) {
+__global__ void __launch_bounds__(FT_THREADS, 3) fattn_tile_kernel(FattnParams p, int gqa_log2) {
     pdl_prologue();
     if (p.vote == 2 && !fattn_tiled_chosen(p.plan)) return;   // the tokens share too few cells: the per-token kernel takes this ubatch
     constexpr int KS = D / 16;            // k-steps of S
