@@ -781,7 +781,11 @@ static const MmqVariant &pick_variant(int64_t N) {
         t[2][3] = make_variant<WTYPE, 4, 2, 2, 4, 3, 2>();   // 128 rows x 64 cols, 8 warps as 4 x 2, 3 stages
         ready[dev] = true;
     }
-    const int cls = N > 32 ? 2 : (N > 16 ? 1 : 0);
+    static const int forced_cls = [] {   // B200_MMQ_CLASS=<0..2>: column class whatever N (tuning aid: narrower CTAs, more column chunks)
+        const char *e = getenv("B200_MMQ_CLASS");
+        return e ? atoi(e) : -1;
+    }();
+    const int cls = (forced_cls >= 0 && forced_cls <= 2) ? forced_cls : (N > 32 ? 2 : (N > 16 ? 1 : 0));
     return table[dev][cls][(forced >= 0 && forced < 4) ? forced : 0];
 }
 
