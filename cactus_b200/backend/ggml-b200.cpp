@@ -585,6 +585,7 @@ struct b200_backend_ctx {
     } cache[4];
     uint64_t stamp = 0, last_h1 = 0, last_h2 = 0;
     int cold_records = 0;    // recordings since the last replay
+    cudaStream_t cap_stream = nullptr;   // recordings are captured here; nothing ever runs on it
     std::vector<uint64_t> dbg_trail;
     // rows of the KV cache that the ubatch's K / V stores write: the one thing that moves from step to step in a decode
     // graph.  The stores take (cache tensor, list of rows); the lists sit in device memory and are refreshed before every run.
@@ -614,6 +615,7 @@ void backend_free(lm_ggml_backend_t backend) {
         if (ctx->ev1) cudaEventDestroy(ctx->ev1);
         if (ctx->ev_act) cudaEventDestroy(ctx->ev_act);
         for (auto & e : ctx->cache) if (e.exec) cudaGraphExecDestroy(e.exec);
+        if (ctx->cap_stream) cudaStreamDestroy(ctx->cap_stream);
         if (ctx->slots_dev) cudaFree(ctx->slots_dev);
         cudaStreamDestroy(ctx->stream);
     }
@@ -1296,8 +1298,8 @@ lm_ggml_status run_nodes(b200_backend_ctx * ctx, lm_ggml_cgraph * cgraph, bool c
 // decode step's node list comes out the same every time: same ops, shapes, addresses (ggml-alloc is deterministic) --
 // except where the ubatch lands in the cache, which the row lists above take out of the launches, and the attended
 // window n_kv, which grows by 256 cells now and then.  A node list is reduced to two 64-bit hashes over everything a
-// launch depends on; a list seen for the first time is recorded into a CUDA graph while it runs, a known one is replayed
-// with one cudaGraphLaunch.  Lists on split weights (several devices and streams) always run directly.
+// launch depends on; a list seen for the first time runs kernel by kernel and is recorded into a CUDA graph meanwhile, a known one is
+// replayed with one cudaGraphLaunch.  Lists on split weights (several devices and streams) always run directly.
 // ---------------------------------------------------------------------------------------------
 std::atomic<uint64_t> g_graph_records{0}, g_graph_replays{0}, g_graph_updates{0};   // updates: recordings that re-used an instance
 
@@ -1378,6 +1380,78 @@ bool graph_signature(const b200_backend_ctx * ctx, const lm_ggml_cgraph * g, uin
     return true;
 }
 
+// Records the launches of a node list into a CUDA graph without running them: the backend's stream is swapped for a
+// capture stream for the duration.  A list that differs from a recorded one only in sizes and addresses (the attended
+// window grew) updates that instance in place, which is much cheaper than a new one.
+bool shadow_record(b200_backend_ctx * ctx, lm_ggml_cgraph * cgraph, uint64_t h1, uint64_t h2, b200_backend_ctx::graph_entry * victim) {
+    if (!ctx->cap_stream && cudaStreamCreateWithFlags(&ctx->cap_stream, cudaStreamNonBlocking) != cudaSuccess) {
+        cudaGetLastError();
+        ctx->cap_stream = nullptr;
+        return false;
+    }
+    const lm_ggml_b200_stats before = ctx->stats;
+    const uint64_t r0 = g_rope_store_groups.load(), a0 = g_add_norm_groups.load(), m0 = g_kq_hint.masks_built.load();
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    bool ok = false;
+    if (cudaStreamBeginCapture(ctx->cap_stream, cudaStreamCaptureModeRelaxed) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    cudaStream_t own = ctx->stream;
+    ctx->stream = ctx->cap_stream;
+    t_recording = true;
+    t_recording_failed = false;
+    const lm_ggml_status rrc = run_nodes(ctx, cgraph, false);
+    t_recording = false;
+    ctx->stream = own;
+    const cudaError_t ee = cudaStreamEndCapture(ctx->cap_stream, &graph);
+    // what one run adds to the counters; the recording itself ran nothing
+    lm_ggml_b200_stats delta = {};
+    delta.nodes = ctx->stats.nodes - before.nodes; delta.mul_mat = ctx->stats.mul_mat - before.mul_mat;
+    delta.flash_attn = ctx->stats.flash_attn - before.flash_attn; delta.act_quantized = ctx->stats.act_quantized - before.act_quantized;
+    delta.mask_indexed = ctx->stats.mask_indexed - before.mask_indexed; delta.rope_stores = ctx->stats.rope_stores - before.rope_stores;
+    const uint64_t dr = g_rope_store_groups.load() - r0, da = g_add_norm_groups.load() - a0, dm = g_kq_hint.masks_built.load() - m0;
+    ctx->stats = before;
+    g_rope_store_groups.store(r0); g_add_norm_groups.store(a0); g_kq_hint.masks_built.store(m0);
+    if (rrc == LM_GGML_STATUS_SUCCESS && ee == cudaSuccess && graph && !t_recording_failed) {
+        b200_backend_ctx::graph_entry * like = nullptr;
+        for (auto & e : ctx->cache)
+            if (e.exec && e.n_nodes == cgraph->n_nodes && (!like || e.stamp > like->stamp)) like = &e;
+        if (like) {
+            cudaGraphExecUpdateResultInfo info;
+            if (cudaGraphExecUpdate(like->exec, graph, &info) == cudaSuccess) {
+                exec = like->exec;
+                like->exec = nullptr;
+                victim = like;
+                g_graph_updates.fetch_add(1, std::memory_order_relaxed);
+            } else {
+                cudaGetLastError();
+                cudaGraphExecDestroy(like->exec);   // it may be half updated
+                like->exec = nullptr;
+            }
+        }
+        if (!exec && cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) exec = nullptr;
+        if (exec && victim) {
+            if (victim->exec) cudaGraphExecDestroy(victim->exec);
+            victim->exec = exec;
+            victim->h1 = h1; victim->h2 = h2;
+            victim->n_nodes = cgraph->n_nodes;
+            victim->stamp = ++ctx->stamp;
+            victim->delta = delta;
+            victim->rope_stores = dr; victim->add_norms = da; victim->masks = dm;
+            g_graph_records.fetch_add(1, std::memory_order_relaxed);
+            ctx->cold_records++;
+            ok = true;
+        } else if (exec) {
+            cudaGraphExecDestroy(exec);
+        }
+    }
+    if (!ok) cudaGetLastError();   // a failed recording leaves no sticky error
+    if (graph) cudaGraphDestroy(graph);
+    return ok;
+}
+
 lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph * cgraph) {
     b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
     device_guard g(ctx->device);
@@ -1388,7 +1462,8 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
 
     lm_ggml_status rc = LM_GGML_STATUS_SUCCESS;
     uint64_t h1 = 0, h2 = 0;
-    bool done = false;
+    bool done = false, want_record = false;
+    b200_backend_ctx::graph_entry * victim = nullptr;   // where a new recording goes: a free entry, else the least recently used
     // B200_GRAPH_DEBUG=1: when a list differs from the one before, say at which node
     static const bool debug = [] { const char * e = getenv("B200_GRAPH_DEBUG"); return e && atoi(e) != 0; }();
     std::vector<uint64_t> trail;
@@ -1409,7 +1484,7 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
             cudaStreamSynchronize(st);
             return LM_GGML_STATUS_ABORTED;
         }
-        b200_backend_ctx::graph_entry * hit = nullptr, * victim = nullptr;   // victim: a free entry, else the least recently used
+        b200_backend_ctx::graph_entry * hit = nullptr;
         for (auto & e : ctx->cache) {
             if (e.exec && e.h1 == h1 && e.h2 == h2) hit = &e;
             if (!victim || (victim->exec && (!e.exec || e.stamp < victim->stamp))) victim = &e;
@@ -1432,65 +1507,7 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
                 done = true;
             }
         } else if (ctx->cold_records < 2 || repeats) {
-            // record while running: capture the launches, instantiate, launch the instance
-            const lm_ggml_b200_stats before = ctx->stats;
-            const uint64_t r0 = g_rope_store_groups.load(), a0 = g_add_norm_groups.load(), m0 = g_kq_hint.masks_built.load();
-            cudaGraph_t graph = nullptr;
-            cudaGraphExec_t exec = nullptr;
-            const auto t_rec0 = std::chrono::steady_clock::now();
-            if (cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed) == cudaSuccess) {
-                t_recording = true;
-                t_recording_failed = false;
-                const lm_ggml_status rrc = run_nodes(ctx, cgraph, false);
-                t_recording = false;
-                const cudaError_t ee = cudaStreamEndCapture(st, &graph);
-                // a list that differs from a recorded one only in sizes and addresses (the attended window grew) updates that
-                // instance in place, which is much cheaper than a new one
-                bool ready = false;
-                if (rrc == LM_GGML_STATUS_SUCCESS && ee == cudaSuccess && graph && !t_recording_failed) {
-                    b200_backend_ctx::graph_entry * like = nullptr;
-                    for (auto & e : ctx->cache)
-                        if (e.exec && e.n_nodes == cgraph->n_nodes && (!like || e.stamp > like->stamp)) like = &e;
-                    if (like) {
-                        cudaGraphExecUpdateResultInfo info;
-                        if (cudaGraphExecUpdate(like->exec, graph, &info) == cudaSuccess) {
-                            exec = like->exec;
-                            like->exec = nullptr;
-                            victim = like;
-                            g_graph_updates.fetch_add(1, std::memory_order_relaxed);
-                        } else {
-                            cudaGetLastError();
-                        }
-                    }
-                    if (!exec && cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) exec = nullptr;
-                    ready = exec && cudaGraphLaunch(exec, st) == cudaSuccess;
-                }
-                if (ready) {
-                    if (victim->exec) cudaGraphExecDestroy(victim->exec);
-                    victim->exec = exec;
-                    victim->h1 = h1; victim->h2 = h2;
-                    victim->n_nodes = cgraph->n_nodes;
-                    victim->stamp = ++ctx->stamp;
-                    victim->delta = {};
-                    victim->delta.nodes = ctx->stats.nodes - before.nodes; victim->delta.mul_mat = ctx->stats.mul_mat - before.mul_mat;
-                    victim->delta.flash_attn = ctx->stats.flash_attn - before.flash_attn; victim->delta.act_quantized = ctx->stats.act_quantized - before.act_quantized;
-                    victim->delta.mask_indexed = ctx->stats.mask_indexed - before.mask_indexed; victim->delta.rope_stores = ctx->stats.rope_stores - before.rope_stores;
-                    victim->rope_stores = g_rope_store_groups.load() - r0;
-                    victim->add_norms = g_add_norm_groups.load() - a0;
-                    victim->masks = g_kq_hint.masks_built.load() - m0;
-                    g_graph_records.fetch_add(1, std::memory_order_relaxed);
-                    ctx->cold_records++;
-                    done = true;
-                } else {
-                    if (exec) cudaGraphExecDestroy(exec);   // (an instance taken over for an update is gone with it: it may be half updated)
-                    cudaGetLastError();   // a failed recording leaves no sticky error; the list runs directly below
-                    ctx->stats = before;
-                    g_rope_store_groups.store(r0); g_add_norm_groups.store(a0); g_kq_hint.masks_built.store(m0);
-                }
-                if (graph) cudaGraphDestroy(graph);
-            }
-            if (debug) fprintf(stderr, "ggml-b200: recording %d nodes took %.2f ms on the host (%s)\n", cgraph->n_nodes,
-                               std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t_rec0).count(), done ? "ok" : "failed");
+            want_record = true;
         }
     }
     if (!done) {
@@ -1498,6 +1515,15 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
         if (rc == LM_GGML_STATUS_SUCCESS) ctx->warmed = true;
     }
     if (rc != LM_GGML_STATUS_SUCCESS) return rc;
+    // An unknown list has just been launched kernel by kernel; while the device works on it the host records the same
+    // launches on a capture stream (nothing runs there), so that the next such list is one cudaGraphLaunch.  Recording
+    // instead of running would leave the device idle for as long as the recording takes (1.6 ms for a 1031-node list).
+    if (want_record) {
+        const auto t_rec0 = std::chrono::steady_clock::now();
+        const bool ok = shadow_record(ctx, cgraph, h1, h2, victim);
+        if (debug) fprintf(stderr, "ggml-b200: recording %d nodes took %.2f ms on the host (%s)\n", cgraph->n_nodes,
+                           std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t_rec0).count(), ok ? "ok" : "failed");
+    }
     if (ctx->timing) {
         cudaEventRecord(ctx->ev1, st);
         cudaEventSynchronize(ctx->ev1);
