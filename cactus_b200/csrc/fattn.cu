@@ -754,8 +754,17 @@ static int flash_attn_impl(bool parity, int64_t D, int64_t H, int64_t Hkv, int64
         if (tpart && (!scratch || scratch_bytes < tpart || !is_aligned(scratch, 16))) pt.nsplit = 1;   // an older scratch size: no splits
         const int tile_tokens = 64 >> gqa_log2;
         dim3 tgrid((unsigned) Hkv, (unsigned) ((Nq + tile_tokens - 1) / tile_tokens), (unsigned) pt.nsplit);
-        if (D == 128) launch_pdl(fattn_tile_kernel<128>, tgrid, dim3(FT_THREADS), 0, st, pt, gqa_log2);
-        else launch_pdl(fattn_tile_kernel<64>, tgrid, dim3(FT_THREADS), 0, st, pt, gqa_log2);
+        // the opt-in to more than 48 KB of shared memory is per function and device
+        static thread_local int tile_smem_dev = -1;
+        int dev_now = 0;
+        cudaGetDevice(&dev_now);
+        if (tile_smem_dev != dev_now) {
+            cudaFuncSetAttribute(fattn_tile_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, fattn_tile_smem_bytes(128));
+            cudaFuncSetAttribute(fattn_tile_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, fattn_tile_smem_bytes(64));
+            tile_smem_dev = dev_now;
+        }
+        if (D == 128) launch_pdl(fattn_tile_kernel<128>, tgrid, dim3(FT_THREADS), (size_t) fattn_tile_smem_bytes(128), st, pt, gqa_log2);
+        else launch_pdl(fattn_tile_kernel<64>, tgrid, dim3(FT_THREADS), (size_t) fattn_tile_smem_bytes(64), st, pt, gqa_log2);
         if (int e = check_launch("fattn_tile")) return e;
         if (pt.nsplit > 1) {
             if (D == 128) launch_pdl(fattn_combine_kernel<128, false>, dim3((unsigned) (Nq * H)), dim3(128), 0, st, pt, 1);

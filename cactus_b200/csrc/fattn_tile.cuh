@@ -4,11 +4,11 @@
 // different work split.  The decode kernel gives every (token, kv-head) its own CTA, so the tokens of one prompt walk the
 // same K/V rows once each.  Here a CTA owns a tile of consecutive tokens of the ubatch and one kv-head: 4 warps x 16 MMA
 // rows, a row being one (token, query head of the group) pair -- 16 / gqa tokens per warp, 64 / gqa per CTA.  The CTA walks
-// the union of its tokens' cells (the OR of their mask words) in chunks of 16 cells; a chunk's K and V rows are staged in
-// shared memory once (cp.async, double buffered) and used by all 64 rows.  A row's own mask value (-inf outside its
+// the union of its tokens' cells (the OR of their mask words) in chunks of 32 cells; a chunk's K and V rows are staged in
+// shared memory once (cp.async, three stages) and used by all 64 rows.  A row's own mask value (-inf outside its
 // sequence and beyond its position) is added to every score, so the causal triangle and ragged tiles that straddle two
 // sequences need no special case.  When the mask holds nothing but 0 and -inf (the index build records that) the row's
-// mask value comes from its mask-word bits (turned, once per round of 1024 cells, into 16 bits per token and chunk in
+// mask value comes from its mask-word bits (turned, once per round of 1024 cells, into 32 bits per token and chunk in
 // shared memory) instead of from the f16 mask in global memory.  Long tiles are cut into KV splits (grid z): split z takes every nsplit-th
 // chunk of the union list, the partial (max, sum, accumulator) triples go to scratch and fattn_combine_kernel finishes.
 //   S = Q K^T   m16n8k16, Q rounded to fp16 as the reference rounds it, K fragments straight from the staged rows
@@ -20,7 +20,7 @@
 namespace b200 {
 
 constexpr int FT_THREADS = 128;
-constexpr int FT_CHUNK = 16;            // cells per step
+constexpr int FT_CHUNK = 32;            // cells per step
 constexpr int FT_RW = 16;               // mask words (of 64 cells) listed per round
 constexpr int FT_LIST = FT_RW * 64;     // cells listed per round at most
 constexpr int FT_STAGES = 3;            // K/V chunks in flight
@@ -33,6 +33,9 @@ __device__ __forceinline__ void ft_cp16(uint32_t smem, const void *g) {
 __device__ __forceinline__ void ft_ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
+
+// dynamic shared memory of the kernel: FT_STAGES stages of K and V rows
+constexpr int fattn_tile_smem_bytes(int D) { return FT_STAGES * 2 * FT_CHUNK * (D * 2 + 16); }
 
 template <int D>
 __global__ void __launch_bounds__(FT_THREADS, 3) fattn_tile_kernel(FattnParams p, int gqa_log2) {
@@ -56,9 +59,9 @@ __global__ void __launch_bounds__(FT_THREADS, 3) fattn_tile_kernel(FattnParams p
     __shared__ unsigned long long tile_words[FT_MAX_TILE][FT_RW];   // the round's words, token by token
     __shared__ unsigned long long ubits[FT_RW];           // their union
     __shared__ int wbase[FT_RW];                          // cells listed before each word
-    __shared__ unsigned short rmask[FT_MAX_TILE][FT_LIST / FT_CHUNK];   // per token and chunk: which of the chunk's 16 cells the token attends to
+    __shared__ unsigned rmask[FT_MAX_TILE][FT_LIST / FT_CHUNK];   // per token and chunk: which of the chunk's 32 cells the token attends to
     __shared__ int list_count, uw_count, warp_cnt[4];
-    __shared__ __align__(16) uint8_t kv_s[FT_STAGES][2][FT_CHUNK * ROW];   // [stage][K, V]
+    extern __shared__ __align__(16) uint8_t kv_s[];   // [stage][K, V][FT_CHUNK rows of ROW bytes] (dynamic: fattn_tile_smem_bytes)
 
     // rows g and g + 8 of this warp: (token, head)
     int64_t tok[2];
@@ -102,7 +105,7 @@ __global__ void __launch_bounds__(FT_THREADS, 3) fattn_tile_kernel(FattnParams p
 
     const char *kbase = p.k + (int64_t) hk * p.k_nb_head;
     const char *vbase = p.v + (int64_t) hk * p.v_nb_head;
-    const uint32_t kv_u32 = (uint32_t) __cvta_generic_to_shared(&kv_s[0][0][0]);
+    const uint32_t kv_u32 = (uint32_t) __cvta_generic_to_shared(kv_s);
     const int n_tile_tok = (int) min((int64_t) (4 * tw), p.Nq - tok0);
 
     // ---- the words the tile attends to at all (one pass over the tokens' word rows, 128 words at a time) ----
@@ -132,8 +135,8 @@ __global__ void __launch_bounds__(FT_THREADS, 3) fattn_tile_kernel(FattnParams p
     }
     const int n_uw = uw_count;
 
-    // one 16-byte piece of a K or V row per copy: D / 8 pieces per row, 16 rows of K then 16 of V.  A thread's copies sit at
-    // fixed places of a stage: copy n of thread tid is piece (tid + 128 n) % PIECES of row ((tid + 128 n) / PIECES) % 16.
+    // one 16-byte piece of a K or V row per copy: D / 8 pieces per row, 32 rows of K then 32 of V.  A thread's copies sit at
+    // fixed places of a stage: copy n of thread tid is piece (tid + 128 n) % PIECES of row ((tid + 128 n) / PIECES) % 32.
     constexpr int PIECES = D / 8, COPIES = 2 * FT_CHUNK * PIECES / FT_THREADS, K_COPIES = COPIES / 2;
     const int st_row0 = tid / PIECES, st_piece = tid % PIECES;   // 128 / PIECES rows apart from copy to copy
     const uint32_t st_dst0 = kv_u32 + (uint32_t) (st_row0 * ROW + st_piece * 16);
@@ -207,7 +210,7 @@ __global__ void __launch_bounds__(FT_THREADS, 3) fattn_tile_kernel(FattnParams p
                     m |= (unsigned) ((tile_words[j][kb >> 6] >> (kb & 63)) & 1ull) << x;
                 }
             }
-            rmask[j][c] = (unsigned short) m;
+            rmask[j][c] = m;
         }
         // this split's chunks: split, split + nsplit, ...; FT_STAGES - 1 of them are on their way while one is multiplied
         int issued = 0;
@@ -228,35 +231,28 @@ __global__ void __launch_bounds__(FT_THREADS, 3) fattn_tile_kernel(FattnParams p
             }
             asm volatile("cp.async.wait_group %0;\n" ::"n"(FT_STAGES - 1) : "memory");
             __syncthreads();   // the stage has landed for every thread (and, first time round, the row masks are written)
-            const uint8_t *Ks = &kv_s[s][0][0];
+            const uint8_t *Ks = kv_s + (s * 2) * (FT_CHUNK * ROW);
             const uint32_t Vs = kv_u32 + (uint32_t) ((s * 2 + 1) * (FT_CHUNK * ROW));
-            // ---- S = Q K^T: two n-tiles of 8 cells ----
-            float sacc[2][4], sodd[2][4];   // even and odd k-steps accumulate apart: two chains of half the length per tile
+            // ---- S = Q K^T: four n-tiles of 8 cells (four independent accumulator chains) ----
+            float sacc[4][4];
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                sacc[c][0] = sacc[c][1] = sacc[c][2] = sacc[c][3] = 0.0f;
-                sodd[c][0] = sodd[c][1] = sodd[c][2] = sodd[c][3] = 0.0f;
-            }
+            for (int c = 0; c < 4; ++c) sacc[c][0] = sacc[c][1] = sacc[c][2] = sacc[c][3] = 0.0f;
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks)
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
+                for (int c = 0; c < 4; ++c) {
                     const uint8_t *krow = Ks + (8 * c + g) * ROW + 4 * t + 32 * ks;
                     const uint32_t b0 = *reinterpret_cast<const uint32_t *>(krow), b1 = *reinterpret_cast<const uint32_t *>(krow + 16);
-                    mma_f16((ks & 1) ? sodd[c] : sacc[c], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+                    mma_f16(sacc[c], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
                 }
-#pragma unroll
-            for (int c = 0; c < 2; ++c)
-#pragma unroll
-                for (int x = 0; x < 4; ++x) sacc[c][x] += sodd[c][x];
             // ---- scores: element [c][2 i + e] is (row g + 8 i, cell 8 c + 2 t + e of the chunk) ----
             const int base = ch * FT_CHUNK;
             float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
             unsigned rm[2];
 #pragma unroll
-            for (int i = 0; i < 2; ++i) rm[i] = live[i] ? (unsigned) rmask[tl[i]][ch] : 0u;
+            for (int i = 0; i < 2; ++i) rm[i] = live[i] ? rmask[tl[i]][ch] : 0u;
 #pragma unroll
-            for (int c = 0; c < 2; ++c)
+            for (int c = 0; c < 4; ++c)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int x = 8 * c + 2 * t + e;
@@ -281,7 +277,7 @@ __global__ void __launch_bounds__(FT_THREADS, 3) fattn_tile_kernel(FattnParams p
                 const float m_use = (m_new == -CUDART_INF_F) ? 0.0f : m_new;
                 float sum = 0.0f;
 #pragma unroll
-                for (int c = 0; c < 2; ++c)
+                for (int c = 0; c < 4; ++c)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const float pr = __expf(sacc[c][2 * i + e] - m_use);
@@ -297,28 +293,31 @@ __global__ void __launch_bounds__(FT_THREADS, 3) fattn_tile_kernel(FattnParams p
                     o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0]; o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1];
                 }
             }
-            // P as A fragments (k = the chunk's 16 cells), fp16 hi + lo
-            uint32_t ph[4], pl[4];
+            // P as A fragments, two k-steps of 16 cells, fp16 hi + lo
+            uint32_t ph[2][4], pl[2][4];
 #pragma unroll
-            for (int c = 0; c < 2; ++c)
+            for (int c = 0; c < 4; ++c)
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
                     const float x0 = sacc[c][2 * i], x1 = sacc[c][2 * i + 1];
                     const __half2 h = __floats2half2_rn(x0, x1);
                     const float2 f = __half22float2(h);
-                    ph[2 * c + i] = *reinterpret_cast<const uint32_t *>(&h);
-                    pl[2 * c + i] = pack_half2(x0 - f.x, x1 - f.y);
+                    ph[c >> 1][2 * (c & 1) + i] = *reinterpret_cast<const uint32_t *>(&h);
+                    pl[c >> 1][2 * (c & 1) + i] = pack_half2(x0 - f.x, x1 - f.y);
                 }
             // ---- O += P V: V^T fragments of two n-tiles per ldmatrix ----
 #pragma unroll
             for (int nt = 0; nt < NT; nt += 2) {
-                uint32_t vb[4];   // {cells 0-7, cells 8-15} of n-tile nt, then of n-tile nt + 1
-                const int mi = lane >> 3, mr = lane & 7;
-                ft_ldmatrix_x4_trans(vb, Vs + (uint32_t) ((8 * (mi & 1) + mr) * ROW + (8 * (nt + (mi >> 1))) * 2));
-                mma_f16(o[nt], ph[0], ph[1], ph[2], ph[3], vb[0], vb[1]);
-                mma_f16(o[nt], pl[0], pl[1], pl[2], pl[3], vb[0], vb[1]);
-                mma_f16(o[nt + 1], ph[0], ph[1], ph[2], ph[3], vb[2], vb[3]);
-                mma_f16(o[nt + 1], pl[0], pl[1], pl[2], pl[3], vb[2], vb[3]);
+#pragma unroll
+                for (int kk = 0; kk < 2; ++kk) {
+                    uint32_t vb[4];   // {cells 0-7, cells 8-15} of this k-step for n-tile nt, then for n-tile nt + 1
+                    const int mi = lane >> 3, mr = lane & 7;
+                    ft_ldmatrix_x4_trans(vb, Vs + (uint32_t) ((16 * kk + 8 * (mi & 1) + mr) * ROW + (8 * (nt + (mi >> 1))) * 2));
+                    mma_f16(o[nt], ph[kk][0], ph[kk][1], ph[kk][2], ph[kk][3], vb[0], vb[1]);
+                    mma_f16(o[nt], pl[kk][0], pl[kk][1], pl[kk][2], pl[kk][3], vb[0], vb[1]);
+                    mma_f16(o[nt + 1], ph[kk][0], ph[kk][1], ph[kk][2], ph[kk][3], vb[2], vb[3]);
+                    mma_f16(o[nt + 1], pl[kk][0], pl[kk][1], pl[kk][2], pl[kk][3], vb[2], vb[3]);
+                }
             }
             __syncthreads();   // this stage may be refilled by the copy issued in the next step
         }
