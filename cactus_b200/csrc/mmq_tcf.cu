@@ -13,19 +13,23 @@
 // and B_lo planes stacked along N, two accumulator halves that the write-back adds) and one of 128 x 64 (A_lo against
 // B_hi, into the first half).  Nothing is rounded that the reference does not round, except the order of the fp32 sums.
 //
-// A CTA (28 warps, one CTA per SM) owns 128 weight rows x up to 64 columns and walks K in groups of 4 blocks.  A hand-over
-// between warps costs a few hundred cycles whatever the mechanism, so every role but the producer is held by several teams
-// that take the groups in turn:
-//   warps 0, 2   issue the MMAs of the even / odd groups (8 K-steps x 2) into an accumulator of their own;
+// A CTA (one per SM) owns 128 weight rows x 64 activation columns (up to 64 columns in all) or x 128 (more) and walks K in
+// groups of 4 blocks.  A hand-over between warps costs a few hundred cycles whatever the mechanism, so the converting
+// roles are held by several teams that take the groups in turn, one team per buffer of its ring (TfCfg):
+//   warp 0       issues the MMAs of every group, in order (8 K-steps x 2), into the one accumulator;
 //   warp 1       producer: four TMA tensor copies per group into a ring of stages -- the packed T16 weight tiles (128-byte
 //                swizzle, so the row-per-thread reads are conflict free), their fp16 scales, the Q8_0 activation tiles in
 //                the fragment order every mul_mat kernel reads, and the activation scales;
-//   warps 4-15   weights, teams of 4 warps (as many as A buffers fit into tensor memory): thread = weight row; unpacks 128 nibbles with the 0x6400 trick
-//                (0x6400 | v is the fp16 1024 + v), multiplies by the block scale and writes A_hi and A_lo straight into
-//                tensor memory (the MMA's A operand); after the last group two teams read the accumulators (32 columns
-//                each) and write the result;
-//   warps 16-27  activations, three teams: int8 -> fp16 (same trick), times the block scale, hi and lo planes into a ring
-//                of shared memory tiles in the K-major core-matrix order of the MMA's B descriptor.
+//   warps 4-15   weights, teams of 4 warps (as many as A buffers fit into tensor memory): thread = weight row; unpacks 128
+//                nibbles with the 0x6400 trick (0x6400 | v is the fp16 1024 + v), multiplies by the block scale and writes
+//                A_hi and A_lo straight into tensor memory (the MMA's A operand); after the last group two teams read
+//                the accumulator (half of the columns each) and write the result;
+//   warps 16-..  activations, teams of 4 or 8 warps: int8 -> fp16 (same trick), times the block scale, hi and lo planes
+//                into a ring of shared memory tiles in the K-major core-matrix order of the MMA's B descriptor.
+// Measured (B200, K 4096 x M 14336): 45.6 us at 64 columns with three terms, 35.3 with two, against 33.1 for the mma.sync
+// kernel; at 128 columns 60.5 / 44.5 against 56.9.  The conversions cost 2300-3000 warp instructions per group on the CUDA
+// cores, more than the group's HBM time, and they slow the issuing thread (103 clk per 128 x 128 x 16 MMA against 64.5 in
+// isolation); the kernel is therefore opt-in (B200_MMQ_TC=2 three terms, =3 two).
 // Within a block both operands use the same permutation of K (the order the nibbles come out of a 32-bit word).
 // Every wait is bounded; on time-out the CTA raises b200_kernel_status, all roles fall through, the producer waits
 // (bounded) for its copies in flight, the issuing warp for its MMAs, the CTA frees its tensor memory and returns.
