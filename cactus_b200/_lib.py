@@ -28,6 +28,7 @@ SIGNATURES = {
     "b200_mul_mat_q": (_i32, [_i32, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _vp, _sz, _i32, _vp]),
     "b200_quantize_activations": (_i32, [_vp, _i64, _i64, _i64, _vp, _sz, _i32, _vp]),
     "b200_mul_mat_q_prequant": (_i32, [_i32, _vp, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _sz, _vp]),
+    "b200_mul_mat_q_prequant_multi": (_i32, [_i32, _i32, C.POINTER(_vp), C.POINTER(_i64), _i64, _vp, _i64, C.POINTER(_vp), _i64, _vp, _sz, _vp]),
     "b200_mul_mat_q_noalloc": (_i32, [_i32, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i32, _vp]),
     "b200_block_dots": (_i32, [_i32, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _vp, _sz, _i32, _vp]),
     "b200_flash_attn_scratch_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64]),

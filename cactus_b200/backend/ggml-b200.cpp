@@ -569,6 +569,7 @@ struct b200_backend_ctx {
     int q8_variant = B200_Q8_AVX2;
     bool fa_parity = false;  // B200_FA_PARITY=1: the reference-order attention kernel (validation)
     bool fuse = true;        // B200_FUSE=0: one kernel per node (except the norm and silu pairs)
+    bool stack = true;       // B200_STACK=0: adjacent products on the same activations run one by one
     rope_store_state rs;
     bool timing = false;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -593,6 +594,7 @@ struct b200_backend_ctx {
     size_t slots_cap = 0;
     std::vector<int32_t> slots_host;
     std::vector<std::pair<const lm_ggml_tensor *, int>> slot_of;   // CPY node -> offset of its row list
+    std::vector<uint8_t> node_done;                                 // per node of the list being run: it ran ahead of its place
 };
 
 lm_ggml_guid_t b200_guid() {
@@ -860,6 +862,7 @@ std::atomic<uint64_t> g_split_mul_mats{0};
 // CUDA-event time of every graph_compute of every backend of the process (B200_TIMING=1), for drivers that cannot reach
 // the backends a llama_context owns
 std::atomic<uint64_t> g_rope_store_groups{0}, g_add_norm_groups{0};   // fused groups of all backends of the process
+std::atomic<uint64_t> g_stacked_products{0};                          // launches that multiplied several weights (recordings included)
 std::mutex g_totals_mu;
 double g_total_device_ms = 0.0;
 uint64_t g_total_timed_graphs = 0;
@@ -1059,6 +1062,31 @@ bool mask_hint_serves(const b200_backend_ctx * ctx, const lm_ggml_tensor * node)
            lm_ggml_is_contiguous(dstt) && s0->ne[0] == d.n_kv && s0->ne[1] == (d.n_tokens + 63) / 64 * 64 && lm_ggml_nelements(s0) == lm_ggml_nelements(dstt);
 }
 
+// ---- running a node before its place in the node order ----
+// ggml-alloc gives a node's destination to it from the node's own place on: earlier, the same memory may still hold a
+// tensor that a node in between reads or writes.  Node j may therefore run together with node i < j only if, for every
+// node k in between that has yet to run, j's destination overlaps neither k's destination nor any of k's sources, and
+// none of j's sources overlaps k's destination (j's inputs exist already).  Checked on the addresses of the graph at hand.
+bool ranges_overlap(const lm_ggml_tensor * a, const lm_ggml_tensor * b) {
+    if (!a || !b || !a->data || !b->data) return false;
+    const char * a0 = (const char *) a->data, * b0 = (const char *) b->data;
+    return a0 < b0 + lm_ggml_nbytes(b) && b0 < a0 + lm_ggml_nbytes(a);
+}
+
+bool can_run_early(const b200_backend_ctx * ctx, const lm_ggml_cgraph * g, int i, int j) {
+    const lm_ggml_tensor * nj = g->nodes[j];
+    for (int k = i + 1; k < j; ++k) {
+        if (ctx->node_done[k]) continue;
+        const lm_ggml_tensor * nk = g->nodes[k];
+        if (ranges_overlap(nj, nk)) return false;
+        for (int s = 0; s < LM_GGML_MAX_SRC; ++s) {
+            if (nk->src[s] && ranges_overlap(nj, nk->src[s])) return false;
+            if (nj->src[s] && ranges_overlap(nj->src[s], nk)) return false;
+        }
+    }
+    return true;
+}
+
 // launches the kernels of a node list on the backend's stream (directly, or into a stream capture)
 lm_ggml_status run_nodes(b200_backend_ctx * ctx, lm_ggml_cgraph * cgraph, bool check_abort) {
     cudaStream_t st = ctx->stream;
@@ -1066,10 +1094,11 @@ lm_ggml_status run_nodes(b200_backend_ctx * ctx, lm_ggml_cgraph * cgraph, bool c
     for (split_peer & p : ctx->peers) p.act_src = nullptr;
     ctx->index_mask = nullptr;
     ctx->rs.cpy_k = nullptr;
+    ctx->node_done.assign((size_t) cgraph->n_nodes, 0);   // nodes that ran ahead of their place
 
     for (int i = 0; i < cgraph->n_nodes; ++i) {
         lm_ggml_tensor * node = cgraph->nodes[i];
-        if (lm_ggml_is_empty(node)) continue;
+        if (lm_ggml_is_empty(node) || ctx->node_done[i]) continue;
         switch (node->op) {
             case LM_GGML_OP_NONE: case LM_GGML_OP_RESHAPE: case LM_GGML_OP_VIEW: case LM_GGML_OP_PERMUTE: case LM_GGML_OP_TRANSPOSE:
                 continue;
@@ -1098,9 +1127,43 @@ lm_ggml_status run_nodes(b200_backend_ctx * ctx, lm_ggml_cgraph * cgraph, bool c
                     ctx->act_src = s1;
                     ctx->stats.act_quantized++;
                 }
-                const size_t wb = b200_mul_mat_workspace_bytes(s0->type, K, M, N);
+                // Other products of the same activations a few nodes on (q, k and v; ffn_gate and ffn_up) join this launch when
+                // they may run ahead of their place (can_run_early): one launch fills the GPU better than three small ones.
+                int n_w = 1;
+                const void * wv[3] = {s0->data, nullptr, nullptr};
+                int64_t Mv[3] = {M, 0, 0};
+                float * dv[3] = {(float *) node->data, nullptr, nullptr};
+                int at[3] = {i, -1, -1};
+                for (int j = i + 1; ctx->stack && n_w < 3 && j < cgraph->n_nodes && j < i + 12 && N > 8; ++j) {
+                    const lm_ggml_tensor * nx = cgraph->nodes[j];
+                    if (nx->op == LM_GGML_OP_FLASH_ATTN_EXT) break;
+                    if (ctx->node_done[j] || nx->op != LM_GGML_OP_MUL_MAT || nx->src[1] != s1) continue;
+                    if (nx->src[0]->type != s0->type || nx->src[0]->ne[0] != K || !nx->src[0]->buffer || buft_is_b200_split(nx->src[0]->buffer->buft) ||
+                        nx->nb[1] != node->nb[1] || Mv[n_w - 1] % 128 != 0 || ((uintptr_t) nx->src[0]->data % 16) || nx->ne[1] * nx->ne[2] * nx->ne[3] != N)
+                        continue;
+                    bool ok = can_run_early(ctx, cgraph, i, j);
+                    for (int k = 0; ok && k < n_w; ++k) ok = !ranges_overlap(nx, cgraph->nodes[at[k]]);   // (the allocator may have given two of them the same memory)
+                    if (getenv("B200_GRAPH_DEBUG") && i < 64) fprintf(stderr, "ggml-b200: %s (node %d) with %s (node %d): %s\n", nx->name, j, node->name, i, ok ? "one launch" : "kept apart");
+                    if (!ok) continue;
+                    wv[n_w] = nx->src[0]->data;
+                    Mv[n_w] = nx->src[0]->ne[1];
+                    dv[n_w] = (float *) nx->data;
+                    at[n_w] = j;
+                    ctx->node_done[j] = 1;
+                    ++n_w;
+                }
+                int64_t M_all = 0;
+                for (int k = 0; k < n_w; ++k) M_all += Mv[k];
+                const size_t wb = b200_mul_mat_workspace_bytes(s0->type, K, M_all, N);
                 void * ws = wb ? ctx->workspace.get(wb, st) : nullptr;
                 if (wb && !ws) return LM_GGML_STATUS_ALLOC_FAILED;
+                if (n_w > 1) {
+                    B200_CHECK(b200_mul_mat_q_prequant_multi(s0->type, n_w, wv, Mv, K, ctx->act.ptr, N, dv, node->nb[1], ws, ws ? ctx->workspace.bytes : 0, st));
+                    ctx->stats.mul_mat += n_w;
+                    ctx->stats.nodes += n_w - 1;
+                    g_stacked_products.fetch_add(1, std::memory_order_relaxed);
+                    break;
+                }
                 B200_CHECK(b200_mul_mat_q_prequant(s0->type, s0->data, K, M, ctx->act.ptr, N, (float *) node->data, node->nb[1], ws,
                                                    ws ? ctx->workspace.bytes : 0, st));
                 ctx->stats.mul_mat++;
@@ -1205,13 +1268,17 @@ lm_ggml_status run_nodes(b200_backend_ctx * ctx, lm_ggml_cgraph * cgraph, bool c
                 else B200_CHECK(b200_mul((const float *) s0->data, (const float *) s1->data, (float *) node->data, d, rows, brows, st));
             } break;
             case LM_GGML_OP_UNARY: {
-                // SILU(gate) * up: the llama FFN gate, fused when the SILU result has no other reader
-                lm_ggml_tensor * next = i + 1 < cgraph->n_nodes ? cgraph->nodes[i + 1] : nullptr;
+                // SILU(gate) * up: the llama FFN gate, fused when the SILU result has no other reader.  The multiply is the next
+                // node that has yet to run (ffn_up sits between the two in the node order and may have run with ffn_gate), and
+                // runs here, ahead of its place, when that is safe.
+                int jn = i + 1;
+                while (jn < cgraph->n_nodes && jn < i + 4 && ctx->node_done[jn]) ++jn;
+                lm_ggml_tensor * next = jn < cgraph->n_nodes ? cgraph->nodes[jn] : nullptr;
                 if (next && next->op == LM_GGML_OP_MUL && (next->src[0] == node || next->src[1] == node) && supports_binary(next) &&
-                    lm_ggml_are_same_shape(next->src[0], next->src[1]) && only_user_is(cgraph, node, next)) {
+                    lm_ggml_are_same_shape(next->src[0], next->src[1]) && only_user_is(cgraph, node, next) && (jn == i + 1 || can_run_early(ctx, cgraph, i, jn))) {
                     const lm_ggml_tensor * other = next->src[0] == node ? next->src[1] : next->src[0];
                     // the product is the input of ffn_down: the same kernel leaves it quantised for that mul_mat
-                    lm_ggml_tensor * mm = i + 2 < cgraph->n_nodes ? cgraph->nodes[i + 2] : nullptr;
+                    lm_ggml_tensor * mm = jn + 1 < cgraph->n_nodes ? cgraph->nodes[jn + 1] : nullptr;
                     const int64_t d = s0->ne[0], rows = lm_ggml_nrows(s0);
                     const bool feeds_mul_mat = mm && mm->op == LM_GGML_OP_MUL_MAT && mm->src[1] == next && d % 32 == 0 && lm_ggml_is_contiguous(s0) &&
                                                lm_ggml_is_contiguous(other) && lm_ggml_is_contiguous(next) && ((uintptr_t) s0->data % 16) == 0 &&
@@ -1225,7 +1292,8 @@ lm_ggml_status run_nodes(b200_backend_ctx * ctx, lm_ggml_cgraph * cgraph, bool c
                     } else {
                         B200_CHECK(b200_silu((const float *) s0->data, (const float *) other->data, (float *) next->data, lm_ggml_nelements(s0), st));
                     }
-                    ++i;
+                    ctx->node_done[jn] = 1;
+                    ctx->stats.nodes++;
                 } else {
                     B200_CHECK(b200_silu((const float *) s0->data, nullptr, (float *) node->data, lm_ggml_nelements(s0), st));
                 }
@@ -1349,7 +1417,7 @@ bool graph_signature(const b200_backend_ctx * ctx, const lm_ggml_cgraph * g, uin
     h.val(g->n_nodes);
     h.val((uintptr_t) ctx->act.ptr); h.val((uintptr_t) ctx->workspace.ptr); h.val((uintptr_t) ctx->fa_scratch.ptr); h.val((uintptr_t) ctx->mask_index.ptr);
     h.val((uintptr_t) ctx->slots_dev);
-    h.val(ctx->fuse); h.val(ctx->fa_parity); h.val(ctx->q8_variant);
+    h.val(ctx->fuse); h.val(ctx->stack); h.val(ctx->fa_parity); h.val(ctx->q8_variant);
     for (int i = 0; i < g->n_nodes; ++i) {
         const lm_ggml_tensor * n = g->nodes[i];
         const int at = slot_offset(ctx, n);
@@ -1469,6 +1537,11 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
     std::vector<uint64_t> trail;
     if (ctx->graphs && ctx->warmed && graph_signature(ctx, cgraph, &h1, &h2, debug ? &trail : nullptr)) {
         if (debug) {
+            static bool listed = false;
+            if (!listed && cgraph->n_nodes > 60) {   // once: the node order of a layer, which decides what can run as one kernel
+                listed = true;
+                for (int k = 0; k < 60; ++k) fprintf(stderr, "ggml-b200: node %d %s %s\n", k, lm_ggml_op_name(cgraph->nodes[k]->op), cgraph->nodes[k]->name);
+            }
             if (h1 != ctx->last_h1 && !ctx->dbg_trail.empty()) {
                 size_t k = 0;
                 while (k < trail.size() && k < ctx->dbg_trail.size() && trail[k] == ctx->dbg_trail[k]) ++k;
@@ -1520,8 +1593,10 @@ lm_ggml_status backend_graph_compute(lm_ggml_backend_t backend, lm_ggml_cgraph *
     // instead of running would leave the device idle for as long as the recording takes (1.6 ms for a 1031-node list).
     if (want_record) {
         const auto t_rec0 = std::chrono::steady_clock::now();
+        const uint64_t l0 = b200_launch_count();
         const bool ok = shadow_record(ctx, cgraph, h1, h2, victim);
-        if (debug) fprintf(stderr, "ggml-b200: recording %d nodes took %.2f ms on the host (%s)\n", cgraph->n_nodes,
+        if (debug) fprintf(stderr, "ggml-b200: recording %d nodes (%llu launches) took %.2f ms on the host (%s)\n", cgraph->n_nodes,
+                           (unsigned long long) (b200_launch_count() - l0),
                            std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t_rec0).count(), ok ? "ok" : "failed");
     }
     if (ctx->timing) {
@@ -1844,6 +1919,8 @@ lm_ggml_backend_t lm_ggml_backend_b200_init(int device) {
     if (v && strcmp(v, "scalar") == 0) ctx->q8_variant = B200_Q8_SCALAR;
     const char * fu = getenv("B200_FUSE");
     ctx->fuse = !(fu && atoi(fu) == 0);
+    const char * sk = getenv("B200_STACK");
+    ctx->stack = !(sk && atoi(sk) == 0);
     const char * gr = getenv("B200_GRAPHS");
     ctx->graphs = !(gr && atoi(gr) == 0);
     const char * fp = getenv("B200_FA_PARITY");

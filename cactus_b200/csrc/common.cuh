@@ -68,6 +68,13 @@ struct PeerDst {
     int n_seg;
     int seg_end[2];
     int64_t seg_shift[3];
+    // The same row ranges can also come from separate weight tensors (ggml allocates a layer's gate and up projections
+    // one by one; multiplying both by the same activations in one launch fills the GPU better than two launches): range i
+    // then reads wseg[i] (scales wseg_qs[i] bytes further) instead of a slice of one stacked tensor.  n_wseg = 0: one
+    // tensor.  Ranges then start on multiples of 128 rows (whole row groups of every kernel shape).
+    int n_wseg;
+    const unsigned char *wseg[3];
+    unsigned long long wseg_qs[3];
 };
 #ifdef __CUDACC__
 __device__ __forceinline__ int64_t peer_row_shift(const PeerDst &peers, int64_t row) {

@@ -254,24 +254,34 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
         uint8_t *st = smem + (it % MMQ_STAGES) * S::STAGE;
         uint32_t bg = (uint32_t) (bg_begin + it);
         uint32_t wbg = bg;   // block-group index into the weight stream, row group included
+        int64_t first_row = cta_rt0 * 16;   // of the row group this copy belongs to
         if (SK) {
             if (sk_head != 0 && it == (int64_t) sk_head) sk_where(it, iss_ct, iss_bg);   // the last piece is copied: on to the start of the range
             bg = iss_bg;
             wbg = iss_ct * (uint32_t) S::CTA_TILES * sk_nbg + iss_bg;
+            first_row = (int64_t) iss_ct * S::CTA_TILES * 16;
             if (++iss_bg == sk_nbg) {
                 iss_bg = sk_tails ? sk_h : 0u;
                 ++iss_ct;
             }
         }
+        // row ranges from separate weight tensors (PeerDst::wseg): the range's tensor, and its first row tile taken off the offsets
+        const uint8_t *wq_base = w, *ws_base = w_sc;
+        if (peers.n_wseg > 0) {
+            const int k = first_row < peers.seg_end[0] ? 0 : ((peers.n_seg > 2 && first_row >= peers.seg_end[1]) ? 2 : 1);
+            wq_base = peers.wseg[k];
+            ws_base = wq_base + peers.wseg_qs[k];
+            if (k > 0) wbg -= (uint32_t) (peers.seg_end[k - 1] / 16) * (uint32_t) dims.n_bg;   // (the sums below stay non-negative)
+        }
 #pragma unroll
         for (int k = 0; k < A_N; ++k) {
             const int c = tid + k * MMQ_THREADS;
-            if (A_CH % MMQ_THREADS == 0 || c < A_CH) cp_async16(st + a_dst[k], w + (size_t) (a_src[k] + wbg * (S::TILE / 16)) * 16);
+            if (A_CH % MMQ_THREADS == 0 || c < A_CH) cp_async16(st + a_dst[k], wq_base + (size_t) (uint32_t) (a_src[k] + wbg * (S::TILE / 16)) * 16);
         }
 #pragma unroll
         for (int k = 0; k < AS_N; ++k) {
             const int c = tid + k * MMQ_THREADS;
-            if (AS_CH % MMQ_THREADS == 0 || c < AS_CH) cp_async16(st + S::A_BYTES + c * 16, w_sc + (size_t) (as_src[k] + wbg * 8) * 16);
+            if (AS_CH % MMQ_THREADS == 0 || c < AS_CH) cp_async16(st + S::A_BYTES + c * 16, ws_base + (size_t) (uint32_t) (as_src[k] + wbg * 8) * 16);
         }
         uint8_t *sb = st + S::A_BYTES + S::AS_BYTES;
 #pragma unroll
@@ -408,8 +418,9 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
                         float v0, v1;
                         unpack2(y[mt][nt][h], v0, v1);
                         if (row < dims.M) {
-                            if (col < act.N) *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + col * dst_nb_row + row * 4) = v0 * WS;
-                            if (col + 1 < act.N) *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + (col + 1) * dst_nb_row + row * 4) = v1 * WS;
+                            const int64_t sh = peer_row_shift(peers, row);   // row ranges that belong to different destination tensors
+                            if (col < act.N) *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + col * dst_nb_row + row * 4 + sh) = v0 * WS;
+                            if (col + 1 < act.N) *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + (col + 1) * dst_nb_row + row * 4 + sh) = v1 * WS;
                         }
                     }
                 }
@@ -640,7 +651,7 @@ struct MmqVariant {
     int ctas_per_sm; // resident CTAs per SM (filled on first use)
     int (*launch)(const TiledDims &, const uint8_t *, const ActDims &, const uint8_t *, float *, int64_t, float *, int, int, int, const PeerDst &, cudaStream_t);
     int (*max_clusters)(int);   // resident clusters of `ksplit` CTAs on this device (0 = cannot be launched that way)
-    int (*launch_streamk)(const TiledDims &, const uint8_t *, const ActDims &, const uint8_t *, float *, int64_t, void *, int, int, int, cudaStream_t);
+    int (*launch_streamk)(const TiledDims &, const uint8_t *, const ActDims &, const uint8_t *, float *, int64_t, void *, int, int, int, const PeerDst &, cudaStream_t);
     size_t streamk_slot_bytes;  // one partial tile of a CTA in the stream-K workspace
 };
 
@@ -656,13 +667,13 @@ static size_t streamk_counter_bytes(int64_t n_groups) { return (size_t) ((n_grou
 // the block groups of a head in the head/tail deal
 template <int WTYPE, int NTW, int WN, int MT, int WM, int STAGES, int MINB>
 static int launch_variant_streamk(const TiledDims &d, const uint8_t *w, const ActDims &a, const uint8_t *aq, float *dst, int64_t dst_nb_row,
-                                  void *workspace, int ctas, int head, int canon, cudaStream_t st) {
+                                  void *workspace, int ctas, int head, int canon, const PeerDst &segs, cudaStream_t st) {
     using S = MmqCfg<WTYPE, NTW, WN, MT, WM, STAGES>;
     const int n_groups = (int) (d.n_rt / S::CTA_TILES);
     launch_pdl(zero_u32_kernel, dim3((unsigned) ((n_groups + 255) / 256)), dim3(256), 0, st, (unsigned *) workspace, n_groups);
     if (int e = check_launch("mmq stream-K counters")) return e;
     launch_pdl(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, MMQ_STREAMK>, dim3((unsigned) ctas), dim3(S::THREADS), S::TOTAL, st, d, w, a, aq, dst,
-               dst_nb_row, (float *) workspace, head, canon, 0, PeerDst{});
+               dst_nb_row, (float *) workspace, head, canon, 0, segs);   // segs: row ranges only, never peers
     return check_launch("mmq stream-K");
 }
 
@@ -908,10 +919,10 @@ int launch_mmq(int wtype, const TiledDims &d, const void *w, const ActDims &a, c
     if (ks > 1 && !cluster && (!workspace || workspace_bytes < per_split * ks)) {
         ks = workspace ? (int) std::max<size_t>(1, workspace_bytes / per_split) : 1;  // fewer splits fit: still correct, only slower
     }
-    if (peers.n == 0 && peers.n_seg <= 1 && workspace) {
+    if (peers.n == 0 && (peers.n_seg <= 1 || peers.n_wseg > 0) && workspace) {   // (the ranges of a row-split rank keep the plain grid)
         int head = 0;
         if (const int ctas = streamk_ctas(v, d, a, ks, cluster, workspace_bytes, &head))
-            return v.launch_streamk(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, workspace, ctas, head, canon ? 1 : 0, st);
+            return v.launch_streamk(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, workspace, ctas, head, canon ? 1 : 0, peers, st);
     }
     if (int e = v.launch(d, (const uint8_t *) w, a, (const uint8_t *) aq, dst, dst_nb_row, (float *) workspace, ks, canon ? 1 : 0, cluster ? 1 : 0, peers, st)) return e;
     if (ks > 1 && !cluster) {

@@ -141,6 +141,44 @@ static int mul_mat_prequant(int wtype, const void *w, int64_t K, int64_t M, cons
     return launch_mmq(wtype, d, w, a, act, dst, dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream, false, peers);
 }
 
+int b200_mul_mat_q_prequant_multi(int wtype, int n_weights, const void *const *w, const int64_t *M, int64_t K, const void *act, int64_t N,
+                                  float *const *dst, int64_t dst_row_stride_bytes, void *workspace, size_t workspace_bytes, b200_stream_t stream) {
+    B200_REQUIRE(n_weights >= 1 && n_weights <= 3 && w && M && dst, "1 to 3 weights");
+    int64_t total = 0;
+    bool whole_groups = true;
+    for (int i = 0; i < n_weights; ++i) {
+        B200_REQUIRE(w[i] && dst[i] && M[i] > 0 && is_aligned(w[i], 16) && is_aligned(dst[i], 4), "null or misaligned weight / destination %d", i);
+        whole_groups = whole_groups && (i == n_weights - 1 || M[i] % 128 == 0);
+        total += M[i];
+    }
+    // one launch needs whole row groups per tensor and the tensor-core kernel; otherwise one product after the other
+    if (n_weights == 1 || !whole_groups || N <= mmvq_max_n()) {
+        for (int i = 0; i < n_weights; ++i)
+            if (int e = b200_mul_mat_q_prequant(wtype, w[i], K, M[i], act, N, dst[i], dst_row_stride_bytes, workspace, workspace_bytes, stream)) return e;
+        return B200_OK;
+    }
+    B200_REQUIRE(shape_ok(wtype, K, total, N), "bad mul_mat shape/type: type %d K %lld M %lld N %lld", wtype, (long long) K, (long long) total, (long long) N);
+    B200_REQUIRE(act && is_aligned(act, 256), "null or misaligned activations");
+    B200_REQUIRE(dst_row_stride_bytes % 4 == 0, "bad dst row stride");
+    B200_REQUIRE(!workspace || is_aligned(workspace, 256), "workspace must be 256-byte aligned");
+    PeerDst segs = {};
+    segs.n_seg = n_weights;
+    segs.n_wseg = n_weights;
+    int64_t row = 0;
+    for (int i = 0; i < n_weights; ++i) {
+        B200_REQUIRE(dst_row_stride_bytes >= M[i] * 4, "bad dst row stride");
+        segs.wseg[i] = (const unsigned char *) w[i];
+        segs.wseg_qs[i] = (unsigned long long) tiled_dims(wtype, K, M[i]).qs_bytes;
+        // a plain mapping puts row r of the stacked product at dst[0] + r floats
+        segs.seg_shift[i] = (int64_t) ((const char *) dst[i] - (const char *) dst[0]) - row * 4;
+        row += M[i];
+        if (i < 2) segs.seg_end[i] = (int) row;
+    }
+    const TiledDims d = tiled_dims(wtype, K, total);
+    const ActDims a = act_dims(K, N);
+    return launch_mmq(wtype, d, w[0], a, act, dst[0], dst_row_stride_bytes, workspace, workspace_bytes, (cudaStream_t) stream, false, segs);
+}
+
 int b200_mul_mat_q(int wtype, const void *w, int64_t K, int64_t M, const float *x, int64_t x_row_stride_bytes, int64_t N,
                    float *dst, int64_t dst_row_stride_bytes, void *scratch, size_t scratch_bytes, int variant, b200_stream_t stream) {
     B200_REQUIRE(shape_ok(wtype, K, M, N), "bad mul_mat shape/type: type %d K %lld M %lld N %lld", wtype, (long long) K, (long long) M, (long long) N);

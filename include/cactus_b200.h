@@ -120,6 +120,14 @@ B200_API int b200_quantize_activations(const float *x, int64_t x_row_stride_byte
 B200_API int b200_mul_mat_q_prequant(int wtype, const void *w, int64_t K, int64_t M, const void *act, int64_t N,
                                      float *dst, int64_t dst_row_stride_bytes, void *workspace, size_t workspace_bytes,
                                      b200_stream_t stream);
+/* Up to three weights of one type and K (a layer's gate and up projections, or q, k and v) against the same quantised
+ * activations in ONE launch: dst[i] = mul_mat(w[i], x) as by b200_mul_mat_q_prequant on each, for separate weight and
+ * destination tensors (what a graph_compute sees: ggml allocates them one by one), with the work of all of them dealt
+ * out together.  All destinations share dst_row_stride_bytes; `workspace` as for one product of M[0] + M[1] + ... rows.
+ * Weights but the last must hold a multiple of 128 rows, else (and for the GEMV widths) the products run one by one. */
+B200_API int b200_mul_mat_q_prequant_multi(int wtype, int n_weights, const void *const *w, const int64_t *M, int64_t K, const void *act,
+                                           int64_t N, float *const *dst, int64_t dst_row_stride_bytes, void *workspace,
+                                           size_t workspace_bytes, b200_stream_t stream);
 /* No counterpart in the reference: b200_mul_mat_q for callers that must not allocate device memory.
  *
  * Some hosts cannot hand this library a scratch buffer: code running under a memory budget that was fixed at

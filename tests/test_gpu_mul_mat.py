@@ -154,3 +154,47 @@ def test_weight_cat_and_row_slice(oracle, wtype):
     whole = host(ops.mul_mat(cat, dev(x)))
     for w, lo in zip(ws, (0, 48, 80)):
         assert rel_max_err(whole[:, lo:lo + w.M], host(ops.mul_mat(w, dev(x)))) < 1e-6
+
+
+@pytest.mark.parametrize("K,Ms,N", [(4096, [14336, 14336], 64), (4096, [4096, 1024, 1024], 64), (512, [256, 128], 20), (1024, [128, 128, 80], 33),
+                                    (2048 + 96, [384, 256], 9), (512, [100, 128], 16), (512, [256, 128], 2)])
+def test_several_weights_in_one_launch_match_the_separate_products(K, Ms, N):
+    """b200_mul_mat_q_prequant_multi: separate weight tensors and separate destinations, one launch (stream-K, cluster
+    split-K, plain grid and the split-K reduction all occur among these shapes; the last two fall back to one product
+    after the other).  The work is dealt out differently than for the single products, so the fp32 sums may come in
+    another order: equal to 1e-5 of the largest value, and within the mul_mat tolerance of the oracle."""
+    import ctypes as C
+
+    from cactus_b200 import ops
+    from cactus_b200._lib import check, lib
+    from cactus_b200.engine import random_blocks
+    L = lib()
+    gen = torch.Generator(device="cuda").manual_seed(K + N + len(Ms))
+    ws = [ops.QWeight.from_blocks(2, K, M, random_blocks(2, M, K, gen)) for M in Ms]
+    x = torch.randn((N, K), device="cuda", generator=gen)
+    act = torch.empty(L.b200_act_bytes(K, N), dtype=torch.uint8, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    check(L.b200_quantize_activations(x.data_ptr(), K * 4, K, N, act.data_ptr(), act.numel(), 0, st))
+    wsp = torch.empty(max(256, L.b200_mul_mat_workspace_bytes(2, K, sum(Ms), N)), dtype=torch.uint8, device="cuda")
+    stride = max(Ms)                                              # one row stride for all destinations, as the entry point asks
+    want, got = [], []
+    for w in ws:
+        o = torch.zeros((N, stride), device="cuda")
+        check(L.b200_mul_mat_q_prequant(2, w.data.data_ptr(), K, w.M, act.data_ptr(), N, o.data_ptr(), stride * 4, wsp.data_ptr(), wsp.numel(), st))
+        want.append(o)
+        got.append(torch.full((N, stride), float("nan"), device="cuda"))
+    wp = (C.c_void_p * len(ws))(*[w.data.data_ptr() for w in ws])
+    mp = (C.c_int64 * len(ws))(*Ms)
+    dp = (C.c_void_p * len(ws))(*[g.data_ptr() for g in got])
+    check(L.b200_mul_mat_q_prequant_multi(2, len(ws), wp, mp, K, act.data_ptr(), N, dp, stride * 4, wsp.data_ptr(), wsp.numel(), st))
+    torch.cuda.synchronize()
+    for w, a, b in zip(ws, got, want):
+        a, b = a[:, :w.M].cpu().numpy(), b[:, :w.M].cpu().numpy()
+        assert np.isfinite(a).all()
+        assert np.abs(a - b).max() <= 1e-5 * np.abs(b).max()
+    if K * sum(Ms) <= 1 << 21:                                    # the oracle on the small cases
+        from oracle.binding import Oracle
+        o = Oracle()
+        for w, a in zip(ws, got):
+            ref, _ = o.mul_mat(2, w.to_blocks().cpu().numpy(), x.cpu().numpy(), 0)
+            assert np.abs(a[:, :w.M].cpu().numpy() - ref).max() / np.abs(ref).max() < 1e-3
