@@ -140,7 +140,9 @@ struct MmqCfg {
 // count.  A CTA whose range ends inside a row group parks its partial tile in the workspace; the CTA that arrives last
 // at a row group (a counter per row group) adds the parts in K order and writes the result, so the sum does not
 // depend on the arrival order and nobody waits for anybody.
-constexpr int MMQ_PLAIN = 0, MMQ_PEER = 1, MMQ_STREAMK = 2;
+// MMQ_PEER and MMQ_STREAMK_SEG know row ranges (other GPUs' buffers, separate weight / destination tensors); the plain
+// kernels carry none of that code: the hot shapes of a decode step must not pay for it
+constexpr int MMQ_PLAIN = 0, MMQ_PEER = 1, MMQ_STREAMK = 2, MMQ_STREAMK_SEG = 3;
 #ifndef MMQ_DEPTH
 #define MMQ_DEPTH 2
 #endif
@@ -165,7 +167,8 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
     const int64_t per = (dims.n_bg + ksplit - 1) / ksplit;
     const int64_t bg_begin = ks * per;
     const int64_t bg_end = min(dims.n_bg, bg_begin + per);
-    constexpr bool SK = MODE == MMQ_STREAMK;
+    constexpr bool SK = MODE == MMQ_STREAMK || MODE == MMQ_STREAMK_SEG;
+    constexpr bool SEGS = MODE == MMQ_PEER || MODE == MMQ_STREAMK_SEG;
     // Stream-K.  Iteration i of the product is block group i % n_bg of row group i / n_bg.  Two ways to deal them out:
     //   even deal (ksplit <= 1): CTA j owns the contiguous iterations [j * total / G, (j + 1) * total / G) -- for
     //     products with more row groups than CTAs; a CTA first does the piece its range ends with, then the rest, so it
@@ -267,7 +270,7 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
         }
         // row ranges from separate weight tensors (PeerDst::wseg): the range's tensor, and its first row tile taken off the offsets
         const uint8_t *wq_base = w, *ws_base = w_sc;
-        if (peers.n_wseg > 0) {
+        if (SEGS && peers.n_wseg > 0) {
             const int k = first_row < peers.seg_end[0] ? 0 : ((peers.n_seg > 2 && first_row >= peers.seg_end[1]) ? 2 : 1);
             wq_base = peers.wseg[k];
             ws_base = wq_base + peers.wseg_qs[k];
@@ -418,7 +421,7 @@ __global__ void __launch_bounds__(WM * WN * 32, MINB) mmq_kernel(TiledDims dims,
                         float v0, v1;
                         unpack2(y[mt][nt][h], v0, v1);
                         if (row < dims.M) {
-                            const int64_t sh = peer_row_shift(peers, row);   // row ranges that belong to different destination tensors
+                            const int64_t sh = SEGS ? peer_row_shift(peers, row) : 0;   // row ranges that belong to different destination tensors
                             if (col < act.N) *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + col * dst_nb_row + row * 4 + sh) = v0 * WS;
                             if (col + 1 < act.N) *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + (col + 1) * dst_nb_row + row * 4 + sh) = v1 * WS;
                         }
@@ -672,8 +675,10 @@ static int launch_variant_streamk(const TiledDims &d, const uint8_t *w, const Ac
     const int n_groups = (int) (d.n_rt / S::CTA_TILES);
     launch_pdl(zero_u32_kernel, dim3((unsigned) ((n_groups + 255) / 256)), dim3(256), 0, st, (unsigned *) workspace, n_groups);
     if (int e = check_launch("mmq stream-K counters")) return e;
-    launch_pdl(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, MMQ_STREAMK>, dim3((unsigned) ctas), dim3(S::THREADS), S::TOTAL, st, d, w, a, aq, dst,
-               dst_nb_row, (float *) workspace, head, canon, 0, segs);   // segs: row ranges only, never peers
+    if (segs.n_seg > 1) launch_pdl(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, MMQ_STREAMK_SEG>, dim3((unsigned) ctas), dim3(S::THREADS), S::TOTAL, st, d, w, a,
+                                   aq, dst, dst_nb_row, (float *) workspace, head, canon, 0, segs);   // segs: row ranges only, never peers
+    else launch_pdl(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, MMQ_STREAMK>, dim3((unsigned) ctas), dim3(S::THREADS), S::TOTAL, st, d, w, a, aq, dst,
+                    dst_nb_row, (float *) workspace, head, canon, 0, PeerDst{});
     return check_launch("mmq stream-K");
 }
 
@@ -751,6 +756,7 @@ static MmqVariant make_variant() {
     v.launch_streamk = launch_variant_streamk<WTYPE, NTW, WN, MT, WM, STAGES, MINB>;
     v.streamk_slot_bytes = (size_t) S::CTA_TILES * 16 * S::NT * 8 * sizeof(float);
     cudaFuncSetAttribute(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, MMQ_STREAMK>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    cudaFuncSetAttribute(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, MMQ_STREAMK_SEG>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     cudaFuncSetAttribute(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, MMQ_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     cudaFuncSetAttribute(mmq_kernel<WTYPE, NTW, WN, MT, WM, STAGES, MINB, MMQ_PEER>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     int n = 0;
