@@ -595,6 +595,9 @@ struct b200_backend_ctx {
     std::vector<int32_t> slots_host;
     std::vector<std::pair<const lm_ggml_tensor *, int>> slot_of;   // CPY node -> offset of its row list
     std::vector<uint8_t> node_done;                                 // per node of the list being run: it ran ahead of its place
+    scratch_buf parked[2];                                          // results of products that ran ahead but whose destination was not free yet
+    struct parked_result { int node, block; size_t stride; };      // stride: the row stride of the launch it ran in
+    std::vector<parked_result> parked_for;
 };
 
 lm_ggml_guid_t b200_guid() {
@@ -613,6 +616,8 @@ void backend_free(lm_ggml_backend_t backend) {
         ctx->workspace.release();
         ctx->fa_scratch.release();
         ctx->mask_index.release();
+        ctx->parked[0].release();
+        ctx->parked[1].release();
         if (ctx->ev0) cudaEventDestroy(ctx->ev0);
         if (ctx->ev1) cudaEventDestroy(ctx->ev1);
         if (ctx->ev_act) cudaEventDestroy(ctx->ev_act);
@@ -1062,6 +1067,11 @@ bool mask_hint_serves(const b200_backend_ctx * ctx, const lm_ggml_tensor * node)
            lm_ggml_is_contiguous(dstt) && s0->ne[0] == d.n_kv && s0->ne[1] == (d.n_tokens + 63) / 64 * 64 && lm_ggml_nelements(s0) == lm_ggml_nelements(dstt);
 }
 
+static bool debug_lists() {
+    static const bool v = [] { const char * e = getenv("B200_GRAPH_DEBUG"); return e && atoi(e) != 0; }();
+    return v;
+}
+
 // ---- running a node before its place in the node order ----
 // ggml-alloc gives a node's destination to it from the node's own place on: earlier, the same memory may still hold a
 // tensor that a node in between reads or writes.  Node j may therefore run together with node i < j only if, for every
@@ -1073,18 +1083,32 @@ bool ranges_overlap(const lm_ggml_tensor * a, const lm_ggml_tensor * b) {
     return a0 < b0 + lm_ggml_nbytes(b) && b0 < a0 + lm_ggml_nbytes(a);
 }
 
-bool can_run_early(const b200_backend_ctx * ctx, const lm_ggml_cgraph * g, int i, int j) {
+// j's sources are not written by any node between i and j that has yet to run
+bool inputs_ready(const b200_backend_ctx * ctx, const lm_ggml_cgraph * g, int i, int j) {
+    const lm_ggml_tensor * nj = g->nodes[j];
+    for (int k = i + 1; k < j; ++k) {
+        if (ctx->node_done[k]) continue;
+        for (int s = 0; s < LM_GGML_MAX_SRC; ++s)
+            if (nj->src[s] && ranges_overlap(nj->src[s], g->nodes[k])) return false;
+    }
+    return true;
+}
+
+// j's destination is not memory that a node between i and j that has yet to run reads or writes
+bool destination_free(const b200_backend_ctx * ctx, const lm_ggml_cgraph * g, int i, int j) {
     const lm_ggml_tensor * nj = g->nodes[j];
     for (int k = i + 1; k < j; ++k) {
         if (ctx->node_done[k]) continue;
         const lm_ggml_tensor * nk = g->nodes[k];
         if (ranges_overlap(nj, nk)) return false;
-        for (int s = 0; s < LM_GGML_MAX_SRC; ++s) {
+        for (int s = 0; s < LM_GGML_MAX_SRC; ++s)
             if (nk->src[s] && ranges_overlap(nj, nk->src[s])) return false;
-            if (nj->src[s] && ranges_overlap(nj->src[s], nk)) return false;
-        }
     }
     return true;
+}
+
+bool can_run_early(const b200_backend_ctx * ctx, const lm_ggml_cgraph * g, int i, int j) {
+    return inputs_ready(ctx, g, i, j) && destination_free(ctx, g, i, j);
 }
 
 // launches the kernels of a node list on the backend's stream (directly, or into a stream capture)
@@ -1095,9 +1119,19 @@ lm_ggml_status run_nodes(b200_backend_ctx * ctx, lm_ggml_cgraph * cgraph, bool c
     ctx->index_mask = nullptr;
     ctx->rs.cpy_k = nullptr;
     ctx->node_done.assign((size_t) cgraph->n_nodes, 0);   // nodes that ran ahead of their place
+    ctx->parked_for.clear();
 
     for (int i = 0; i < cgraph->n_nodes; ++i) {
         lm_ggml_tensor * node = cgraph->nodes[i];
+        if (ctx->node_done[i] == 2) {   // a product that ran ahead into scratch: its destination is its own from here on
+            for (const auto & pk : ctx->parked_for)
+                if (pk.node == i) {
+                    if (!cuda_ok(cudaMemcpy2DAsync(node->data, node->nb[1], ctx->parked[pk.block].ptr, pk.stride, (size_t) node->ne[0] * 4,
+                                                   (size_t) (node->ne[1] * node->ne[2] * node->ne[3]), cudaMemcpyDeviceToDevice, st), "cudaMemcpy2DAsync(parked product)"))
+                        return LM_GGML_STATUS_FAILED;
+                }
+            continue;
+        }
         if (lm_ggml_is_empty(node) || ctx->node_done[i]) continue;
         switch (node->op) {
             case LM_GGML_OP_NONE: case LM_GGML_OP_RESHAPE: case LM_GGML_OP_VIEW: case LM_GGML_OP_PERMUTE: case LM_GGML_OP_TRANSPOSE:
@@ -1127,29 +1161,41 @@ lm_ggml_status run_nodes(b200_backend_ctx * ctx, lm_ggml_cgraph * cgraph, bool c
                     ctx->act_src = s1;
                     ctx->stats.act_quantized++;
                 }
-                // Other products of the same activations a few nodes on (q, k and v; ffn_gate and ffn_up) join this launch when
-                // they may run ahead of their place (can_run_early): one launch fills the GPU better than three small ones.
+                // Other products of the same activations a few nodes on (q, k and v; ffn_gate and ffn_up) join this launch: one
+                // launch fills the GPU better than three small ones.  A product whose inputs exist runs ahead of its place --
+                // into its own destination when that memory is free already and has this product's row stride
+                // (destination_free), else into scratch of the backend, from where a device copy moves the result to its
+                // destination when the node's turn comes (q, k, v: ggml-alloc gives k the block that q's product vacates).
                 int n_w = 1;
                 const void * wv[3] = {s0->data, nullptr, nullptr};
                 int64_t Mv[3] = {M, 0, 0};
                 float * dv[3] = {(float *) node->data, nullptr, nullptr};
                 int at[3] = {i, -1, -1};
+                int n_parked = 0;
                 for (int j = i + 1; ctx->stack && n_w < 3 && j < cgraph->n_nodes && j < i + 12 && N > 8; ++j) {
                     const lm_ggml_tensor * nx = cgraph->nodes[j];
                     if (nx->op == LM_GGML_OP_FLASH_ATTN_EXT) break;
                     if (ctx->node_done[j] || nx->op != LM_GGML_OP_MUL_MAT || nx->src[1] != s1) continue;
                     if (nx->src[0]->type != s0->type || nx->src[0]->ne[0] != K || !nx->src[0]->buffer || buft_is_b200_split(nx->src[0]->buffer->buft) ||
-                        nx->nb[1] != node->nb[1] || Mv[n_w - 1] % 128 != 0 || ((uintptr_t) nx->src[0]->data % 16) || nx->ne[1] * nx->ne[2] * nx->ne[3] != N)
+                        Mv[n_w - 1] % 128 != 0 || ((uintptr_t) nx->src[0]->data % 16) || nx->ne[1] * nx->ne[2] * nx->ne[3] != N || nx->nb[0] != 4 ||
+                        (int64_t) nx->src[0]->ne[1] * 4 > (int64_t) node->nb[1] || !inputs_ready(ctx, cgraph, i, j))
                         continue;
-                    bool ok = can_run_early(ctx, cgraph, i, j);
-                    for (int k = 0; ok && k < n_w; ++k) ok = !ranges_overlap(nx, cgraph->nodes[at[k]]);   // (the allocator may have given two of them the same memory)
-                    if (getenv("B200_GRAPH_DEBUG") && i < 64) fprintf(stderr, "ggml-b200: %s (node %d) with %s (node %d): %s\n", nx->name, j, node->name, i, ok ? "one launch" : "kept apart");
-                    if (!ok) continue;
+                    bool direct = nx->nb[1] == node->nb[1] && destination_free(ctx, cgraph, i, j);
+                    for (int k = 0; direct && k < n_w; ++k) direct = !ranges_overlap(nx, cgraph->nodes[at[k]]);   // (the allocator may have given two of them the same memory)
+                    float * to = (float *) nx->data;
+                    if (!direct) {
+                        if (n_parked >= 2) continue;
+                        to = (float *) ctx->parked[n_parked].get((size_t) N * node->nb[1], st);
+                        if (!to) continue;
+                        ctx->parked_for.push_back({j, n_parked, (size_t) node->nb[1]});
+                        ++n_parked;
+                    }
+                    if (debug_lists() && i < 64) fprintf(stderr, "ggml-b200: %s (node %d) joins %s (node %d)%s\n", nx->name, j, node->name, i, direct ? "" : " through scratch");
                     wv[n_w] = nx->src[0]->data;
                     Mv[n_w] = nx->src[0]->ne[1];
-                    dv[n_w] = (float *) nx->data;
+                    dv[n_w] = to;
                     at[n_w] = j;
-                    ctx->node_done[j] = 1;
+                    ctx->node_done[j] = direct ? 1 : 2;   // 2: the result waits in scratch for the node's turn
                     ++n_w;
                 }
                 int64_t M_all = 0;
@@ -1417,6 +1463,7 @@ bool graph_signature(const b200_backend_ctx * ctx, const lm_ggml_cgraph * g, uin
     h.val(g->n_nodes);
     h.val((uintptr_t) ctx->act.ptr); h.val((uintptr_t) ctx->workspace.ptr); h.val((uintptr_t) ctx->fa_scratch.ptr); h.val((uintptr_t) ctx->mask_index.ptr);
     h.val((uintptr_t) ctx->slots_dev);
+    h.val((uintptr_t) ctx->parked[0].ptr); h.val((uintptr_t) ctx->parked[1].ptr);
     h.val(ctx->fuse); h.val(ctx->stack); h.val(ctx->fa_parity); h.val(ctx->q8_variant);
     for (int i = 0; i < g->n_nodes; ++i) {
         const lm_ggml_tensor * n = g->nodes[i];
