@@ -107,6 +107,28 @@ def test_decode_steps_replay_a_cuda_graph_with_the_same_results():
     assert on["device_masks"] == off["device_masks"] and on["rope_store_groups"] == off["rope_store_groups"], (on, off)
 
 
+def test_products_joined_into_one_launch_keep_parity():
+    """20 sequences, so prompt and decode ubatches are wider than the GEMV: q + k + v run as one launch (k and v through
+    scratch and a copy at their turn), ffn_gate + ffn_up as one, SILU x up + quantiser as one kernel ahead of the multiply's
+    place.  The work of a joined launch is dealt out differently, so sums may come in another order: both runs must hold
+    the model-level bounds against the reference CPU run, and with B200_STACK=0 nothing is joined."""
+    if not os.path.exists(HARNESS):
+        pytest.skip("tests/_bin/harness was not built")
+    args = ["model", "--head-q4", "--seqs", "20", "--max-prompt", "40", "--decode", "4", "--device-mask"]
+    out = {}
+    for stack in ("1", "0"):
+        env = dict(os.environ, B200_STACK=stack, B200_GRAPH_DEBUG="1")
+        p = subprocess.run([HARNESS, *args], capture_output=True, text=True, timeout=600, env=env)
+        lines = [json.loads(line) for line in p.stdout.splitlines() if line.startswith("{")]
+        assert lines and p.returncode == 0, p.stderr[-2000:]
+        out[stack] = (lines[-1], p.stderr)
+    (on, on_log), (off, off_log) = out["1"], out["0"]
+    assert "joins Qcur-0" in on_log and "through scratch" in on_log and "joins ffn_gate-0" in on_log, on_log[-1500:]
+    assert "joins" not in off_log
+    for r in (on, off):
+        assert r["worst_rel"] < 3e-2 and r["greedy_agree"] >= 0.95, r
+
+
 def test_host_made_failures_abort_callback_and_failing_allocator():
     """Failure paths without a GPU fault (tests/backend/faults.cpp): an abort callback that says stop gives
     LM_GGML_STATUS_ABORTED (1), a cudaMalloc that fails gives no buffer and LM_GGML_STATUS_ALLOC_FAILED (-2); after each the
