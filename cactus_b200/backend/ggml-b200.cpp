@@ -594,6 +594,7 @@ struct b200_backend_ctx {
     size_t slots_cap = 0;
     std::vector<int32_t> slots_host;
     std::vector<std::pair<const lm_ggml_tensor *, int>> slot_of;   // CPY node -> offset of its row list
+    std::vector<int64_t> slot_first;                                // first cache row of each list
     std::vector<uint8_t> node_done;                                 // per node of the list being run: it ran ahead of its place
     scratch_buf parked[2];                                          // results of products that ran ahead but whose destination was not free yet
     struct parked_result { int node, block; size_t stride; };      // stride: the row stride of the launch it ran in
@@ -974,10 +975,12 @@ int slot_offset(const b200_backend_ctx * ctx, const lm_ggml_tensor * cpy) {
 bool prepare_row_lists(b200_backend_ctx * ctx, const lm_ggml_cgraph * g) {
     ctx->slot_of.clear();
     ctx->slots_host.clear();
+    ctx->slot_first.clear();
     for (int i = 0; i < g->n_nodes; ++i) {
         int64_t rows, re, first;
         if (!row_store(g->nodes[i], &rows, &re, &first) || rows > (1 << 20)) continue;
         ctx->slot_of.emplace_back(g->nodes[i], (int) ctx->slots_host.size());
+        ctx->slot_first.push_back(first);
         for (int64_t r = 0; r < rows; ++r) ctx->slots_host.push_back((int32_t) (first + r));
     }
     if (ctx->slots_host.empty()) return true;
@@ -1109,6 +1112,83 @@ bool destination_free(const b200_backend_ctx * ctx, const lm_ggml_cgraph * g, in
 
 bool can_run_early(const b200_backend_ctx * ctx, const lm_ggml_cgraph * g, int i, int j) {
     return inputs_ready(ctx, g, i, j) && destination_free(ctx, g, i, j);
+}
+
+// every node that reads t, directly or through reshapes and views, is `reader`, and t is no graph output
+bool only_reader_is(const lm_ggml_cgraph * g, const lm_ggml_tensor * t, const lm_ggml_tensor * reader) {
+    for (int i = 0; i < g->n_nodes; ++i) {
+        const lm_ggml_tensor * n = g->nodes[i];
+        if (n == reader || n->op == LM_GGML_OP_RESHAPE || n->op == LM_GGML_OP_VIEW) continue;
+        for (int s = 0; s < LM_GGML_MAX_SRC; ++s)
+            if (n->src[s] && through_views(n->src[s]) == t) return false;
+    }
+    for (int i = 0; i < g->n_nodes; ++i) {
+        const lm_ggml_tensor * n = g->nodes[i];
+        if ((n->op == LM_GGML_OP_RESHAPE || n->op == LM_GGML_OP_VIEW) && through_views(n) == t && (n->flags & LM_GGML_TENSOR_FLAG_OUTPUT)) return false;
+    }
+    return !(t->flags & LM_GGML_TENSOR_FLAG_OUTPUT);
+}
+
+// ROPE(q) when the k and v products of the same layer have run ahead into scratch (they joined q's launch): one kernel
+// rotates q into its destination, rotates k out of scratch into its cache rows and stores v out of scratch into its cache
+// rows -- what ROPE(q), the two copies out of scratch, ROPE(k) + K store and the V store would do in five steps.  The k and
+// v products, ROPE(k) and the two CPY nodes are then done: nothing else reads their results (checked), and the cache rows
+// they write are read by nothing before the attention of the layer.
+bool rope_all_group(b200_backend_ctx * ctx, const lm_ggml_cgraph * g, int i) {
+    const lm_ggml_tensor * rq = g->nodes[i], * q_in = rq->src[0];
+    if (q_in->type != LM_GGML_TYPE_F32 || !lm_ggml_is_contiguous(rq) || !lm_ggml_is_contiguous(q_in) || rq->ne[3] != 1) return false;
+    int i_rk = -1, i_ck = -1, i_cv = -1, i_k = -1, i_v = -1;
+    for (int j = i + 1; j < g->n_nodes && j < i + 24; ++j) {
+        const lm_ggml_tensor * n = g->nodes[j];
+        if (n->op == LM_GGML_OP_FLASH_ATTN_EXT) break;
+        if (n->op == LM_GGML_OP_ROPE && i_rk < 0 && !ctx->node_done[j]) i_rk = j;
+        else if (n->op == LM_GGML_OP_CPY && i_rk >= 0 && i_ck < 0 && n->src[0] == g->nodes[i_rk]) i_ck = j;
+        else if (n->op == LM_GGML_OP_CPY && i_cv < 0 && n->src[0] && through_views(n->src[0])->op == LM_GGML_OP_MUL_MAT) i_cv = j;
+    }
+    if (i_rk < 0 || i_ck < 0 || i_cv < 0) return false;
+    const lm_ggml_tensor * rk = g->nodes[i_rk], * ck = g->nodes[i_ck], * cv = g->nodes[i_cv];
+    const lm_ggml_tensor * kp = through_views(rk->src[0]), * vp = through_views(cv->src[0]);
+    const b200_backend_ctx::parked_result * pk = nullptr, * pv = nullptr;
+    for (int j = 0; j < g->n_nodes && (i_k < 0 || i_v < 0); ++j) {
+        if (g->nodes[j] == kp) i_k = j;
+        if (g->nodes[j] == vp) i_v = j;
+    }
+    if (i_k < 0 || i_v < 0 || ctx->node_done[i_k] != 2 || ctx->node_done[i_v] != 2) return false;   // both wait in scratch
+    for (const auto & e : ctx->parked_for) {
+        if (e.node == i_k) pk = &e;
+        if (e.node == i_v) pv = &e;
+    }
+    if (!pk || !pv) return false;
+    // same rotation for q and k
+    if (memcmp(rq->op_params, rk->op_params, sizeof(rq->op_params)) != 0 || rq->src[1] != rk->src[1] || rq->src[2] != rk->src[2]) return false;
+    const int64_t D = rq->ne[0], H = rq->ne[1], T = rq->ne[2], Hkv = rk->ne[1];
+    if (rk->ne[0] != D || rk->ne[2] != T || rk->ne[3] != 1 || kp->ne[0] != Hkv * D || vp->ne[0] != Hkv * D) return false;
+    const int at_k = slot_offset(ctx, ck), at_v = slot_offset(ctx, cv);
+    if (at_k < 0 || at_v < 0) return false;
+    for (int64_t r = 0; r < T; ++r)
+        if (ctx->slots_host[(size_t) at_k + r] != ctx->slots_host[(size_t) at_v + r]) return false;   // one row list serves both stores
+    const lm_ggml_tensor * kc = ck->src[1]->view_src, * vc = cv->src[1]->view_src;
+    if (kc->ne[0] != Hkv * D || vc->ne[0] != Hkv * D) return false;
+    if (!only_reader_is(g, kp, rk) || !only_user_is(g, rk, ck) || !only_reader_is(g, vp, cv)) return false;
+    if (((uintptr_t) q_in->data % 8) || ((uintptr_t) rq->data % 8) || (pk->stride % 8) || (pv->stride % 8)) return false;
+    const int32_t * p = (const int32_t *) rq->op_params;
+    float freq_base, freq_scale, attn_factor;
+    memcpy(&freq_base, p + 5, sizeof(float));
+    memcpy(&freq_scale, p + 6, sizeof(float));
+    memcpy(&attn_factor, p + 8, sizeof(float));
+    if (b200_rope_store_to((const float *) q_in->data, (float *) rq->data, q_in->nb[1], q_in->nb[2], (const float *) ctx->parked[pk->block].ptr, D * 4,
+                           (int64_t) pk->stride, (const float *) ctx->parked[pv->block].ptr, (int64_t) pv->stride, D, H, Hkv, T, p[1],
+                           (const int32_t *) rq->src[1]->data, rq->src[2] ? (const float *) rq->src[2]->data : nullptr, freq_base, freq_scale, attn_factor,
+                           ctx->slots_dev + at_k, kc->data, (int64_t) kc->nb[1], vc->data, (int64_t) vc->nb[1], ctx->stream) != B200_OK) {
+        B200_LOG_ERROR("ggml-b200: ROPE group: %s\n", b200_last_error());
+        return false;   // the separate kernels take over
+    }
+    ctx->node_done[i_k] = ctx->node_done[i_v] = ctx->node_done[i_rk] = ctx->node_done[i_ck] = ctx->node_done[i_cv] = 1;
+    ctx->stats.nodes += 3;
+    ctx->stats.rope_stores++;
+    g_rope_store_groups.fetch_add(1, std::memory_order_relaxed);
+    if (debug_lists() && i < 64) fprintf(stderr, "ggml-b200: %s, %s and the K / V stores as one kernel\n", rq->name, rk->name);
+    return true;
 }
 
 // launches the kernels of a node list on the backend's stream (directly, or into a stream capture)
@@ -1345,6 +1425,7 @@ lm_ggml_status run_nodes(b200_backend_ctx * ctx, lm_ggml_cgraph * cgraph, bool c
                 }
             } break;
             case LM_GGML_OP_ROPE: {
+                if (ctx->fuse && ctx->stack && s0->type == LM_GGML_TYPE_F32 && rope_all_group(ctx, cgraph, i)) break;   // q, k and both cache stores by one kernel
                 if (ctx->fuse && s0->type == LM_GGML_TYPE_F32 && rope_store_group(ctx, cgraph, i)) break;   // rotated and stored into the cache by one kernel
                 const int32_t * p = (const int32_t *) node->op_params;
                 float freq_base, freq_scale, attn_factor;
@@ -1464,6 +1545,8 @@ bool graph_signature(const b200_backend_ctx * ctx, const lm_ggml_cgraph * g, uin
     h.val((uintptr_t) ctx->act.ptr); h.val((uintptr_t) ctx->workspace.ptr); h.val((uintptr_t) ctx->fa_scratch.ptr); h.val((uintptr_t) ctx->mask_index.ptr);
     h.val((uintptr_t) ctx->slots_dev);
     h.val((uintptr_t) ctx->parked[0].ptr); h.val((uintptr_t) ctx->parked[1].ptr);
+    // where the row lists start relative to the first one (a kernel that serves two stores with one list relies on it)
+    for (size_t k = 0; k < ctx->slot_first.size(); ++k) h.val(ctx->slot_first[k] - ctx->slot_first[0]);
     h.val(ctx->fuse); h.val(ctx->stack); h.val(ctx->fa_parity); h.val(ctx->q8_variant);
     for (int i = 0; i < g->n_nodes; ++i) {
         const lm_ggml_tensor * n = g->nodes[i];
