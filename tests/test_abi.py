@@ -58,6 +58,12 @@ def test_size_queries_and_argument_checks_without_a_gpu():
     rows = (C.c_int64 * 2)(32, 16)
     rc = L.b200_mul_mat_q_rowsplit_stacked(2, None, 64, 64, None, 4, 0, 1, None, 1024, 2, rows, cols, None, 0, None, None)
     assert rc == -1 and b"the parts hold 48 rows" in L.b200_last_error()
+    # several weights in one launch: 1 to 3 of them, none null
+    rc = L.b200_mul_mat_q_prequant_multi(2, 4, None, None, 64, None, 16, None, 1024, None, 0, None)
+    assert rc == -1 and b"1 to 3 weights" in L.b200_last_error()
+    wp, mp, dp = (C.c_void_p * 2)(None, None), (C.c_int64 * 2)(128, 128), (C.c_void_p * 2)(None, None)
+    rc = L.b200_mul_mat_q_prequant_multi(2, 2, wp, mp, 64, None, 16, dp, 1024, None, 0, None)
+    assert rc == -1 and b"weight / destination 0" in L.b200_last_error()
     rc = L.b200_mul_mat_q_rowsplit_stacked(2, None, 64, 64, None, 4, 0, 1, None, 1024, 4, rows, cols, None, 0, None, None)
     assert rc == -1 and b"1 to 3 parts" in L.b200_last_error()
 
@@ -79,9 +85,3 @@ def test_plugin_exports_the_loader_entry_points():
     syms = subprocess.run(["nm", "-D", "--defined-only", so], capture_output=True, text=True).stdout
     for name in ("lm_ggml_backend_init", "lm_ggml_backend_score", "lm_ggml_backend_b200_reg", "lm_ggml_backend_b200_init"):
         assert f" T {name}" in syms, name
-    # several weights in one launch: 1 to 3 of them, none null
-    rc = L.b200_mul_mat_q_prequant_multi(2, 4, None, None, 64, None, 16, None, 1024, None, 0, None)
-    assert rc == -1 and b"1 to 3 weights" in L.b200_last_error()
-    wp, mp, dp = (C.c_void_p * 2)(None, None), (C.c_int64 * 2)(128, 128), (C.c_void_p * 2)(None, None)
-    rc = L.b200_mul_mat_q_prequant_multi(2, 2, wp, mp, 64, None, 16, dp, 1024, None, 0, None)
-    assert rc == -1 and b"weight / destination 0" in L.b200_last_error()
