@@ -432,6 +432,27 @@ def gpu_arm(args):
     h2d = 4 * N_SEQ * 4
     d2h = N_SEQ * cfg.vocab * 4 + N_SEQ * 4
 
+    # ---- one sequence decoding alone on the same engine (the GEMV path): device-timed, inputs resident ----
+    one_seq = None
+    if rank == 0 and world == 1 and not rows and not args.small and not args.no_extras:
+        reset_state()
+        longest = int(np.argmax(lens))
+        n1 = 32
+        for s in range(n1 + 3):
+            if s == 3:
+                torch.cuda.synchronize()
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record()
+            tok, pos, seq, slots = decode_step_inputs(lens, head, s)
+            eng.inp[:, 0] = torch.tensor([int(tok[longest]), int(pos[longest]), int(seq[longest]), int(slots[longest])], dtype=torch.int32, device="cuda")
+            eng.run_device(1)
+        t1.record()
+        t1.synchronize()
+        ms1 = t0.elapsed_time(t1) / n1
+        one_seq = {"ms_per_token": round(ms1, 4), "tok_s": round(1e3 / ms1, 1), "context": int(lens[longest]),
+                   "weight_stream_frac_of_hbm_peak": round(cfg.weight_bytes_per_step() / (ms1 / 1e3) / 1e9 / peaks()[0], 3),
+                   "launches_per_token": int(eng.launches_per_step[1])}
+
     roof = mul_mat_roofline(eng, cfg) if (rank == 0 and not rows) else None
     peer_status = split.status() if rows else 0
     cpu = None
@@ -454,6 +475,8 @@ def gpu_arm(args):
         if world == 1:
             rowsplit["8b"] = {"n_gpus": 1, "ms_per_step": round(ms_max / K, 4), "tok_s": round(value, 1), "peer_status": 0, "steps": K}
     extras = other_configs(L, local) if (rank == 0 and world == 1 and not args.small and not args.no_extras) else None
+    if extras is not None and one_seq is not None:
+        extras["llama_8b_one_sequence_decode"] = one_seq
     plugin = plugin_record() if (rank == 0 and world == 1 and not args.small and not args.no_extras) else None
 
     if rank == 0:
