@@ -29,6 +29,14 @@ bool pdl_enabled() {
     return v == 1;
 }
 
+int pdl_early_rows() {
+    static const int v = [] {
+        const char *e = getenv("B200_PDL_EARLY_ROWS");
+        return e ? atoi(e) : 1;
+    }();
+    return v;
+}
+
 void count_launch(int n) { g_launches.fetch_add((uint64_t) n, std::memory_order_relaxed); }
 
 int check_launch(const char *what) {

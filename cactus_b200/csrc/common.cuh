@@ -28,12 +28,25 @@ static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; 
 // its first statement (pdl_prologue) waits until the previous kernel has completed and its writes are visible, so only
 // the launch itself and the CTA start-up overlap.  B200_PDL=0 turns the launch attribute off.
 bool pdl_enabled();
+// With a single token row every kernel of a step is a few microseconds of latency and the weight stream of a product
+// waits behind each of them.  Up to this many rows (B200_PDL_EARLY_ROWS, default 1; 0 switches it off) the row kernels
+// let the next kernel's CTAs take their places at once (pdl_prologue(true)), and the few-column product asks for its
+// weights -- which no kernel of a step writes -- to be brought into L2 before it waits for the kernel ahead of it.
+int pdl_early_rows();
 #ifdef __CUDACC__
 __device__ __forceinline__ void pdl_prologue() {
 #ifdef B200_PDL_EARLY_TRIGGER   // lets the next kernel's CTAs take their places for the whole run of this one: measured slower
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 #endif
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+}
+__device__ __forceinline__ void pdl_prologue(bool early) {
+    if (early) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+}
+// a hint without effect on results: `bytes` (a multiple of 16) from the 16-byte aligned global address p are wanted in L2
+__device__ __forceinline__ void prefetch_l2_bulk(const void *p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(__cvta_generic_to_global(p)), "r"(bytes) : "memory");
 }
 // placed where a long kernel's CTA has only its write-back left: once every CTA of the grid is there (or gone), the next
 // kernel's CTAs may be placed

@@ -142,6 +142,7 @@ struct FattnParams {
     int slots;       // CTAs of this kernel the device holds at once
     int vote;        // both attention kernels were launched and the plan decides which one works (the other returns at once):
                      // 1 = these are the per-token kernel's launches, 2 = the query-tiled kernel's
+    int early;       // one or two tokens: the combine pass lets the next kernel's CTAs in at once (pdl_early_rows)
 };
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -529,7 +530,7 @@ __global__ void __launch_bounds__(128) fattn_parity_kernel(FattnParams p) {
 
 template <int D, bool QUANT>
 __global__ void __launch_bounds__(D) fattn_combine_kernel(FattnParams p, int ctas_per_token) {
-    pdl_prologue();
+    pdl_prologue(p.early != 0);
     if (p.vote == 1 && fattn_tiled_chosen(p.plan)) return;    // the query-tiled kernel wrote the result
     if (p.vote == 2 && !fattn_tiled_chosen(p.plan)) return;   // this is the query-tiled kernel's combine pass and the per-token kernel worked
     const float *__restrict__ partial = p.partial;
@@ -745,6 +746,7 @@ static int flash_attn_impl(bool parity, int64_t D, int64_t H, int64_t Hkv, int64
     int gqa_log2 = 0;
     while ((1 << gqa_log2) < gqa) ++gqa_log2;
     p.vote = 0;
+    p.early = Nq <= pdl_early_rows() ? 1 : 0;
     if (!act && dst && fattn_tile_possible(Nq, gqa) && p.nw <= 2048) {
         FattnParams pt = p;
         pt.vote = index ? 2 : 0;

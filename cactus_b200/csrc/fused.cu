@@ -19,8 +19,8 @@ template <int LAYOUT>
 __global__ void __launch_bounds__(1024) add_rms_norm_quantize_kernel(float *x, int64_t x_nb_row, const float *res,
                                                                     int64_t res_nb_row, const float *__restrict__ w, float *h,
                                                                     int64_t h_nb_row, int64_t d, int64_t N, float eps, int64_t nb, int64_t nbp,
-                                                                    uint8_t *__restrict__ out, size_t d_offset, int variant) {
-    pdl_prologue();
+                                                                    uint8_t *__restrict__ out, size_t d_offset, int variant, int early) {
+    pdl_prologue(early != 0);
     constexpr int GMAX = 4;   // groups of 4 elements per thread: d <= 16 * blockDim.x
     const int64_t n = blockIdx.x;
     const bool row_real = n < N;
@@ -72,8 +72,8 @@ template <int LAYOUT>
 __global__ void __launch_bounds__(256) silu_mul_quantize_kernel(const float *gate, const float *up, int64_t nb_row,
                                                                float *dst, int64_t dst_nb_row,
                                                                int64_t N, int64_t n_rows_padded, int64_t nb, int64_t nbp,
-                                                               uint8_t *__restrict__ out, size_t d_offset, int variant) {
-    pdl_prologue();
+                                                               uint8_t *__restrict__ out, size_t d_offset, int variant, int early) {
+    pdl_prologue(early != 0);
     const int64_t gid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
     const int j = (int) (gid & 7);
     const int64_t blk = gid >> 3;
@@ -103,8 +103,8 @@ __global__ void __launch_bounds__(512) rope_store_kernel(const float *q, float *
                                                         int64_t D, int64_t H, int64_t Hkv, int n_dims, const int32_t *__restrict__ pos,
                                                         const float *__restrict__ ff, float theta_scale, float freq_scale, float attn_factor,
                                                         const int32_t *__restrict__ slots, __half *__restrict__ kc, int64_t kc_nb_row,
-                                                        __half *__restrict__ vc, int64_t vc_nb_row) {
-    pdl_prologue();
+                                                        __half *__restrict__ vc, int64_t vc_nb_row, int early) {
+    pdl_prologue(early != 0);
     extern __shared__ float cs[];   // [n_dims/2] cos, [n_dims/2] sin, [n_dims/2] theta
     const int64_t t = blockIdx.x;
     const int half_dims = n_dims / 2;
@@ -178,12 +178,13 @@ int b200_add_rms_norm_quantize(float *x, int64_t x_nb_row, const float *residual
     const unsigned grid = (unsigned) (a.n_nt * 8);
     const unsigned threads = rms_threads(d);
     cudaStream_t st = (cudaStream_t) stream;
+    const int early = rows <= pdl_early_rows() ? 1 : 0;
     if (act_layout(rows) == 3) {
         launch_pdl(add_rms_norm_quantize_kernel<3>, dim3(grid), dim3(threads), 0, st, x, x_nb_row, residual, residual_nb_row, w, h, h_nb_row, d, rows, eps, a.nb, a.nbp,
-                                                                  (uint8_t *) scratch, a.d_offset, variant);
+                                                                  (uint8_t *) scratch, a.d_offset, variant, early);
     } else {
         launch_pdl(add_rms_norm_quantize_kernel<1>, dim3(grid), dim3(threads), 0, st, x, x_nb_row, residual, residual_nb_row, w, h, h_nb_row, d, rows, eps, a.nb, a.nbp,
-                                                                  (uint8_t *) scratch, a.d_offset, variant);
+                                                                  (uint8_t *) scratch, a.d_offset, variant, early);
     }
     return check_launch("add_rms_norm_quantize");
 }
@@ -201,10 +202,11 @@ int b200_silu_mul_quantize(const float *gate, const float *up, int64_t nb_row, f
     const int64_t threads = rows_padded * a.nbp * 8;
     const unsigned grid = (unsigned) ((threads + 255) / 256);
     cudaStream_t st = (cudaStream_t) stream;
+    const int early = N <= pdl_early_rows() ? 1 : 0;
     if (act_layout(N) == 3) {
-        launch_pdl(silu_mul_quantize_kernel<3>, dim3(grid), dim3(256), 0, st, gate, up, nb_row, dst, dst_nb_row, N, rows_padded, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
+        launch_pdl(silu_mul_quantize_kernel<3>, dim3(grid), dim3(256), 0, st, gate, up, nb_row, dst, dst_nb_row, N, rows_padded, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant, early);
     } else {
-        launch_pdl(silu_mul_quantize_kernel<1>, dim3(grid), dim3(256), 0, st, gate, up, nb_row, dst, dst_nb_row, N, rows_padded, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
+        launch_pdl(silu_mul_quantize_kernel<1>, dim3(grid), dim3(256), 0, st, gate, up, nb_row, dst, dst_nb_row, N, rows_padded, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant, early);
     }
     return check_launch("silu_mul_quantize");
 }
@@ -231,7 +233,7 @@ int b200_rope_store_to(const float *q, float *q_dst, int64_t q_nb_head, int64_t 
     const float theta_scale = powf(freq_base, -2.0f / (float) n_dims);
     launch_pdl(rope_store_kernel, dim3((unsigned) T), dim3(512), (size_t) (n_dims + n_dims / 2) * sizeof(float), (cudaStream_t) stream,
         q, q_dst, q_nb_head, q_nb_tok, k, k_nb_head, k_nb_tok, v, v_nb_tok, D, H, Hkv, n_dims, pos, freq_factors, theta_scale, freq_scale, attn_factor,
-        slots, (__half *) k_cache, k_cache_nb_row, (__half *) v_cache, v_cache_nb_row);
+        slots, (__half *) k_cache, k_cache_nb_row, (__half *) v_cache, v_cache_nb_row, T <= pdl_early_rows() ? 1 : 0);
     return check_launch("rope_store");
 }
 

@@ -41,34 +41,60 @@ __global__ void __launch_bounds__(256) set_rows_f16_kernel(const float *__restri
     reinterpret_cast<__half *>(reinterpret_cast<char *>(dst) + (int64_t) slots[r] * dst_nb_row)[c] = __float2half_rn(v);
 }
 
-// first index of the maximum of each row (ties: lowest index, as a linear scan finds it)
-__global__ void __launch_bounds__(256) argmax_rows_kernel(const float *__restrict__ x, int64_t x_nb_row, int64_t d,
-                                                         int32_t *__restrict__ out) {
+// first index of the maximum of each row (ties: lowest index, as a linear scan finds it).  One CTA of 1024 threads per row,
+// 16-byte loads where the row allows them: a vocabulary-sized row is a chain of dependent compares per thread, so the time
+// is the number of elements a thread walks
+constexpr int ARGMAX_THREADS = 1024;
+__global__ void __launch_bounds__(ARGMAX_THREADS) argmax_rows_kernel(const float *__restrict__ x, int64_t x_nb_row, int64_t d,
+                                                                    int32_t *__restrict__ out) {
     const int64_t r = blockIdx.x;
     const float *row = reinterpret_cast<const float *>(reinterpret_cast<const char *>(x) + r * x_nb_row);
     float best = -CUDART_INF_F;
-    int64_t bi = 0x7fffffff;
-    for (int64_t i = threadIdx.x; i < d; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best) { best = v; bi = i; }
-    }
-    __shared__ float sv[256];
-    __shared__ int si[256];
-    sv[threadIdx.x] = best;
-    si[threadIdx.x] = (int) bi;
-    __syncthreads();
-    for (int s = 128; s > 0; s >>= 1) {
-        if ((int) threadIdx.x < s) {
-            const float ov = sv[threadIdx.x + s];
-            const int oi = si[threadIdx.x + s];
-            if (ov > sv[threadIdx.x] || (ov == sv[threadIdx.x] && oi < si[threadIdx.x])) {
-                sv[threadIdx.x] = ov;
-                si[threadIdx.x] = oi;
-            }
+    int bi = 0x7fffffff;
+    int64_t done = 0;
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        const int64_t n4 = d >> 2;
+        const float4 *row4 = reinterpret_cast<const float4 *>(row);
+#pragma unroll 4
+        for (int64_t i = threadIdx.x; i < n4; i += ARGMAX_THREADS) {
+            const float4 v = __ldg(row4 + i);
+            const int b = (int) (i << 2);
+            if (v.x > best) { best = v.x; bi = b; }
+            if (v.y > best) { best = v.y; bi = b + 1; }
+            if (v.z > best) { best = v.z; bi = b + 2; }
+            if (v.w > best) { best = v.w; bi = b + 3; }
         }
-        __syncthreads();
+        done = n4 << 2;
     }
-    if (threadIdx.x == 0) out[r] = si[0];
+    for (int64_t i = done + threadIdx.x; i < d; i += ARGMAX_THREADS) {
+        const float v = row[i];
+        if (v > best) { best = v; bi = (int) i; }
+    }
+    // a thread's candidate is the first maximum among its own elements; between threads the lower index wins a tie
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    __shared__ float sv[ARGMAX_THREADS / 32];
+    __shared__ int si[ARGMAX_THREADS / 32];
+    if ((threadIdx.x & 31) == 0) {
+        sv[threadIdx.x >> 5] = best;
+        si[threadIdx.x >> 5] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = sv[threadIdx.x];
+        bi = si[threadIdx.x];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (threadIdx.x == 0) out[r] = bi == 0x7fffffff ? 0 : bi;   // nothing above -inf: a linear scan stays at index 0
+    }
 }
 
 }  // namespace b200
@@ -107,7 +133,7 @@ int b200_set_rows_f16(const float *x, int64_t x_nb_row, const int32_t *slots, vo
 int b200_argmax_rows(const float *x, int64_t x_nb_row, int64_t d, int64_t rows, int32_t *out, b200_stream_t stream) {
     B200_REQUIRE(x && out && d > 0 && rows >= 0 && x_nb_row % 4 == 0, "bad argmax arguments");
     if (rows == 0) return B200_OK;
-    argmax_rows_kernel<<<(unsigned) rows, 256, 0, (cudaStream_t) stream>>>(x, x_nb_row, d, out);
+    argmax_rows_kernel<<<(unsigned) rows, ARGMAX_THREADS, 0, (cudaStream_t) stream>>>(x, x_nb_row, d, out);
     return check_launch("argmax_rows");
 }
 

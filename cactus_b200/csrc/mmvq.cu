@@ -23,11 +23,21 @@ namespace b200 {
 template <int WTYPE, int NC, int MMVQ_WARPS, int DEPTH = 1>
 __global__ void __launch_bounds__(MMVQ_WARPS * 32) mmvq_kernel(TiledDims dims, const uint8_t *__restrict__ w, ActDims act,
                                                               const uint8_t *__restrict__ aq, float *__restrict__ dst,
-                                                              int64_t dst_nb_row, PeerDst peers) {
+                                                              int64_t dst_nb_row, PeerDst peers, int early) {
+    const int64_t rt = blockIdx.x;
+    if (early) {
+        // the weights of this row tile (one contiguous run of tiles, one of scales) do not depend on the kernel ahead:
+        // let the next kernel in, ask for the weights in L2, and only then wait for the activations
+        pdl_trigger();
+        const uint8_t *q0 = w + rt * dims.n_bg * dims.tile_bytes;
+        for (int64_t bg = threadIdx.x; bg < dims.n_bg; bg += MMVQ_WARPS * 32) prefetch_l2_bulk(q0 + bg * dims.tile_bytes, (uint32_t) dims.tile_bytes);
+        const uint8_t *s0 = w + dims.qs_bytes + rt * dims.n_bg * 128;
+        for (int64_t c = threadIdx.x; c * 16 < dims.n_bg; c += MMVQ_WARPS * 32)
+            prefetch_l2_bulk(s0 + c * 2048, (uint32_t) (min((int64_t) 16, dims.n_bg - c * 16) * 128));
+    }
     pdl_prologue();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int64_t rt = blockIdx.x;
     float y[2][NC];
 #pragma unroll
     for (int n = 0; n < NC; ++n) y[0][n] = y[1][n] = 0.0f;
@@ -179,6 +189,7 @@ static int launch_mmvq_n(const TiledDims &d, const uint8_t *w, const ActDims &a,
         return e ? atoi(e) : 0;
     }();
     const dim3 grid((unsigned) d.n_rt);
+    const int early = (peers.n == 0 && a.N <= pdl_early_rows()) ? 1 : 0;
     const int64_t sms = mmvq_sm_count();
     int cfg = forced;
     if (cfg != 41 && cfg != 42 && cfg != 81 && cfg != 82 && cfg != 161 && cfg != 162) {
@@ -188,12 +199,12 @@ static int launch_mmvq_n(const TiledDims &d, const uint8_t *w, const ActDims &a,
         else cfg = 42;
     }
     switch (cfg) {
-        case 41: launch_pdl(mmvq_kernel<WTYPE, NC, 4, 1>, grid, dim3(128), 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
-        case 42: launch_pdl(mmvq_kernel<WTYPE, NC, 4, 2>, grid, dim3(128), 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
-        case 81: launch_pdl(mmvq_kernel<WTYPE, NC, 8, 1>, grid, dim3(256), 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
-        case 82: launch_pdl(mmvq_kernel<WTYPE, NC, 8, 2>, grid, dim3(256), 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
-        case 161: launch_pdl(mmvq_kernel<WTYPE, NC, 16, 1>, grid, dim3(512), 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
-        default: launch_pdl(mmvq_kernel<WTYPE, NC, 16, 2>, grid, dim3(512), 0, st, d, w, a, aq, dst, dst_nb_row, peers); break;
+        case 41: launch_pdl(mmvq_kernel<WTYPE, NC, 4, 1>, grid, dim3(128), 0, st, d, w, a, aq, dst, dst_nb_row, peers, early); break;
+        case 42: launch_pdl(mmvq_kernel<WTYPE, NC, 4, 2>, grid, dim3(128), 0, st, d, w, a, aq, dst, dst_nb_row, peers, early); break;
+        case 81: launch_pdl(mmvq_kernel<WTYPE, NC, 8, 1>, grid, dim3(256), 0, st, d, w, a, aq, dst, dst_nb_row, peers, early); break;
+        case 82: launch_pdl(mmvq_kernel<WTYPE, NC, 8, 2>, grid, dim3(256), 0, st, d, w, a, aq, dst, dst_nb_row, peers, early); break;
+        case 161: launch_pdl(mmvq_kernel<WTYPE, NC, 16, 1>, grid, dim3(512), 0, st, d, w, a, aq, dst, dst_nb_row, peers, early); break;
+        default: launch_pdl(mmvq_kernel<WTYPE, NC, 16, 2>, grid, dim3(512), 0, st, d, w, a, aq, dst, dst_nb_row, peers, early); break;
     }
     return check_launch("mmvq");
 }

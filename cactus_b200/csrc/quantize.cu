@@ -15,8 +15,8 @@ namespace b200 {
 template <int LAYOUT>
 __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float *__restrict__ x, int64_t x_nb_row, int64_t K,
                                                            int64_t N, int64_t n_rows_padded, int64_t nb, int64_t nbp,
-                                                           uint8_t *__restrict__ out, size_t d_offset, int variant) {
-    pdl_prologue();
+                                                           uint8_t *__restrict__ out, size_t d_offset, int variant, int early) {
+    pdl_prologue(early != 0);
     const int64_t gid = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
     const int j = (int) (gid & 7);             // which group of 4 elements inside the block
     const int64_t blk = gid >> 3;              // (row, block) index
@@ -210,8 +210,9 @@ int launch_quantize_b8(const float *x, int64_t x_nb_row, int64_t K, int64_t N, v
     const ActDims a = act_dims(K, N);
     const int64_t threads = a.n_nt * 8 * a.nbp * 8;
     const int64_t grid = (threads + 255) / 256;
-    if (layout == 3) launch_pdl(quantize_q8_0_kernel<3>, dim3((unsigned) grid), dim3(256), 0, st, x, x_nb_row, K, N, a.n_nt * 8, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
-    else launch_pdl(quantize_q8_0_kernel<1>, dim3((unsigned) grid), dim3(256), 0, st, x, x_nb_row, K, N, a.n_nt * 8, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant);
+    const int early = N <= pdl_early_rows() ? 1 : 0;
+    if (layout == 3) launch_pdl(quantize_q8_0_kernel<3>, dim3((unsigned) grid), dim3(256), 0, st, x, x_nb_row, K, N, a.n_nt * 8, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant, early);
+    else launch_pdl(quantize_q8_0_kernel<1>, dim3((unsigned) grid), dim3(256), 0, st, x, x_nb_row, K, N, a.n_nt * 8, a.nb, a.nbp, (uint8_t *) scratch, a.d_offset, variant, early);
     return check_launch("quantize_q8_0 (activations)");
 }
 
@@ -287,7 +288,7 @@ int b200_quantize_q8_0(const float *x, int64_t x_row_stride_bytes, int64_t K, in
     const int64_t nb = K / 32;
     const int64_t threads = N * nb * 8;
     quantize_q8_0_kernel<0><<<(unsigned) ((threads + 255) / 256), 256, 0, (cudaStream_t) stream>>>(
-        x, x_row_stride_bytes, K, N, N, nb, nb, (uint8_t *) dst_blocks, 0, variant);
+        x, x_row_stride_bytes, K, N, N, nb, nb, (uint8_t *) dst_blocks, 0, variant, 0);
     return check_launch("quantize_q8_0");
 }
 

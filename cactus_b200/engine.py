@@ -289,15 +289,20 @@ class LlamaEngine:
             qs, kst, vst = self.q.stride(0) * 4, self.k.stride(0) * 4, self.v.stride(0) * 4
             check(L.b200_rope_store(self.q.data_ptr(), D * 4, qs, self.k.data_ptr(), D * 4, kst, self.v.data_ptr(), vst, D, H, Hkv, T, D,
                                     pos, None, cfg.rope_theta, 1.0, 1.0, slots, kc.data_ptr(), kvd * 2, vc.data_ptr(), kvd * 2, st))
-            # (b200_flash_attn_ext_quant would leave the quantised activations directly, but measured 70.5 us against
-            # 57.5 + 2.5 for the two launches at this shape: the attention kernel sits at its register limit)
-            check(L.b200_flash_attn_ext_indexed(D, H, Hkv, T, nkv, self.q.data_ptr(), qs, D * 4, kc.data_ptr(), kvd * 2, D * 2,
-                                                vc.data_ptr(), kvd * 2, D * 2, self.mask.data_ptr(), nkv * 2, self.index.data_ptr(),
-                                                D ** -0.5, 0.0, 0.0, (self.attn_part if self.hp else self.attn).data_ptr(), self.fa_scratch.data_ptr(),
-                                                self.fa_scratch.numel(), st))
-            if self.hp:   # every rank's heads side by side, on every rank
-                self.split.allgather(self.attn_part, T, H * D, self.attn, st)
-            self._quant(self.attn, d, T, self.act_d)
+            attn_args = (D, H, Hkv, T, nkv, self.q.data_ptr(), qs, D * 4, kc.data_ptr(), kvd * 2, D * 2, vc.data_ptr(), kvd * 2, D * 2,
+                         self.mask.data_ptr(), nkv * 2, self.index.data_ptr(), D ** -0.5, 0.0, 0.0)
+            if T <= 2 and not self.hp:
+                # one or two tokens: every launch is a few microseconds of latency, so the attention leaves its output
+                # quantised itself (bit-identical to the two launches).  At the 64-token batch the separate quantiser
+                # is faster (70.5 us against 57.5 + 2.5: the attention kernel sits at its register limit there)
+                check(L.b200_flash_attn_ext_quant(*attn_args, None, self.act_d.data_ptr(), self.act_d.numel(), V, self.fa_scratch.data_ptr(),
+                                                  self.fa_scratch.numel(), st))
+            else:
+                check(L.b200_flash_attn_ext_indexed(*attn_args, (self.attn_part if self.hp else self.attn).data_ptr(), self.fa_scratch.data_ptr(),
+                                                    self.fa_scratch.numel(), st))
+                if self.hp:   # every rank's heads side by side, on every rank
+                    self.split.allgather(self.attn_part, T, H * D, self.attn, st)
+                self._quant(self.attn, d, T, self.act_d)
             self._mm(p + "attn_output.weight", self.act_d, T, self.tmp)
             norm_quant(p + "ffn_norm.weight", self.tmp)
             if self.fused:

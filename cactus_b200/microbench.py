@@ -4,6 +4,7 @@
     python -m cactus_b200.microbench fattn --seqs 64 --ctx 900 --reps 3
     python -m cactus_b200.microbench fattn --cfg2 a --copies 8       # the 512-token prefill ubatch of 16 ragged sequences
     python -m cactus_b200.microbench quantize --K 4096 --N 64
+    python -m cactus_b200.microbench decode --seqs 1 --ctx 2048 --layers 32   # whole decode steps of the 8B architecture
     python -m cactus_b200.microbench umma-rate                      # tcgen05.mma issue rates per kind and shape (csrc/probes)
 
 `--copies` distinct weight tensors are cycled so the weights streamed per pass exceed the 126 MB L2.
@@ -204,6 +205,48 @@ def bench_quantize(a):
     return {"kernel": "quantize_q8_0", "K": a.K, "N": a.N, "ms_per_launch": ms, "GBps": (a.N * a.K * 4 + a.N * a.K * 34 / 32) / ms / 1e6}
 
 
+def bench_decode(a):
+    """Whole decode steps of the Llama-3-8B architecture (`--layers` of its layers) on the graph engine: `--seqs` sequences
+    of `--ctx` cached cells each, one token per sequence and step, inputs resident on the device."""
+    from dataclasses import replace
+
+    from .engine import LLAMA_3_8B, LlamaEngine, LlamaWeights
+    cfg = replace(LLAMA_3_8B, n_layer=a.layers)
+    S, ctx = a.seqs, a.ctx
+    steps = 16
+    n_cells = max(a.cells, (S * (ctx + steps + 4) + 255) // 256 * 256)
+    eng = LlamaEngine(LlamaWeights.random(cfg, seed=0), n_cells, max_tokens=S)
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    for il in range(cfg.n_layer):
+        eng.k_cache[il][:S * ctx].copy_(torch.randn((S * ctx, eng.k_cache[il].shape[1]), device="cuda", generator=gen).half())
+        eng.v_cache[il][:S * ctx].copy_(torch.randn((S * ctx, eng.v_cache[il].shape[1]), device="cuda", generator=gen).half())
+    cells = torch.arange(S * ctx, device="cuda", dtype=torch.int32)
+    eng.cell_seq[:S * ctx] = cells // ctx       # sequence s owns the contiguous run [s * ctx, (s + 1) * ctx)
+    eng.cell_pos[:S * ctx] = cells % ctx
+    seq = torch.arange(S, device="cuda", dtype=torch.int32)
+    rng = np.random.default_rng(2)
+
+    def step(i):
+        eng.inp[0, :S] = torch.from_numpy(rng.integers(0, cfg.vocab, S).astype(np.int32)).cuda()
+        eng.inp[1, :S] = ctx + i
+        eng.inp[2, :S] = seq
+        eng.inp[3, :S] = S * ctx + i * S + seq
+        eng.run_device(S)
+
+    for i in range(3):
+        step(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(3, 3 + a.reps):
+        step(i)
+    e1.record()
+    e1.synchronize()
+    ms = e0.elapsed_time(e1) / a.reps
+    return {"kernel": "decode step", "layers": cfg.n_layer, "sequences": S, "context": ctx, "cells": n_cells, "ms_per_step": ms, "tok_s": S * 1e3 / ms,
+            "launches_per_step": int(eng.launches_per_step[S]), "weight_GBps": cfg.weight_bytes_per_step() / ms / 1e6}
+
+
 def run_umma_rate():
     """Builds csrc/probes/umma_rate.cu (a stand-alone program) next to the library and runs it; returns its report."""
     import os
@@ -223,7 +266,7 @@ def main():
         print(run_umma_rate())
         return
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["mul_mat", "fattn", "quantize"])
+    ap.add_argument("kernel", choices=["mul_mat", "fattn", "quantize", "decode"])
     ap.add_argument("--ragged", action="store_true", help="fattn: the benchmark's ragged sequence lengths instead of --seqs x --ctx")
     ap.add_argument("--head-major", action="store_true", help="fattn: address the cache as [Hkv][cells][D] instead of the reference's [cells][Hkv][D]")
     ap.add_argument("--quant", action="store_true", help="fattn: b200_flash_attn_ext_quant (quantised output only)")
@@ -239,8 +282,10 @@ def main():
     ap.add_argument("--D", type=int, default=128)
     ap.add_argument("--H", type=int, default=32)
     ap.add_argument("--Hkv", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=32, help="decode: layers of the 8B architecture")
+    ap.add_argument("--cells", type=int, default=8192, help="decode: cells of the unified cache (grown to what the sequences need)")
     a = ap.parse_args()
-    fn = {"mul_mat": bench_mul_mat, "fattn": bench_fattn, "quantize": bench_quantize}[a.kernel]
+    fn = {"mul_mat": bench_mul_mat, "fattn": bench_fattn, "quantize": bench_quantize, "decode": bench_decode}[a.kernel]
     if a.kernel == "fattn" and a.cfg2:
         fn = bench_fattn_prefill
     r = fn(a)

@@ -225,3 +225,12 @@ def get_rows(table, ids: torch.Tensor) -> torch.Tensor:
     out = torch.empty((n, d), dtype=torch.float32, device=ids.device)
     check(lib().b200_get_rows_f32(table.data_ptr(), table.stride(0) * 4, ids.data_ptr(), out.data_ptr(), d * 4, d, n, _stream()))
     return out
+
+
+def argmax_rows(x: torch.Tensor) -> torch.Tensor:
+    """First index of the maximum of every row of an f32 matrix (rows may be strided): the greedy choice the reference
+    makes on the logits of a token (cactus/cactus_completion.cpp:210)."""
+    assert x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1
+    out = torch.empty(x.shape[0], dtype=torch.int32, device=x.device)
+    check(lib().b200_argmax_rows(x.data_ptr(), x.stride(0) * 4, x.shape[1], x.shape[0], out.data_ptr(), _stream()))
+    return out

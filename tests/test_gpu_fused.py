@@ -104,6 +104,7 @@ def test_rope_store(T):
 @pytest.mark.parametrize("Nq,n_kv,H,Hkv,D", [(13, 1024, 8, 2, 128),     # ragged tokens, padding columns, one KV split
                                             (64, 2048, 32, 8, 128),    # the decode batch shape
                                             (2, 16384, 8, 2, 128),     # few tokens over a long cache: several KV splits + combine kernel
+                                            (1, 4096, 32, 8, 128),     # one token (single-sequence decode): the engine's path for up to two tokens
                                             (9, 512, 4, 4, 64)])       # head size 64, no grouping
 def test_flash_attn_quantised_output(Nq, n_kv, H, Hkv, D):
     """b200_flash_attn_ext_quant leaves exactly what the attention followed by the activation quantiser leaves."""

@@ -65,3 +65,22 @@ def test_k_shift_rope_f16_and_f16_copy(golden):
     torch.cuda.synchronize()
     after = cache.cpu().numpy()
     assert np.array_equal(after[:4], before[5:9]) and np.array_equal(after[4:], before[4:])
+
+
+def test_argmax_rows_first_maximum_on_aligned_and_unaligned_rows():
+    """The greedy choice: lowest index among equal maxima, on rows that start on and off 16-byte boundaries, with
+    lengths that are and are not multiples of four, at the vocabulary size and below one pass of the CTA."""
+    from cactus_b200 import ops
+    rng = np.random.default_rng(5)
+    for d, stride, off in ((128256, 128256, 0), (32000, 32004, 0), (32001, 32003, 1), (4099, 4099, 3), (37, 40, 2), (1, 4, 0)):
+        rows = 5
+        buf = rng.standard_normal(off + rows * stride).astype(np.float32)
+        a = buf[off:off + rows * stride].reshape(rows, stride)[:, :d]
+        a[1, :] = -np.inf                                  # nothing beats the start value: index 0
+        if d > 8:
+            a[2, [d - 1, d // 2, 7]] = 9.0                 # equal maxima: the first one
+            a[3, d - 1] = 11.0                             # the maximum in the ragged tail
+            a[4, :] = np.round(a[4, :])                    # many ties
+        t = dev(buf)[off:off + rows * stride].view(rows, stride)[:, :d]
+        got = host(ops.argmax_rows(t))
+        assert np.array_equal(got, a.argmax(-1).astype(np.int32)), (d, stride, off, got, a.argmax(-1))
