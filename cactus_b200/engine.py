@@ -11,6 +11,7 @@ same calls are issued by the ggml backend plug-in from graph_compute.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import numpy as np
@@ -162,6 +163,11 @@ class LlamaEngine:
         assert n_cells % 256 == 0, "the cache is padded to 256 cells for flash attention (cactus/llama-kv-cache.cpp:20-23)"
         self.w, self.cfg, self.n_cells, self.max_tokens, self.variant = weights, weights.cfg, n_cells, max_tokens, variant
         self.use_graphs = use_graphs
+        # up to this many tokens the attention leaves its output quantised itself (b200_flash_attn_ext_quant: one launch
+        # less per layer, bit-identical).  Off: measured on B200 it is slower at every token count -- one sequence of the
+        # 8B architecture 2.52-2.58 ms per token against 2.40 with the separate quantiser, the 64-token batch 70.5 us per
+        # attention against 57.5 + 2.5 (the attention kernel sits at its register limit).  B200_FA_QUANT_MAX_T sets it.
+        self.fa_quant_max_tokens = int(os.environ.get("B200_FA_QUANT_MAX_T", "0"))
         # row split (cactus_b200.rowsplit.RowSplit): ``weights`` then holds this rank's rows of every mul_mat weight,
         # each product is joined into buffers the peers can write, everything else is replicated
         self.split = split
@@ -291,10 +297,7 @@ class LlamaEngine:
                                     pos, None, cfg.rope_theta, 1.0, 1.0, slots, kc.data_ptr(), kvd * 2, vc.data_ptr(), kvd * 2, st))
             attn_args = (D, H, Hkv, T, nkv, self.q.data_ptr(), qs, D * 4, kc.data_ptr(), kvd * 2, D * 2, vc.data_ptr(), kvd * 2, D * 2,
                          self.mask.data_ptr(), nkv * 2, self.index.data_ptr(), D ** -0.5, 0.0, 0.0)
-            if T <= 2 and not self.hp:
-                # one or two tokens: every launch is a few microseconds of latency, so the attention leaves its output
-                # quantised itself (bit-identical to the two launches).  At the 64-token batch the separate quantiser
-                # is faster (70.5 us against 57.5 + 2.5: the attention kernel sits at its register limit there)
+            if T <= self.fa_quant_max_tokens and not self.hp:
                 check(L.b200_flash_attn_ext_quant(*attn_args, None, self.act_d.data_ptr(), self.act_d.numel(), V, self.fa_scratch.data_ptr(),
                                                   self.fa_scratch.numel(), st))
             else:
