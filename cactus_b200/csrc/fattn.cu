@@ -33,6 +33,7 @@ constexpr int FA_THREADS = 128;
 #define FA_PREFETCH_K 1   // the next chunk's K rows are loaded during the softmax and P V MMAs of the current one (32 more registers)
 #endif
 constexpr int FA_SUPER_WORDS = 32;  // 2048 cells listed per round
+constexpr int FA_MIN_SPLIT_WORDS = 2;   // 64-cell words a KV split walks at least (when the mask index gives a token's word count)
 constexpr int FA_ADAPTIVE_SPLITS = 2;   // most KV splits a long sequence is cut into when the batch is small
 
 // ---- mask scan: one warp per 64 cells of one token row ------------------------------------------
@@ -706,6 +707,10 @@ static int flash_attn_impl(bool parity, int64_t D, int64_t H, int64_t Hkv, int64
         ns = FA_ADAPTIVE_SPLITS;
         w0 = -1;
     }
+    // a split of fewer than two 64-cell words is more launch and combine work than it saves: a token takes at most half as
+    // many splits as it has words (measured on one sequence of 2048 cells: 16 splits 2.41 ms per 8B step, 32 splits 2.45,
+    // 8 splits 2.46).  The token's word count is known on the device only, so this needs the mask index.
+    if (!parity && ns > 1 && w0 == 0 && index) w0 = FA_MIN_SPLIT_WORDS;
     const size_t part = ns > 1 ? (size_t) Nq * H * ns * (D + 2) * sizeof(float) : 0;
     if (part && (!scratch || scratch_bytes < part)) return set_error(B200_E_SCRATCH, "flash_attn scratch too small: %zu < %zu", scratch_bytes, part);
     B200_REQUIRE(!part || is_aligned(scratch, 16), "scratch must be 16-byte aligned");
